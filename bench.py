@@ -1,0 +1,327 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 W4A16 linear layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--sections a,b]
+
+One JSON line on stdout (rank 0).  The headline workload is the decode batch sweep of the
+27B-class MLP shapes: one "step" is, for each M in {1,2,4,8,16}, the fused gate/up linear
+(K=5120, N=34816) followed by the down linear (K=17408, N=5120) -- ten launches of the
+dequant-GEMV.  `value` is algorithmic bytes per step / device time per step, weights and
+activations resident in HBM; weights rotate over several distinct copies larger than L2.
+With N > 1 GPUs the same sweep runs as the tensor-parallel MLP (gate/up column-split, SwiGLU,
+down row-split, one all-reduce), total work fixed ("strong").
+
+`--impl reference` times the CPU restatement of the reference's algorithm (the oracle port,
+all host threads) on a bounded sample of the same workload: the reference engine has no CPU
+implementation of this path and its kernels are built for Jetson Thor only.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(ROOT, "qwen3-27b-thor-runner_b200"), os.path.join(ROOT, "oracle"),
+           os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+H, I = 5120, 17408
+SHAPES = {"gate_up": (2 * I, H), "down": (H, I), "qkv": (7168, 5120), "o": (5120, 6144)}   # name -> (N, K)
+DECODE_MS = (1, 2, 4, 8, 16)
+L2_BYTES = 126 << 20
+
+
+def alg_bytes(N, K, M, residual=False):
+    return N * K // 2 + N * K // 16 + 2 * M * K + 2 * M * N * (2 if residual else 1)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason sampling during the timed region (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        time.sleep(0.15)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(",") for r in open(self.f.name).read().strip().splitlines() if r.count(",") >= 8]
+        os.unlink(self.f.name)
+        sm, reasons = [], set()
+        for r in rows:
+            r = [x.strip() for x in r]
+            try:
+                sm.append(float(r[1]))
+                out["sm_max_mhz"] = float(r[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            sm.sort()
+            out["sm_mhz"] = sm[len(sm) // 2]
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+        return out
+
+
+# ----------------------------------------------------------------------------- synthetic data (device)
+
+def device_weight(N, K, seed, dev):
+    """Nibbles uniform over the 16 codes; block scale = E4M3(max|w|/6), w ~ N(0, 0.02) x16 (sigma 0.02)."""
+    import torch
+    g = torch.Generator(device=dev).manual_seed(seed)
+    packed = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
+    scale = torch.empty((N, K // 16), dtype=torch.uint8, device=dev)
+    rows = max(1, (64 << 20) // (K * 4))
+    for r0 in range(0, N, rows):
+        r1 = min(N, r0 + rows)
+        w = torch.randn((r1 - r0, K // 16, 16), device=dev, generator=g) * 0.02
+        s = w.abs().amax(dim=-1) / 6.0
+        scale[r0:r1] = s.to(torch.float8_e4m3fn).view(torch.uint8)
+    return packed, scale
+
+
+def device_acts(M, K, seed, dev):
+    import torch
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- CPU baseline (oracle port)
+
+def cpu_baseline_sweep(seconds_hint=15.0):
+    """Times the oracle (scalar C port of the reference algorithm) on the host cores: the decode
+    sweep M in {1,2,4,8,16} over a row slice of both MLP shapes, rows split over all threads."""
+    import numpy as np
+    import oracle_binding as ob
+    import util
+    threads = os.cpu_count() or 1
+    # ~2.2 ns per multiply-accumulate per thread on the scalar port; size the slice for seconds_hint.
+    total_macs = sum(N * K * sum(DECODE_MS) for (N, K) in (SHAPES["gate_up"], SHAPES["down"]))
+    frac = min(1.0, seconds_hint * threads / (total_macs * 2.2e-9))
+    nbytes, t_total, desc = 0, 0.0, []
+    for name in ("gate_up", "down"):
+        N, K = SHAPES[name]
+        n = max(threads, int(N * frac) // 16 * 16)
+        packed, scale = util.make_weight(n, K, seed=0)
+        for M in DECODE_MS:
+            A = util.make_bf16((M, K), seed=M)
+            t0 = time.perf_counter()
+            ob.linear(A, packed, scale, 1.0, mode=ob.GEMV, threads=threads)
+            t_total += time.perf_counter() - t0
+            nbytes += alg_bytes(n, K, M)
+        desc.append(f"{name}: first {n} of {N} rows")
+    return dict(value=nbytes / t_total / 1e9, unit="GB/s", cores=threads, kind="port",
+                sample="decode sweep M in {1,2,4,8,16}; " + "; ".join(desc) + f"; {t_total:.1f} s of wall time"), t_total
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    per = max(2.0, min(20.0, 120.0 / (steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_baseline_sweep(per / 4)
+    vals, tt = [], 0.0
+    for _ in range(steps):
+        cb, t = cpu_baseline_sweep(per)
+        vals.append(cb["value"])
+        tt += t
+    cb["value"] = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": "decode_gemv_hbm_gbs", "value": cb["value"], "unit": "GB/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * tt / steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc",
+            "data": "synthetic",
+            "config": {"workload": "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + down 5120x17408 "
+                                   "(bounded row slice per step, CPU oracle port, all host threads)"},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- our arm
+
+class Rotating:
+    """Distinct device copies of one weight, used round-robin so that no launch finds its
+    weights in L2 (total footprint >= 2 x L2)."""
+
+    def __init__(self, N, K, dev, seed):
+        per = N * K // 2 + N * K // 16
+        self.n = max(2, -(-2 * L2_BYTES // per) + 1)
+        self.w = [device_weight(N, K, seed + i, dev) for i in range(self.n)]
+        self.i = 0
+
+    def next(self):
+        self.i = (self.i + 1) % self.n
+        return self.w[self.i]
+
+
+def time_region(fn, steps, torch):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps   # ms per step
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sections", default="decode,prefill,stream,e2e,cpu,refkernel",
+                    help="extra measurements to add to the JSON line")
+    ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import nvfp4
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 or args.gpus > 1:
+        import bench_tp
+        return bench_tp.main(args, world, rank, local_rank)
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    sections = set(args.sections.split(","))
+    peaks = load_peaks()
+    shapes = dict(SHAPES)
+    if args.small:
+        shapes = {"gate_up": (34816 // 4, 5120), "down": (5120, 17408 // 4), "qkv": (7168, 5120), "o": (5120, 6144)}
+    h = nvfp4.Handle(0, 1 << 30)
+    stream = torch.cuda.current_stream()
+
+    rot = {name: Rotating(*shapes[name], dev, seed=10 * i) for i, name in enumerate(("gate_up", "down"))}
+    acts = {(name, M): device_acts(M, shapes[name][1], seed=M, dev=dev) for name in rot for M in DECODE_MS}
+    outs = {(name, M): torch.empty((M, shapes[name][0]), dtype=torch.bfloat16, device=dev)
+            for name in rot for M in DECODE_MS}
+
+    def launch(name, M):
+        N, K = shapes[name]
+        p, s = rot[name].next()
+        h.linear(acts[(name, M)], M, p, s, 1.0, N, K, outs[(name, M)], stream=stream)
+
+    def step():
+        for M in DECODE_MS:
+            launch("gate_up", M)
+            launch("down", M)
+
+    step_bytes = sum(alg_bytes(*shapes[n], M) for n in rot for M in DECODE_MS)
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    l0 = h.launch_count()
+    ms = time_region(step, args.steps, torch)
+    launches = h.launch_count() - l0
+    # Second pass over the same steps with an event pair around every launch: per-kernel durations.
+    per = {}
+    evs = []
+    for _ in range(args.steps):
+        for M in DECODE_MS:
+            for name in ("gate_up", "down"):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                launch(name, M)
+                b.record()
+                evs.append((name, M, a, b))
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    for name, M, a, b in evs:
+        per.setdefault((name, M), []).append(a.elapsed_time(b) * 1e-3)
+    value = step_bytes / (ms * 1e-3) / 1e9
+
+    sweep = []
+    for (name, M), ts in sorted(per.items()):
+        ts.sort()
+        t = sum(ts) / len(ts)
+        gbs = alg_bytes(*shapes[name], M) / t / 1e9
+        sweep.append({"shape": name, "M": M, "us": round(t * 1e6, 2), "us_min": round(ts[0] * 1e6, 2),
+                      "GBps": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                      "frac_of_8TBps": round(gbs / 8000.0, 4)})
+    gu = [x for x in sweep if x["shape"] == "gate_up"]
+    ach = sum(alg_bytes(*shapes["gate_up"], x["M"]) for x in gu) / sum(x["us"] * 1e-6 for x in gu) / 1e9
+    roofline = {"bound": "hbm", "kernel": "decode GEMV, gate_up 34816x5120, mean over M in {1,2,4,8,16}",
+                "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4), "traffic": None}
+
+    line = {"metric": "decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc", "data": "synthetic",
+            "config": {"workload": "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + down 5120x17408"
+                                   + (" (SMALL shapes)" if args.small else ""),
+                       "l2": f"weights rotate over {rot['gate_up'].n}/{rot['down'].n} distinct copies (> 2 x L2)",
+                       "global_scale": 1.0, "scale_sigma": 0.02, "seed": 0,
+                       "decode_impl": h.get_option("decode_impl"), "prefill_impl": h.get_option("prefill_impl")},
+            "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "decode_sweep": sweep}
+
+    if "e2e" in sections:
+        import bench_sections
+        line["e2e"] = bench_sections.e2e(h, shapes, rot, args, torch, alg_bytes, DECODE_MS)
+    if "prefill" in sections:
+        import bench_sections
+        line["prefill"] = bench_sections.prefill(h, shapes, rot, peaks, torch, small=args.small)
+    if "stream" in sections and not args.small:
+        import bench_sections
+        line["layer_stream"] = bench_sections.layer_stream(h, SHAPES, peaks, torch, alg_bytes)
+    if "refkernel" in sections:
+        import bench_sections
+        line["reference_kernels_on_this_gpu"] = bench_sections.reference_kernels(shapes, rot, acts, outs, torch,
+                                                                                 alg_bytes, DECODE_MS)
+    if "cpu" in sections:
+        line["cpu_baseline"], _ = cpu_baseline_sweep(15.0)
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,167 @@
+"""Secondary measurements of bench.py: the end-to-end host-buffer path, the prefill sweep,
+the 64-layer weight stream and the reference engine's own kernels on the same GPU."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def e2e(h, shapes, rot, args, torch, alg_bytes, decode_ms):
+    """The decode sweep through nvfp4_linear_host: activations start in pinned HOST memory and
+    outputs end there, every call copies H2D, launches, copies D2H and synchronises."""
+    hin, hout = {}, {}
+    for name in rot:
+        N, K = shapes[name]
+        for M in decode_ms:
+            hin[(name, M)] = torch.randn((M, K)).to(torch.bfloat16).pin_memory()
+            hout[(name, M)] = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def step():
+        for M in decode_ms:
+            for name in ("gate_up", "down"):
+                N, K = shapes[name]
+                p, s = rot[name].next()
+                h.linear_host(hin[(name, M)], M, p, s, 1.0, N, K, hout[(name, M)], stream=stream)
+
+    for _ in range(3):
+        step()
+    e0, e1 = _events(torch)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    step_bytes = sum(alg_bytes(*shapes[n], M) for n in rot for M in decode_ms)
+    h2d = sum(hin[k].numel() * 2 for k in hin)
+    d2h = sum(hout[k].numel() * 2 for k in hout)
+    return {"value": round(step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "api": "nvfp4_linear_host (pinned host activations in, pinned host outputs back, weights device-resident)"}
+
+
+def prefill(h, shapes, rot, peaks, torch, small=False):
+    """configs[2]: M in {64,256,2048,8192} on the two MLP shapes; TFLOP/s = 2*M*N*K / time."""
+    dev = torch.device("cuda:0")
+    fast = True
+    out = []
+    ms_list = (64, 256, 2048, 8192)
+    for name in ("gate_up", "down"):
+        N, K = shapes[name]
+        for M in ms_list:
+            A = torch.randn((M, K), device=dev).to(torch.bfloat16)
+            C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            p, s = rot[name].next()
+            st = h.linear(A, M, p, s, 1.0, N, K, C, check=False)
+            if st != 0:
+                out.append({"shape": name, "M": M, "error": int(st)})
+                continue
+            torch.cuda.synchronize()
+            # one launch tells how long this path takes; slow (debug) paths are measured once only
+            e0, e1 = _events(torch)
+            e0.record()
+            h.linear(A, M, *rot[name].next(), 1.0, N, K, C)
+            e1.record()
+            torch.cuda.synchronize()
+            t1 = e0.elapsed_time(e1)
+            iters = 1 if t1 > 200 else max(3, min(20, int(200 / max(t1, 1e-3))))
+            e0, e1 = _events(torch)
+            e0.record()
+            for _ in range(iters):
+                h.linear(A, M, *rot[name].next(), 1.0, N, K, C)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            out.append({"shape": name, "M": M, "ms": round(ms, 4), "TFLOPs": round(tf, 1),
+                        "frac_of_measured_bf16_burst": round(tf / peaks["bf16_tflops"], 4),
+                        "frac_of_measured_bf16_sustained": round(tf / peaks["bf16_tflops_sustained"], 4),
+                        "frac_of_2250_nominal": round(tf / 2250.0, 4)})
+            if ms > 2000:
+                fast = False
+            del A, C
+            if not fast:
+                break
+    return out
+
+
+def layer_stream(h, SHAPES, peaks, torch, alg_bytes, layers=64):
+    """configs[3]: 64 layers x {qkv, o, gate_up, down}, every tensor distinct (12.08 GB of weights),
+    M in {1,2,4}: time per token-step of all 256 linears and sustained GB/s."""
+    import bench
+    dev = torch.device("cuda:0")
+    names = ("qkv", "o", "gate_up", "down")
+    ws = []
+    for l in range(layers):
+        ws.append({n: bench.device_weight(*SHAPES[n], seed=1000 + 4 * l + i, dev=dev) for i, n in enumerate(names)})
+    res = []
+    for M in (1, 2, 4):
+        acts = {n: bench.device_acts(M, SHAPES[n][1], seed=M, dev=dev) for n in names}
+        outs = {n: torch.empty((M, SHAPES[n][0]), dtype=torch.bfloat16, device=dev) for n in names}
+
+        def token_step():
+            for l in range(layers):
+                for n in names:
+                    N, K = SHAPES[n]
+                    p, s = ws[l][n]
+                    h.linear(acts[n], M, p, s, 1.0, N, K, outs[n])
+
+        token_step()
+        token_step()
+        e0, e1 = _events(torch)
+        torch.cuda.synchronize()
+        e0.record()
+        reps = 5
+        for _ in range(reps):
+            token_step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        nbytes = layers * sum(alg_bytes(*SHAPES[n], M) for n in names)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res.append({"M": M, "ms_per_token_step": round(ms, 4), "GBps": round(gbs, 1),
+                    "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBps": round(gbs / 8000.0, 4),
+                    "launch_mode": "stream launches (no graph)"})
+    del ws
+    torch.cuda.empty_cache()
+    return res
+
+
+def reference_kernels(shapes, rot, acts, outs, torch, alg_bytes, decode_ms):
+    """The reference engine's kernels (its own source compiled for sm_100a into oracle/_ref) on the
+    same device buffers: what the reference would do on this GPU, beside ours."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle_binding as ob
+    if not ob.ref_available():
+        return {"unavailable": "oracle/_ref/libref_fp4.so not built"}
+    ref = ob.load_ref()
+    st = torch.cuda.current_stream().cuda_stream
+    out = []
+    for name in ("gate_up", "down"):
+        N, K = shapes[name]
+        for M in decode_ms:
+            A, C = acts[(name, M)], outs[(name, M)]
+
+            def go():
+                p, s = rot[name].next()
+                ref.ref_fp4_gemm(A.data_ptr(), p.data_ptr(), s.data_ptr(), 1.0, N, K, C.data_ptr(), M, st)
+
+            go(); go()
+            e0, e1 = _events(torch)
+            torch.cuda.synchronize()
+            e0.record()
+            iters = 5
+            for _ in range(iters):
+                go()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) / iters * 1e-3
+            out.append({"shape": name, "M": M, "us": round(t * 1e6, 2),
+                        "GBps": round(alg_bytes(N, K, M) / t / 1e9, 1)})
+    return out

@@ -1,0 +1,150 @@
+/*
+ * nvfp4_b200 — C ABI of the B200 (sm_100a) NVFP4 W4A16 linear layer.
+ *
+ * Drop-in boundary for the reference engine's FP4 operator set
+ * (namespace qwen_thor::ops, src/engine/dense_gemm_fp4.h:25-72) and the weight
+ * descriptor it takes (struct QuantizedWeight, src/engine/layer.h:197-204).
+ *
+ * Data format (identical to the reference's):
+ *   packed  uint8 [N, K/2]   two E2M1 codes per byte, low nibble = even k
+ *   scale   uint8 [N, K/16]  unsigned E4M3, one per 16 consecutive k of a row
+ *   global_scale  float      W[n,k] = e2m1(code) * ue4m3(scale) / global_scale
+ *   activations / outputs    BF16, row-major [M, K] / [M, N]
+ * All data pointers are DEVICE pointers owned by the caller.  Every call is
+ * asynchronous on the given stream, allocates nothing and never synchronises.
+ * There is no CPU fallback: without a CUDA device every call fails.
+ *
+ * Status codes: 0 = OK; < 0 = argument / shape error (NVFP4_E_*); > 0 = a
+ * cudaError_t raised by a launch.
+ */
+#ifndef NVFP4_B200_H
+#define NVFP4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* nvfp4_stream_t; /* == cudaStream_t */
+typedef struct nvfp4_handle nvfp4_handle;
+
+enum {
+    NVFP4_OK = 0,
+    NVFP4_E_NULL = -1,       /* a required pointer is NULL */
+    NVFP4_E_SHAPE = -2,      /* M,N,K out of range, K % 16 != 0, ... */
+    NVFP4_E_ALIGN = -3,      /* a pointer or row pitch breaks the alignment rule */
+    NVFP4_E_WORKSPACE = -4,  /* handle workspace too small for this call */
+    NVFP4_E_ALIAS = -5,      /* A aliases the output */
+    NVFP4_E_SCALE = -6,      /* global_scale is 0, negative, inf or NaN */
+    NVFP4_E_DEVICE = -7,     /* no CUDA device / wrong device / not sm_100 */
+    NVFP4_E_OPTION = -8,     /* unknown option or value */
+    NVFP4_E_TP = -9          /* tensor-parallel set-up error */
+};
+
+/* Layout-identical to qwen_thor::core::QuantizedWeight (src/engine/layer.h:197-204):
+ * ptr@0, ptr@8, float@16, float@20, int@24, int@28, sizeof 32.  input_scale is
+ * carried but unused in W4A16 (src/engine/dense_gemm_fp4.h:21). */
+typedef struct nvfp4_quantized_weight {
+    uint8_t* packed;
+    uint8_t* scale;
+    float global_scale;
+    float input_scale;
+    int N;
+    int K;
+} nvfp4_quantized_weight;
+
+/* ---- lifecycle ---------------------------------------------------------
+ * Replaces the reference's process-global state (lazy dequant scratch and
+ * cuBLAS handles, src/engine/dense_gemm_fp4_sm110.cu:428,470-486) and its
+ * init_fp4_cublaslt()/cleanup_fp4_cublaslt() hooks (:430-441): one handle per
+ * device, workspace sized once at creation. */
+int nvfp4_create(int device, size_t workspace_bytes, nvfp4_handle** out);
+int nvfp4_destroy(nvfp4_handle* h);
+/* Workspace needed so that every call with M<=max_M, N<=max_N, K<=max_K succeeds. */
+int nvfp4_workspace_bytes(int max_M, int max_N, int max_K, size_t* bytes);
+const char* nvfp4_status_string(int status);
+
+/* Kernel-selection knobs for tests and benchmarks.
+ *   "decode_impl":  0 = auto, 1 = scalar CUDA-core GEMV, 2 = TMA ring + MMA GEMV
+ *   "prefill_impl": 0 = auto, 1 = dequant-to-workspace + CUDA-core GEMM (debug),
+ *                   2 = fused dequant + tcgen05 GEMM
+ *   "decode_max_m": largest M routed to the GEMV path (default 16)            */
+int nvfp4_set_option(nvfp4_handle* h, const char* name, int value);
+int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value);
+
+/* ---- the linear layer ---------------------------------------------------
+ * C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual[M,N]) ), FP32 accumulation,
+ * residual added in FP32 before the single rounding; residual may be NULL and
+ * may alias C.  One entry point for the reference's four:
+ *   invoke_fp4_gemv      (dense_gemm_fp4_sm110.cu:360-375)  M=1, residual NULL
+ *   invoke_fp4_gemv_add  (:377-393)                          M=1
+ *   invoke_fp4_gemm      (:539-584)                          residual NULL
+ *   invoke_fp4_gemm_add  (:586-632)
+ * Requirements: K % 16 == 0; A, C, residual 16-byte aligned; packed 16-byte
+ * aligned; K % 32 == 0 for the fast paths (other K take the scalar path). */
+int nvfp4_linear(nvfp4_handle* h, const void* A_bf16, int M,
+                 const uint8_t* packed, const uint8_t* scale_ue4m3, float global_scale,
+                 int N, int K, const void* residual_bf16_or_null, void* C_bf16,
+                 nvfp4_stream_t stream);
+
+/* Two linears sharing A: C1 = A*W1^T, C2 = A*W2^T, both [N,K].
+ * Replaces invoke_fp4_dual_gemv (:395-416), generalised to any M. */
+int nvfp4_linear_dual(nvfp4_handle* h, const void* A_bf16, int M,
+                      const uint8_t* packed1, const uint8_t* scale1, float global_scale1,
+                      const uint8_t* packed2, const uint8_t* scale2, float global_scale2,
+                      int N, int K, void* C1_bf16, void* C2_bf16, nvfp4_stream_t stream);
+
+/* out[n,k] = bf16( e2m1 * (ue4m3 * (1.0f/global_scale)) ), bit-exact to
+ * fp4_dequant_kernel (:444-467). */
+int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* scale_ue4m3,
+                       float global_scale, int N, int K, void* out_bf16, nvfp4_stream_t stream);
+
+/* out[M,I] = bf16( silu(gate) * up ).  up != NULL: gate and up are [M,I]
+ * (invoke_swiglu, src/engine/light_ops.cu:172-208).  up == NULL: gate points at
+ * a merged [M,2I] tensor, gate = cols [0,I), up = cols [I,2I)
+ * (invoke_swiglu_merged, src/engine/light_ops.cu:1542-1587). */
+int nvfp4_swiglu(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16_or_null,
+                 int M, int I, void* out_bf16, nvfp4_stream_t stream);
+
+/* ---- reference-shaped entry points --------------------------------------
+ * Same argument meaning as the reference functions of the same name (void
+ * return, no validation surfaced); they run on a lazily created per-device
+ * default handle and stash the status for nvfp4_last_status().  The C++ shim
+ * nvfp4_qwen_thor_shim.hpp maps qwen_thor::ops::invoke_fp4_* onto these. */
+void nvfp4_invoke_fp4_gemv(const void* A, const nvfp4_quantized_weight* W, void* C,
+                           nvfp4_stream_t stream);
+void nvfp4_invoke_fp4_gemv_add(const void* A, const nvfp4_quantized_weight* W, void* C,
+                               const void* residual, nvfp4_stream_t stream);
+void nvfp4_invoke_fp4_dual_gemv(const void* A, const nvfp4_quantized_weight* W1,
+                                const nvfp4_quantized_weight* W2, void* C1, void* C2,
+                                nvfp4_stream_t stream);
+void nvfp4_invoke_fp4_gemm(const void* A, const nvfp4_quantized_weight* W, void* C, int M,
+                           nvfp4_stream_t stream);
+void nvfp4_invoke_fp4_gemm_add(const void* A, const nvfp4_quantized_weight* W, void* D,
+                               const void* residual, int M, nvfp4_stream_t stream);
+void nvfp4_init_fp4_cublaslt(void);    /* init_fp4_cublaslt (:430-434): creates the default handle */
+void nvfp4_cleanup_fp4_cublaslt(void); /* cleanup_fp4_cublaslt (:436-441): destroys it */
+int nvfp4_last_status(void);
+/* Workspace of the default handle; call before its first use (default 64 MiB). */
+int nvfp4_default_handle_workspace(size_t bytes);
+
+/* ---- host-memory convenience (the end-to-end path of the benchmark) ------
+ * Same as nvfp4_linear but A, residual and C are HOST pointers (pinned for
+ * best speed); copies A (and residual) to the device, runs the layer on the
+ * handle's staging buffers, copies C back and synchronises the stream.
+ * Weights stay device-resident, as in the reference engine.  Staging space
+ * comes out of the handle workspace. */
+int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M,
+                      const uint8_t* packed_dev, const uint8_t* scale_dev, float global_scale,
+                      int N, int K, const void* residual_host_or_null, void* C_host,
+                      nvfp4_stream_t stream);
+
+/* Number of kernels this library has launched on the handle since creation. */
+int nvfp4_launch_count(nvfp4_handle* h, unsigned long long* count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H */

@@ -1,0 +1,365 @@
+// Host side of the C ABI: handle lifecycle, argument validation, kernel selection
+// and the reference-shaped entry points.  No call here allocates, frees or
+// synchronises after nvfp4_create (nvfp4_linear_host excepted: it is the
+// host-buffer convenience path and synchronises by contract).
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "nvfp4_internal.h"
+
+using namespace nvfp4;
+
+struct nvfp4_handle {
+    nvfp4_device_info dev{};
+    char* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int decode_impl = 0;
+    int prefill_impl = 0;
+    int decode_max_m = 16;
+    unsigned long long launches = 0;
+};
+
+namespace {
+
+constexpr size_t kDecodeScratchBytes = 4u << 20;   // split-K partials + tile counters of the GEMV kernel
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_scale(float gs) {
+    if (!(gs > 0.0f) || !std::isfinite(gs)) return NVFP4_E_SCALE;
+    return NVFP4_OK;
+}
+
+int validate_linear(const nvfp4_handle* h, const void* A, int M, const uint8_t* packed, const uint8_t* scale,
+                    float gs, int N, int K, const void* residual, const void* C) {
+    if (!h || !A || !packed || !scale || !C) return NVFP4_E_NULL;
+    if (M < 0 || N <= 0 || K <= 0 || (K & 15) != 0) return NVFP4_E_SHAPE;
+    if ((long long)N * K / 2 > (1LL << 40)) return NVFP4_E_SHAPE;
+    if (int e = check_scale(gs)) return e;
+    if (!aligned16(A) || !aligned16(C) || (residual && !aligned16(residual))) return NVFP4_E_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(packed) & 7u) != 0) return NVFP4_E_ALIGN;
+    // A must not overlap the output (the reference has the same unstated rule:
+    // every block re-reads A while others already store C).
+    const char* a0 = static_cast<const char*>(A);
+    const char* a1 = a0 + (size_t)M * K * 2;
+    const char* c0 = static_cast<const char*>(C);
+    const char* c1 = c0 + (size_t)M * N * 2;
+    if (M > 0 && a0 < c1 && c0 < a1) return NVFP4_E_ALIAS;
+    return NVFP4_OK;
+}
+
+int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
+
+// One linear call on device buffers.
+int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
+    if (a.M == 0) return NVFP4_OK;
+    if (a.M <= h->decode_max_m) {
+        int impl = h->decode_impl;
+        if (impl == 0) impl = decode_mma_supported(a) ? 2 : 1;
+        if (impl == 2) {
+            if (!decode_mma_supported(a)) return NVFP4_E_SHAPE;
+            size_t need = decode_mma_scratch_bytes(a, h->dev);
+            if (need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+            int nl = 0;
+            cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
+            h->launches += (unsigned long long)nl;
+            return cuda_status(e);
+        }
+        // Scalar path: at most 16 tokens per launch.
+        for (int m0 = 0; m0 < a.M; m0 += 16) {
+            LinearArgs b = a;
+            b.M = (a.M - m0 < 16) ? a.M - m0 : 16;
+            b.A = static_cast<const char*>(a.A) + (size_t)m0 * a.K * 2;
+            b.C = static_cast<char*>(a.C) + (size_t)m0 * a.N * 2;
+            if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
+            cudaError_t e = launch_decode_simple(b, s);
+            h->launches += 1;
+            if (e != cudaSuccess) return (int)e;
+        }
+        return NVFP4_OK;
+    }
+    int impl = h->prefill_impl;
+    if (impl == 0) impl = prefill_umma_supported(a) ? 2 : 1;
+    if (impl == 2) {
+        if (!prefill_umma_supported(a)) return NVFP4_E_SHAPE;
+        int nl = 0;
+        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, h->workspace_bytes, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
+    // Debug path: dequantise the whole weight into the workspace, then a CUDA-core GEMM.
+    const size_t need = (size_t)a.N * a.K * 2;
+    if (need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+    cudaError_t e = launch_dequant_bf16(a.packed, a.scale, a.inv_gs, a.N, a.K, h->workspace, s);
+    h->launches += 1;
+    if (e != cudaSuccess) return (int)e;
+    e = launch_gemm_bf16_simple(a.A, h->workspace, a.residual, a.C, a.M, a.N, a.K, s);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* nvfp4_status_string(int status) {
+    switch (status) {
+        case NVFP4_OK: return "ok";
+        case NVFP4_E_NULL: return "null pointer argument";
+        case NVFP4_E_SHAPE: return "unsupported shape (need M>=0, N>0, K>0, K % 16 == 0)";
+        case NVFP4_E_ALIGN: return "misaligned pointer (A, C, residual: 16 bytes; packed: 8 bytes)";
+        case NVFP4_E_WORKSPACE: return "handle workspace too small for this call";
+        case NVFP4_E_ALIAS: return "A overlaps the output";
+        case NVFP4_E_SCALE: return "global_scale must be finite and > 0";
+        case NVFP4_E_DEVICE: return "no usable CUDA device (compute capability 10.x required)";
+        case NVFP4_E_OPTION: return "unknown option or value";
+        case NVFP4_E_TP: return "tensor-parallel set-up error";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorString((cudaError_t)status);
+    return "unknown status";
+}
+
+int nvfp4_workspace_bytes(int max_M, int max_N, int max_K, size_t* bytes) {
+    if (!bytes) return NVFP4_E_NULL;
+    if (max_M < 0 || max_N <= 0 || max_K <= 0) return NVFP4_E_SHAPE;
+    // GEMV scratch + host-convenience staging (A, residual, C) + prefill scratch.
+    size_t staging = ((size_t)max_M * max_K * 2 + 255) / 256 * 256 + 2 * (((size_t)max_M * max_N * 2 + 255) / 256 * 256);
+    *bytes = kDecodeScratchBytes + staging + prefill_umma_scratch_bytes(max_M, max_N, max_K);
+    return NVFP4_OK;
+}
+
+int nvfp4_create(int device, size_t workspace_bytes, nvfp4_handle** out) {
+    if (!out) return NVFP4_E_NULL;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        (void)cudaGetLastError();
+        return NVFP4_E_DEVICE;
+    }
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return NVFP4_E_DEVICE;
+    if (prop.major != 10) return NVFP4_E_DEVICE;   // the kernels are built for sm_100a only
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return (int)e;
+    nvfp4_handle* h = new nvfp4_handle();
+    h->dev.device = device;
+    h->dev.sm_count = prop.multiProcessorCount;
+    h->dev.cc_major = prop.major;
+    h->dev.cc_minor = prop.minor;
+    h->dev.smem_optin = prop.sharedMemPerBlockOptin;
+    if (workspace_bytes < kDecodeScratchBytes) workspace_bytes = kDecodeScratchBytes;
+    e = cudaMalloc(&h->workspace, workspace_bytes);
+    if (e == cudaSuccess) e = cudaMemset(h->workspace, 0, workspace_bytes);
+    if (e == cudaSuccess) e = configure_kernels(h->dev);
+    cudaSetDevice(prev);
+    if (e != cudaSuccess) {
+        if (h->workspace) cudaFree(h->workspace);
+        delete h;
+        return (int)e;
+    }
+    h->workspace_bytes = workspace_bytes;
+    *out = h;
+    return NVFP4_OK;
+}
+
+int nvfp4_destroy(nvfp4_handle* h) {
+    if (!h) return NVFP4_E_NULL;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(h->dev.device);
+    cudaError_t e = cudaFree(h->workspace);
+    cudaSetDevice(prev);
+    delete h;
+    return cuda_status(e);
+}
+
+int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
+    if (!h || !name) return NVFP4_E_NULL;
+    if (!std::strcmp(name, "decode_impl")) {
+        if (value < 0 || value > 2) return NVFP4_E_OPTION;
+        h->decode_impl = value;
+    } else if (!std::strcmp(name, "prefill_impl")) {
+        if (value < 0 || value > 2) return NVFP4_E_OPTION;
+        h->prefill_impl = value;
+    } else if (!std::strcmp(name, "decode_max_m")) {
+        if (value < 0 || value > 16) return NVFP4_E_OPTION;
+        h->decode_max_m = value;
+    } else {
+        return NVFP4_E_OPTION;
+    }
+    return NVFP4_OK;
+}
+
+int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
+    if (!h || !name || !value) return NVFP4_E_NULL;
+    if (!std::strcmp(name, "decode_impl")) *value = h->decode_impl;
+    else if (!std::strcmp(name, "prefill_impl")) *value = h->prefill_impl;
+    else if (!std::strcmp(name, "decode_max_m")) *value = h->decode_max_m;
+    else if (!std::strcmp(name, "sm_count")) *value = h->dev.sm_count;
+    else return NVFP4_E_OPTION;
+    return NVFP4_OK;
+}
+
+int nvfp4_launch_count(nvfp4_handle* h, unsigned long long* count) {
+    if (!h || !count) return NVFP4_E_NULL;
+    *count = h->launches;
+    return NVFP4_OK;
+}
+
+int nvfp4_linear(nvfp4_handle* h, const void* A, int M, const uint8_t* packed, const uint8_t* scale,
+                 float global_scale, int N, int K, const void* residual, void* C, nvfp4_stream_t stream) {
+    if (int e = validate_linear(h, A, M, packed, scale, global_scale, N, K, residual, C)) return e;
+    LinearArgs a{A, packed, scale, 1.0f / global_scale, residual, C, M, N, K};
+    return run_linear(h, a, stream);
+}
+
+int nvfp4_linear_dual(nvfp4_handle* h, const void* A, int M, const uint8_t* packed1, const uint8_t* scale1,
+                      float gs1, const uint8_t* packed2, const uint8_t* scale2, float gs2, int N, int K,
+                      void* C1, void* C2, nvfp4_stream_t stream) {
+    if (int e = validate_linear(h, A, M, packed1, scale1, gs1, N, K, nullptr, C1)) return e;
+    if (int e = validate_linear(h, A, M, packed2, scale2, gs2, N, K, nullptr, C2)) return e;
+    // Two back-to-back launches on one stream: A (tens of KB) stays in L2 between
+    // them, which is all the reference's single dual launch buys.
+    LinearArgs a{A, packed1, scale1, 1.0f / gs1, nullptr, C1, M, N, K};
+    if (int e = run_linear(h, a, stream)) return e;
+    LinearArgs b{A, packed2, scale2, 1.0f / gs2, nullptr, C2, M, N, K};
+    return run_linear(h, b, stream);
+}
+
+int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* scale, float global_scale,
+                       int N, int K, void* out, nvfp4_stream_t stream) {
+    if (!h || !packed || !scale || !out) return NVFP4_E_NULL;
+    if (N <= 0 || K <= 0 || (K & 15) != 0) return NVFP4_E_SHAPE;
+    if (int e = check_scale(global_scale)) return e;
+    if (!aligned16(out) || (reinterpret_cast<uintptr_t>(packed) & 7u)) return NVFP4_E_ALIGN;
+    cudaError_t e = launch_dequant_bf16(packed, scale, 1.0f / global_scale, N, K, out, stream);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
+int nvfp4_swiglu(nvfp4_handle* h, const void* gate, const void* up, int M, int I, void* out,
+                 nvfp4_stream_t stream) {
+    if (!h || !gate || !out) return NVFP4_E_NULL;
+    if (M < 0 || I <= 0) return NVFP4_E_SHAPE;
+    if (M == 0) return NVFP4_OK;
+    const bool merged = (up == nullptr);
+    if (merged) up = static_cast<const char*>(gate) + (size_t)I * 2;
+    // The vector path needs 16-byte aligned rows; otherwise only the merged/unmerged
+    // row starts must be 2-byte aligned, which any bf16 pointer is.  Keep it simple
+    // and strict: 16-byte alignment of every row start when I >= 8.
+    if (I >= 8 && (!aligned16(gate) || !aligned16(up) || !aligned16(out) || (I & 7) != 0)) return NVFP4_E_ALIGN;
+    cudaError_t e = launch_swiglu(gate, up, merged ? 2LL * I : (long long)I, M, I, out, stream);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
+int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M, const uint8_t* packed, const uint8_t* scale,
+                      float global_scale, int N, int K, const void* residual_host, void* C_host,
+                      nvfp4_stream_t stream) {
+    if (!h || !A_host || !C_host || !packed || !scale) return NVFP4_E_NULL;
+    if (M < 0 || N <= 0 || K <= 0 || (K & 15) != 0) return NVFP4_E_SHAPE;
+    if (int e = check_scale(global_scale)) return e;
+    const size_t a_bytes = ((size_t)M * K * 2 + 255) / 256 * 256;
+    const size_t c_bytes = ((size_t)M * N * 2 + 255) / 256 * 256;
+    const size_t tail = a_bytes + c_bytes;   // staging lives at the END of the workspace
+    if (h->workspace_bytes < kDecodeScratchBytes + tail) return NVFP4_E_WORKSPACE;
+    char* dA = h->workspace + h->workspace_bytes - tail;
+    char* dC = dA + a_bytes;
+    cudaError_t e = cudaMemcpyAsync(dA, A_host, (size_t)M * K * 2, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return (int)e;
+    const void* dR = nullptr;
+    if (residual_host) {   // the residual is staged straight into the output buffer (C may alias residual)
+        e = cudaMemcpyAsync(dC, residual_host, (size_t)M * N * 2, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return (int)e;
+        dR = dC;
+    }
+    // Shrink the workspace seen by the kernels so that their scratch never reaches the staging area.
+    nvfp4_handle view = *h;
+    view.workspace_bytes = h->workspace_bytes - tail;
+    LinearArgs a{dA, packed, scale, 1.0f / global_scale, dR, dC, M, N, K};
+    int st = run_linear(&view, a, stream);
+    h->launches = view.launches;
+    if (st) return st;
+    e = cudaMemcpyAsync(C_host, dC, (size_t)M * N * 2, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return (int)e;
+    return cuda_status(cudaStreamSynchronize(stream));
+}
+
+// ---- reference-shaped entry points on a per-device default handle ---------------------
+
+namespace {
+std::mutex g_mu;
+nvfp4_handle* g_default[64] = {};
+size_t g_default_ws = 64u << 20;
+thread_local int g_last_status = 0;
+
+nvfp4_handle* default_handle() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_default[dev]) {
+        nvfp4_handle* h = nullptr;
+        g_last_status = nvfp4_create(dev, g_default_ws, &h);
+        g_default[dev] = h;
+    }
+    return g_default[dev];
+}
+
+void linear_on_default(const void* A, const nvfp4_quantized_weight* W, void* C, const void* residual, int M,
+                       nvfp4_stream_t s) {
+    if (!W) { g_last_status = NVFP4_E_NULL; return; }
+    nvfp4_handle* h = default_handle();
+    if (!h) { if (!g_last_status) g_last_status = NVFP4_E_DEVICE; return; }
+    g_last_status = nvfp4_linear(h, A, M, W->packed, W->scale, W->global_scale, W->N, W->K, residual, C, s);
+}
+}  // namespace
+
+int nvfp4_default_handle_workspace(size_t bytes) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_default_ws = bytes;
+    return NVFP4_OK;
+}
+
+void nvfp4_init_fp4_cublaslt(void) { (void)default_handle(); }
+
+void nvfp4_cleanup_fp4_cublaslt(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (auto& h : g_default) {
+        if (h) { nvfp4_destroy(h); h = nullptr; }
+    }
+}
+
+int nvfp4_last_status(void) { return g_last_status; }
+
+void nvfp4_invoke_fp4_gemv(const void* A, const nvfp4_quantized_weight* W, void* C, nvfp4_stream_t s) {
+    linear_on_default(A, W, C, nullptr, 1, s);
+}
+void nvfp4_invoke_fp4_gemv_add(const void* A, const nvfp4_quantized_weight* W, void* C, const void* residual,
+                               nvfp4_stream_t s) {
+    linear_on_default(A, W, C, residual, 1, s);
+}
+void nvfp4_invoke_fp4_dual_gemv(const void* A, const nvfp4_quantized_weight* W1, const nvfp4_quantized_weight* W2,
+                                void* C1, void* C2, nvfp4_stream_t s) {
+    if (!W1 || !W2) { g_last_status = NVFP4_E_NULL; return; }
+    nvfp4_handle* h = default_handle();
+    if (!h) { if (!g_last_status) g_last_status = NVFP4_E_DEVICE; return; }
+    // The reference takes N and K from W1 for both weights (dense_gemm_fp4_sm110.cu:405-406).
+    g_last_status = nvfp4_linear_dual(h, A, 1, W1->packed, W1->scale, W1->global_scale, W2->packed, W2->scale,
+                                      W2->global_scale, W1->N, W1->K, C1, C2, s);
+}
+void nvfp4_invoke_fp4_gemm(const void* A, const nvfp4_quantized_weight* W, void* C, int M, nvfp4_stream_t s) {
+    linear_on_default(A, W, C, nullptr, M, s);
+}
+void nvfp4_invoke_fp4_gemm_add(const void* A, const nvfp4_quantized_weight* W, void* D, const void* residual,
+                               int M, nvfp4_stream_t s) {
+    linear_on_default(A, W, D, residual, M, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// Internal declarations shared by the host-side dispatcher and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/nvfp4_b200.h"
+
+namespace nvfp4 {
+
+// Arguments of one linear call after validation.  All pointers are device pointers.
+struct LinearArgs {
+    const void* A;          // [M,K] bf16
+    const uint8_t* packed;  // [N,K/2]
+    const uint8_t* scale;   // [N,K/16]
+    float inv_gs;           // 1.0f / global_scale, computed on the host in FP32
+    const void* residual;   // [M,N] bf16 or nullptr
+    void* C;                // [M,N] bf16
+    int M, N, K;
+};
+
+struct nvfp4_device_info {
+    int device;
+    int sm_count;
+    int cc_major, cc_minor;
+    size_t smem_optin;
+};
+
+// --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
+cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);
+
+// --- dequant_swiglu.cu
+cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, float inv_gs, int N, int K,
+                                void* out, cudaStream_t s);
+cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
+                          void* out, cudaStream_t s);
+
+// --- prefill_simple.cu: C = A * Wdq^T with Wdq bf16 [N,K] already dequantised (debug path).
+cudaError_t launch_gemm_bf16_simple(const void* A, const void* Wdq, const void* residual, void* C,
+                                    int M, int N, int K, cudaStream_t s);
+
+// --- decode_mma.cu: TMA-fed shared-memory ring + register dequant + warp MMA GEMV (M <= 16).
+bool decode_mma_supported(const LinearArgs& a);
+size_t decode_mma_scratch_bytes(const LinearArgs& a, const nvfp4_device_info& dev);
+cudaError_t launch_decode_mma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch, int* launches,
+                              cudaStream_t s);
+
+// --- prefill_umma.cu: fused dequant + tcgen05 BF16 GEMM with TMEM accumulators.
+bool prefill_umma_supported(const LinearArgs& a);
+size_t prefill_umma_scratch_bytes(int max_M, int max_N, int max_K);
+cudaError_t launch_prefill_umma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch,
+                                size_t scratch_bytes, int* launches, cudaStream_t s);
+
+// Sets the per-kernel attributes (dynamic shared memory opt-in) once per device.
+cudaError_t configure_kernels(const nvfp4_device_info& dev);
+
+}  // namespace nvfp4

@@ -1,0 +1,155 @@
+"""ctypes binding of libnvfp4_b200.so (the C ABI declared in include/nvfp4_b200.h).
+
+Host-side helper for tests and benchmarks: it adds nothing to the data path -- every
+method forwards raw device pointers to the C entry point of the same name.  There is
+no CPU fallback: loading fails loudly when the CUDA library has not been built.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libnvfp4_b200.so")
+
+c_void_p, c_int, c_float, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+
+
+class QuantizedWeight(ctypes.Structure):
+    """Layout of qwen_thor::core::QuantizedWeight (reference src/engine/layer.h:197-204)."""
+    _fields_ = [("packed", c_void_p), ("scale", c_void_p), ("global_scale", c_float),
+                ("input_scale", c_float), ("N", c_int), ("K", c_int)]
+
+
+# name -> (restype, argtypes); every symbol include/nvfp4_b200.h declares.
+SIGNATURES = {
+    "nvfp4_create": (c_int, [c_int, c_size_t, ctypes.POINTER(c_void_p)]),
+    "nvfp4_destroy": (c_int, [c_void_p]),
+    "nvfp4_workspace_bytes": (c_int, [c_int, c_int, c_int, ctypes.POINTER(c_size_t)]),
+    "nvfp4_status_string": (ctypes.c_char_p, [c_int]),
+    "nvfp4_set_option": (c_int, [c_void_p, ctypes.c_char_p, c_int]),
+    "nvfp4_get_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(c_int)]),
+    "nvfp4_linear": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int,
+                             c_void_p, c_void_p, c_void_p]),
+    "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                  c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_invoke_fp4_gemv": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p]),
+    "nvfp4_invoke_fp4_gemv_add": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p,
+                                         c_void_p]),
+    "nvfp4_invoke_fp4_dual_gemv": (None, [c_void_p, ctypes.POINTER(QuantizedWeight),
+                                          ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p, c_void_p]),
+    "nvfp4_invoke_fp4_gemm": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_int, c_void_p]),
+    "nvfp4_invoke_fp4_gemm_add": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p, c_int,
+                                         c_void_p]),
+    "nvfp4_init_fp4_cublaslt": (None, []),
+    "nvfp4_cleanup_fp4_cublaslt": (None, []),
+    "nvfp4_last_status": (c_int, []),
+    "nvfp4_default_handle_workspace": (c_int, [c_size_t]),
+    "nvfp4_linear_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int,
+                                  c_void_p, c_void_p, c_void_p]),
+    "nvfp4_launch_count": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_ulonglong)]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library and attach signatures.  Raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `make -C {_HERE}` "
+                "(or __graft_entry__.build()); there is no fallback path")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+class Nvfp4Error(RuntimeError):
+    def __init__(self, status):
+        self.status = status
+        super().__init__(f"nvfp4 status {status}: {load().nvfp4_status_string(status).decode()}")
+
+
+def _ptr(t):
+    """Device/host address of a torch tensor, an int, or None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+class Handle:
+    """One library handle on one device (nvfp4_create / nvfp4_destroy)."""
+
+    def __init__(self, device=0, workspace_bytes=64 << 20):
+        self.lib = load()
+        h = c_void_p()
+        st = self.lib.nvfp4_create(device, workspace_bytes, ctypes.byref(h))
+        if st:
+            raise Nvfp4Error(st)
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.nvfp4_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st):
+        if st:
+            raise Nvfp4Error(st)
+
+    def set_option(self, name, value):
+        self._check(self.lib.nvfp4_set_option(self.h, name.encode(), value))
+
+    def get_option(self, name):
+        v = c_int()
+        self._check(self.lib.nvfp4_get_option(self.h, name.encode(), ctypes.byref(v)))
+        return v.value
+
+    def launch_count(self):
+        v = ctypes.c_ulonglong()
+        self._check(self.lib.nvfp4_launch_count(self.h, ctypes.byref(v)))
+        return v.value
+
+    def linear(self, A, M, packed, scale, global_scale, N, K, C, residual=None, stream=None, check=True):
+        st = self.lib.nvfp4_linear(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,
+                                   _ptr(residual), _ptr(C), _stream(stream))
+        if check:
+            self._check(st)
+        return st
+
+    def linear_dual(self, A, M, p1, s1, gs1, p2, s2, gs2, N, K, C1, C2, stream=None):
+        self._check(self.lib.nvfp4_linear_dual(self.h, _ptr(A), M, _ptr(p1), _ptr(s1), gs1, _ptr(p2), _ptr(s2),
+                                               gs2, N, K, _ptr(C1), _ptr(C2), _stream(stream)))
+
+    def dequant(self, packed, scale, global_scale, N, K, out, stream=None):
+        self._check(self.lib.nvfp4_dequant_bf16(self.h, _ptr(packed), _ptr(scale), global_scale, N, K,
+                                                _ptr(out), _stream(stream)))
+
+    def swiglu(self, gate, up, M, I, out, stream=None):
+        self._check(self.lib.nvfp4_swiglu(self.h, _ptr(gate), _ptr(up), M, I, _ptr(out), _stream(stream)))
+
+    def linear_host(self, A_host, M, packed, scale, global_scale, N, K, C_host, residual_host=None, stream=None):
+        self._check(self.lib.nvfp4_linear_host(self.h, _ptr(A_host), M, _ptr(packed), _ptr(scale), global_scale,
+                                               N, K, _ptr(residual_host), _ptr(C_host), _stream(stream)))

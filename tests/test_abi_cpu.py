@@ -1,0 +1,89 @@
+"""CPU tests of the drop-in boundary: the shared library loads and exports every symbol the
+public headers declare; without a GPU the entry points fail loudly instead of falling back."""
+import ctypes
+import glob
+import os
+import re
+
+import pytest
+
+import nvfp4
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = open(path).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", text))
+    return names
+
+
+def libs():
+    out = [nvfp4.load()]
+    tp = os.path.join(os.path.dirname(nvfp4.LIB_PATH), "libnvfp4_b200_tp.so")
+    if os.path.exists(tp):
+        try:
+            out.append(ctypes.CDLL(tp))
+        except OSError:
+            pass
+    return out
+
+
+def test_library_exports_every_declared_symbol():
+    loaded = libs()
+    decl = declared_symbols()
+    assert len(decl) >= 20
+    tp_built = len(loaded) > 1
+    for name in sorted(decl):
+        if name.startswith("nvfp4_tp_") and not tp_built:
+            continue
+        assert any(hasattr(l, name) for l in loaded), f"{name} declared in include/ but not exported"
+
+
+def test_binding_covers_header():
+    decl = {n for n in declared_symbols() if not n.startswith("nvfp4_tp_")}
+    assert decl == set(nvfp4.SIGNATURES), decl ^ set(nvfp4.SIGNATURES)
+
+
+def test_quantized_weight_layout():
+    qw = nvfp4.QuantizedWeight
+    assert ctypes.sizeof(qw) == 32
+    assert [getattr(qw, f).offset for f in ("packed", "scale", "global_scale", "input_scale", "N", "K")] == \
+        [0, 8, 16, 20, 24, 28]
+
+
+def test_no_cpu_fallback_without_gpu():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("this check is for GPU-less hosts")
+    with pytest.raises(nvfp4.Nvfp4Error) as e:
+        nvfp4.Handle(0, 1 << 20)
+    assert e.value.status == -7
+    lib = nvfp4.load()
+    assert lib.nvfp4_status_string(-7).decode().startswith("no usable CUDA device")
+    # the reference-shaped entry points record the failure instead of computing anything
+    qw = nvfp4.QuantizedWeight(None, None, 1.0, 1.0, 16, 16)
+    lib.nvfp4_invoke_fp4_gemv(None, ctypes.byref(qw), None, None)
+    assert lib.nvfp4_last_status() != 0
+
+
+def test_workspace_query_and_null_checks():
+    lib = nvfp4.load()
+    n = ctypes.c_size_t()
+    assert lib.nvfp4_workspace_bytes(16, 34816, 5120, ctypes.byref(n)) == 0 and n.value >= 4 << 20
+    assert lib.nvfp4_workspace_bytes(16, 0, 5120, ctypes.byref(n)) == -2
+    assert lib.nvfp4_linear(None, None, 1, None, None, 1.0, 16, 16, None, None, None) == -1
+    assert lib.nvfp4_destroy(None) == -1
+
+
+def test_no_cluster_multicast_anywhere():
+    """No source file may carry a TMA / bulk load with cluster multicast."""
+    pat = re.compile(r"multicast::cluster")
+    for ext in ("cu", "cuh", "h", "hpp", "cpp", "py"):
+        for path in glob.glob(os.path.join(ROOT, "**", f"*.{ext}"), recursive=True):
+            if "/_work/" in path or "/gpurun_out/" in path or path.endswith("test_abi_cpu.py"):
+                continue
+            assert not pat.search(open(path, errors="ignore").read()), path

@@ -1,0 +1,407 @@
+"""GPU parity tests: the CUDA library, called through its C ABI, against the CPU oracle, the
+committed reference-kernel outputs and (when oracle/_ref is present) the reference engine's
+own kernels run side by side.  Tolerance: dequantised weights bit-exact; linear outputs
+relative Frobenius error <= 1e-3 against the FP32-accumulate, single-rounding oracle."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+import nvfp4
+import oracle_binding as ob
+import util
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_b200.npz")
+
+
+def run_linear(h, A, packed, scale, gs, residual=None, inplace=True):
+    import torch
+    M, K = A.shape
+    N = packed.shape[0]
+    dA, dp, ds = util.to_dev(A), util.to_dev(packed), util.to_dev(scale)
+    dC = torch.full((M, N), 0x7FC0, dtype=torch.int16, device="cuda")   # NaN canary
+    dR = None
+    if residual is not None:
+        if inplace:
+            dC.copy_(util.to_dev(residual))
+            dR = dC
+        else:
+            dR = util.to_dev(residual)
+    h.linear(dA, M, dp, ds, gs, N, K, dC, residual=dR)
+    torch.cuda.synchronize()
+    return util.to_host_u16(dC)
+
+
+def impls(h, kind):
+    """Kernel variants worth testing for `kind` ('decode' or 'prefill'): auto plus each explicit one."""
+    return [0, 1, 2]
+
+
+def with_impl(h, kind, impl, fn):
+    h.set_option(f"{kind}_impl", impl)
+    try:
+        return fn()
+    except nvfp4.Nvfp4Error as e:
+        if impl == 2 and e.status in (-2, 801):   # shape not taken by the fast kernel / kernel not built
+            pytest.skip(f"{kind}_impl=2 does not take this shape")
+        raise
+    finally:
+        h.set_option(f"{kind}_impl", 0)
+
+
+# ---------------------------------------------------------------- dequant: bit-exact
+
+@pytest.mark.parametrize("gs", [1.0, 1.7, 2688.0])
+def test_dequant_exhaustive_table_bitwise(handle, gs):
+    import torch
+    packed = np.tile(np.array([(2 * j) | ((2 * j + 1) << 4) for j in range(8)], np.uint8), (256, 1))
+    scale = np.arange(256, dtype=np.uint8).reshape(256, 1)
+    out = torch.zeros(256, 16, dtype=torch.int16, device="cuda")
+    handle.dequant(util.to_dev(packed), util.to_dev(scale), gs, 256, 16, out)
+    torch.cuda.synchronize()
+    assert np.array_equal(util.to_host_u16(out), ob.dequant(packed, scale, gs))
+
+
+@pytest.mark.parametrize("N,K,sigma", [(37, 256, 0.02), (128, 5120, 0.02), (64, 1024, 0.14)])
+def test_dequant_random_bitwise(handle, N, K, sigma):
+    import torch
+    packed, scale = util.make_weight(N, K, seed=5, sigma=sigma)
+    out = torch.zeros(N, K, dtype=torch.int16, device="cuda")
+    handle.dequant(util.to_dev(packed), util.to_dev(scale), 1.0, N, K, out)
+    torch.cuda.synchronize()
+    assert np.array_equal(util.to_host_u16(out), ob.dequant(packed, scale, 1.0))
+
+
+# ---------------------------------------------------------------- decode (M <= 16)
+
+@pytest.mark.parametrize("impl", [0, 1, 2])
+def test_config0_gemv(handle, impl):
+    """BASELINE config 0: M=1, K=N=5120, seed 0, global scale 1.0."""
+    N = K = 5120
+    packed, scale = util.make_weight(N, K, seed=0)
+    A = util.make_bf16((1, K), seed=0)
+    got = with_impl(handle, "decode", impl, lambda: run_linear(handle, A, packed, scale, 1.0))
+    want = ob.linear(A, packed, scale, 1.0, threads=8)
+    assert ob.rel_frobenius(got, want) <= TOL
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_decode_small_shapes_exhaustive(handle, impl):
+    def body():
+        worst = 0.0
+        for K in (16, 32, 48, 64, 128, 256, 512):
+            for N in (1, 2, 3, 7, 8, 9, 15, 16, 17, 33):
+                packed, scale = util.make_weight(N, K, seed=K * 100 + N, sigma=0.14)
+                for M in (1, 2, 3, 4, 5, 7, 8, 9, 15, 16):
+                    A = util.make_bf16((M, K), seed=M)
+                    R = util.make_bf16((M, N), seed=M + 50) if (M + N) % 2 else None
+                    got = run_linear(handle, A, packed, scale, 1.0, residual=R)
+                    want = ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMV)
+                    worst = max(worst, ob.rel_frobenius(got, want))
+        return worst
+    assert with_impl(handle, "decode", impl, body) <= TOL
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("N,K", [(512, 5120), (256, 17408), (1000, 2048), (148 * 16 + 16, 1024), (96, 6144)])
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
+def test_decode_mlp_like_shapes(handle, impl, N, K, M):
+    packed, scale = util.make_weight(N, K, seed=N + K)
+    A = util.make_bf16((M, K), seed=M)
+    R = util.make_bf16((M, N), seed=M + 9)
+    got = with_impl(handle, "decode", impl, lambda: run_linear(handle, A, packed, scale, 1.0, residual=R))
+    want = ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMV, threads=8)
+    assert ob.rel_frobenius(got, want) <= TOL
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_decode_fuzz(handle, impl):
+    rng = np.random.default_rng(1234)
+
+    def body():
+        worst = 0.0
+        for it in range(40):
+            K = int(rng.integers(1, 80)) * 32
+            N = int(rng.integers(1, 700))
+            M = int(rng.integers(1, 17))
+            gs = float(rng.choice([1.0, 1.0, 0.37, 7.25, 2048.0]))
+            sigma = float(rng.choice([0.02, 0.14, 1.0]))
+            packed, scale = util.make_weight(N, K, seed=it, sigma=sigma)
+            A = util.make_bf16((M, K), seed=1000 + it, std=float(rng.choice([1.0, 30.0, 0.01])))
+            R = util.make_bf16((M, N), seed=2000 + it) if it % 3 else None
+            got = run_linear(handle, A, packed, scale, gs, residual=R, inplace=bool(it % 2))
+            want = ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMV)
+            worst = max(worst, ob.rel_frobenius(got, want))
+        return worst
+    assert with_impl(handle, "decode", impl, body) <= TOL
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_decode_extreme_scales(handle, impl):
+    """Every scale code 0..255 (subnormal, normal, top-bit-set, 0x7F/0xFF = 480) in one weight."""
+    N, K = 64, 1024
+    rng = np.random.default_rng(9)
+    packed = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    scale = rng.integers(0, 256, (N, K // 16), dtype=np.uint8)
+    A = util.make_bf16((3, K), seed=4)
+    got = with_impl(handle, "decode", impl, lambda: run_linear(handle, A, packed, scale, 1.0))
+    want = ob.linear(A, packed, scale, 1.0, mode=ob.GEMV)
+    assert ob.rel_frobenius(got, want) <= TOL
+
+
+def test_one_hot_activation_returns_dequantised_column(handle):
+    """A = e_k  =>  C[0,:] == dequant(W)[:,k] bit for bit (products and sums are exact)."""
+    N, K = 300, 640
+    packed, scale = util.make_weight(N, K, seed=77, sigma=0.14)
+    wq = ob.dequant(packed, scale, 1.0)
+    for impl in (1, 2):
+        for k in (0, 1, 15, 16, 333, 639):
+            A = np.zeros((1, K), np.uint16)
+            A[0, k] = 0x3F80
+            try:
+                handle.set_option("decode_impl", impl)
+                got = run_linear(handle, A, packed, scale, 1.0)
+            except nvfp4.Nvfp4Error:
+                continue
+            finally:
+                handle.set_option("decode_impl", 0)
+            canon = lambda x: np.where((x & 0x7FFF) == 0, 0, x)   # -0 (negative code x zero scale) == +0
+            assert np.array_equal(canon(got[0]), canon(wq[:, k])), (impl, k)
+
+
+def test_dual_and_reference_shaped_entry_points(handle):
+    import torch
+    lib = nvfp4.load()
+    N, K = 96, 512
+    p1, s1 = util.make_weight(N, K, seed=1)
+    p2, s2 = util.make_weight(N, K, seed=2)
+    A = util.make_bf16((1, K), seed=3)
+    R = util.make_bf16((1, N), seed=4)
+    dA, dp1, ds1, dp2, ds2 = map(util.to_dev, (A, p1, s1, p2, s2))
+    c1 = torch.zeros(1, N, dtype=torch.int16, device="cuda")
+    c2 = torch.zeros(1, N, dtype=torch.int16, device="cuda")
+    handle.linear_dual(dA, 1, dp1, ds1, 1.0, dp2, ds2, 2.0, N, K, c1, c2)
+    torch.cuda.synchronize()
+    w1, w2 = ob.linear(A, p1, s1, 1.0), ob.linear(A, p2, s2, 2.0)
+    assert ob.rel_frobenius(util.to_host_u16(c1), w1) <= TOL and ob.rel_frobenius(util.to_host_u16(c2), w2) <= TOL
+
+    st = torch.cuda.current_stream().cuda_stream
+    qw1 = nvfp4.QuantizedWeight(dp1.data_ptr(), ds1.data_ptr(), 1.0, 1.0, N, K)
+    qw2 = nvfp4.QuantizedWeight(dp2.data_ptr(), ds2.data_ptr(), 2.0, 1.0, N, K)
+    lib.nvfp4_init_fp4_cublaslt()
+    c1.zero_(); c2.zero_()
+    lib.nvfp4_invoke_fp4_gemv(dA.data_ptr(), ctypes.byref(qw1), c1.data_ptr(), st)
+    assert lib.nvfp4_last_status() == 0
+    lib.nvfp4_invoke_fp4_dual_gemv(dA.data_ptr(), ctypes.byref(qw1), ctypes.byref(qw2), c1.data_ptr(),
+                                   c2.data_ptr(), st)
+    assert lib.nvfp4_last_status() == 0
+    torch.cuda.synchronize()
+    assert ob.rel_frobenius(util.to_host_u16(c1), w1) <= TOL and ob.rel_frobenius(util.to_host_u16(c2), w2) <= TOL
+    # gemv_add in place (C aliases residual), as src/engine/layer.cu:102 calls it
+    hid = util.to_dev(R)
+    lib.nvfp4_invoke_fp4_gemv_add(dA.data_ptr(), ctypes.byref(qw1), hid.data_ptr(), hid.data_ptr(), st)
+    assert lib.nvfp4_last_status() == 0
+    torch.cuda.synchronize()
+    assert ob.rel_frobenius(util.to_host_u16(hid), ob.linear(A, p1, s1, 1.0, residual=R)) <= TOL
+    # gemm / gemm_add with M = 4
+    A4 = util.make_bf16((4, K), seed=8)
+    R4 = util.make_bf16((4, N), seed=9)
+    dA4 = util.to_dev(A4)
+    o = torch.zeros(4, N, dtype=torch.int16, device="cuda")
+    lib.nvfp4_invoke_fp4_gemm(dA4.data_ptr(), ctypes.byref(qw2), o.data_ptr(), 4, st)
+    assert lib.nvfp4_last_status() == 0
+    hid4 = util.to_dev(R4)
+    lib.nvfp4_invoke_fp4_gemm_add(dA4.data_ptr(), ctypes.byref(qw2), hid4.data_ptr(), hid4.data_ptr(), 4, st)
+    assert lib.nvfp4_last_status() == 0
+    torch.cuda.synchronize()
+    assert ob.rel_frobenius(util.to_host_u16(o), ob.linear(A4, p2, s2, 2.0)) <= TOL
+    assert ob.rel_frobenius(util.to_host_u16(hid4), ob.linear(A4, p2, s2, 2.0, residual=R4)) <= TOL
+    # an invalid call is recorded, not executed
+    bad = nvfp4.QuantizedWeight(dp1.data_ptr(), ds1.data_ptr(), 1.0, 1.0, N, 24)
+    lib.nvfp4_invoke_fp4_gemv(dA.data_ptr(), ctypes.byref(bad), c1.data_ptr(), st)
+    assert lib.nvfp4_last_status() == -2
+    lib.nvfp4_cleanup_fp4_cublaslt()
+
+
+def test_argument_validation(handle):
+    import torch
+    N, K = 32, 64
+    p, s = util.make_weight(N, K, seed=1)
+    dp, ds = util.to_dev(p), util.to_dev(s)
+    buf = torch.zeros(4096, dtype=torch.int16, device="cuda")
+    a, c = buf.data_ptr(), buf.data_ptr() + 2048
+    call = lambda **kw: handle.linear(kw.get("A", a), kw.get("M", 1), dp, ds, kw.get("gs", 1.0), kw.get("N", N),
+                                      kw.get("K", K), kw.get("C", c), residual=kw.get("R"), check=False)
+    assert call() == 0
+    assert call(K=24) == -2 and call(N=0) == -2 and call(M=-1) == -2
+    assert call(A=a + 2) == -3 and call(C=c + 4) == -3 and call(R=c + 8) == -3
+    assert call(C=a) == -5                      # A aliases C
+    assert call(gs=0.0) == -6 and call(gs=-1.0) == -6 and call(gs=float("nan")) == -6
+    assert call(M=0) == 0
+    torch.cuda.synchronize()
+    handle.set_option("prefill_impl", 1)
+    try:   # debug prefill path needs 2*N*K bytes of workspace: 512 MiB handle cannot hold 40000 x 8192
+        st = handle.lib.nvfp4_linear(handle.h, a, 17, dp.data_ptr(), ds.data_ptr(), 1.0, 40000, 8192, None, c,
+                                     torch.cuda.current_stream().cuda_stream)
+        assert st == -4
+    finally:
+        handle.set_option("prefill_impl", 0)
+    with pytest.raises(nvfp4.Nvfp4Error):
+        handle.set_option("decode_impl", 7)
+
+
+def test_launch_counter(handle):
+    N, K = 64, 256
+    p, s = util.make_weight(N, K, seed=1)
+    before = handle.launch_count()
+    run_linear(handle, util.make_bf16((2, K), seed=2), p, s, 1.0)
+    assert handle.launch_count() > before
+
+
+# ---------------------------------------------------------------- SwiGLU
+
+@pytest.mark.parametrize("T,I", [(1, 17408), (3, 136), (5, 8), (2, 2176)])
+def test_swiglu(handle, T, I):
+    import torch
+    merged = util.make_bf16((T, 2 * I), seed=T + I, std=2.0)
+    d = util.to_dev(merged)
+    out = torch.zeros(T, I, dtype=torch.int16, device="cuda")
+    handle.swiglu(d, None, T, I, out)
+    torch.cuda.synchronize()
+    want = ob.swiglu_merged(merged)
+    assert util.bf16_ulp_diff(util.to_host_u16(out), want) <= 1
+    g = util.to_dev(np.ascontiguousarray(merged[:, :I]))
+    u = util.to_dev(np.ascontiguousarray(merged[:, I:]))
+    out2 = torch.zeros(T, I, dtype=torch.int16, device="cuda")
+    handle.swiglu(g, u, T, I, out2)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+# ---------------------------------------------------------------- prefill (M > 16)
+
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(17, 64, 256), (64, 256, 512), (100, 300, 1024), (128, 256, 5120),
+                                   (256, 512, 2048), (300, 1000, 640)])
+def test_prefill_small(handle, impl, M, N, K):
+    packed, scale = util.make_weight(N, K, seed=M + N, sigma=0.14)
+    A = util.make_bf16((M, K), seed=M)
+    R = util.make_bf16((M, N), seed=N) if M % 2 == 0 else None
+    got = with_impl(handle, "prefill", impl, lambda: run_linear(handle, A, packed, scale, 1.0, residual=R))
+    want = ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMM, threads=8)
+    assert ob.rel_frobenius(got, want) <= TOL
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_prefill_global_scale(handle, impl):
+    """global_scale != 1: the library keeps FP32 block scales for every M (the reference's M<=8
+    arithmetic); the reference's M>8 path rounds weights to BF16 first, which moves its own
+    result by ~1e-3, so that distance is only bounded loosely here."""
+    M, N, K = 64, 128, 1024
+    packed, scale = util.make_weight(N, K, seed=3, sigma=0.14)
+    A = util.make_bf16((M, K), seed=4)
+    got = with_impl(handle, "prefill", impl, lambda: run_linear(handle, A, packed, scale, 2.6))
+    if impl == 1:   # the debug path is the reference's two-step structure: BF16-rounded weights
+        assert ob.rel_frobenius(got, ob.linear(A, packed, scale, 2.6, mode=ob.GEMM, threads=8)) <= TOL
+    else:
+        assert ob.rel_frobenius(got, ob.linear(A, packed, scale, 2.6, mode=ob.GEMV, threads=8)) <= TOL
+        assert ob.rel_frobenius(got, ob.linear(A, packed, scale, 2.6, mode=ob.GEMM, threads=8)) <= 3e-3
+
+
+# ---------------------------------------------------------------- host-buffer convenience path
+
+def test_linear_host(handle):
+    import torch
+    N, K, M = 128, 512, 3
+    packed, scale = util.make_weight(N, K, seed=6)
+    A = util.make_bf16((M, K), seed=7)
+    R = util.make_bf16((M, N), seed=8)
+    hA = torch.from_numpy(A.view(np.int16)).pin_memory()
+    hR = torch.from_numpy(R.view(np.int16)).pin_memory()
+    hC = torch.zeros(M, N, dtype=torch.int16).pin_memory()
+    handle.linear_host(hA, M, util.to_dev(packed), util.to_dev(scale), 1.0, N, K, hC, residual_host=hR)
+    assert ob.rel_frobenius(hC.numpy().view(np.uint16), ob.linear(A, packed, scale, 1.0, residual=R)) <= TOL
+
+
+# ---------------------------------------------------------------- against the reference itself
+
+@pytest.mark.skipif(not os.path.exists(GOLDEN), reason="golden file not generated yet")
+def test_against_committed_reference_outputs(handle):
+    import torch
+    import make_reference_golden as mg
+    g = np.load(GOLDEN)
+    for name, c in mg.cases().items():
+        want = g[name]
+        if c["kind"] == "dequant":
+            out = torch.zeros(256, 16, dtype=torch.int16, device="cuda")
+            handle.dequant(util.to_dev(c["packed"]), util.to_dev(c["scale"]), c["gs"], 256, 16, out)
+            torch.cuda.synchronize()
+            assert np.array_equal(util.to_host_u16(out).T, want), name
+        elif c["kind"] == "linear":
+            got = run_linear(handle, c["A"], c["packed"], c["scale"], c["gs"], residual=c["residual"])
+            tol = TOL if (c["gs"] == 1.0 or c["A"].shape[0] <= 8) else 3e-3
+            assert ob.rel_frobenius(got, want) <= tol, name
+        elif c["kind"] == "dual":
+            a = run_linear(handle, c["A"], c["packed"], c["scale"], c["gs"])
+            b = run_linear(handle, c["A"], c["packed2"], c["scale2"], c["gs2"])
+            assert ob.rel_frobenius(np.concatenate([a, b], axis=1), want) <= TOL, name
+        elif c["kind"] == "swiglu":
+            T, I = c["merged"].shape[0], c["merged"].shape[1] // 2
+            out = torch.zeros(T, I, dtype=torch.int16, device="cuda")
+            handle.swiglu(util.to_dev(c["merged"]), None, T, I, out)
+            torch.cuda.synchronize()
+            assert util.bf16_ulp_diff(util.to_host_u16(out), want) <= 1, name
+
+
+@pytest.mark.skipif(not ob.ref_available(), reason="oracle/_ref not built")
+def test_side_by_side_with_reference_kernels(handle):
+    """The reference's kernels and ours on the same device buffers, BASELINE-like shapes."""
+    import torch
+    ref = ob.load_ref()
+    st = torch.cuda.current_stream().cuda_stream
+    for (N, K, M) in [(5120, 5120, 1), (2048, 5120, 4), (1024, 17408, 8), (512, 2048, 16), (256, 1024, 64)]:
+        packed, scale = util.make_weight(N, K, seed=N + M)
+        A = util.make_bf16((M, K), seed=M)
+        dA, dp, ds = util.to_dev(A), util.to_dev(packed), util.to_dev(scale)
+        o_ref = torch.zeros(M, N, dtype=torch.int16, device="cuda")
+        o_our = torch.zeros(M, N, dtype=torch.int16, device="cuda")
+        ref.ref_fp4_gemm(dA.data_ptr(), dp.data_ptr(), ds.data_ptr(), 1.0, N, K, o_ref.data_ptr(), M, st)
+        handle.linear(dA, M, dp, ds, 1.0, N, K, o_our)
+        torch.cuda.synchronize()
+        assert ob.rel_frobenius(util.to_host_u16(o_our), util.to_host_u16(o_ref)) <= TOL, (N, K, M)
+
+
+# ---------------------------------------------------------------- full-size, size-independent properties
+
+@pytest.mark.parametrize("N,K", [(34816, 5120), (5120, 17408)])
+def test_full_size_properties(handle, N, K):
+    """BASELINE's MLP shapes: (a) doubling the activations doubles every output exactly,
+    (b) zero activations return the residual bit for bit, (c) sampled rows match the oracle."""
+    import torch
+    M = 4
+    g = torch.Generator(device="cuda").manual_seed(N)
+    packed = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    scale = torch.randint(1, 9, (N, K // 16), dtype=torch.uint8, device="cuda", generator=g)
+    A = util.make_bf16((M, K), seed=1)
+    R = util.make_bf16((M, N), seed=2)
+    dA = util.to_dev(A)
+    dA2 = util.to_dev((A + 0x0080).astype(np.uint16))          # exponent + 1 = exactly 2x
+    c1 = torch.zeros(M, N, dtype=torch.int16, device="cuda")
+    c2 = torch.zeros(M, N, dtype=torch.int16, device="cuda")
+    handle.linear(dA, M, packed, scale, 1.0, N, K, c1)
+    handle.linear(dA2, M, packed, scale, 1.0, N, K, c2)
+    zero = torch.zeros(M, K, dtype=torch.int16, device="cuda")
+    c3 = util.to_dev(R)
+    handle.linear(zero, M, packed, scale, 1.0, N, K, c3, residual=c3)
+    torch.cuda.synchronize()
+    h1, h2 = util.to_host_u16(c1), util.to_host_u16(c2)
+    nz = (h1 & 0x7FFF) != 0
+    assert np.array_equal(h2[nz], (h1[nz] + 0x0080).astype(np.uint16))
+    assert np.array_equal(util.to_host_u16(c3), R)
+    rows = np.random.default_rng(N).choice(N, 64, replace=False)
+    hp, hs = packed.cpu().numpy(), scale.cpu().numpy()
+    sub = ob.linear(A, np.ascontiguousarray(hp[rows]), np.ascontiguousarray(hs[rows]), 1.0, mode=ob.GEMV)
+    assert ob.rel_frobenius(np.ascontiguousarray(h1[:, rows]), sub) <= TOL
