@@ -141,6 +141,12 @@ int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M,
                       int N, int K, const void* residual_host_or_null, void* C_host,
                       nvfp4_stream_t stream);
 
+/* Reads the sticky device-side status word of the handle (synchronises the device).
+ * 0 = no kernel of this handle ever gave up a bounded wait; otherwise the code of the first
+ * wait that ran out (0x1xx producer ring slot, 0x2xx consumer ring slot, 0x300 cross-CTA
+ * partial flag, 0x4xx tensor-core pipeline). */
+int nvfp4_device_status(nvfp4_handle* h, unsigned int* status);
+
 /* Number of kernels this library has launched on the handle since creation. */
 int nvfp4_launch_count(nvfp4_handle* h, unsigned long long* count);
 

@@ -207,6 +207,17 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     return NVFP4_OK;
 }
 
+int nvfp4_device_status(nvfp4_handle* h, unsigned int* status) {
+    if (!h || !status) return NVFP4_E_NULL;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(h->dev.device);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(status, h->workspace, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+    cudaSetDevice(prev);
+    return cuda_status(e);
+}
+
 int nvfp4_launch_count(nvfp4_handle* h, unsigned long long* count) {
     if (!h || !count) return NVFP4_E_NULL;
     *count = h->launches;
@@ -281,11 +292,11 @@ int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M, const uint8_t*
         dR = dC;
     }
     // Shrink the workspace seen by the kernels so that their scratch never reaches the staging area.
-    nvfp4_handle view = *h;
-    view.workspace_bytes = h->workspace_bytes - tail;
+    const size_t full_bytes = h->workspace_bytes;
+    h->workspace_bytes = full_bytes - tail;
     LinearArgs a{dA, packed, scale, 1.0f / global_scale, dR, dC, M, N, K};
-    int st = run_linear(&view, a, stream);
-    h->launches = view.launches;
+    int st = run_linear(h, a, stream);
+    h->workspace_bytes = full_bytes;
     if (st) return st;
     e = cudaMemcpyAsync(C_host, dC, (size_t)M * N * 2, cudaMemcpyDeviceToHost, stream);
     if (e != cudaSuccess) return (int)e;

@@ -25,6 +25,7 @@ struct nvfp4_device_info {
     int sm_count;
     int cc_major, cc_minor;
     size_t smem_optin;
+    unsigned int decode_epoch;   // bumped per GEMV launch; tags the cross-CTA flags in the scratch
 };
 
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
@@ -43,8 +44,9 @@ cudaError_t launch_gemm_bf16_simple(const void* A, const void* Wdq, const void* 
 // --- decode_mma.cu: TMA-fed shared-memory ring + register dequant + warp MMA GEMV (M <= 16).
 bool decode_mma_supported(const LinearArgs& a);
 size_t decode_mma_scratch_bytes(const LinearArgs& a, const nvfp4_device_info& dev);
-cudaError_t launch_decode_mma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch, int* launches,
+cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
                               cudaStream_t s);
+cudaError_t configure_decode_mma();
 
 // --- prefill_umma.cu: fused dequant + tcgen05 BF16 GEMM with TMEM accumulators.
 bool prefill_umma_supported(const LinearArgs& a);

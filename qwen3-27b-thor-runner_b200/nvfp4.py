@@ -48,6 +48,7 @@ SIGNATURES = {
     "nvfp4_linear_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int,
                                   c_void_p, c_void_p, c_void_p]),
     "nvfp4_launch_count": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_ulonglong)]),
+    "nvfp4_device_status": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint)]),
 }
 
 _lib = None
@@ -130,6 +131,11 @@ class Handle:
     def launch_count(self):
         v = ctypes.c_ulonglong()
         self._check(self.lib.nvfp4_launch_count(self.h, ctypes.byref(v)))
+        return v.value
+
+    def device_status(self):
+        v = ctypes.c_uint()
+        self._check(self.lib.nvfp4_device_status(self.h, ctypes.byref(v)))
         return v.value
 
     def linear(self, A, M, packed, scale, global_scale, N, K, C, residual=None, stream=None, check=True):

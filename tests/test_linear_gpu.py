@@ -253,6 +253,11 @@ def test_argument_validation(handle):
         handle.set_option("decode_impl", 7)
 
 
+def test_device_status_clean(handle):
+    """No bounded wait in any kernel launched so far has run out."""
+    assert handle.device_status() == 0
+
+
 def test_launch_counter(handle):
     N, K = 64, 256
     p, s = util.make_weight(N, K, seed=1)
