@@ -2,23 +2,28 @@
 //
 //   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
 //
-// Structure (one CTA per SM, 1 producer warp + 8 consumer warps):
-//   * The weight matrix is cut into units of 128 rows x 256 k (16 KB of packed codes + 2 KB of
-//     block scales).  The units, ordered row-tile-major, are split evenly over the CTAs
-//     ("stream-K"): every CTA streams the same number of bytes (+-1 unit) whatever N and K are.
-//   * The producer warp feeds a multi-stage shared-memory ring: per unit two TMA tile copies
-//     (packed codes with the 128-byte swizzle, scales) and 16-byte cp.async copies of the
-//     activation slice, all completing on one mbarrier.  No cluster multicast anywhere.
-//   * Each consumer warp owns 16 of the 128 rows.  Codes are expanded in registers: two E2M1
-//     nibbles -> one bf16x2 register by mask, integer multiply (places sign and exponent/mantissa
-//     bits) and mask, then one bf16x2 multiply by the block scale taken from a 256-entry
-//     shared-memory table.  Every product lut*scale is exact in BF16 (2 + 4 significant bits).
-//     The dot products run on the tensor cores (mma.sync m16n8k16, weights as the 16-row operand,
-//     the <= 8 tokens as the 8-column operand) with FP32 accumulators -- CUDA cores alone cannot
-//     convert AND multiply-accumulate 0.56 B/element at HBM speed for M > 1.
+// Structure (one CTA per SM, 1 producer warp + 16 consumer warps in two groups of 8):
+//   * The weight matrix is cut into half-units of 128 rows x 256 k (16 KB of packed codes + 2 KB
+//     of block scales).  The half-units, ordered row-tile-major, are split evenly over the CTAs
+//     ("stream-K"): every CTA streams the same number of bytes (+-1 half-unit) whatever N, K are.
+//   * The producer warp feeds a multi-stage shared-memory ring with TMA tile copies (packed codes
+//     with the 128-byte swizzle, scales), completing on the stage's mbarrier.  A stage carries two
+//     consecutive half-units (36 KB): large enough that one issuing thread keeps HBM busy.  No
+//     cluster multicast anywhere.
+//   * Consumer group h works on half-unit h of every stage; each of its 8 warps owns 16 of the 128
+//     rows.  Codes are expanded in registers: two E2M1 nibbles -> one bf16x2 register by mask,
+//     integer multiply (places sign and exponent/mantissa bits) and mask, then one bf16x2 multiply
+//     by the block scale taken from a 256-entry shared-memory table.  Every product lut*scale is
+//     exact in BF16 (2 + 4 significant bits).  The dot products run on the tensor cores (mma.sync
+//     m16n8k16, weights as the 16-row operand, the <= 8 tokens as the 8-column operand) with FP32
+//     accumulators -- CUDA cores alone cannot convert AND multiply-accumulate 0.56 B/element at
+//     HBM speed for M > 1.
+//   * Activations: when they fit, the CTA's whole k range stays resident in shared memory, stored
+//     once in MMA fragment order by the consumer warps; otherwise the producer lanes cp.async the
+//     slice of each stage and the consumers permute it on the fly.
 //   * A row tile whose K range is split over several CTAs is finished by the CTA that holds its
-//     first unit: the others store FP32 partials to the handle's scratch and raise a flag; the
-//     owner adds them in a fixed order (deterministic), applies 2^32/global_scale and the
+//     first half-unit: the others store FP32 partials to the handle's scratch and raise a flag;
+//     the owner adds them in a fixed order (deterministic), applies 2^32/global_scale and the
 //     residual in FP32 and rounds once to BF16.  Its wait on the flags is bounded.
 //
 // Arithmetic: group products are summed in FP32 by the MMA, block scales are applied exactly
@@ -35,30 +40,25 @@
 namespace nvfp4 {
 namespace {
 
-constexpr int kRT = 128;                          // rows per unit
-constexpr int kKC = 256;                          // k elements per unit
-constexpr int kConsumerWarps = 8;
+constexpr int kRT = 128;                          // rows per half-unit
+constexpr int kKC = 256;                          // k elements per half-unit
+constexpr int kGroupWarps = 8;                    // warps that share one half-unit (16 rows each)
+constexpr int kGroups = 2;                        // consumer groups: group h takes half-unit h of every stage
+constexpr int kConsumerWarps = kGroupWarps * kGroups;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;   // + producer warp
-constexpr int kPackedBytes = kRT * kKC / 2;       // 16384
-constexpr int kScaleBytes = kRT * kKC / 16;       // 2048
-constexpr int kActRowBytes = kKC * 2;             // 512 per token
+constexpr int kPackedBytes = kRT * kKC / 2;       // 16384 per half-unit
+constexpr int kScaleBytes = kRT * kKC / 16;       // 2048 per half-unit
+constexpr int kActRowBytes = kKC * 2;             // 512 per token per half-unit
 constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 output tile
 constexpr uint32_t kTxBytes = kPackedBytes + kScaleBytes;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 227 * 1024;
 
 // Scratch layout (handle workspace): status word, per-CTA flags, per-CTA partial tiles.
 constexpr size_t kFlagsOffset = 256;
 constexpr size_t kPartialOffset = 8192;
 constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / 4);
-
-template <int NT> struct Cfg {
-    static constexpr int kStages = (NT == 1) ? 8 : 7;
-    static constexpr int kActBytes = NT * 8 * kActRowBytes;
-    static constexpr int kStageBytes = kPackedBytes + kScaleBytes + kActBytes;
-    static constexpr int kOutBytes = NT * 8 * kOutLd * 4;
-    static constexpr int kSmemBytes = 1024 /*align slack*/ + kStages * kStageBytes + kOutBytes + 1024 /*table*/ +
-                                      2 * kStages * 8 + 64;
-};
 
 struct DecodeParams {
     const __nv_bfloat16* A;
@@ -67,14 +67,17 @@ struct DecodeParams {
     unsigned char* scratch;
     float final_scale;   // 2^32 / global_scale
     int M, N, K;
-    int units, kchunks;  // total units, units per row tile
+    int units, kchunks;  // total half-units, half-units per row tile
+    int stages;          // ring depth (each stage holds up to two half-units)
+    int act_slots;       // resident mode: activation slots held in shared memory
+    int act_all;         // resident mode: 1 = slot index is the k-chunk, 0 = position in the CTA's span
     unsigned int epoch;
 };
 
-// Two E2M1 codes (one per 16-bit half of x, already isolated at bit `shift` of each half)
+// Two E2M1 codes (one per 16-bit half of x, already isolated by the caller's mask)
 // -> bf16x2 holding e2m1 * 2^-126 : sign at bit 15, (e e m) at bits 8..6 of each half.
-// mul places the nibble at [15:12] and at [9:6]; the mask keeps the sign from the first copy and
-// the magnitude from the second.
+// The multiply copies the nibble to [15:12] and to [9:6]; the mask keeps the sign from the first
+// copy and the magnitude from the second.
 __device__ __forceinline__ uint32_t place_pair(uint32_t isolated, uint32_t mul) {
     return (isolated * mul) & 0x81C081C0u;
 }
@@ -87,21 +90,36 @@ __device__ __forceinline__ void expand_u32(uint32_t q, uint32_t S, uint32_t (&d)
     d[3] = ptx::mul_bf16x2(place_pair(q2 & 0x00F000F0u, 0x0104u), S);   // elements 3,7
 }
 
-template <int NT>
+// 16-byte chunk c (0..31) of a 512-byte token row is stored at chunk position
+// (c & ~7) | ((c & 7) ^ ((c >> 3) | (tok & 1) << 2)): the consumers' 128-bit loads (lanes = 8 tokens
+// x 4 chunk groups) then hit 8 different bank groups.
+__device__ __forceinline__ int act_phys_chunk(int c, int tok) {
+    return (c & ~7) | ((c & 7) ^ (((c >> 3) & 3) | ((tok & 1) << 2)));
+}
+
+// NT: 8-token column tiles (1: M <= 8, 2: M <= 16).
+// RES: activations of the CTA's whole k range stay resident in shared memory in MMA fragment
+//      order (loaded once by the consumer warps); otherwise they travel with each stage in
+//      natural order (cp.async by the producer lanes) and are permuted by the consumers.
+// PROBE selects measurement-only variants (the library instantiates PROBE = 0 only):
+//   bit 0: consumers skip the math (ring hand-shake only)   bit 3: producer moves no data
+template <int NT, bool RES, int PROBE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const DecodeParams p) {
-    using C_ = Cfg<NT>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* s_packed = smem;                                          // kStages x 16 KB, 1024-aligned
-    unsigned char* s_scale = s_packed + C_::kStages * kPackedBytes;          // kStages x 2 KB
-    unsigned char* s_act = s_scale + C_::kStages * kScaleBytes;              // kStages x NT*4 KB
-    float* s_out = reinterpret_cast<float*>(s_act + C_::kStages * C_::kActBytes);
-    uint32_t* s_table = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(s_out) + C_::kOutBytes);
+    const int stages = p.stages;
+    constexpr int kStageActBytes = RES ? 0 : 2 * NT * 8 * kActRowBytes;
+    unsigned char* s_packed = smem;                                       // stages x 2 x 16 KB, 1024-aligned
+    unsigned char* s_scale = s_packed + stages * 2 * kPackedBytes;        // stages x 2 x 2 KB
+    unsigned char* s_act = s_scale + stages * 2 * kScaleBytes;            // RES: slots x M x 512 B, else stages x 2 x NT*4 KB
+    const int act_bytes = RES ? p.act_slots * p.M * kActRowBytes : stages * kStageActBytes;
+    float* s_out = reinterpret_cast<float*>(s_act + act_bytes);           // kGroups FP32 tiles
+    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_out + kGroups * NT * 8 * kOutLd);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_table + 256);
-    uint64_t* empty_bar = full_bar + C_::kStages;
-    volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + C_::kStages);
+    uint64_t* empty_bar = full_bar + kMaxStages;
+    volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     unsigned int* flags = reinterpret_cast<unsigned int*>(p.scratch + kFlagsOffset);
@@ -113,9 +131,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     const long long u_end = (long long)(cta + 1) * p.units / G;
 
     if (tid == 0) {
-        for (int s = 0; s < C_::kStages; ++s) {
-            ptx::mbar_init(&full_bar[s], 1 + 32);             // expect_tx arrive + one cp.async arrive per producer lane
-            ptx::mbar_init(&empty_bar[s], kConsumerWarps);
+        for (int s = 0; s < stages; ++s) {
+            ptx::mbar_init(&full_bar[s], RES ? 1 : 1 + 32);   // expect_tx arrive (+ one cp.async arrive per producer lane)
+            ptx::mbar_init(&empty_bar[s], kConsumerWarps);    // every consumer warp releases every stage
         }
         *s_abort = 0;
         ptx::fence_mbar_init();
@@ -137,46 +155,89 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         }
         const uint64_t pol_stream = ptx::policy_evict_first();
         int it = 0;
-        for (long long u = u_begin; u < u_end; ++u, ++it) {
-            const int stage = it % C_::kStages;
-            const uint32_t ph = (uint32_t)((it / C_::kStages) & 1);
-            ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0x100u + (unsigned)stage);
-            const int tile = (int)(u / p.kchunks), kc = (int)(u % p.kchunks);
-            const int row0 = tile * kRT, k0 = kc * kKC;
-            if (lane == 0) {
-                ptx::mbar_arrive_expect_tx(&full_bar[stage], kTxBytes);
-                ptx::tma_load_2d(s_packed + stage * kPackedBytes, &tm_packed, &full_bar[stage], k0 >> 1, row0, pol_stream);
-                ptx::tma_load_2d(s_scale + stage * kScaleBytes, &tm_scale, &full_bar[stage], k0 >> 4, row0, pol_stream);
+        long long hu = u_begin;
+        while (hu < u_end) {
+            const int tile = (int)(hu / p.kchunks);
+            const long long tile_end = (long long)(tile + 1) * p.kchunks;
+            const long long seg_end = tile_end < u_end ? tile_end : u_end;
+            const int row0 = tile * kRT;
+            while (hu < seg_end) {
+                const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
+                const int stage = it % stages;
+                const uint32_t ph = (uint32_t)((it / stages) & 1);
+                ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0x100u + (unsigned)stage);
+                const int k0 = (int)(hu % p.kchunks) * kKC;
+                if (lane == 0) {
+                    if (PROBE & 8) {
+                        ptx::mbar_arrive(&full_bar[stage]);
+                    } else {
+                        ptx::mbar_arrive_expect_tx(&full_bar[stage], kTxBytes * cnt);
+                        for (int h = 0; h < cnt; ++h) {
+                            ptx::tma_load_2d(s_packed + (stage * 2 + h) * kPackedBytes, &tm_packed, &full_bar[stage],
+                                             (k0 + h * kKC) >> 1, row0, pol_stream);
+                            ptx::tma_load_2d(s_scale + (stage * 2 + h) * kScaleBytes, &tm_scale, &full_bar[stage],
+                                             (k0 + h * kKC) >> 4, row0, pol_stream);
+                        }
+                    }
+                }
+                if (!RES) {
+                    unsigned char* act = s_act + stage * kStageActBytes;
+                    for (int i = lane; i < cnt * p.M * 32; i += 32) {
+                        const int h = i / (p.M * 32), r = i % (p.M * 32);
+                        const int tok = r >> 5, c = r & 31;
+                        const int k = k0 + h * kKC + c * 8;
+                        const bool in = k < p.K;
+                        ptx::cp_async_16(act + (h * NT * 8 + tok) * kActRowBytes + act_phys_chunk(c, tok) * 16,
+                                         p.A + (size_t)tok * p.K + (in ? k : 0), in ? 16u : 0u);
+                    }
+                    ptx::cp_async_mbar_arrive_noinc(&full_bar[stage]);
+                }
+                hu += cnt;
+                ++it;
             }
-            unsigned char* act = s_act + stage * C_::kActBytes;
-            for (int i = lane; i < p.M * 32; i += 32) {
-                const int tok = i >> 5, c = i & 31;
-                const int k = k0 + c * 8;
-                const bool in = k < p.K;
-                const __nv_bfloat16* src = p.A + (size_t)tok * p.K + (in ? k : 0);
-                const int phys = (c & ~7) | ((c & 7) ^ (((c >> 3) & 3) | ((tok & 1) << 2)));
-                ptx::cp_async_16(act + tok * kActRowBytes + phys * 16, src, in ? 16u : 0u);
-            }
-            ptx::cp_async_mbar_arrive_noinc(&full_bar[stage]);
         }
         return;
     }
 
     // ---------------------------------------------------------------------- consumer warps
+    const int grp = warp / kGroupWarps, gw = warp % kGroupWarps;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = warp * 16 + g;                       // tile rows r0 and r0 + 8
+    const int r0 = gw * 16 + g;                                // tile rows r0 and r0 + 8
     // Shared-memory offsets that do not change from stage to stage.
     const int off_w0 = r0 * 128 + (((2 * t) ^ g) << 4);       // row r0, logical 16-byte chunk 2t   (swizzle: chunk ^ (row & 7))
     const int off_w1 = r0 * 128 + (((2 * t + 1) ^ g) << 4);   // row r0, chunk 2t+1
     const int off_s = r0 * 16 + 4 * t;                         // 4 scale bytes: blocks 4t..4t+3 of the row
-    const int act_sw = t | ((g & 1) << 2);
-    const int off_a = g * kActRowBytes + t * 128;              // token g, chunks 8t..8t+7 (low 3 bits swizzled)
+    const int tok0 = RES ? (g < p.M ? g : 0) : g;              // token feeding MMA column g (columns >= M are never stored)
+    const int tok1 = RES ? (g + 8 < p.M ? g + 8 : 0) : g + 8;
+    const int act_sw0 = t | ((tok0 & 1) << 2), act_sw1 = t | ((tok1 & 1) << 2);
+    float* my_out = s_out + grp * (NT * 8 * kOutLd);
+
+    if (RES) {
+        // Resident activations: every 16-byte chunk (8 consecutive k of one token) is stored as
+        // (x0,x4)(x1,x5)(x2,x6)(x3,x7), the B fragments of the two MMAs that consume it.
+        const int per_slot = p.M * 32;
+        for (int i = tid; i < p.act_slots * per_slot; i += kConsumerThreads) {
+            const int j = i / per_slot, r = i % per_slot;
+            const int tok = r >> 5, c = r & 31;
+            const int kc = p.act_all ? j : (int)((u_begin + j) % p.kchunks);
+            const int k = kc * kKC + c * 8;
+            uint4 x = make_uint4(0u, 0u, 0u, 0u);
+            if (k < p.K) x = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)tok * p.K + k));
+            uint4 y;
+            y.x = ptx::prmt(x.x, x.z, 0x5410u);   // (x0,x4)
+            y.y = ptx::prmt(x.x, x.z, 0x7632u);   // (x1,x5)
+            y.z = ptx::prmt(x.y, x.w, 0x5410u);   // (x2,x6)
+            y.w = ptx::prmt(x.y, x.w, 0x7632u);   // (x3,x7)
+            *reinterpret_cast<uint4*>(s_act + (size_t)(j * p.M + tok) * kActRowBytes + act_phys_chunk(c, tok) * 16) = y;
+        }
+        ptx::named_barrier_sync(1, kConsumerThreads);
+    }
 
     int it = 0;
-    long long u = u_begin;
-    while (u < u_end) {
-        const int tile = (int)(u / p.kchunks);
-        const int kc_first = (int)(u % p.kchunks);
+    long long hu = u_begin;
+    while (hu < u_end) {
+        const int tile = (int)(hu / p.kchunks);
+        const int kc_first = (int)(hu % p.kchunks);
         const long long tile_end = (long long)(tile + 1) * p.kchunks;
         const long long seg_end = tile_end < u_end ? tile_end : u_end;
 
@@ -186,41 +247,58 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[nt][j] = 0.0f;
 
-        for (; u < seg_end; ++u, ++it) {
-            const int stage = it % C_::kStages;
-            const uint32_t ph = (uint32_t)((it / C_::kStages) & 1);
+        for (; hu < seg_end; ++it) {
+            const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
+            const long long my_hu = hu + grp;
+            hu += cnt;
+            const int stage = it % stages;
+            const uint32_t ph = (uint32_t)((it / stages) & 1);
+            // Every warp waits on every stage in order (an mbarrier waiter may not skip a phase);
+            // group 1 has nothing to do in a stage that carries a single half-unit.
             ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0x200u + (unsigned)stage);
-            const unsigned char* wp = s_packed + stage * kPackedBytes;
-            const unsigned char* sp = s_scale + stage * kScaleBytes;
-            const unsigned char* ap = s_act + stage * C_::kActBytes;
-            const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
-            const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
-            const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + off_w0 + 8 * 128);
-            const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + off_w1 + 8 * 128);
-            const uint32_t sa = *reinterpret_cast<const uint32_t*>(sp + off_s);
-            const uint32_t sb = *reinterpret_cast<const uint32_t*>(sp + off_s + 8 * 16);
-            const uint32_t qa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
-            const uint32_t qb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-            uint32_t Sa = 0, Sb = 0;
-#pragma unroll
-            for (int uu = 0; uu < 8; ++uu) {
-                if ((uu & 1) == 0) {
-                    Sa = s_table[(sa >> (8 * (uu >> 1))) & 0xFFu];
-                    Sb = s_table[(sb >> (8 * (uu >> 1))) & 0xFFu];
+            if (!(PROBE & 1) && grp < cnt) {
+                const unsigned char* wp = s_packed + (stage * 2 + grp) * kPackedBytes;
+                const unsigned char* sp = s_scale + (stage * 2 + grp) * kScaleBytes + off_s;
+                const unsigned char* ap0;
+                const unsigned char* ap1;
+                if (RES) {
+                    const int slot = p.act_all ? (int)(my_hu % p.kchunks) : (int)(my_hu - u_begin);
+                    ap0 = s_act + (size_t)(slot * p.M + tok0) * kActRowBytes + t * 128;
+                    ap1 = s_act + (size_t)(slot * p.M + tok1) * kActRowBytes + t * 128;
+                } else {
+                    ap0 = s_act + stage * kStageActBytes + (grp * NT * 8 + tok0) * kActRowBytes + t * 128;
+                    ap1 = s_act + stage * kStageActBytes + (grp * NT * 8 + tok1) * kActRowBytes + t * 128;
                 }
-                uint32_t da[4], db[4];
-                expand_u32(qa[uu], Sa, da);
-                expand_u32(qb[uu], Sb, db);
-                const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // elements (0,4 | 1,5) of this 8-group
-                const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // elements (2,6 | 3,7)
+                const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
+                const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
+                const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + off_w0 + 8 * 128);
+                const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + off_w1 + 8 * 128);
+                const uint32_t qa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
+                const uint32_t qb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
+                uint32_t Sa = 0, Sb = 0;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const uint4 x = *reinterpret_cast<const uint4*>(ap + nt * 8 * kActRowBytes + off_a + ((uu ^ act_sw) << 4));
-                    // x = (x0,x1) (x2,x3) (x4,x5) (x6,x7)  ->  (x0,x4) (x1,x5) (x2,x6) (x3,x7)
-                    const uint32_t b04 = ptx::prmt(x.x, x.z, 0x5410u), b15 = ptx::prmt(x.x, x.z, 0x7632u);
-                    const uint32_t b26 = ptx::prmt(x.y, x.w, 0x5410u), b37 = ptx::prmt(x.y, x.w, 0x7632u);
-                    ptx::mma_bf16_16x8x16(acc[nt], a_lo, b04, b15);
-                    ptx::mma_bf16_16x8x16(acc[nt], a_hi, b26, b37);
+                for (int uu = 0; uu < 8; ++uu) {
+                    if ((uu & 1) == 0) {
+                        Sa = s_table[sp[uu >> 1]];
+                        Sb = s_table[sp[8 * 16 + (uu >> 1)]];
+                    }
+                    uint32_t da[4], db[4];
+                    expand_u32(qa[uu], Sa, da);
+                    expand_u32(qb[uu], Sb, db);
+                    const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // elements (0,4 | 1,5) of this 8-group
+                    const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // elements (2,6 | 3,7)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint4 x = *reinterpret_cast<const uint4*>((nt ? ap1 : ap0) + ((uu ^ (nt ? act_sw1 : act_sw0)) << 4));
+                        if (RES) {
+                            ptx::mma_bf16_16x8x16(acc[nt], a_lo, x.x, x.y);
+                            ptx::mma_bf16_16x8x16(acc[nt], a_hi, x.z, x.w);
+                        } else {
+                            // natural order (x0,x1)(x2,x3)(x4,x5)(x6,x7) -> (x0,x4)(x1,x5) | (x2,x6)(x3,x7)
+                            ptx::mma_bf16_16x8x16(acc[nt], a_lo, ptx::prmt(x.x, x.z, 0x5410u), ptx::prmt(x.x, x.z, 0x7632u));
+                            ptx::mma_bf16_16x8x16(acc[nt], a_hi, ptx::prmt(x.y, x.w, 0x5410u), ptx::prmt(x.y, x.w, 0x7632u));
+                        }
+                    }
                 }
             }
             __syncwarp();
@@ -232,18 +310,19 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         const bool complete = owner && (seg_end == tile_end);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            s_out[(nt * 8 + 2 * t) * kOutLd + r0] = acc[nt][0];
-            s_out[(nt * 8 + 2 * t + 1) * kOutLd + r0] = acc[nt][1];
-            s_out[(nt * 8 + 2 * t) * kOutLd + r0 + 8] = acc[nt][2];
-            s_out[(nt * 8 + 2 * t + 1) * kOutLd + r0 + 8] = acc[nt][3];
+            my_out[(nt * 8 + 2 * t) * kOutLd + r0] = acc[nt][0];
+            my_out[(nt * 8 + 2 * t + 1) * kOutLd + r0] = acc[nt][1];
+            my_out[(nt * 8 + 2 * t) * kOutLd + r0 + 8] = acc[nt][2];
+            my_out[(nt * 8 + 2 * t + 1) * kOutLd + r0 + 8] = acc[nt][3];
         }
         ptx::named_barrier_sync(1, kConsumerThreads);
+        const float* out_b = s_out + NT * 8 * kOutLd;
         const int row_base = tile * kRT;
         if (!owner) {
             float* slot = partials + (size_t)cta * (NT * 8 * kRT);
             for (int i = tid; i < p.M * kRT; i += kConsumerThreads) {
                 const int m = i / kRT, r = i % kRT;
-                __stcg(slot + m * kRT + r, s_out[m * kOutLd + r]);
+                __stcg(slot + m * kRT + r, s_out[m * kOutLd + r] + out_b[m * kOutLd + r]);
             }
             __threadfence();
             ptx::named_barrier_sync(1, kConsumerThreads);
@@ -271,7 +350,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 const int m = i / kRT, r = i % kRT;
                 const int n = row_base + r;
                 if (n >= p.N) continue;
-                float v = s_out[m * kOutLd + r];
+                float v = s_out[m * kOutLd + r] + out_b[m * kOutLd + r];
                 for (int c = cta + 1; c <= last; ++c) v += __ldcg(partials + (size_t)c * (NT * 8 * kRT) + m * kRT + r);
                 v *= p.final_scale;
                 const size_t o = (size_t)m * p.N + n;
@@ -279,7 +358,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 p.C[o] = __float2bfloat16_rn(v);
             }
         }
-        ptx::named_barrier_sync(1, kConsumerThreads);   // s_out is reused by the next segment
+        ptx::named_barrier_sync(1, kConsumerThreads);   // the FP32 tiles are reused by the next segment
     }
 }
 
@@ -329,21 +408,24 @@ size_t decode_mma_scratch_bytes(const LinearArgs& a, const nvfp4_device_info& de
 }
 
 cudaError_t configure_decode_mma() {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg<1>::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                Cfg<2>::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    return e;
 }
 
-cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
-                              cudaStream_t s) {
-    CUtensorMap tmp, tms;
-    if (!make_u8_map(&tmp, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, (uint64_t)a.K / 2, 128, kRT,
-                     CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_u8_map(&tms, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, (uint64_t)a.K / 16, 16, kRT,
-                     CU_TENSOR_MAP_SWIZZLE_NONE))
-        return cudaErrorInvalidValue;
+namespace {
+
+// Shared-memory plan of one launch: resident activations when they fit beside a ring of at
+// least three stages, otherwise activations travel with the stages.
+struct DecodePlan {
+    DecodeParams p;
+    int grid, nt, smem;
+    bool resident;
+};
+
+bool plan_decode(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch, DecodePlan* out) {
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16*>(a.A);
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
@@ -354,13 +436,49 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
     p.kchunks = a.K / kKC;
     const long long tiles = (a.N + kRT - 1) / kRT;
     p.units = (int)(tiles * p.kchunks);
-    p.epoch = ++dev.decode_epoch;
     int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
     if (grid > p.units) grid = p.units;
-    if (a.M <= 8)
-        decode_mma_kernel<1><<<grid, kThreads, Cfg<1>::kSmemBytes, s>>>(tmp, tms, p);
-    else
-        decode_mma_kernel<2><<<grid, kThreads, Cfg<2>::kSmemBytes, s>>>(tmp, tms, p);
+    const int nt = a.M <= 8 ? 1 : 2;
+    const int fixed = 1024 + kGroups * nt * 8 * kOutLd * 4 + 1024 + 2 * kMaxStages * 8 + 64;
+    const int stage_w = 2 * (kPackedBytes + kScaleBytes);
+    const int max_span = (p.units + grid - 1) / grid;
+    p.act_all = p.kchunks <= max_span ? 1 : 0;
+    p.act_slots = p.act_all ? p.kchunks : max_span;
+    const int act_res = p.act_slots * a.M * kActRowBytes;
+    int stages = (kSmemBudget - fixed - act_res) / stage_w;
+    const bool resident = stages >= 3;
+    if (!resident) stages = (kSmemBudget - fixed) / (stage_w + 2 * nt * 8 * kActRowBytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return false;
+    p.stages = stages;
+    out->p = p;
+    out->grid = grid;
+    out->nt = nt;
+    out->resident = resident;
+    out->smem = fixed + stages * stage_w + (resident ? act_res : stages * 2 * nt * 8 * kActRowBytes);
+    return true;
+}
+
+}  // namespace
+
+cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
+                              cudaStream_t s) {
+    CUtensorMap tmp, tms;
+    if (!make_u8_map(&tmp, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, (uint64_t)a.K / 2, 128, kRT,
+                     CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_u8_map(&tms, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, (uint64_t)a.K / 16, 16, kRT,
+                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorInvalidValue;
+    DecodePlan pl;
+    if (!plan_decode(a, dev, scratch, &pl)) return cudaErrorInvalidValue;
+    pl.p.epoch = ++dev.decode_epoch;
+    if (pl.nt == 1) {
+        if (pl.resident) decode_mma_kernel<1, true><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+        else decode_mma_kernel<1, false><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+    } else {
+        if (pl.resident) decode_mma_kernel<2, true><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+        else decode_mma_kernel<2, false><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+    }
     if (launches) *launches = 1;
     return cudaGetLastError();
 }
