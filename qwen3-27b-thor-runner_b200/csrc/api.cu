@@ -59,9 +59,10 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
     if (a.M <= h->decode_max_m) {
         int impl = h->decode_impl;
-        if (impl == 0) impl = decode_mma_supported(a) ? 2 : 1;
+        const bool fast_ok = decode_mma_supported(a) && decode_mma_fits(a, h->dev);
+        if (impl == 0) impl = fast_ok ? 2 : 1;
         if (impl == 2) {
-            if (!decode_mma_supported(a)) return NVFP4_E_SHAPE;
+            if (!fast_ok) return NVFP4_E_SHAPE;
             size_t need = decode_mma_scratch_bytes(a, h->dev);
             if (need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
             int nl = 0;

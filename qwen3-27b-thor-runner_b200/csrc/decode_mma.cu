@@ -11,16 +11,16 @@
 //     consecutive half-units (36 KB): large enough that one issuing thread keeps HBM busy.  No
 //     cluster multicast anywhere.
 //   * Consumer group h works on half-unit h of every stage; each of its 8 warps owns 16 of the 128
-//     rows.  Codes are expanded in registers: two E2M1 nibbles -> one bf16x2 register by mask,
-//     integer multiply (places sign and exponent/mantissa bits) and mask, then one bf16x2 multiply
-//     by the block scale taken from a 256-entry shared-memory table.  Every product lut*scale is
-//     exact in BF16 (2 + 4 significant bits).  The dot products run on the tensor cores (mma.sync
-//     m16n8k16, weights as the 16-row operand, the <= 8 tokens as the 8-column operand) with FP32
-//     accumulators -- CUDA cores alone cannot convert AND multiply-accumulate 0.56 B/element at
-//     HBM speed for M > 1.
-//   * Activations: when they fit, the CTA's whole k range stays resident in shared memory, stored
-//     once in MMA fragment order by the consumer warps; otherwise the producer lanes cp.async the
-//     slice of each stage and the consumers permute it on the fly.
+//     rows.  Codes are expanded in registers: cvt.rn.f16x2.e2m1x2 turns one packed byte into two
+//     exact FP16 values, one f16x2 multiply applies the block scale taken from a 256-entry
+//     shared-memory table.  Every product lut*scale is exact in FP16 (2 + 4 significant bits, all
+//     within [2^-10, 2880]).  The dot products run on the tensor cores (mma.sync m16n8k16, weights
+//     as the 16-row operand, the <= 8 tokens as the 8-column operand) with FP32 accumulators --
+//     CUDA cores alone cannot convert AND multiply-accumulate 0.56 B/element at HBM speed.
+//   * Activations: the CTA's whole k range stays resident in shared memory as FP16, converted
+//     once by the consumer warps with an exact per-token power-of-two scale (largest magnitude ->
+//     [2^14, 2^15)), so BF16's wider exponent range costs nothing; the scale is undone in FP32.
+//     More than 8 tokens, or activations too large for shared memory, run as several launches.
 //   * A row tile whose K range is split over several CTAs is finished by the CTA that holds its
 //     first half-unit: the others store FP32 partials to the handle's scratch and raise a flag;
 //     the owner adds them in a fixed order (deterministic), applies 2^32/global_scale and the
@@ -49,46 +49,32 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;   // + producer warp
 constexpr int kPackedBytes = kRT * kKC / 2;       // 16384 per half-unit
 constexpr int kScaleBytes = kRT * kKC / 16;       // 2048 per half-unit
-constexpr int kActRowBytes = kKC * 2;             // 512 per token per half-unit
+constexpr int kActRowBytes = kKC * 2;             // 512 per token per half-unit (FP16)
+constexpr int kMaxTokens = 8;                     // tokens per launch (one 8-column MMA tile)
 constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 output tile
 constexpr uint32_t kTxBytes = kPackedBytes + kScaleBytes;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 227 * 1024;
 
 // Scratch layout (handle workspace): status word, per-CTA flags, per-CTA partial tiles.
-constexpr size_t kFlagsOffset = 256;
-constexpr size_t kPartialOffset = 8192;
-constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / 4);
+// A flag word holds the launch epoch once the CTA's partial for that 16-row slab is stored.
+constexpr size_t kFlagsOffset = 256;          // kGroupWarps flag words per CTA (one per 16-row slab)
+constexpr size_t kPartialOffset = 16384;
+constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kGroupWarps));
 
 struct DecodeParams {
     const __nv_bfloat16* A;
     const __nv_bfloat16* residual;
     __nv_bfloat16* C;
     unsigned char* scratch;
-    float final_scale;   // 2^32 / global_scale
-    int M, N, K;
+    float inv_gs;        // 1 / global_scale
+    int M, N, K;         // M <= 8 tokens in this launch
     int units, kchunks;  // total half-units, half-units per row tile
     int stages;          // ring depth (each stage holds up to two half-units)
-    int act_slots;       // resident mode: activation slots held in shared memory
-    int act_all;         // resident mode: 1 = slot index is the k-chunk, 0 = position in the CTA's span
+    int act_slots;       // activation slots (k-chunks of 256) held in shared memory
+    int act_all;         // 1 = slot index is the k-chunk, 0 = position in the CTA's span
     unsigned int epoch;
 };
-
-// Two E2M1 codes (one per 16-bit half of x, already isolated by the caller's mask)
-// -> bf16x2 holding e2m1 * 2^-126 : sign at bit 15, (e e m) at bits 8..6 of each half.
-// The multiply copies the nibble to [15:12] and to [9:6]; the mask keeps the sign from the first
-// copy and the magnitude from the second.
-__device__ __forceinline__ uint32_t place_pair(uint32_t isolated, uint32_t mul) {
-    return (isolated * mul) & 0x81C081C0u;
-}
-
-__device__ __forceinline__ void expand_u32(uint32_t q, uint32_t S, uint32_t (&d)[4]) {
-    const uint32_t q2 = q >> 8;
-    d[0] = ptx::mul_bf16x2(place_pair(q & 0x000F000Fu, 0x1040u), S);    // elements 0,4
-    d[1] = ptx::mul_bf16x2(place_pair(q & 0x00F000F0u, 0x0104u), S);    // elements 1,5
-    d[2] = ptx::mul_bf16x2(place_pair(q2 & 0x000F000Fu, 0x1040u), S);   // elements 2,6
-    d[3] = ptx::mul_bf16x2(place_pair(q2 & 0x00F000F0u, 0x0104u), S);   // elements 3,7
-}
 
 // 16-byte chunk c (0..31) of a 512-byte token row is stored at chunk position
 // (c & ~7) | ((c & 7) ^ ((c >> 3) | (tok & 1) << 2)): the consumers' 128-bit loads (lanes = 8 tokens
@@ -97,27 +83,34 @@ __device__ __forceinline__ int act_phys_chunk(int c, int tok) {
     return (c & ~7) | ((c & 7) ^ (((c >> 3) & 3) | ((tok & 1) << 2)));
 }
 
-// NT: 8-token column tiles (1: M <= 8, 2: M <= 16).
-// RES: activations of the CTA's whole k range stay resident in shared memory in MMA fragment
-//      order (loaded once by the consumer warps); otherwise they travel with each stage in
-//      natural order (cp.async by the producer lanes) and are permuted by the consumers.
+// Eight packed E2M1 codes (one 32-bit word, 8 consecutive k of one row) -> four f16x2 registers
+// holding e2m1 * block scale, in k order.  The hardware conversion is exact and the products
+// are exact in FP16 (2 x 4 significant bits; every value within [2^-10, 2880]).
+__device__ __forceinline__ void expand_u32(uint32_t q, uint32_t S, uint32_t (&d)[4]) {
+    uint32_t e[4];
+    ptx::cvt_e2m1x8_to_f16x2(q, e);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[i] = ptx::mul_f16x2(e[i], S);
+}
+
 // PROBE selects measurement-only variants (the library instantiates PROBE = 0 only):
 //   bit 0: consumers skip the math (ring hand-shake only)   bit 3: producer moves no data
-template <int NT, bool RES, int PROBE = 0>
+//   bit 4: no activation staging                            bit 5: no epilogue
+template <int PROBE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const DecodeParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int stages = p.stages;
-    constexpr int kStageActBytes = RES ? 0 : 2 * NT * 8 * kActRowBytes;
     unsigned char* s_packed = smem;                                       // stages x 2 x 16 KB, 1024-aligned
     unsigned char* s_scale = s_packed + stages * 2 * kPackedBytes;        // stages x 2 x 2 KB
-    unsigned char* s_act = s_scale + stages * 2 * kScaleBytes;            // RES: slots x M x 512 B, else stages x 2 x NT*4 KB
-    const int act_bytes = RES ? p.act_slots * p.M * kActRowBytes : stages * kStageActBytes;
-    float* s_out = reinterpret_cast<float*>(s_act + act_bytes);           // kGroups FP32 tiles
-    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_out + kGroups * NT * 8 * kOutLd);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_table + 256);
+    unsigned char* s_act = s_scale + stages * 2 * kScaleBytes;            // slots x M x 512 B of FP16
+    float* s_out = reinterpret_cast<float*>(s_act + p.act_slots * p.M * kActRowBytes);   // kGroups FP32 tiles
+    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_out + kGroups * kMaxTokens * kOutLd);
+    float* s_tokscale = reinterpret_cast<float*>(s_table + 256);          // [0..7] scale, [8..15] 1/scale per token
+    unsigned int* s_amax = reinterpret_cast<unsigned int*>(s_tokscale + 16);   // [0..7] largest |activation| bits per token
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_amax + 16);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
 
@@ -129,45 +122,42 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     const int cta = blockIdx.x, G = gridDim.x;
     const long long u_begin = (long long)cta * p.units / G;
     const long long u_end = (long long)(cta + 1) * p.units / G;
+    const int kc_begin = (int)(u_begin % p.kchunks);
 
-    if (tid == 0) {
-        for (int s = 0; s < stages; ++s) {
-            ptx::mbar_init(&full_bar[s], RES ? 1 : 1 + 32);   // expect_tx arrive (+ one cp.async arrive per producer lane)
-            ptx::mbar_init(&empty_bar[s], kConsumerWarps);    // every consumer warp releases every stage
+    // The producer lane sets the ring up itself and starts streaming weights at once; the
+    // consumers meet it at named barrier 2 (they need the initialised mbarriers, it needs nothing
+    // from them), so the first stages are in flight while the activations are still being staged.
+    if (warp == kConsumerWarps) {
+        if (lane == 0) {
+            for (int s = 0; s < stages; ++s) {
+                ptx::mbar_init(&full_bar[s], 1);                  // the producer's expect_tx arrive
+                ptx::mbar_init(&empty_bar[s], kConsumerWarps);    // every consumer warp releases every stage
+            }
+            *s_abort = 0;
+            ptx::fence_mbar_init();
         }
-        *s_abort = 0;
-        ptx::fence_mbar_init();
+        __syncwarp();
+        ptx::named_barrier_arrive(2, kThreads);
     }
-    // Block-scale table: code byte -> bf16x2 (both halves) of ue4m3(code) * 2^94.  With the 2^-126
-    // of the placed E2M1 value the product is lut * scale * 2^-32, always a normal BF16.
-    if (tid < 256) {
-        const float s = ue4m3_to_float((uint32_t)tid) * 1.9807040628566084e28f;   // 2^94
-        const uint32_t b = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(s));
-        s_table[tid] = b | (b << 16);
-    }
-    __syncthreads();
-
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp
         if (lane == 0) {
             ptx::prefetch_tensormap(&tm_packed);
             ptx::prefetch_tensormap(&tm_scale);
-        }
-        const uint64_t pol_stream = ptx::policy_evict_first();
-        int it = 0;
-        long long hu = u_begin;
-        while (hu < u_end) {
-            const int tile = (int)(hu / p.kchunks);
-            const long long tile_end = (long long)(tile + 1) * p.kchunks;
-            const long long seg_end = tile_end < u_end ? tile_end : u_end;
-            const int row0 = tile * kRT;
-            while (hu < seg_end) {
-                const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
-                const int stage = it % stages;
-                const uint32_t ph = (uint32_t)((it / stages) & 1);
-                ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0x100u + (unsigned)stage);
-                const int k0 = (int)(hu % p.kchunks) * kKC;
-                if (lane == 0) {
+            const uint64_t pol_stream = ptx::policy_evict_first();
+            int stage = 0;
+            uint32_t ph = 0;
+            long long hu = u_begin;
+            int tile = (int)(u_begin / p.kchunks);
+            int kc = kc_begin;                                // k-chunk of hu inside its row tile
+            while (hu < u_end) {
+                const long long tile_end = hu - kc + p.kchunks;
+                const long long seg_end = tile_end < u_end ? tile_end : u_end;
+                const int row0 = tile * kRT;
+                while (hu < seg_end) {
+                    const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
+                    ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0x100u + (unsigned)stage);
+                    const int k0 = kc * kKC;
                     if (PROBE & 8) {
                         ptx::mbar_arrive(&full_bar[stage]);
                     } else {
@@ -179,21 +169,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                                              (k0 + h * kKC) >> 4, row0, pol_stream);
                         }
                     }
+                    hu += cnt;
+                    kc += cnt;
+                    if (++stage == stages) { stage = 0; ph ^= 1u; }
                 }
-                if (!RES) {
-                    unsigned char* act = s_act + stage * kStageActBytes;
-                    for (int i = lane; i < cnt * p.M * 32; i += 32) {
-                        const int h = i / (p.M * 32), r = i % (p.M * 32);
-                        const int tok = r >> 5, c = r & 31;
-                        const int k = k0 + h * kKC + c * 8;
-                        const bool in = k < p.K;
-                        ptx::cp_async_16(act + (h * NT * 8 + tok) * kActRowBytes + act_phys_chunk(c, tok) * 16,
-                                         p.A + (size_t)tok * p.K + (in ? k : 0), in ? 16u : 0u);
-                    }
-                    ptx::cp_async_mbar_arrive_noinc(&full_bar[stage]);
-                }
-                hu += cnt;
-                ++it;
+                if (kc >= p.kchunks) { kc = 0; ++tile; }
             }
         }
         return;
@@ -207,68 +187,122 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     const int off_w0 = r0 * 128 + (((2 * t) ^ g) << 4);       // row r0, logical 16-byte chunk 2t   (swizzle: chunk ^ (row & 7))
     const int off_w1 = r0 * 128 + (((2 * t + 1) ^ g) << 4);   // row r0, chunk 2t+1
     const int off_s = r0 * 16 + 4 * t;                         // 4 scale bytes: blocks 4t..4t+3 of the row
-    const int tok0 = RES ? (g < p.M ? g : 0) : g;              // token feeding MMA column g (columns >= M are never stored)
-    const int tok1 = RES ? (g + 8 < p.M ? g + 8 : 0) : g + 8;
-    const int act_sw0 = t | ((tok0 & 1) << 2), act_sw1 = t | ((tok1 & 1) << 2);
-    float* my_out = s_out + grp * (NT * 8 * kOutLd);
+    const int tok = g < p.M ? g : 0;                           // token feeding MMA column g (columns >= M are never stored)
+    const int act_sw = t | ((tok & 1) << 2);
 
-    if (RES) {
-        // Resident activations: every 16-byte chunk (8 consecutive k of one token) is stored as
-        // (x0,x4)(x1,x5)(x2,x6)(x3,x7), the B fragments of the two MMAs that consume it.
+    // Block-scale table: code byte -> f16x2 (both halves) of ue4m3(code); exact (4 significant bits).
+    if (tid < 256) {
+        const uint32_t b = (uint32_t)__half_as_ushort(__float2half_rn(ue4m3_to_float((uint32_t)tid)));
+        s_table[tid] = b | (b << 16);
+    }
+    if (tid < 16) s_amax[tid] = 0u;
+    ptx::named_barrier_sync(2, kThreads);            // mbarriers initialised (the producer only arrives)
+    ptx::named_barrier_sync(1, kConsumerThreads);
+
+    // Resident activations.  Chunk id = (slot * M + token) * 32 + c names 8 consecutive k of one
+    // token; every thread takes ids tid, tid + 512, ... four at a time so that the loads overlap.
+    // Pass A finds, per token, the largest magnitude over the k range this CTA works on; the
+    // per-token power-of-two scale maps it to [2^14, 2^15), so the FP16 copy loses nothing that
+    // matters (an element keeps all 8 significant bits unless it is below 2^-28 of the largest)
+    // and never overflows.  Pass B converts and stores in natural k order.  The scale is undone in
+    // FP32 in the epilogue.
+    if (!(PROBE & 16)) {
         const int per_slot = p.M * 32;
-        for (int i = tid; i < p.act_slots * per_slot; i += kConsumerThreads) {
-            const int j = i / per_slot, r = i % per_slot;
-            const int tok = r >> 5, c = r & 31;
-            const int kc = p.act_all ? j : (int)((u_begin + j) % p.kchunks);
+        const int total = p.act_slots * per_slot;
+        const int kc0 = p.act_all ? 0 : kc_begin;
+        auto chunk_src = [&](int id, int& j, int& tk, int& c) -> const uint4* {
+            j = id / per_slot;
+            const int r = id - j * per_slot;
+            tk = r >> 5;
+            c = r & 31;
+            int kc = kc0 + j;
+            if (kc >= p.kchunks) kc -= p.kchunks;
             const int k = kc * kKC + c * 8;
-            uint4 x = make_uint4(0u, 0u, 0u, 0u);
-            if (k < p.K) x = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)tok * p.K + k));
-            uint4 y;
-            y.x = ptx::prmt(x.x, x.z, 0x5410u);   // (x0,x4)
-            y.y = ptx::prmt(x.x, x.z, 0x7632u);   // (x1,x5)
-            y.z = ptx::prmt(x.y, x.w, 0x5410u);   // (x2,x6)
-            y.w = ptx::prmt(x.y, x.w, 0x7632u);   // (x3,x7)
-            *reinterpret_cast<uint4*>(s_act + (size_t)(j * p.M + tok) * kActRowBytes + act_phys_chunk(c, tok) * 16) = y;
+            return k < p.K ? reinterpret_cast<const uint4*>(p.A + (size_t)tk * p.K + k) : nullptr;
+        };
+        // Pass A: one trip to global memory, eight chunks in flight per thread; the raw BF16 chunk
+        // goes to its final (swizzled) place, the magnitudes feed the per-token maximum.
+        for (int base = tid; base < total; base += 8 * kConsumerThreads) {
+            uint4 x[8];
+            int tk[8], dst[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                x[u] = make_uint4(0u, 0u, 0u, 0u);
+                tk[u] = 0;
+                dst[u] = -1;
+                const int id = base + u * kConsumerThreads;
+                if (id < total) {
+                    int j, c;
+                    const uint4* src = chunk_src(id, j, tk[u], c);
+                    if (src) x[u] = __ldg(src);
+                    dst[u] = (j * p.M + tk[u]) * kActRowBytes + act_phys_chunk(c, tk[u]) * 16;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (dst[u] < 0) continue;   // uniform across the warp: total is a multiple of 32
+                const uint32_t v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+                uint32_t m = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) m = max(m, max(v[i] & 0x7FFFu, (v[i] >> 16) & 0x7FFFu));
+                // the 32 lanes of a warp hold the 32 chunks of one (slot, token) row
+                m = __reduce_max_sync(0xffffffffu, m);
+                if (lane == 0 && m) atomicMax(&s_amax[tk[u]], m);
+                *reinterpret_cast<uint4*>(s_act + dst[u]) = x[u];
+            }
+        }
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        if (tid < p.M) {
+            const int e8 = (int)(s_amax[tid] >> 7);           // biased BF16 exponent of the largest element
+            int se = 268 - e8;                                // scale = 2^(141 - e8): largest -> exponent 14
+            se = se < 1 ? 1 : (se > 254 ? 254 : se);
+            s_tokscale[tid] = __uint_as_float((uint32_t)se << 23);
+            s_tokscale[8 + tid] = __uint_as_float((uint32_t)(254 - se) << 23);
+        }
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        // Pass B: BF16 -> scaled FP16 in place (token rows are 512 bytes, so the token of a chunk
+        // is its row index modulo M).
+        const int nchunks = total;                            // 16-byte chunks in the resident area
+        for (int i = tid; i < nchunks; i += kConsumerThreads) {
+            const int row = i >> 5;
+            const float sc = s_tokscale[row % p.M];
+            uint4* ptr = reinterpret_cast<uint4*>(s_act + (size_t)i * 16);
+            const uint4 x = *ptr;
+            const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+            uint32_t y[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                y[q] = ptx::pack_f16x2(__uint_as_float(v[q] << 16) * sc, __uint_as_float(v[q] & 0xFFFF0000u) * sc);
+            *ptr = make_uint4(y[0], y[1], y[2], y[3]);
         }
         ptx::named_barrier_sync(1, kConsumerThreads);
     }
 
-    int it = 0;
+    int stage = 0;
+    uint32_t ph = 0;
     long long hu = u_begin;
+    int tile = (int)(u_begin / p.kchunks);
+    int kc = kc_begin;                                         // k-chunk of hu inside its row tile
+    int seg_parity = 0;
     while (hu < u_end) {
-        const int tile = (int)(hu / p.kchunks);
-        const int kc_first = (int)(hu % p.kchunks);
-        const long long tile_end = (long long)(tile + 1) * p.kchunks;
+        const int kc_first = kc;
+        const long long tile_end = hu - kc + p.kchunks;
         const long long seg_end = tile_end < u_end ? tile_end : u_end;
 
-        float acc[NT][4];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.0f;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-        for (; hu < seg_end; ++it) {
+        while (hu < seg_end) {
             const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
-            const long long my_hu = hu + grp;
+            const int slot = p.act_all ? kc + grp : (int)(hu - u_begin) + grp;
             hu += cnt;
-            const int stage = it % stages;
-            const uint32_t ph = (uint32_t)((it / stages) & 1);
+            kc += cnt;
             // Every warp waits on every stage in order (an mbarrier waiter may not skip a phase);
             // group 1 has nothing to do in a stage that carries a single half-unit.
             ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0x200u + (unsigned)stage);
             if (!(PROBE & 1) && grp < cnt) {
                 const unsigned char* wp = s_packed + (stage * 2 + grp) * kPackedBytes;
                 const unsigned char* sp = s_scale + (stage * 2 + grp) * kScaleBytes + off_s;
-                const unsigned char* ap0;
-                const unsigned char* ap1;
-                if (RES) {
-                    const int slot = p.act_all ? (int)(my_hu % p.kchunks) : (int)(my_hu - u_begin);
-                    ap0 = s_act + (size_t)(slot * p.M + tok0) * kActRowBytes + t * 128;
-                    ap1 = s_act + (size_t)(slot * p.M + tok1) * kActRowBytes + t * 128;
-                } else {
-                    ap0 = s_act + stage * kStageActBytes + (grp * NT * 8 + tok0) * kActRowBytes + t * 128;
-                    ap1 = s_act + stage * kStageActBytes + (grp * NT * 8 + tok1) * kActRowBytes + t * 128;
-                }
+                const unsigned char* ap = s_act + (size_t)(slot * p.M + tok) * kActRowBytes + t * 128;
                 const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
                 const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
                 const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + off_w0 + 8 * 128);
@@ -285,80 +319,83 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     uint32_t da[4], db[4];
                     expand_u32(qa[uu], Sa, da);
                     expand_u32(qb[uu], Sb, db);
-                    const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // elements (0,4 | 1,5) of this 8-group
-                    const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // elements (2,6 | 3,7)
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const uint4 x = *reinterpret_cast<const uint4*>((nt ? ap1 : ap0) + ((uu ^ (nt ? act_sw1 : act_sw0)) << 4));
-                        if (RES) {
-                            ptx::mma_bf16_16x8x16(acc[nt], a_lo, x.x, x.y);
-                            ptx::mma_bf16_16x8x16(acc[nt], a_hi, x.z, x.w);
-                        } else {
-                            // natural order (x0,x1)(x2,x3)(x4,x5)(x6,x7) -> (x0,x4)(x1,x5) | (x2,x6)(x3,x7)
-                            ptx::mma_bf16_16x8x16(acc[nt], a_lo, ptx::prmt(x.x, x.z, 0x5410u), ptx::prmt(x.x, x.z, 0x7632u));
-                            ptx::mma_bf16_16x8x16(acc[nt], a_hi, ptx::prmt(x.y, x.w, 0x5410u), ptx::prmt(x.y, x.w, 0x7632u));
-                        }
-                    }
+                    const uint4 x = *reinterpret_cast<const uint4*>(ap + ((uu ^ act_sw) << 4));
+                    const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // k 0..3 of this 8-group: rows g, g+8
+                    const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // k 4..7
+                    ptx::mma_f16_16x8x16(acc, a_lo, x.x, x.y);
+                    ptx::mma_f16_16x8x16(acc, a_hi, x.z, x.w);
                 }
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty_bar[stage]);
+            if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
 
         // ------------------------------------------------------------ segment epilogue
+        // Rows belong to warp pairs (warp gw of either group), so every pair finishes its 16 rows
+        // on its own: group 1 hands its sums over through shared memory (two buffers alternating
+        // per segment, one 64-thread barrier per segment), group 0 finishes from registers --
+        // thread (g,t) holds rows r0, r0+8 x tokens 2t, 2t+1.  The other warps keep streaming.
         const bool owner = (kc_first == 0);
         const bool complete = owner && (seg_end == tile_end);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            my_out[(nt * 8 + 2 * t) * kOutLd + r0] = acc[nt][0];
-            my_out[(nt * 8 + 2 * t + 1) * kOutLd + r0] = acc[nt][1];
-            my_out[(nt * 8 + 2 * t) * kOutLd + r0 + 8] = acc[nt][2];
-            my_out[(nt * 8 + 2 * t + 1) * kOutLd + r0 + 8] = acc[nt][3];
+        float* xchg = s_out + (seg_parity ? kMaxTokens * kOutLd : 0);
+        seg_parity ^= 1;
+        if (PROBE & 32) { if (kc >= p.kchunks) { kc = 0; ++tile; } continue; }
+        if (grp == 1) {
+            xchg[(2 * t) * kOutLd + r0] = acc[0];
+            xchg[(2 * t + 1) * kOutLd + r0] = acc[1];
+            xchg[(2 * t) * kOutLd + r0 + 8] = acc[2];
+            xchg[(2 * t + 1) * kOutLd + r0 + 8] = acc[3];
         }
-        ptx::named_barrier_sync(1, kConsumerThreads);
-        const float* out_b = s_out + NT * 8 * kOutLd;
-        const int row_base = tile * kRT;
-        if (!owner) {
-            float* slot = partials + (size_t)cta * (NT * 8 * kRT);
-            for (int i = tid; i < p.M * kRT; i += kConsumerThreads) {
-                const int m = i / kRT, r = i % kRT;
-                __stcg(slot + m * kRT + r, s_out[m * kOutLd + r] + out_b[m * kOutLd + r]);
-            }
-            __threadfence();
-            ptx::named_barrier_sync(1, kConsumerThreads);
-            if (tid == 0) ptx::st_release_gpu(&flags[cta], p.epoch);
-        } else {
-            int last = cta;   // contributors are CTAs cta+1 .. last
-            if (!complete) {
-                while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
-                if (tid == 0) {
-                    const long long t0 = clock64();
-                    for (int c = cta + 1; c <= last; ++c) {
-                        while (ptx::ld_acquire_gpu(&flags[c]) != p.epoch) {
-                            if (*s_abort) break;
-                            if (clock64() - t0 > ptx::kWaitBudgetClocks) {
-                                *s_abort = 1;
-                                atomicCAS(status, 0u, 0x300u);
-                                break;
+        ptx::named_barrier_sync(4 + gw, 64);
+        if (grp == 0) {
+            const int m0 = 2 * t, m1 = 2 * t + 1;
+            const float us0 = s_tokscale[8 + m0], us1 = s_tokscale[8 + m1];
+            float v[4] = {(acc[0] + xchg[m0 * kOutLd + r0]) * us0, (acc[1] + xchg[m1 * kOutLd + r0]) * us1,
+                          (acc[2] + xchg[m0 * kOutLd + r0 + 8]) * us0, (acc[3] + xchg[m1 * kOutLd + r0 + 8]) * us1};
+            const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
+            const int mm[4] = {m0, m1, m0, m1};
+            if (!owner) {
+                float* slot = partials + (size_t)cta * (kMaxTokens * kRT);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (mm[i] < p.M) __stcg(slot + mm[i] * kRT + rr[i], v[i]);
+                __syncwarp();
+                if (lane == 0) ptx::st_release_gpu(&flags[cta * kGroupWarps + gw], p.epoch);
+            } else {
+                int last = cta;   // contributors are CTAs cta+1 .. last
+                if (!complete) {
+                    while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
+                    if (lane == 0) {
+                        const long long t0 = clock64();
+                        for (int c = cta + 1; c <= last; ++c) {
+                            while (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) != p.epoch) {
+                                if (*s_abort) break;
+                                if (clock64() - t0 > ptx::kWaitBudgetClocks) {
+                                    *s_abort = 1;
+                                    atomicCAS(status, 0u, 0x300u);
+                                    break;
+                                }
                             }
                         }
                     }
+                    __syncwarp();
                 }
-                ptx::named_barrier_sync(1, kConsumerThreads);
-            }
-            for (int i = tid; i < p.M * kRT; i += kConsumerThreads) {
-                const int m = i / kRT, r = i % kRT;
-                const int n = row_base + r;
-                if (n >= p.N) continue;
-                float v = s_out[m * kOutLd + r] + out_b[m * kOutLd + r];
-                for (int c = cta + 1; c <= last; ++c) v += __ldcg(partials + (size_t)c * (NT * 8 * kRT) + m * kRT + r);
-                v *= p.final_scale;
-                const size_t o = (size_t)m * p.N + n;
-                if (p.residual) v += __bfloat162float(p.residual[o]);
-                p.C[o] = __float2bfloat16_rn(v);
+                const int row_base = tile * kRT;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int n = row_base + rr[i];
+                    if (mm[i] >= p.M || n >= p.N) continue;
+                    float x = v[i];
+                    for (int c = cta + 1; c <= last; ++c) x += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
+                    x *= p.inv_gs;
+                    const size_t o = (size_t)mm[i] * p.N + n;
+                    if (p.residual) x += __bfloat162float(p.residual[o]);
+                    p.C[o] = __float2bfloat16_rn(x);
+                }
             }
         }
-        ptx::named_barrier_sync(1, kConsumerThreads);   // the FP32 tiles are reused by the next segment
+        if (kc >= p.kchunks) { kc = 0; ++tile; }
     }
 }
 
@@ -402,64 +439,63 @@ bool decode_mma_supported(const LinearArgs& a) {
     return true;
 }
 
-size_t decode_mma_scratch_bytes(const LinearArgs& a, const nvfp4_device_info& dev) {
-    const int nt = a.M <= 8 ? 1 : 2;
-    return kPartialOffset + (size_t)dev.sm_count * nt * 8 * kRT * 4;
+size_t decode_mma_scratch_bytes(const LinearArgs&, const nvfp4_device_info& dev) {
+    return kPartialOffset + (size_t)dev.sm_count * kMaxTokens * kRT * 4;
 }
 
 cudaError_t configure_decode_mma() {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mma_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
-    return e;
+    return cudaFuncSetAttribute(decode_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
 }
 
 namespace {
 
-// Shared-memory plan of one launch: resident activations when they fit beside a ring of at
-// least three stages, otherwise activations travel with the stages.
+// Shared-memory plan of one launch of m <= 8 tokens: the ring gets what the resident
+// activations leave, and needs at least three stages.
 struct DecodePlan {
     DecodeParams p;
-    int grid, nt, smem;
-    bool resident;
+    int grid, smem;
 };
 
-bool plan_decode(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch, DecodePlan* out) {
+bool plan_decode(const LinearArgs& a, int m, const nvfp4_device_info& dev, void* scratch, DecodePlan* out) {
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16*>(a.A);
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.C = static_cast<__nv_bfloat16*>(a.C);
     p.scratch = static_cast<unsigned char*>(scratch);
-    p.final_scale = a.inv_gs * 4294967296.0f;
-    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.inv_gs = a.inv_gs;
+    p.M = m; p.N = a.N; p.K = a.K;
     p.kchunks = a.K / kKC;
     const long long tiles = (a.N + kRT - 1) / kRT;
     p.units = (int)(tiles * p.kchunks);
     int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
     if (grid > p.units) grid = p.units;
-    const int nt = a.M <= 8 ? 1 : 2;
-    const int fixed = 1024 + kGroups * nt * 8 * kOutLd * 4 + 1024 + 2 * kMaxStages * 8 + 64;
+    const int fixed = 1024 + kGroups * kMaxTokens * kOutLd * 4 + 1024 + 128 + 2 * kMaxStages * 8 + 64;
     const int stage_w = 2 * (kPackedBytes + kScaleBytes);
     const int max_span = (p.units + grid - 1) / grid;
     p.act_all = p.kchunks <= max_span ? 1 : 0;
     p.act_slots = p.act_all ? p.kchunks : max_span;
-    const int act_res = p.act_slots * a.M * kActRowBytes;
-    int stages = (kSmemBudget - fixed - act_res) / stage_w;
-    const bool resident = stages >= 3;
-    if (!resident) stages = (kSmemBudget - fixed) / (stage_w + 2 * nt * 8 * kActRowBytes);
+    const long long act_res = (long long)p.act_slots * m * kActRowBytes;
+    long long stages = (kSmemBudget - fixed - act_res) / stage_w;
+    if (stages < 3) return false;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 2) return false;
-    p.stages = stages;
+    p.stages = (int)stages;
     out->p = p;
     out->grid = grid;
-    out->nt = nt;
-    out->resident = resident;
-    out->smem = fixed + stages * stage_w + (resident ? act_res : stages * 2 * nt * 8 * kActRowBytes);
+    out->smem = fixed + (int)stages * stage_w + (int)act_res;
     return true;
 }
 
+// Largest token count per launch (<= 8) whose activations fit beside the ring; 0 if none.
+int decode_tokens_per_launch(const LinearArgs& a, const nvfp4_device_info& dev) {
+    DecodePlan pl;
+    for (int m = a.M < kMaxTokens ? a.M : kMaxTokens; m >= 1; --m)
+        if (plan_decode(a, m, dev, nullptr, &pl)) return m;
+    return 0;
+}
+
 }  // namespace
+
+bool decode_mma_fits(const LinearArgs& a, const nvfp4_device_info& dev) { return decode_tokens_per_launch(a, dev) > 0; }
 
 cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
                               cudaStream_t s) {
@@ -469,18 +505,26 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         !make_u8_map(&tms, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, (uint64_t)a.K / 16, 16, kRT,
                      CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
-    DecodePlan pl;
-    if (!plan_decode(a, dev, scratch, &pl)) return cudaErrorInvalidValue;
-    pl.p.epoch = ++dev.decode_epoch;
-    if (pl.nt == 1) {
-        if (pl.resident) decode_mma_kernel<1, true><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
-        else decode_mma_kernel<1, false><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
-    } else {
-        if (pl.resident) decode_mma_kernel<2, true><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
-        else decode_mma_kernel<2, false><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+    const int per = decode_tokens_per_launch(a, dev);
+    if (per <= 0) return cudaErrorInvalidValue;
+    int n = 0;
+    // More than `per` tokens: one launch per group of tokens (each streams the weights again).
+    for (int m0 = 0; m0 < a.M; m0 += per) {
+        LinearArgs b = a;
+        const int m = a.M - m0 < per ? a.M - m0 : per;
+        b.A = static_cast<const char*>(a.A) + (size_t)m0 * a.K * 2;
+        b.C = static_cast<char*>(a.C) + (size_t)m0 * a.N * 2;
+        if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
+        DecodePlan pl;
+        if (!plan_decode(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
+        pl.p.epoch = ++dev.decode_epoch;
+        decode_mma_kernel<0><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+        ++n;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { if (launches) *launches = n; return e; }
     }
-    if (launches) *launches = 1;
-    return cudaGetLastError();
+    if (launches) *launches = n;
+    return cudaSuccess;
 }
 
 }  // namespace nvfp4

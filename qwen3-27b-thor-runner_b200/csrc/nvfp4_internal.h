@@ -43,6 +43,7 @@ cudaError_t launch_gemm_bf16_simple(const void* A, const void* Wdq, const void* 
 
 // --- decode_mma.cu: TMA-fed shared-memory ring + register dequant + warp MMA GEMV (M <= 16).
 bool decode_mma_supported(const LinearArgs& a);
+bool decode_mma_fits(const LinearArgs& a, const nvfp4_device_info& dev);   // activations fit in shared memory
 size_t decode_mma_scratch_bytes(const LinearArgs& a, const nvfp4_device_info& dev);
 cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
                               cudaStream_t s);
