@@ -87,8 +87,9 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (impl == 0) impl = prefill_umma_supported(a) ? 2 : 1;
     if (impl == 2) {
         if (!prefill_umma_supported(a)) return NVFP4_E_SHAPE;
+        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > h->workspace_bytes) return NVFP4_E_WORKSPACE;
         int nl = 0;
-        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, h->workspace_bytes, &nl, s);
+        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }

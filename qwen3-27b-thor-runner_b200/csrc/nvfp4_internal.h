@@ -52,8 +52,9 @@ cudaError_t configure_decode_mma();
 // --- prefill_umma.cu: fused dequant + tcgen05 BF16 GEMM with TMEM accumulators.
 bool prefill_umma_supported(const LinearArgs& a);
 size_t prefill_umma_scratch_bytes(int max_M, int max_N, int max_K);
+// scratch[0] is the handle's status word; the FP16 activation copy lives at scratch + offset.
 cudaError_t launch_prefill_umma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch,
-                                size_t scratch_bytes, int* launches, cudaStream_t s);
+                                size_t scratch_bytes, size_t offset, int* launches, cudaStream_t s);
 
 // Sets the per-kernel attributes (dynamic shared memory opt-in) once per device.
 cudaError_t configure_kernels(const nvfp4_device_info& dev);

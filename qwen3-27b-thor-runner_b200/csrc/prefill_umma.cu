@@ -1,10 +1,432 @@
-// placeholder until the kernel lands
+// Prefill GEMM for M > 16: fused NVFP4 dequantisation + tcgen05 tensor-core GEMM.
+//
+//   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
+//
+// One persistent CTA per SM works on 128-token x 256-weight-row output tiles:
+//   warp 0      TMA producer: activation tiles (128 tokens x 64 k, FP16, 128-byte swizzle) into a
+//               4-stage ring, raw weight stages (256 rows x 256 k of packed codes + scales, 36 KB)
+//               into a 2-stage ring.  Plain tiled TMA, never cluster multicast.
+//   warps 8-15  dequantise: thread = one weight row; per 64-k block two 128-bit loads of codes,
+//               cvt.rn.f16x2.e2m1x2 + one f16x2 multiply by the block scale (exact products), eight
+//               128-bit stores into the K-major, 128-byte-swizzled B operand tile (2 buffers).
+//   warp 1      one elected thread issues tcgen05.mma (kind::f16, M=128, N=256, K=16) from the two
+//               shared-memory operands into a TMEM accumulator (2 x 256 columns, double buffered)
+//               and commits completion to the mbarriers that recycle the operand buffers.
+//   warps 4-7   epilogue: tcgen05.ld the FP32 accumulator (lane = token), undo the per-token
+//               activation scale and apply 1/global_scale in FP32, add the residual, round once to
+//               BF16, 64 contiguous bytes per thread per step.
+//
+// Operands are FP16 because the hardware E2M1 conversion produces FP16 and every e2m1 x ue4m3
+// product is exact in FP16.  A small pre-pass turns the BF16 activations into FP16 with an exact
+// per-token power-of-two scale (largest magnitude -> [2^14, 2^15)) in the handle workspace, so
+// BF16's wider exponent range costs nothing; accumulation is FP32 in TMEM.  The arithmetic is
+// the reference's GEMM (src/engine/dense_gemm_fp4_sm110.cu:558-583) with exact instead of
+// BF16-rounded weights (identical when global_scale = 1) and no materialised [N,K] matrix.
+//
+// Every mbarrier wait is bounded; a wait that runs out records its code in the handle's status
+// word and the kernel winds down (TMEM is always freed).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
+#include "ptx.cuh"
+
 namespace nvfp4 {
-bool prefill_umma_supported(const LinearArgs&) { return false; }
-size_t prefill_umma_scratch_bytes(int, int, int) { return 0; }
-cudaError_t launch_prefill_umma(const LinearArgs&, const nvfp4_device_info&, void*, size_t, int*, cudaStream_t) {
-    return cudaErrorNotSupported;
+namespace {
+
+constexpr int BM = 128;            // tokens per tile   (UMMA M)
+constexpr int BN = 256;            // weight rows per tile (UMMA N)
+constexpr int BK = 64;             // k per MMA operand block (128 bytes of FP16: one swizzle row)
+constexpr int WK = 256;            // k per raw weight stage (4 operand blocks)
+constexpr int kAStages = 4, kWStages = 2, kBBufs = 2, kAccs = 2;
+constexpr int kABytes = BM * BK * 2;          // 16 KB
+constexpr int kBBytes = BN * BK * 2;          // 32 KB
+constexpr int kWPackedBytes = BN * WK / 2;    // 32 KB
+constexpr int kWScaleBytes = BN * WK / 16;    // 4 KB
+constexpr int kThreads = 512;
+constexpr int kDequantWarps = 8, kEpiWarps = 4;
+constexpr int kSmemBytes = 1024 + kAStages * kABytes + kWStages * (kWPackedBytes + kWScaleBytes) +
+                           kBBufs * kBBytes + 1024 /*table*/ + 256 /*barriers, tmem slot, abort*/;
+
+struct PrefillParams {
+    const __nv_bfloat16* residual;
+    __nv_bfloat16* C;
+    const float* unscale;      // per token: 1 / activation scale
+    unsigned int* status;
+    float inv_gs;
+    int M, N, K;
+    int m_tiles, n_tiles;
+};
+
+// ---------------------------------------------------------------- tcgen05 helpers
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    // K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                              // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+    return d;
 }
-cudaError_t configure_kernels(const nvfp4_device_info&) { return configure_decode_mma(); }
+// kind::f16, A = B = FP16, D = FP32, both operands K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(ptx::smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_packed,
+                    const __grid_constant__ CUtensorMap tm_scale, const PrefillParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* s_a = smem;                                        // kAStages x 16 KB
+    unsigned char* s_b = s_a + kAStages * kABytes;                    // kBBufs x 32 KB
+    unsigned char* s_wp = s_b + kBBufs * kBBytes;                     // kWStages x 32 KB packed codes
+    unsigned char* s_ws = s_wp + kWStages * kWPackedBytes;            // kWStages x 4 KB scales
+    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_ws + kWStages * kWScaleBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_table + 256);
+    uint64_t* afull = bars;                  // [kAStages]
+    uint64_t* aempty = afull + kAStages;     // [kAStages]
+    uint64_t* wfull = aempty + kAStages;     // [kWStages]
+    uint64_t* wempty = wfull + kWStages;     // [kWStages]
+    uint64_t* bfull = wempty + kWStages;     // [kBBufs]
+    uint64_t* bempty = bfull + kBBufs;       // [kBBufs]
+    uint64_t* tfull = bempty + kBBufs;       // [kAccs]
+    uint64_t* tempty = tfull + kAccs;        // [kAccs]
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + kAccs);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int kstages = p.K / WK;
+
+    if (tid == 0) {
+        for (int i = 0; i < kAStages; ++i) { ptx::mbar_init(&afull[i], 1); ptx::mbar_init(&aempty[i], 1); }
+        for (int i = 0; i < kWStages; ++i) { ptx::mbar_init(&wfull[i], 1); ptx::mbar_init(&wempty[i], kDequantWarps); }
+        for (int i = 0; i < kBBufs; ++i) { ptx::mbar_init(&bfull[i], kDequantWarps); ptx::mbar_init(&bempty[i], 1); }
+        for (int i = 0; i < kAccs; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kEpiWarps); }
+        *s_abort = 0;
+        ptx::fence_mbar_init();
+    }
+    if (tid < 256) {
+        const uint32_t b = (uint32_t)__half_as_ushort(__float2half_rn(ue4m3_to_float((uint32_t)tid)));
+        s_table[tid] = b | (b << 16);
+    }
+    if (warp == 1) {   // one warp owns the TMEM allocation: 512 columns = two 128 x 256 FP32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(ptx::smem_u32(s_tmem)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tm_act);
+            ptx::prefetch_tensormap(&tm_packed);
+            ptx::prefetch_tensormap(&tm_scale);
+            const uint64_t pol_w = ptx::policy_evict_first(), pol_a = ptx::policy_evict_last();
+            int sa = 0, sw = 0;
+            uint32_t pa = 0, pw = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+                for (int ks = 0; ks < kstages; ++ks) {
+                    ptx::mbar_wait(&wempty[sw], pw ^ 1u, s_abort, p.status, 0x410u + sw);
+                    ptx::mbar_arrive_expect_tx(&wfull[sw], kWPackedBytes + kWScaleBytes);
+                    ptx::tma_load_2d(s_wp + sw * kWPackedBytes, &tm_packed, &wfull[sw], ks * (WK / 2), nt * BN, pol_w);
+                    ptx::tma_load_2d(s_ws + sw * kWScaleBytes, &tm_scale, &wfull[sw], ks * (WK / 16), nt * BN, pol_w);
+                    if (++sw == kWStages) { sw = 0; pw ^= 1u; }
+                    for (int j = 0; j < WK / BK; ++j) {
+                        ptx::mbar_wait(&aempty[sa], pa ^ 1u, s_abort, p.status, 0x400u + sa);
+                        ptx::mbar_arrive_expect_tx(&afull[sa], kABytes);
+                        ptx::tma_load_2d(s_a + sa * kABytes, &tm_act, &afull[sa], ks * WK + j * BK, mt * BM, pol_a);
+                        if (++sa == kAStages) { sa = 0; pa ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int sa = 0, sb = 0, acc = 0;
+            uint32_t pa = 0, pb = 0, pt = 0;
+            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+                ptx::mbar_wait(&tempty[acc], pt ^ 1u, s_abort, p.status, 0x440u + acc);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+                for (int kb = 0; kb < kstages * (WK / BK); ++kb) {
+                    ptx::mbar_wait(&afull[sa], pa, s_abort, p.status, 0x420u + sa);
+                    ptx::mbar_wait(&bfull[sb], pb, s_abort, p.status, 0x430u + sb);
+                    tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(s_a + sa * kABytes);
+                    const uint32_t b_addr = ptx::smem_u32(s_b + sb * kBBytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&aempty[sa]);      // operand buffers are free once these MMAs have read them
+                    umma_commit(&bempty[sb]);
+                    if (++sa == kAStages) { sa = 0; pa ^= 1u; }
+                    if (++sb == kBBufs) { sb = 0; pb ^= 1u; }
+                }
+                umma_commit(&tfull[acc]);          // accumulator complete
+                if (++acc == kAccs) { acc = 0; pt ^= 1u; }
+            }
+        }
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------------ dequantise: thread = weight row
+        const int row = tid - 8 * 32;                     // 0..255
+        const int sw7 = row & 7;
+        int sw = 0, sb = 0;
+        uint32_t pw = 0, pb = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            for (int ks = 0; ks < kstages; ++ks) {
+                ptx::mbar_wait(&wfull[sw], pw, s_abort, p.status, 0x450u + sw);
+                const unsigned char* wp = s_wp + sw * kWPackedBytes + row * 128;
+                const uint4 sc16 = *reinterpret_cast<const uint4*>(s_ws + sw * kWScaleBytes + row * 16);
+                const uint32_t scw[4] = {sc16.x, sc16.y, sc16.z, sc16.w};
+#pragma unroll
+                for (int j = 0; j < WK / BK; ++j) {
+                    // packed bytes [32j, 32j+32) of the row = logical 16-byte chunks 2j, 2j+1
+                    const uint4 q0 = *reinterpret_cast<const uint4*>(wp + (((2 * j) ^ sw7) << 4));
+                    const uint4 q1 = *reinterpret_cast<const uint4*>(wp + (((2 * j + 1) ^ sw7) << 4));
+                    const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                    ptx::mbar_wait(&bempty[sb], pb ^ 1u, s_abort, p.status, 0x460u + sb);
+                    unsigned char* bp = s_b + sb * kBBytes + row * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {          // chunk c = 8 consecutive k = one 32-bit word of codes
+                        const uint32_t S = s_table[(scw[j] >> (8 * (c >> 1))) & 0xFFu];
+                        uint32_t e[4];
+                        ptx::cvt_e2m1x8_to_f16x2(q[c], e);
+                        *reinterpret_cast<uint4*>(bp + ((c ^ sw7) << 4)) =
+                            make_uint4(ptx::mul_f16x2(e[0], S), ptx::mul_f16x2(e[1], S), ptx::mul_f16x2(e[2], S),
+                                       ptx::mul_f16x2(e[3], S));
+                    }
+                    ptx::fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&bfull[sb]);
+                    if (++sb == kBBufs) { sb = 0; pb ^= 1u; }
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&wempty[sw]);
+                if (++sw == kWStages) { sw = 0; pw ^= 1u; }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue: thread = token row
+        const int ew = warp - 4;                          // TMEM lanes 32*ew .. 32*ew+31
+        int acc = 0;
+        uint32_t pt = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+            const int m = mt * BM + ew * 32 + lane;
+            ptx::mbar_wait(&tfull[acc], pt, s_abort, p.status, 0x470u + acc);
+            tc_fence_after();
+            const float mul = (m < p.M ? p.unscale[m] : 0.0f) * p.inv_gs;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)acc * BN;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(t_addr + c0, r);
+                const int n0 = nt * BN + c0;
+                if (m < p.M && n0 < p.N) {
+                    const size_t o = (size_t)m * p.N + n0;
+                    if (n0 + 32 <= p.N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]) * mul;
+                            if (p.residual) {
+                                const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + o + v * 8);
+                                const uint32_t rv[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    f[2 * i] += bf16_bits_to_float(rv[i] & 0xFFFFu);
+                                    f[2 * i + 1] += bf16_bits_to_float(rv[i] >> 16);
+                                }
+                            }
+                            uint32_t ov[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                                ov[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                            *reinterpret_cast<uint4*>(p.C + o + v * 8) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+                        }
+                    } else {
+                        for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
+                            float f = __uint_as_float(r[i]) * mul;
+                            if (p.residual) f += __bfloat162float(p.residual[o + i]);
+                            p.C[o + i] = __float2bfloat16_rn(f);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tempty[acc]);
+            if (++acc == kAccs) { acc = 0; pt ^= 1u; }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// BF16 activations -> FP16 scaled by an exact per-token power of two; one CTA per token.
+__global__ void __launch_bounds__(256)
+act_to_f16_kernel(const __nv_bfloat16* __restrict__ A, __half* __restrict__ out, float* __restrict__ unscale, int K) {
+    __shared__ unsigned int s_max;
+    const int m = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(A + (size_t)m * K);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)m * K);
+    if (threadIdx.x == 0) s_max = 0u;
+    __syncthreads();
+    unsigned int amax = 0;
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        const uint4 x = __ldg(src + i);
+        const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) amax = max(amax, max(v[q] & 0x7FFFu, (v[q] >> 16) & 0x7FFFu));
+    }
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if ((threadIdx.x & 31) == 0 && amax) atomicMax(&s_max, amax);
+    __syncthreads();
+    int se = 268 - (int)(s_max >> 7);      // scale = 2^(141 - biased exponent): largest -> exponent 14
+    se = se < 1 ? 1 : (se > 254 ? 254 : se);
+    const float sc = __uint_as_float((uint32_t)se << 23);
+    if (threadIdx.x == 0) unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        const uint4 x = __ldg(src + i);
+        const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+        uint32_t y[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            y[q] = ptx::pack_f16x2(__uint_as_float(v[q] << 16) * sc, __uint_as_float(v[q] & 0xFFFF0000u) * sc);
+        dst[i] = make_uint4(y[0], y[1], y[2], y[3]);
+    }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(p);
+    }
+    return fn;
+}
+
+bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int esize, const void* base, uint64_t cols, uint64_t rows,
+              uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+    EncodeFn enc = get_encode();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * (uint64_t)esize};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t act_bytes(int M, int K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }
+
+}  // namespace
+
+bool prefill_umma_supported(const LinearArgs& a) {
+    if (a.M < 1 || (a.K % WK) != 0 || (a.N % 8) != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
+    return true;
+}
+
+// FP16 copy of the activations + one FP32 per token.
+size_t prefill_umma_scratch_bytes(int max_M, int /*max_N*/, int max_K) {
+    if (max_M <= 16) return 0;
+    return act_bytes(max_M, max_K) + ((size_t)max_M * 4 + 255) / 256 * 256;
+}
+
+cudaError_t configure_prefill_umma() {
+    return cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+// scratch: [0, 256) status word (shared with the GEMV kernel), then from `offset` the FP16 activations.
+cudaError_t launch_prefill_umma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch, size_t scratch_bytes,
+                                size_t offset, int* launches, cudaStream_t s) {
+    const size_t need = prefill_umma_scratch_bytes(a.M, a.N, a.K);
+    if (offset + need > scratch_bytes) return cudaErrorMemoryAllocation;
+    char* base = static_cast<char*>(scratch) + offset;
+    __half* ah = reinterpret_cast<__half*>(base);
+    float* unscale = reinterpret_cast<float*>(base + act_bytes(a.M, a.K));
+    CUtensorMap tma, tmp, tms;
+    if (!make_map(&tma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ah, (uint64_t)a.K, (uint64_t)a.M, BK, BM,
+                  CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, BN,
+                  CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, BN,
+                  CU_TENSOR_MAP_SWIZZLE_NONE))
+        return cudaErrorInvalidValue;
+    act_to_f16_kernel<<<a.M, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(a.A), ah, unscale, a.K);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    PrefillParams p{};
+    p.residual = static_cast<const __nv_bfloat16*>(a.residual);
+    p.C = static_cast<__nv_bfloat16*>(a.C);
+    p.unscale = unscale;
+    p.status = static_cast<unsigned int*>(scratch);
+    p.inv_gs = a.inv_gs;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.m_tiles = (a.M + BM - 1) / BM;
+    p.n_tiles = (a.N + BN - 1) / BN;
+    int grid = p.m_tiles * p.n_tiles;
+    if (grid > dev.sm_count) grid = dev.sm_count;
+    prefill_umma_kernel<<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
+    if (launches) *launches = 2;
+    return cudaGetLastError();
+}
+
+cudaError_t configure_kernels(const nvfp4_device_info&) {
+    cudaError_t e = configure_decode_mma();
+    if (e == cudaSuccess) e = configure_prefill_umma();
+    return e;
+}
+
 }  // namespace nvfp4
