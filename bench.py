@@ -211,7 +211,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--sections", default="decode,prefill,stream,e2e,cpu,refkernel",
+    ap.add_argument("--sections", default="decode,prefill,stream,e2e,cpu,refkernel,tp",
                     help="extra measurements to add to the JSON line")
     ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
     args = ap.parse_args()
@@ -264,21 +264,24 @@ def main():
     l0 = h.launch_count()
     ms = time_region(step, args.steps, torch)
     launches = h.launch_count() - l0
-    # Second pass over the same steps with an event pair around every launch: per-kernel durations.
+    # Second pass, same launches regrouped: for every (shape, M) the `steps` launches of the timed
+    # region run back to back between one event pair (weights still rotate), which gives the
+    # kernel's average launch duration without an event gap between launches.
     per = {}
     evs = []
-    for _ in range(args.steps):
-        for M in DECODE_MS:
-            for name in ("gate_up", "down"):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
+    for M in DECODE_MS:
+        for name in ("gate_up", "down"):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            launch(name, M)
+            a.record()
+            for _ in range(args.steps):
                 launch(name, M)
-                b.record()
-                evs.append((name, M, a, b))
+            b.record()
+            evs.append((name, M, a, b))
     torch.cuda.synchronize()
     clocks = sampler.stop()
     for name, M, a, b in evs:
-        per.setdefault((name, M), []).append(a.elapsed_time(b) * 1e-3)
+        per[(name, M)] = [a.elapsed_time(b) * 1e-3 / args.steps]
     value = step_bytes / (ms * 1e-3) / 1e9
 
     sweep = []
@@ -318,6 +321,22 @@ def main():
         import bench_sections
         line["reference_kernels_on_this_gpu"] = bench_sections.reference_kernels(shapes, rot, acts, outs, torch,
                                                                                  alg_bytes, DECODE_MS)
+    if "tp" in sections and not args.small:
+        # configs[4] at one GPU: the MLP block (gate_up -> SwiGLU -> down), the base of the 2/4/8-GPU runs
+        import bench_tp
+        import nvfp4_tp
+        comm1 = nvfp4_tp.Comm(None, 0, 1)
+
+        def make_one(max_M):
+            out = []
+            for c in range(3 if max_M <= 256 else 2):
+                gp, gs = device_weight(2 * I, H, seed=100 + 2 * c, dev=dev)
+                dp, ds = device_weight(H, I, seed=101 + 2 * c, dev=dev)
+                out.append(nvfp4_tp.TpMlp(h, comm1, H, I, gp, gs, 1.0, dp, ds, 1.0, max_M))
+            return out
+
+        line["tp_mlp"] = bench_tp.run_tp_mlp_table(torch, None, make_one, H, dev, 1, args.steps)
+        comm1.close()
     if "cpu" in sections:
         line["cpu_baseline"], _ = cpu_baseline_sweep(15.0)
     print(json.dumps(line))

@@ -1,7 +1,193 @@
-"""Multi-GPU leg of bench.py: the tensor-parallel NVFP4 MLP.  Filled in with the TP library."""
+"""Multi-GPU leg of bench.py: the tensor-parallel NVFP4 MLP (one process per GPU, NCCL).
+
+The step is the decode sweep of the single-GPU benchmark run through the MLP block: for each M
+in {1,2,4,8,16} one forward = gate/up linear (column-split) -> SwiGLU -> down linear (row-split)
+-> one all-reduce of the [M, 5120] BF16 partials.  Total work is fixed as N grows ("strong");
+`value` counts the algorithmic bytes of the UNSPLIT weights and activations per step.  The
+`tp_mlp` key adds tokens/s at M in {1, 8, 256, 4096}.
+"""
 import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+TP_MS = (1, 8, 256, 4096)
+
+
+def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
+    """tokens/s of the MLP block at M in TP_MS (max over ranks of the device time)."""
+    out = []
+    for M in TP_MS:
+        mlps = make_mlp(M)
+        X = torch.randn((M, H), device=dev).to(torch.bfloat16)
+        Y = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
+        for i in range(3):
+            mlps[i % len(mlps)].forward(X, M, Y)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, steps if M <= 256 else min(steps, 5))
+        e0.record()
+        for i in range(reps):
+            mlps[i % len(mlps)].forward(X, M, Y)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        out.append({"M": M, "ms": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1)})
+        for m in mlps:
+            m.close()
+        del mlps
+        torch.cuda.empty_cache()
+    return out
 
 
 def main(args, world, rank, local_rank):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(ROOT, "qwen3-27b-thor-runner_b200"))
+    import bench
+    import nvfp4
+    import nvfp4_tp
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    dist.init_process_group("nccl", device_id=dev)
+    H, I = bench.H, bench.I
+    h = nvfp4.Handle(local_rank, 1 << 30)
     if rank == 0:
-        print(json.dumps({"metric": "decode_gemv_hbm_gbs", "n_gpus": world, "unavailable": "tensor-parallel path not built yet"}))
+        uid = torch.tensor(list(nvfp4_tp.unique_id()), dtype=torch.uint8, device=dev)
+    else:
+        uid = torch.zeros(nvfp4_tp.UNIQUE_ID_BYTES, dtype=torch.uint8, device=dev)
+    dist.broadcast(uid, 0)
+    comm = nvfp4_tp.Comm(bytes(uid.cpu().tolist()), rank, world)
+    peaks = bench.load_peaks()
+
+    def make_mlp_set(max_M, copies=None):
+        """Distinct MLPs (same seeds on every rank) whose shards together exceed 2 x L2."""
+        shard = (2 * I * H + H * I) * 9 // 16 // world
+        n = copies or max(2, -(-2 * bench.L2_BYTES // shard) + 1)
+        out = []
+        for c in range(n):
+            gp, gs = bench.device_weight(2 * I, H, seed=100 + 2 * c, dev=dev)
+            dp, ds = bench.device_weight(H, I, seed=101 + 2 * c, dev=dev)
+            out.append(nvfp4_tp.TpMlp(h, comm, H, I, gp, gs, 1.0, dp, ds, 1.0, max_M))
+            del gp, gs, dp, ds
+        torch.cuda.empty_cache()
+        return out
+
+    # ---- parity: a small block against the partition-aware CPU oracle (rank 0 checks)
+    parity = None
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_binding as ob
+        import util
+        h_, i_, m_ = 512, 256 * world, 4
+        gu_p, gu_s = util.make_weight(2 * i_, h_, seed=1)
+        dn_p, dn_s = util.make_weight(h_, i_, seed=2)
+        Xs, Rs = util.make_bf16((m_, h_), seed=3), util.make_bf16((m_, h_), seed=4)
+        small = nvfp4_tp.TpMlp(h, comm, h_, i_, util.to_dev(gu_p).to(dev), util.to_dev(gu_s).to(dev), 1.0,
+                               util.to_dev(dn_p).to(dev), util.to_dev(dn_s).to(dev), 1.0, m_)
+        out = util.to_dev(Rs).to(dev)
+        small.forward(util.to_dev(Xs).to(dev), m_, out, residual=out)
+        torch.cuda.synchronize()
+        if rank == 0:
+            want = ob.tp_mlp(Xs, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs, partial_bf16=True)
+            parity = {"rel_frobenius_vs_partition_aware_oracle": float(ob.rel_frobenius(util.to_host_u16(out), want)),
+                      "rel_frobenius_vs_unsplit_oracle": float(ob.rel_frobenius(
+                          util.to_host_u16(out), ob.mlp(Xs, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs)))}
+        small.close()
+    except Exception as e:  # the oracle is a checker only; the timing below does not depend on it
+        parity = {"error": repr(e)}
+
+    # ---- timed region: decode sweep through the MLP block
+    mlps = make_mlp_set(16)
+    X = {M: bench.device_acts(M, H, seed=M, dev=dev) for M in bench.DECODE_MS}
+    Y = {M: torch.empty((M, H), dtype=torch.bfloat16, device=dev) for M in bench.DECODE_MS}
+    state = {"i": 0}
+
+    def step():
+        for M in bench.DECODE_MS:
+            state["i"] = (state["i"] + 1) % len(mlps)
+            mlps[state["i"]].forward(X[M], M, Y[M])
+
+    for _ in range(args.warmup):
+        step()
+    sampler = bench.ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    dist.barrier()
+    l0 = h.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    launches = h.launch_count() - l0
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    step_bytes = sum(bench.alg_bytes(2 * I, H, M) + bench.alg_bytes(H, I, M) for M in bench.DECODE_MS)
+    value = step_bytes / (ms * 1e-3) / 1e9
+
+    # ---- end to end: tokens start in pinned host memory, results end there
+    hX = {M: torch.randn((M, H)).to(torch.bfloat16).pin_memory() for M in bench.DECODE_MS}
+    hY = {M: torch.empty((M, H), dtype=torch.bfloat16).pin_memory() for M in bench.DECODE_MS}
+
+    def e2e_step():
+        for M in bench.DECODE_MS:
+            state["i"] = (state["i"] + 1) % len(mlps)
+            X[M].copy_(hX[M], non_blocking=True)
+            mlps[state["i"]].forward(X[M], M, Y[M])
+            hY[M].copy_(Y[M], non_blocking=True)
+            torch.cuda.synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e = {"value": round(step_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
+           "h2d_bytes_per_step": sum(v.numel() * 2 for v in hX.values()),
+           "d2h_bytes_per_step": sum(v.numel() * 2 for v in hY.values()),
+           "api": "nvfp4_tp_mlp_forward on every rank; tokens copied from pinned host memory, results copied back"}
+    for m in mlps:
+        m.close()
+    del mlps
+    torch.cuda.empty_cache()
+
+    table = run_tp_mlp_table(torch, dist, lambda M: make_mlp_set(M, copies=(None if M <= 256 else 2)), H, dev, world,
+                             args.steps)
+    if rank == 0:
+        agg_peak = peaks["hbm_gbs"] * world
+        line = {"metric": "decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc", "data": "synthetic",
+                "config": {"workload": "configs[1] decode sweep M in {1,2,4,8,16} run as the configs[4] tensor-parallel MLP: "
+                                       "gate_up 34816x5120 column-split, SwiGLU, down 5120x17408 row-split, one NCCL "
+                                       "all-reduce of [M,5120] BF16 per forward",
+                           "parallelism": f"tp{world}", "l2": "MLP instances rotate; their shards exceed 2 x L2",
+                           "global_scale": 1.0, "scale_sigma": 0.02},
+                "roofline": {"bound": "hbm", "kernel": "whole MLP forward (3 kernels + all-reduce), aggregate over ranks",
+                             "achieved": round(value, 1), "peak": agg_peak, "peak_source": peaks["source"], "unit": "GB/s",
+                             "frac": round(value / agg_peak, 4), "traffic": None},
+                "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "tp_mlp": table, "parity": parity}
+        print(json.dumps(line))
+    comm.close()
+    dist.destroy_process_group()

@@ -108,6 +108,11 @@ int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* sc
 int nvfp4_swiglu(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16_or_null,
                  int M, int I, void* out_bf16, nvfp4_stream_t stream);
 
+/* Same with explicit row strides (in elements): gate and up rows are in_stride apart, output
+ * rows out_stride apart.  Used where the SwiGLU output feeds a K-padded weight shard. */
+int nvfp4_swiglu_strided(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16, int M, int I,
+                         long long in_stride, void* out_bf16, long long out_stride, nvfp4_stream_t stream);
+
 /* ---- reference-shaped entry points --------------------------------------
  * Same argument meaning as the reference functions of the same name (void
  * return, no validation surfaced); they run on a lazily created per-device

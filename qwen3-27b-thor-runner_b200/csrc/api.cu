@@ -257,20 +257,26 @@ int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* sc
     return cuda_status(e);
 }
 
+int nvfp4_swiglu_strided(nvfp4_handle* h, const void* gate, const void* up, int M, int I, long long in_stride,
+                         void* out, long long out_stride, nvfp4_stream_t stream) {
+    if (!h || !gate || !up || !out) return NVFP4_E_NULL;
+    if (M < 0 || I <= 0 || in_stride < I || out_stride < I) return NVFP4_E_SHAPE;
+    if (M == 0) return NVFP4_OK;
+    // The vector path needs 16-byte aligned row starts.
+    if (I >= 8 && (!aligned16(gate) || !aligned16(up) || !aligned16(out) || (I & 7) || (in_stride & 7) || (out_stride & 7)))
+        return NVFP4_E_ALIGN;
+    cudaError_t e = launch_swiglu(gate, up, in_stride, M, I, out, out_stride, stream);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
 int nvfp4_swiglu(nvfp4_handle* h, const void* gate, const void* up, int M, int I, void* out,
                  nvfp4_stream_t stream) {
     if (!h || !gate || !out) return NVFP4_E_NULL;
-    if (M < 0 || I <= 0) return NVFP4_E_SHAPE;
-    if (M == 0) return NVFP4_OK;
+    if (I <= 0) return NVFP4_E_SHAPE;
     const bool merged = (up == nullptr);
     if (merged) up = static_cast<const char*>(gate) + (size_t)I * 2;
-    // The vector path needs 16-byte aligned rows; otherwise only the merged/unmerged
-    // row starts must be 2-byte aligned, which any bf16 pointer is.  Keep it simple
-    // and strict: 16-byte alignment of every row start when I >= 8.
-    if (I >= 8 && (!aligned16(gate) || !aligned16(up) || !aligned16(out) || (I & 7) != 0)) return NVFP4_E_ALIGN;
-    cudaError_t e = launch_swiglu(gate, up, merged ? 2LL * I : (long long)I, M, I, out, stream);
-    h->launches += 1;
-    return cuda_status(e);
+    return nvfp4_swiglu_strided(h, gate, up, M, I, merged ? 2LL * I : (long long)I, out, I, stream);
 }
 
 int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M, const uint8_t* packed, const uint8_t* scale,

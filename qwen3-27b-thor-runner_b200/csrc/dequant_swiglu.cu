@@ -40,7 +40,7 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
-              __nv_bfloat16* __restrict__ out, long long row_stride_in, int M, int I) {
+              __nv_bfloat16* __restrict__ out, long long row_stride_in, long long row_stride_out, int M, int I) {
     const int vec_per_row = I >> 3;
     const long long total = (long long)M * vec_per_row;
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -57,7 +57,7 @@ swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __res
             const __nv_bfloat162 r = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
             o[j] = *reinterpret_cast<const uint32_t*>(&r);
         }
-        *reinterpret_cast<uint4*>(out + (size_t)m * I + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(out + (size_t)m * row_stride_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
     }
     // I % 8 tail columns, scalar.
     const int tail0 = vec_per_row * 8;
@@ -67,7 +67,7 @@ swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __res
             const int m = (int)(t / (I - tail0)), c = tail0 + (int)(t % (I - tail0));
             const float g = __bfloat162float(gate[(size_t)m * row_stride_in + c]);
             const float u = __bfloat162float(up[(size_t)m * row_stride_in + c]);
-            out[(size_t)m * I + c] = __float2bfloat16_rn(silu(g) * u);
+            out[(size_t)m * row_stride_out + c] = __float2bfloat16_rn(silu(g) * u);
         }
     }
 }
@@ -91,11 +91,11 @@ cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, flo
 }
 
 cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
-                          void* out, cudaStream_t s) {
+                          void* out, long long row_stride_out, cudaStream_t s) {
     const long long vecs = (long long)M * ((I + 7) >> 3);
     swiglu_kernel<<<grid_for(vecs, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gate),
                                                     static_cast<const __nv_bfloat16*>(up),
-                                                    static_cast<__nv_bfloat16*>(out), row_stride_in, M, I);
+                                                    static_cast<__nv_bfloat16*>(out), row_stride_in, row_stride_out, M, I);
     return cudaGetLastError();
 }
 

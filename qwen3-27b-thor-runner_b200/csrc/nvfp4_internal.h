@@ -35,7 +35,7 @@ cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);
 cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, float inv_gs, int N, int K,
                                 void* out, cudaStream_t s);
 cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
-                          void* out, cudaStream_t s);
+                          void* out, long long row_stride_out, cudaStream_t s);
 
 // --- prefill_simple.cu: C = A * Wdq^T with Wdq bf16 [N,K] already dequantised (debug path).
 cudaError_t launch_gemm_bf16_simple(const void* A, const void* Wdq, const void* residual, void* C,

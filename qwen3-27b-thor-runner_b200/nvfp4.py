@@ -33,6 +33,8 @@ SIGNATURES = {
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_swiglu_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p,
+                                     ctypes.c_longlong, c_void_p]),
     "nvfp4_invoke_fp4_gemv": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p]),
     "nvfp4_invoke_fp4_gemv_add": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p,
                                          c_void_p]),

@@ -1,0 +1,128 @@
+"""Host side of the tensor-parallel NVFP4 MLP: ctypes binding of libnvfp4_b200_tp.so
+(include/nvfp4_b200_tp.h) and the numpy statement of its sharding rule, which the CPU
+(gloo) tests run against the oracle.  One process per GPU; the communicator id travels over
+whatever channel the caller has (the benchmark broadcasts it with torch.distributed)."""
+import ctypes
+import os
+
+import numpy as np
+
+import nvfp4
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+TP_LIB_PATH = os.path.join(_HERE, "lib", "libnvfp4_b200_tp.so")
+UNIQUE_ID_BYTES = 128
+
+c_void_p, c_int, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+TP_SIGNATURES = {
+    "nvfp4_tp_unique_id": (c_int, [c_void_p]),
+    "nvfp4_tp_comm_create": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p)]),
+    "nvfp4_tp_comm_destroy": (c_int, [c_void_p]),
+    "nvfp4_tp_mlp_create": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                    c_float, c_int, ctypes.POINTER(c_void_p)]),
+    "nvfp4_tp_mlp_destroy": (c_int, [c_void_p]),
+    "nvfp4_tp_mlp_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "nvfp4_tp_mlp_shard_bytes": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
+}
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        nvfp4.load()
+        if not os.path.exists(TP_LIB_PATH):
+            raise RuntimeError(f"{TP_LIB_PATH} is missing: build it with `make -C {_HERE}`")
+        lib = ctypes.CDLL(TP_LIB_PATH)
+        for name, (res, args) in TP_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+# ------------------------------------------------------------------ sharding rule (numpy, host)
+
+def shard_gate_up(packed, scale, rank, world):
+    """Merged gate/up [2I, H]: rank r keeps gate rows and up rows [r*I/P, (r+1)*I/P), merged again."""
+    I = packed.shape[0] // 2
+    assert I % (16 * world) == 0
+    ip = I // world
+    rows = np.r_[rank * ip:(rank + 1) * ip, I + rank * ip:I + (rank + 1) * ip]
+    return np.ascontiguousarray(packed[rows]), np.ascontiguousarray(scale[rows])
+
+
+def shard_down(packed, scale, rank, world):
+    """Down [H, I]: rank r keeps K columns [r*I/P, (r+1)*I/P), K zero-padded to a multiple of 256
+    (zero codes and zero scales: the padding contributes exactly nothing)."""
+    H, I = packed.shape[0], packed.shape[1] * 2
+    assert I % (16 * world) == 0
+    ip = I // world
+    kp = (ip + 255) // 256 * 256
+    p = np.zeros((H, kp // 2), np.uint8)
+    s = np.zeros((H, kp // 16), np.uint8)
+    p[:, :ip // 2] = packed[:, rank * ip // 2:(rank + 1) * ip // 2]
+    s[:, :ip // 16] = scale[:, rank * ip // 16:(rank + 1) * ip // 16]
+    return p, s
+
+
+def pad_activation(act, kp):
+    """[M, I/P] BF16 bits -> [M, kp] with zero padding."""
+    out = np.zeros((act.shape[0], kp), act.dtype)
+    out[:, :act.shape[1]] = act
+    return out
+
+
+# ------------------------------------------------------------------ device objects
+
+class Comm:
+    def __init__(self, unique_id, rank, world):
+        self.lib = load()
+        c = c_void_p()
+        buf = None if unique_id is None else ctypes.create_string_buffer(bytes(unique_id), UNIQUE_ID_BYTES)
+        st = self.lib.nvfp4_tp_comm_create(buf, rank, world, ctypes.byref(c))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        self.c, self.rank, self.world = c, rank, world
+
+    def close(self):
+        if getattr(self, "c", None):
+            self.lib.nvfp4_tp_comm_destroy(self.c)
+            self.c = None
+
+
+def unique_id():
+    buf = ctypes.create_string_buffer(UNIQUE_ID_BYTES)
+    st = load().nvfp4_tp_unique_id(buf)
+    if st:
+        raise nvfp4.Nvfp4Error(st)
+    return bytes(buf.raw)
+
+
+class TpMlp:
+    def __init__(self, handle, comm, H, I, gu_packed, gu_scale, gu_gs, dn_packed, dn_scale, dn_gs, max_M):
+        self.lib = load()
+        m = c_void_p()
+        st = self.lib.nvfp4_tp_mlp_create(handle.h, comm.c, H, I, gu_packed.data_ptr(), gu_scale.data_ptr(), gu_gs,
+                                          dn_packed.data_ptr(), dn_scale.data_ptr(), dn_gs, max_M, ctypes.byref(m))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        self.m, self.H, self.I = m, H, I
+
+    def forward(self, X, M, out, residual=None, stream=None):
+        st = self.lib.nvfp4_tp_mlp_forward(self.m, X.data_ptr(), M, None if residual is None else residual.data_ptr(),
+                                           out.data_ptr(), nvfp4._stream(stream))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def shard_bytes(self):
+        v = ctypes.c_size_t()
+        self.lib.nvfp4_tp_mlp_shard_bytes(self.m, ctypes.byref(v))
+        return v.value
+
+    def close(self):
+        if getattr(self, "m", None):
+            self.lib.nvfp4_tp_mlp_destroy(self.m)
+            self.m = None

@@ -44,8 +44,11 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_binding_covers_header():
+    import nvfp4_tp
     decl = {n for n in declared_symbols() if not n.startswith("nvfp4_tp_")}
     assert decl == set(nvfp4.SIGNATURES), decl ^ set(nvfp4.SIGNATURES)
+    tp = {n for n in declared_symbols() if n.startswith("nvfp4_tp_")}
+    assert tp == set(nvfp4_tp.TP_SIGNATURES), tp ^ set(nvfp4_tp.TP_SIGNATURES)
 
 
 def test_quantized_weight_layout():

@@ -1,0 +1,104 @@
+"""CPU tests of the tensor-parallel MLP's host-side logic: the sharding rule, the K padding and
+the one-all-reduce composition, run as two gloo ranks with the CPU oracle standing in for the
+per-rank kernels, against the partition-aware oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import nvfp4_tp
+import oracle_binding as ob
+import util
+
+
+def test_shards_tile_the_full_weight():
+    H, I, P = 256, 512, 4
+    gu_p, gu_s = util.make_weight(2 * I, H, seed=1)
+    dn_p, dn_s = util.make_weight(H, I, seed=2)
+    gates, ups, cols = [], [], []
+    for r in range(P):
+        p, s = nvfp4_tp.shard_gate_up(gu_p, gu_s, r, P)
+        assert p.shape == (2 * I // P, H // 2) and s.shape == (2 * I // P, H // 16)
+        gates.append(p[:I // P]); ups.append(p[I // P:])
+        dp, ds = nvfp4_tp.shard_down(dn_p, dn_s, r, P)
+        assert dp.shape[1] * 2 % 256 == 0 and ds.shape[1] * 16 == dp.shape[1] * 2
+        cols.append(dp[:, :I // P // 2])
+        assert not dp[:, I // P // 2:].any() and not ds[:, I // P // 16:].any()
+    assert np.array_equal(np.concatenate(gates + ups), gu_p)
+    assert np.array_equal(np.concatenate(cols, axis=1), dn_p)
+
+
+def test_padding_contributes_nothing():
+    H, I = 256, 2176   # I/P = 272 at P = 8 is not a multiple of 256: padded to 512
+    dn_p, dn_s = util.make_weight(H, I, seed=3)
+    A = util.make_bf16((3, I), seed=4)
+    for P in (8,):
+        ip = I // P
+        for r in (0, 5):
+            p, s = nvfp4_tp.shard_down(dn_p, dn_s, r, P)
+            a = nvfp4_tp.pad_activation(np.ascontiguousarray(A[:, r * ip:(r + 1) * ip]), p.shape[1] * 2)
+            got = ob.linear(a, p, s, 1.0, mode=ob.GEMV)
+            want = ob.linear(np.ascontiguousarray(A[:, r * ip:(r + 1) * ip]),
+                             np.ascontiguousarray(dn_p[:, r * ip // 2:(r + 1) * ip // 2]),
+                             np.ascontiguousarray(dn_s[:, r * ip // 16:(r + 1) * ip // 16]), 1.0, mode=ob.GEMV)
+            assert ob.rel_frobenius(got, want) < 1e-6
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _rank_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, H, I = 3, 256, 512
+        gu_p, gu_s = util.make_weight(2 * I, H, seed=11)
+        dn_p, dn_s = util.make_weight(H, I, seed=12)
+        X = util.make_bf16((M, H), seed=13)
+        R = util.make_bf16((M, H), seed=14)
+        # what nvfp4_tp_mlp_forward does on one rank, with the oracle as the kernel
+        p, s = nvfp4_tp.shard_gate_up(gu_p, gu_s, rank, world)
+        gate_up = ob.linear(X, p, s, 1.0)
+        act = ob.swiglu_merged(gate_up)
+        dp, ds = nvfp4_tp.shard_down(dn_p, dn_s, rank, world)
+        part = ob.linear(nvfp4_tp.pad_activation(act, dp.shape[1] * 2), dp, ds, 1.0, residual=R if rank == 0 else None)
+        t = torch.from_numpy(ob.bf16_to_f32(part).copy())
+        dist.all_reduce(t)                     # one sum all-reduce of the [M, H] partials
+        got = ob.f32_to_bf16(t.numpy())
+        q.put((rank, got))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_two_rank_gloo_matches_partition_aware_oracle(world):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    M, H, I = 3, 256, 512
+    gu_p, gu_s = util.make_weight(2 * I, H, seed=11)
+    dn_p, dn_s = util.make_weight(H, I, seed=12)
+    X = util.make_bf16((M, H), seed=13)
+    R = util.make_bf16((M, H), seed=14)
+    assert np.array_equal(outs[0], outs[1])    # every rank ends with the same tensor
+    full = ob.mlp(X, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R)
+    aware = ob.tp_mlp(X, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R, partial_bf16=True)
+    # BF16 partials: close to the partition-aware oracle, a BF16 rounding away from the unsplit MLP
+    assert ob.rel_frobenius(outs[0], aware) < 5e-3
+    assert ob.rel_frobenius(outs[0], full) < 1e-2
