@@ -40,7 +40,8 @@ enum {
     NVFP4_E_SCALE = -6,      /* global_scale is 0, negative, inf or NaN */
     NVFP4_E_DEVICE = -7,     /* no CUDA device / wrong device / not sm_100 */
     NVFP4_E_OPTION = -8,     /* unknown option or value */
-    NVFP4_E_TP = -9          /* tensor-parallel set-up error */
+    NVFP4_E_TP = -9,         /* tensor-parallel set-up error */
+    NVFP4_E_LIMIT = -10      /* beyond the fixed maximum of the allocation-free entry point */
 };
 
 /* Layout-identical to qwen_thor::core::QuantizedWeight (src/engine/layer.h:197-204):
@@ -88,6 +89,26 @@ int nvfp4_linear(nvfp4_handle* h, const void* A_bf16, int M,
                  const uint8_t* packed, const uint8_t* scale_ue4m3, float global_scale,
                  int N, int K, const void* residual_bf16_or_null, void* C_bf16,
                  nvfp4_stream_t stream);
+
+/* The GEMV for callers that must not allocate device memory (no counterpart in the reference:
+ * there the scratch is a lazily grown global buffer).  Same arguments and result as nvfp4_linear
+ * without a handle: the cross-CTA scratch of the GEMV kernel sits in a fixed ~656 KB array inside
+ * the library's device image (held by every GPU that loads the library, until the process exits),
+ * so the call performs no cudaMalloc / cudaFree of any kind.  It serves hosts whose device memory
+ * is fully planned before they start calling -- e.g. an engine that gives all remaining HBM to its
+ * KV-cache pool at start-up, where a later allocation by this library could fail or break the
+ * engine's budget.
+ * Limits (else NVFP4_E_LIMIT): M <= 16, K % 256 == 0, packed and scale 16-byte aligned, and the
+ * FP16 copy of <= 8 tokens' activations must fit in shared memory beside the weight ring; the
+ * grid is capped at 160 CTAs, the size the array was laid out for.
+ * The first call on each device looks up the array's device address and sets the kernel's
+ * shared-memory attribute; make that first call before capturing a stream.  All calls share the
+ * one array: it keeps the previous call's flags and partial sums, which is harmless because every
+ * flag carries its call's sequence number and every partial is rewritten before it is read, but
+ * two calls that overlap on the GPU (different streams) race on it -- issue them on one stream. */
+int nvfp4_linear_decode_noalloc(const void* A_bf16, int M, const uint8_t* packed, const uint8_t* scale_ue4m3,
+                                float global_scale, int N, int K, const void* residual_bf16_or_null,
+                                void* C_bf16, nvfp4_stream_t stream);
 
 /* Two linears sharing A: C1 = A*W1^T, C2 = A*W2^T, both [N,K].
  * Replaces invoke_fp4_dual_gemv (:395-416), generalised to any M. */

@@ -120,6 +120,9 @@ const char* nvfp4_status_string(int status) {
         case NVFP4_E_DEVICE: return "no usable CUDA device (compute capability 10.x required)";
         case NVFP4_E_OPTION: return "unknown option or value";
         case NVFP4_E_TP: return "tensor-parallel set-up error";
+        case NVFP4_E_LIMIT:
+            return "beyond the fixed maximum of the allocation-free GEMV (need M <= 16, K % 256 == 0, activations of 8 "
+                   "tokens fitting in shared memory)";
         default: break;
     }
     if (status > 0) return cudaGetErrorString((cudaError_t)status);

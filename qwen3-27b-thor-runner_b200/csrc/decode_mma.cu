@@ -33,6 +33,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
@@ -528,3 +530,93 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
 }
 
 }  // namespace nvfp4
+
+// ----------------------------------------------------------------------------------------------
+// Allocation-free GEMV entry point.
+//
+// Some hosts of this library must never call cudaMalloc once they are running: an inference
+// engine that sizes its KV-cache pool to whatever device memory is left at start-up (the
+// reference engine does) has nothing to give later, so an allocation made by a plug-in can
+// fail or push the engine over its own budget; code running under a fixed memory plan is in
+// the same position.  For them the GEMV is offered without a handle: the cross-CTA scratch
+// (flags + FP32 partial tiles) that nvfp4_linear takes from the handle workspace lives in a
+// fixed array in the library's device image instead.
+//
+// The array costs kNoAllocScratchBytes (about 656 KB) on every GPU that loads the library, for
+// the life of the process.  Limits that follow from its fixed size and from the absence of a
+// workspace: at most 160 CTAs (the grid is capped there), M <= 16, K % 256 == 0, and the
+// activations of 8 tokens or fewer must fit in shared memory beside the weight ring; anything
+// else is refused with NVFP4_E_LIMIT.
+namespace nvfp4 {
+namespace {
+
+constexpr int kNoAllocMaxGrid = 160;
+constexpr size_t kNoAllocScratchBytes = kPartialOffset + (size_t)kNoAllocMaxGrid * kMaxTokens * kRT * 4;
+
+// File-scope device array: in HOST code this name is only a handle for the runtime, not an
+// address a kernel can use.  noalloc_setup() asks the runtime for the real device address
+// (cudaGetSymbolAddress) once per device and the kernel is always given that pointer.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+struct NoAllocState {
+    bool ready = false;
+    void* scratch = nullptr;      // device address of g_noalloc_scratch on this device
+    nvfp4_device_info dev{};
+};
+NoAllocState g_noalloc[64];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current: device facts, the kernel's shared-memory opt-in
+// and the device address of the scratch array.  Nothing here allocates.
+int noalloc_setup(int device, NoAllocState** out) {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    NoAllocState& st = g_noalloc[device];
+    if (!st.ready) {
+        int sms = 0, major = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        if (e != cudaSuccess) return (int)e;
+        if (major != 10) return NVFP4_E_DEVICE;
+        e = configure_decode_mma();
+        if (e != cudaSuccess) return (int)e;
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) return e != cudaSuccess ? (int)e : NVFP4_E_DEVICE;
+        st.scratch = ptr;
+        st.dev.device = device;
+        st.dev.sm_count = sms < kNoAllocMaxGrid ? sms : kNoAllocMaxGrid;   // the grid never exceeds the scratch
+        st.dev.cc_major = major;
+        st.dev.decode_epoch = 0;
+        st.ready = true;
+    }
+    *out = &st;
+    return NVFP4_OK;
+}
+
+}  // namespace
+}  // namespace nvfp4
+
+extern "C" int nvfp4_linear_decode_noalloc(const void* A, int M, const uint8_t* packed, const uint8_t* scale,
+                                           float global_scale, int N, int K, const void* residual, void* C,
+                                           nvfp4_stream_t stream) {
+    using namespace nvfp4;
+    if (!A || !packed || !scale || !C) return NVFP4_E_NULL;
+    if (M < 0 || N <= 0 || K <= 0 || (K & 15) != 0) return NVFP4_E_SHAPE;
+    if (!(global_scale > 0.0f) || !(global_scale <= 3.0e38f)) return NVFP4_E_SCALE;
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+    if (mis(A) || mis(C) || (residual && mis(residual)) || mis(packed) || mis(scale)) return NVFP4_E_ALIGN;
+    const char* a0 = static_cast<const char*>(A);
+    const char* c0 = static_cast<const char*>(C);
+    if (M > 0 && a0 < c0 + (size_t)M * N * 2 && c0 < a0 + (size_t)M * K * 2) return NVFP4_E_ALIAS;
+    if (M == 0) return NVFP4_OK;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return NVFP4_E_DEVICE;
+    NoAllocState* st = nullptr;
+    if (int e = noalloc_setup(device, &st)) return e;
+    LinearArgs a{A, packed, scale, 1.0f / global_scale, residual, C, M, N, K};
+    if (M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, st->dev)) return NVFP4_E_LIMIT;
+    if (decode_mma_scratch_bytes(a, st->dev) > kNoAllocScratchBytes) return NVFP4_E_LIMIT;
+    int launches = 0;
+    cudaError_t e = launch_decode_mma(a, st->dev, st->scratch, &launches, stream);
+    return e == cudaSuccess ? NVFP4_OK : (int)e;
+}

@@ -29,6 +29,8 @@ SIGNATURES = {
     "nvfp4_get_option": (c_int, [c_void_p, ctypes.c_char_p, ctypes.POINTER(c_int)]),
     "nvfp4_linear": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int,
                              c_void_p, c_void_p, c_void_p]),
+    "nvfp4_linear_decode_noalloc": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
+                                            c_void_p, c_void_p]),
     "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
