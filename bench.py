@@ -126,30 +126,38 @@ def device_acts(M, K, seed, dev):
 
 # ----------------------------------------------------------------------------- CPU baseline (oracle port)
 
+_CPU_DATA = {}   # synthetic host tensors of the CPU baseline, generated once
+
+
 def cpu_baseline_sweep(seconds_hint=15.0):
     """Times the oracle (scalar C port of the reference algorithm) on the host cores: the decode
-    sweep M in {1,2,4,8,16} over a row slice of both MLP shapes, rows split over all threads."""
+    sweep M in {1,2,4,8,16} over both MLP shapes (all rows), rows split over all threads, repeated
+    until about `seconds_hint` seconds of CPU work (threads x wall time) have been spent."""
     import numpy as np
     import oracle_binding as ob
     import util
     threads = os.cpu_count() or 1
-    # ~2.2 ns per multiply-accumulate per thread on the scalar port; size the slice for seconds_hint.
-    total_macs = sum(N * K * sum(DECODE_MS) for (N, K) in (SHAPES["gate_up"], SHAPES["down"]))
-    frac = min(1.0, seconds_hint * threads / (total_macs * 2.2e-9))
-    nbytes, t_total, desc = 0, 0.0, []
+    data = _CPU_DATA
     for name in ("gate_up", "down"):
+        if name in data:
+            continue
         N, K = SHAPES[name]
-        n = max(threads, int(N * frac) // 16 * 16)
-        packed, scale = util.make_weight(n, K, seed=0)
-        for M in DECODE_MS:
-            A = util.make_bf16((M, K), seed=M)
-            t0 = time.perf_counter()
-            ob.linear(A, packed, scale, 1.0, mode=ob.GEMV, threads=threads)
-            t_total += time.perf_counter() - t0
-            nbytes += alg_bytes(n, K, M)
-        desc.append(f"{name}: first {n} of {N} rows")
+        packed, scale = util.make_weight(N, K, seed=0)
+        data[name] = (packed, scale, {M: util.make_bf16((M, K), seed=M) for M in DECODE_MS})
+    nbytes, t_total, reps = 0, 0.0, 0
+    while reps == 0 or (t_total * threads < seconds_hint and reps < 50):
+        for name in ("gate_up", "down"):
+            N, K = SHAPES[name]
+            packed, scale, acts = data[name]
+            for M in DECODE_MS:
+                t0 = time.perf_counter()
+                ob.linear(acts[M], packed, scale, 1.0, mode=ob.GEMV, threads=threads)
+                t_total += time.perf_counter() - t0
+                nbytes += alg_bytes(N, K, M)
+        reps += 1
     return dict(value=nbytes / t_total / 1e9, unit="GB/s", cores=threads, kind="port",
-                sample="decode sweep M in {1,2,4,8,16}; " + "; ".join(desc) + f"; {t_total:.1f} s of wall time"), t_total
+                sample=f"{reps} x decode sweep M in {{1,2,4,8,16}} on gate_up 34816x5120 + down 5120x17408 (all rows), "
+                       f"{t_total:.1f} s wall on {threads} threads = {t_total * threads:.0f} s of CPU work"), t_total
 
 
 def run_reference_arm(args):
@@ -157,9 +165,9 @@ def run_reference_arm(args):
     if rank != 0:
         return
     steps = max(1, args.steps)
-    per = max(2.0, min(20.0, 120.0 / (steps + args.warmup)))
+    per = max(4.0, min(20.0, 150.0 / (steps + args.warmup)))   # CPU-seconds per step: the whole run stays in minutes
     for _ in range(args.warmup):
-        cpu_baseline_sweep(per / 4)
+        cpu_baseline_sweep(1.0)
     vals, tt = [], 0.0
     for _ in range(steps):
         cb, t = cpu_baseline_sweep(per)
@@ -194,8 +202,27 @@ class Rotating:
         return self.w[self.i]
 
 
-def time_region(fn, steps, torch):
+def time_region(fn, steps, torch, graph=True):
+    """Device time per call of fn over `steps` calls.  graph=True: the `steps` calls are captured
+    into one CUDA graph (the library's launches are capturable: no allocation, no synchronisation)
+    and one replay is timed, so the figure is free of host launch overhead; the replay executes
+    exactly the kernels the calls would."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(steps):
+                    fn()
+            g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            g.replay()
+            e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
     torch.cuda.synchronize()
     e0.record()
     for _ in range(steps):
@@ -214,6 +241,8 @@ def main():
     ap.add_argument("--sections", default="decode,prefill,stream,e2e,cpu,refkernel,tp",
                     help="extra measurements to add to the JSON line")
     ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
+    ap.add_argument("--prefill-ms", default="64,256,2048,8192", help="token counts of the prefill section")
+    ap.add_argument("--no-graph", action="store_true", help="time stream launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
@@ -249,7 +278,7 @@ def main():
     def launch(name, M):
         N, K = shapes[name]
         p, s = rot[name].next()
-        h.linear(acts[(name, M)], M, p, s, 1.0, N, K, outs[(name, M)], stream=stream)
+        h.linear(acts[(name, M)], M, p, s, 1.0, N, K, outs[(name, M)], stream=torch.cuda.current_stream())
 
     def step():
         for M in DECODE_MS:
@@ -261,27 +290,19 @@ def main():
         step()
     sampler = ClockSampler(0)
     sampler.start()
+    use_graph = not args.no_graph
     l0 = h.launch_count()
-    ms = time_region(step, args.steps, torch)
-    launches = h.launch_count() - l0
+    ms = time_region(step, args.steps, torch, graph=use_graph)
+    launches = h.launch_count() - l0   # kernels launched by the K steps (= kernels in the timed replay)
     # Second pass, same launches regrouped: for every (shape, M) the `steps` launches of the timed
     # region run back to back between one event pair (weights still rotate), which gives the
     # kernel's average launch duration without an event gap between launches.
     per = {}
-    evs = []
     for M in DECODE_MS:
         for name in ("gate_up", "down"):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             launch(name, M)
-            a.record()
-            for _ in range(args.steps):
-                launch(name, M)
-            b.record()
-            evs.append((name, M, a, b))
-    torch.cuda.synchronize()
+            per[(name, M)] = [time_region(lambda: launch(name, M), args.steps, torch, graph=use_graph) * 1e-3]
     clocks = sampler.stop()
-    for name, M, a, b in evs:
-        per[(name, M)] = [a.elapsed_time(b) * 1e-3 / args.steps]
     value = step_bytes / (ms * 1e-3) / 1e9
 
     sweep = []
@@ -305,6 +326,7 @@ def main():
                                    + (" (SMALL shapes)" if args.small else ""),
                        "l2": f"weights rotate over {rot['gate_up'].n}/{rot['down'].n} distinct copies (> 2 x L2)",
                        "global_scale": 1.0, "scale_sigma": 0.02, "seed": 0,
+                       "timing": "one CUDA-graph replay of the K steps" if use_graph else "K steps of stream launches",
                        "decode_impl": h.get_option("decode_impl"), "prefill_impl": h.get_option("prefill_impl")},
             "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "decode_sweep": sweep}
 
@@ -313,7 +335,8 @@ def main():
         line["e2e"] = bench_sections.e2e(h, shapes, rot, args, torch, alg_bytes, DECODE_MS)
     if "prefill" in sections:
         import bench_sections
-        line["prefill"] = bench_sections.prefill(h, shapes, rot, peaks, torch, small=args.small)
+        line["prefill"] = bench_sections.prefill(h, shapes, rot, peaks, torch, small=args.small,
+                                                  ms_list=tuple(int(x) for x in args.prefill_ms.split(",")))
     if "stream" in sections and not args.small:
         import bench_sections
         line["layer_stream"] = bench_sections.layer_stream(h, SHAPES, peaks, torch, alg_bytes)

@@ -10,7 +10,8 @@
 //     with the 128-byte swizzle, scales), completing on the stage's mbarrier.  A stage carries two
 //     consecutive half-units (36 KB): large enough that one issuing thread keeps HBM busy.  No
 //     cluster multicast anywhere.
-//   * Consumer group h works on half-unit h of every stage; each of its 8 warps owns 16 of the 128
+//   * Consumer group h works on half-unit h of every stage (two groups in a 17-warp CTA, one in a
+//     9-warp CTA, see GROUPS); each of a group's 8 warps owns 16 of the 128
 //     rows.  Codes are expanded in registers: cvt.rn.f16x2.e2m1x2 turns one packed byte into two
 //     exact FP16 values, one f16x2 multiply applies the block scale taken from a 256-entry
 //     shared-memory table.  Every product lut*scale is exact in FP16 (2 + 4 significant bits, all
@@ -45,10 +46,10 @@ namespace {
 constexpr int kRT = 128;                          // rows per half-unit
 constexpr int kKC = 256;                          // k elements per half-unit
 constexpr int kGroupWarps = 8;                    // warps that share one half-unit (16 rows each)
-constexpr int kGroups = 2;                        // consumer groups: group h takes half-unit h of every stage
-constexpr int kConsumerWarps = kGroupWarps * kGroups;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;   // + producer warp
+// GROUPS consumer groups per CTA; group h takes half-unit h of every stage, so a stage carries
+// GROUPS half-units.  GROUPS = 2: one 17-warp CTA per SM.  GROUPS = 1: 9-warp CTAs, two per SM
+// when the activations are small -- the prologue and the epilogue chains of one CTA then
+// overlap the other CTA's streaming.
 constexpr int kPackedBytes = kRT * kKC / 2;       // 16384 per half-unit
 constexpr int kScaleBytes = kRT * kKC / 16;       // 2048 per half-unit
 constexpr int kActRowBytes = kKC * 2;             // 512 per token per half-unit (FP16)
@@ -56,7 +57,8 @@ constexpr int kMaxTokens = 8;                     // tokens per launch (one 8-co
 constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 output tile
 constexpr uint32_t kTxBytes = kPackedBytes + kScaleBytes;
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 227 * 1024;
+constexpr int kSmemBudget = 227 * 1024;           // one CTA per SM
+constexpr int kSmemBudgetHalf = 113 * 1024;       // two CTAs per SM
 
 // Scratch layout (handle workspace): status word, per-CTA flags, per-CTA partial tiles.
 // A flag word holds the launch epoch once the CTA's partial for that 16-row slab is stored.
@@ -98,18 +100,22 @@ __device__ __forceinline__ void expand_u32(uint32_t q, uint32_t S, uint32_t (&d)
 // PROBE selects measurement-only variants (the library instantiates PROBE = 0 only):
 //   bit 0: consumers skip the math (ring hand-shake only)   bit 3: producer moves no data
 //   bit 4: no activation staging                            bit 5: no epilogue
-template <int PROBE = 0>
-__global__ void __launch_bounds__(kThreads, 1)
+//   bit 6: XOR instead of the MMAs                          bit 7: no activation loads in the loop
+template <int GROUPS, int PROBE = 0>
+__global__ void __launch_bounds__((kGroupWarps * GROUPS + 1) * 32, 3 - GROUPS)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const DecodeParams p) {
+    constexpr int kConsumerWarps = kGroupWarps * GROUPS;
+    constexpr int kConsumerThreads = kConsumerWarps * 32;
+    constexpr int kThreads = kConsumerThreads + 32;   // + producer warp
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int stages = p.stages;
-    unsigned char* s_packed = smem;                                       // stages x 2 x 16 KB, 1024-aligned
-    unsigned char* s_scale = s_packed + stages * 2 * kPackedBytes;        // stages x 2 x 2 KB
-    unsigned char* s_act = s_scale + stages * 2 * kScaleBytes;            // slots x M x 512 B of FP16
-    float* s_out = reinterpret_cast<float*>(s_act + p.act_slots * p.M * kActRowBytes);   // kGroups FP32 tiles
-    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_out + kGroups * kMaxTokens * kOutLd);
+    unsigned char* s_packed = smem;                                       // stages x GROUPS x 16 KB, 1024-aligned
+    unsigned char* s_scale = s_packed + stages * GROUPS * kPackedBytes;   // stages x GROUPS x 2 KB
+    unsigned char* s_act = s_scale + stages * GROUPS * kScaleBytes;       // slots x M x 512 B of FP16
+    float* s_out = reinterpret_cast<float*>(s_act + p.act_slots * p.M * kActRowBytes);   // 2 FP32 exchange tiles
+    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_out + 2 * kMaxTokens * kOutLd);
     float* s_tokscale = reinterpret_cast<float*>(s_table + 256);          // [0..7] scale, [8..15] 1/scale per token
     unsigned int* s_amax = reinterpret_cast<unsigned int*>(s_tokscale + 16);   // [0..7] largest |activation| bits per token
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_amax + 16);
@@ -157,7 +163,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 const long long seg_end = tile_end < u_end ? tile_end : u_end;
                 const int row0 = tile * kRT;
                 while (hu < seg_end) {
-                    const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
+                    const int cnt = (seg_end - hu) >= GROUPS ? GROUPS : 1;
                     ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0x100u + (unsigned)stage);
                     const int k0 = kc * kKC;
                     if (PROBE & 8) {
@@ -165,9 +171,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     } else {
                         ptx::mbar_arrive_expect_tx(&full_bar[stage], kTxBytes * cnt);
                         for (int h = 0; h < cnt; ++h) {
-                            ptx::tma_load_2d(s_packed + (stage * 2 + h) * kPackedBytes, &tm_packed, &full_bar[stage],
+                            ptx::tma_load_2d(s_packed + (stage * GROUPS + h) * kPackedBytes, &tm_packed, &full_bar[stage],
                                              (k0 + h * kKC) >> 1, row0, pol_stream);
-                            ptx::tma_load_2d(s_scale + (stage * 2 + h) * kScaleBytes, &tm_scale, &full_bar[stage],
+                            ptx::tma_load_2d(s_scale + (stage * GROUPS + h) * kScaleBytes, &tm_scale, &full_bar[stage],
                                              (k0 + h * kKC) >> 4, row0, pol_stream);
                         }
                     }
@@ -192,6 +198,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     const int tok = g < p.M ? g : 0;                           // token feeding MMA column g (columns >= M are never stored)
     const int act_sw = t | ((tok & 1) << 2);
 
+    // Programmatic dependent launch: the next kernel of the stream may start its own weight
+    // streaming while this grid drains; whatever depends on the previous grid (activations,
+    // residual, the outputs and the cross-CTA scratch) is only touched after griddep_wait().
+    ptx::griddep_launch_dependents();
     // Block-scale table: code byte -> f16x2 (both halves) of ue4m3(code); exact (4 significant bits).
     if (tid < 256) {
         const uint32_t b = (uint32_t)__half_as_ushort(__float2half_rn(ue4m3_to_float((uint32_t)tid)));
@@ -208,6 +218,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // matters (an element keeps all 8 significant bits unless it is below 2^-28 of the largest)
     // and never overflows.  Pass B converts and stores in natural k order.  The scale is undone in
     // FP32 in the epilogue.
+    ptx::griddep_wait();
     if (!(PROBE & 16)) {
         const int per_slot = p.M * 32;
         const int total = p.act_slots * per_slot;
@@ -293,8 +304,35 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
+        // Segment bookkeeping known up front.  An owner whose contributors have already published
+        // their partials (the usual case: a contributor's share is the first thing it computes)
+        // fetches them now, off the critical path; otherwise it waits for them at the end.
+        const bool owner = (kc_first == 0);
+        const bool complete = owner && (seg_end == tile_end);
+        const int m0 = 2 * t, m1 = 2 * t + 1;
+        const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
+        const int mm[4] = {m0, m1, m0, m1};
+        int last = cta;                              // contributors are CTAs cta+1 .. last
+        float pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        bool prefetched = complete;
+        if (grp == 0 && owner && !complete && !(PROBE & 32)) {
+            while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
+            int ready = 1;
+            if (lane == 0)
+                for (int c = cta + 1; c <= last; ++c) ready &= (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) == p.epoch);
+            ready = __shfl_sync(0xffffffffu, ready, 0);
+            if (ready) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (mm[i] < p.M)
+                        for (int c = cta + 1; c <= last; ++c)
+                            pre[i] += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
+                prefetched = true;
+            }
+        }
+
         while (hu < seg_end) {
-            const int cnt = (seg_end - hu) >= 2 ? 2 : 1;
+            const int cnt = (seg_end - hu) >= GROUPS ? GROUPS : 1;
             const int slot = p.act_all ? kc + grp : (int)(hu - u_begin) + grp;
             hu += cnt;
             kc += cnt;
@@ -302,8 +340,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             // group 1 has nothing to do in a stage that carries a single half-unit.
             ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0x200u + (unsigned)stage);
             if (!(PROBE & 1) && grp < cnt) {
-                const unsigned char* wp = s_packed + (stage * 2 + grp) * kPackedBytes;
-                const unsigned char* sp = s_scale + (stage * 2 + grp) * kScaleBytes + off_s;
+                const unsigned char* wp = s_packed + (stage * GROUPS + grp) * kPackedBytes;
+                const unsigned char* sp = s_scale + (stage * GROUPS + grp) * kScaleBytes + off_s;
                 const unsigned char* ap = s_act + (size_t)(slot * p.M + tok) * kActRowBytes + t * 128;
                 const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
                 const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
@@ -311,22 +349,42 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + off_w1 + 8 * 128);
                 const uint32_t qa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
                 const uint32_t qb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-                uint32_t Sa = 0, Sb = 0;
+#ifndef NVFP4_DM_VARIANT
+#define NVFP4_DM_VARIANT 0
+#endif
+                // The four block scales of each row (blocks 4t..4t+3 of the half-unit), looked up once.
+                uint32_t Sa[4], Sb[4];
+                {
+                    const uint32_t ba = *reinterpret_cast<const uint32_t*>(sp);
+                    const uint32_t bb = *reinterpret_cast<const uint32_t*>(sp + 8 * 16);
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        Sa[b] = s_table[(ba >> (8 * b)) & 0xFFu];
+                        Sb[b] = s_table[(bb >> (8 * b)) & 0xFFu];
+                    }
+                }
+                float acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // second accumulator: halves the MMA dependency chain
 #pragma unroll
                 for (int uu = 0; uu < 8; ++uu) {
-                    if ((uu & 1) == 0) {
-                        Sa = s_table[sp[uu >> 1]];
-                        Sb = s_table[sp[8 * 16 + (uu >> 1)]];
-                    }
                     uint32_t da[4], db[4];
-                    expand_u32(qa[uu], Sa, da);
-                    expand_u32(qb[uu], Sb, db);
-                    const uint4 x = *reinterpret_cast<const uint4*>(ap + ((uu ^ act_sw) << 4));
+                    expand_u32(qa[uu], Sa[uu >> 1], da);
+                    expand_u32(qb[uu], Sb[uu >> 1], db);
+                    uint4 x = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
+                    if (!(PROBE & 128)) x = *reinterpret_cast<const uint4*>(ap + ((uu ^ act_sw) << 4));
                     const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // k 0..3 of this 8-group: rows g, g+8
                     const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // k 4..7
-                    ptx::mma_f16_16x8x16(acc, a_lo, x.x, x.y);
-                    ptx::mma_f16_16x8x16(acc, a_hi, x.z, x.w);
+                    if (PROBE & 64) {   // measurement only: keep the conversions alive without the tensor core
+                        acc[0] = __uint_as_float(__float_as_uint(acc[0]) ^ da[0] ^ db[1] ^ x.x);
+                        acc[1] = __uint_as_float(__float_as_uint(acc[1]) ^ da[1] ^ db[2] ^ x.y);
+                        acc[2] = __uint_as_float(__float_as_uint(acc[2]) ^ da[2] ^ db[3] ^ x.z);
+                        acc[3] = __uint_as_float(__float_as_uint(acc[3]) ^ da[3] ^ db[0] ^ x.w);
+                    } else {
+                        ptx::mma_f16_16x8x16(acc, a_lo, x.x, x.y);
+                        ptx::mma_f16_16x8x16(acc2, a_hi, x.z, x.w);
+                    }
                 }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty_bar[stage]);
@@ -338,25 +396,27 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         // on its own: group 1 hands its sums over through shared memory (two buffers alternating
         // per segment, one 64-thread barrier per segment), group 0 finishes from registers --
         // thread (g,t) holds rows r0, r0+8 x tokens 2t, 2t+1.  The other warps keep streaming.
-        const bool owner = (kc_first == 0);
-        const bool complete = owner && (seg_end == tile_end);
         float* xchg = s_out + (seg_parity ? kMaxTokens * kOutLd : 0);
         seg_parity ^= 1;
         if (PROBE & 32) { if (kc >= p.kchunks) { kc = 0; ++tile; } continue; }
-        if (grp == 1) {
-            xchg[(2 * t) * kOutLd + r0] = acc[0];
-            xchg[(2 * t + 1) * kOutLd + r0] = acc[1];
-            xchg[(2 * t) * kOutLd + r0 + 8] = acc[2];
-            xchg[(2 * t + 1) * kOutLd + r0 + 8] = acc[3];
+        if (GROUPS == 2) {
+            if (grp == 1) {
+                xchg[(2 * t) * kOutLd + r0] = acc[0];
+                xchg[(2 * t + 1) * kOutLd + r0] = acc[1];
+                xchg[(2 * t) * kOutLd + r0 + 8] = acc[2];
+                xchg[(2 * t + 1) * kOutLd + r0 + 8] = acc[3];
+            }
+            ptx::named_barrier_sync(4 + gw, 64);
         }
-        ptx::named_barrier_sync(4 + gw, 64);
         if (grp == 0) {
-            const int m0 = 2 * t, m1 = 2 * t + 1;
             const float us0 = s_tokscale[8 + m0], us1 = s_tokscale[8 + m1];
-            float v[4] = {(acc[0] + xchg[m0 * kOutLd + r0]) * us0, (acc[1] + xchg[m1 * kOutLd + r0]) * us1,
-                          (acc[2] + xchg[m0 * kOutLd + r0 + 8]) * us0, (acc[3] + xchg[m1 * kOutLd + r0 + 8]) * us1};
-            const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
-            const int mm[4] = {m0, m1, m0, m1};
+            if (GROUPS == 2) {
+                acc[0] += xchg[m0 * kOutLd + r0];
+                acc[1] += xchg[m1 * kOutLd + r0];
+                acc[2] += xchg[m0 * kOutLd + r0 + 8];
+                acc[3] += xchg[m1 * kOutLd + r0 + 8];
+            }
+            float v[4] = {acc[0] * us0, acc[1] * us1, acc[2] * us0, acc[3] * us1};
             if (!owner) {
                 float* slot = partials + (size_t)cta * (kMaxTokens * kRT);
 #pragma unroll
@@ -365,9 +425,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 __syncwarp();
                 if (lane == 0) ptx::st_release_gpu(&flags[cta * kGroupWarps + gw], p.epoch);
             } else {
-                int last = cta;   // contributors are CTAs cta+1 .. last
-                if (!complete) {
-                    while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
+                if (!prefetched) {
                     if (lane == 0) {
                         const long long t0 = clock64();
                         for (int c = cta + 1; c <= last; ++c) {
@@ -382,15 +440,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                         }
                     }
                     __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (mm[i] < p.M)
+                            for (int c = cta + 1; c <= last; ++c)
+                                pre[i] += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
                 }
                 const int row_base = tile * kRT;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int n = row_base + rr[i];
                     if (mm[i] >= p.M || n >= p.N) continue;
-                    float x = v[i];
-                    for (int c = cta + 1; c <= last; ++c) x += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
-                    x *= p.inv_gs;
+                    float x = (v[i] + pre[i]) * p.inv_gs;
                     const size_t o = (size_t)mm[i] * p.N + n;
                     if (p.residual) x += __bfloat162float(p.residual[o]);
                     p.C[o] = __float2bfloat16_rn(x);
@@ -446,7 +507,7 @@ size_t decode_mma_scratch_bytes(const LinearArgs&, const nvfp4_device_info& dev)
 }
 
 cudaError_t configure_decode_mma() {
-    return cudaFuncSetAttribute(decode_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    return cudaFuncSetAttribute(decode_mma_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
 }
 
 namespace {
@@ -455,10 +516,10 @@ namespace {
 // activations leave, and needs at least three stages.
 struct DecodePlan {
     DecodeParams p;
-    int grid, smem;
+    int grid, smem, groups;
 };
 
-bool plan_decode(const LinearArgs& a, int m, const nvfp4_device_info& dev, void* scratch, DecodePlan* out) {
+bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, void* scratch, DecodePlan* out) {
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16*>(a.A);
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
@@ -469,22 +530,30 @@ bool plan_decode(const LinearArgs& a, int m, const nvfp4_device_info& dev, void*
     p.kchunks = a.K / kKC;
     const long long tiles = (a.N + kRT - 1) / kRT;
     p.units = (int)(tiles * p.kchunks);
-    int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
+    int grid = grid_cap < kMaxGrid ? grid_cap : kMaxGrid;
     if (grid > p.units) grid = p.units;
-    const int fixed = 1024 + kGroups * kMaxTokens * kOutLd * 4 + 1024 + 128 + 2 * kMaxStages * 8 + 64;
-    const int stage_w = 2 * (kPackedBytes + kScaleBytes);
+    const int fixed = 1024 + 2 * kMaxTokens * kOutLd * 4 + 1024 + 128 + 2 * kMaxStages * 8 + 64;
+    const int stage_w = groups * (kPackedBytes + kScaleBytes);
+    const int budget = groups == 2 ? kSmemBudget : kSmemBudgetHalf;
     const int max_span = (p.units + grid - 1) / grid;
     p.act_all = p.kchunks <= max_span ? 1 : 0;
     p.act_slots = p.act_all ? p.kchunks : max_span;
     const long long act_res = (long long)p.act_slots * m * kActRowBytes;
-    long long stages = (kSmemBudget - fixed - act_res) / stage_w;
+    long long stages = (budget - fixed - act_res) / stage_w;
     if (stages < 3) return false;
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = (int)stages;
     out->p = p;
     out->grid = grid;
+    out->groups = groups;
     out->smem = fixed + (int)stages * stage_w + (int)act_res;
     return true;
+}
+
+// One 17-warp CTA per SM.  (Two 9-warp CTAs per SM, GROUPS = 1, measured 1-2 us slower per launch
+// on the MLP shapes: both CTAs of an SM start and end together, so nothing overlaps.)
+bool plan_decode(const LinearArgs& a, int m, const nvfp4_device_info& dev, void* scratch, DecodePlan* out) {
+    return plan_decode_groups(a, m, 2, dev.sm_count, scratch, out);
 }
 
 // Largest token count per launch (<= 8) whose activations fit beside the ring; 0 if none.
@@ -520,9 +589,18 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         DecodePlan pl;
         if (!plan_decode(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
         pl.p.epoch = ++dev.decode_epoch;
-        decode_mma_kernel<0><<<pl.grid, kThreads, pl.smem, s>>>(tmp, tms, pl.p);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(pl.grid);
+        cfg.blockDim = dim3((2 * kGroupWarps + 1) * 32);
+        cfg.dynamicSmemBytes = pl.smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<2, 0>, tmp, tms, pl.p);
         ++n;
-        cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { if (launches) *launches = n; return e; }
     }
     if (launches) *launches = n;
@@ -615,7 +693,6 @@ extern "C" int nvfp4_linear_decode_noalloc(const void* A, int M, const uint8_t* 
     if (int e = noalloc_setup(device, &st)) return e;
     LinearArgs a{A, packed, scale, 1.0f / global_scale, residual, C, M, N, K};
     if (M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, st->dev)) return NVFP4_E_LIMIT;
-    if (decode_mma_scratch_bytes(a, st->dev) > kNoAllocScratchBytes) return NVFP4_E_LIMIT;
     int launches = 0;
     cudaError_t e = launch_decode_mma(a, st->dev, st->scratch, &launches, stream);
     return e == cudaSuccess ? NVFP4_OK : (int)e;

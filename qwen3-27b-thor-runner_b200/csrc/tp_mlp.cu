@@ -1,6 +1,7 @@
 // Tensor-parallel NVFP4 MLP: per-rank shards, two linears + SwiGLU from the core library, one
 // NCCL all-reduce of the BF16 down-projection partials.  Host-side orchestration only; the
 // kernels are the core library's.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <nccl.h>
 
@@ -20,7 +21,30 @@ struct nvfp4_tp_mlp {
     uint8_t *gu_packed = nullptr, *gu_scale = nullptr, *dn_packed = nullptr, *dn_scale = nullptr;
     float gu_gs = 1.0f, dn_gs = 1.0f;
     void *gate_up_out = nullptr, *act = nullptr;      // [max_M, 2*Ip], [max_M, Kp] (pad columns stay zero)
+    void* res_copy = nullptr;                          // [max_M, H]: the residual of an in-place call
 };
+
+namespace {
+
+// out = bf16(float(out) + float(residual)), 8 elements per thread; n % 8 == 0 (H % 256 == 0).
+__global__ void __launch_bounds__(256) add_residual_kernel(uint4* out, const uint4* residual, long long n8) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const uint4 a = out[i], b = residual[i];
+        const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float lo = __uint_as_float(av[j] << 16) + __uint_as_float(bv[j] << 16);
+            const float hi = __uint_as_float(av[j] & 0xFFFF0000u) + __uint_as_float(bv[j] & 0xFFFF0000u);
+            const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+            o[j] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -60,7 +84,7 @@ int nvfp4_tp_comm_destroy(nvfp4_tp_comm* c) {
 int nvfp4_tp_mlp_destroy(nvfp4_tp_mlp* m) {
     if (!m) return NVFP4_E_NULL;
     cudaFree(m->gu_packed); cudaFree(m->gu_scale); cudaFree(m->dn_packed); cudaFree(m->dn_scale);
-    cudaFree(m->gate_up_out); cudaFree(m->act);
+    cudaFree(m->gate_up_out); cudaFree(m->act); cudaFree(m->res_copy);
     delete m;
     return NVFP4_OK;
 }
@@ -86,6 +110,7 @@ int nvfp4_tp_mlp_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int I, cons
     alloc((void**)&m->dn_scale, (size_t)H * m->Kp / 16);
     alloc(&m->gate_up_out, (size_t)max_M * gu_rows * 2);
     alloc(&m->act, (size_t)max_M * m->Kp * 2);
+    alloc(&m->res_copy, (size_t)max_M * H * 2);
     if (e == cudaSuccess) e = cudaMemset(m->dn_packed, 0, (size_t)H * m->Kp / 2);   // zero codes and zero scales
     if (e == cudaSuccess) e = cudaMemset(m->dn_scale, 0, (size_t)H * m->Kp / 16);   // in the K padding
     if (e == cudaSuccess) e = cudaMemset(m->act, 0, (size_t)max_M * m->Kp * 2);     // pad activations stay zero
@@ -119,13 +144,25 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     const char* gate = static_cast<const char*>(m->gate_up_out);
     st = nvfp4_swiglu_strided(m->h, gate, gate + (size_t)m->Ip * 2, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
     if (st) return st;
-    // The residual joins exactly one partial (rank 0's), so the sum carries it once.
-    const void* res = (m->comm->rank == 0) ? residual : nullptr;
-    st = nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, res, out, s);
-    if (st) return st;
-    if (P > 1) {
-        if (ncclAllReduce(out, out, (size_t)M * m->H, ncclBfloat16, ncclSum, m->comm->comm, s) != ncclSuccess)
+    if (P == 1) return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
+    // The partials travel without the residual (a partial rounded to BF16 next to a residual ten
+    // times its size would lose its low bits); it is added once, in FP32, after the sum.
+    const void* res_src = residual;
+    if (residual == out) {   // in place: keep a copy of the residual while `out` carries the partial
+        if (cudaMemcpyAsync(m->res_copy, residual, (size_t)M * m->H * 2, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
             return NVFP4_E_TP;
+        res_src = m->res_copy;
+    }
+    st = nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, nullptr, out, s);
+    if (st) return st;
+    if (ncclAllReduce(out, out, (size_t)M * m->H, ncclBfloat16, ncclSum, m->comm->comm, s) != ncclSuccess)
+        return NVFP4_E_TP;
+    if (res_src) {
+        const long long n8 = (long long)M * m->H / 8;
+        int blocks = (int)((n8 + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        add_residual_kernel<<<blocks, 256, 0, s>>>(static_cast<uint4*>(out), static_cast<const uint4*>(res_src), n8);
+        if (cudaGetLastError() != cudaSuccess) return NVFP4_E_TP;
     }
     return NVFP4_OK;
 }

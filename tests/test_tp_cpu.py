@@ -69,10 +69,11 @@ def _rank_main(rank, world, port, q):
         gate_up = ob.linear(X, p, s, 1.0)
         act = ob.swiglu_merged(gate_up)
         dp, ds = nvfp4_tp.shard_down(dn_p, dn_s, rank, world)
-        part = ob.linear(nvfp4_tp.pad_activation(act, dp.shape[1] * 2), dp, ds, 1.0, residual=R if rank == 0 else None)
+        part = ob.linear(nvfp4_tp.pad_activation(act, dp.shape[1] * 2), dp, ds, 1.0)
         t = torch.from_numpy(ob.bf16_to_f32(part).copy())
-        dist.all_reduce(t)                     # one sum all-reduce of the [M, H] partials
-        got = ob.f32_to_bf16(t.numpy())
+        dist.all_reduce(t)                     # one sum all-reduce of the [M, H] BF16 partials
+        summed = ob.bf16_to_f32(ob.f32_to_bf16(t.numpy()))              # the collective delivers BF16
+        got = ob.f32_to_bf16(summed + ob.bf16_to_f32(R))                # residual added once, after the sum
         q.put((rank, got))
     finally:
         dist.destroy_process_group()
