@@ -71,7 +71,9 @@ const char* nvfp4_status_string(int status);
  *   "decode_impl":  0 = auto, 1 = scalar CUDA-core GEMV, 2 = TMA ring + MMA GEMV
  *   "prefill_impl": 0 = auto, 1 = dequant-to-workspace + CUDA-core GEMM (debug),
  *                   2 = fused dequant + tcgen05 GEMM
- *   "decode_max_m": largest M routed to the GEMV path (default 16)            */
+ *   "decode_max_m": largest M routed to the GEMV path (default 16)
+ *   "prefill_stream_k": 1 (default) = output tiles left over after whole waves of tiles are
+ *                   split along K over all SMs; 0 = whole tiles only                */
 int nvfp4_set_option(nvfp4_handle* h, const char* name, int value);
 int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value);
 

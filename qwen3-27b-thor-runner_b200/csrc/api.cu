@@ -94,12 +94,14 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
         return cuda_status(e);
     }
     // Debug path: dequantise the whole weight into the workspace, then a CUDA-core GEMM.
+    // The matrix goes behind the status word, flags and partial tiles of the fast kernels.
+    const size_t skip = kDecodeScratchBytes + prefill_umma_reserved_bytes();
     const size_t need = (size_t)a.N * a.K * 2;
-    if (need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
-    cudaError_t e = launch_dequant_bf16(a.packed, a.scale, a.inv_gs, a.N, a.K, h->workspace, s);
+    if (skip + need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+    cudaError_t e = launch_dequant_bf16(a.packed, a.scale, a.inv_gs, a.N, a.K, h->workspace + skip, s);
     h->launches += 1;
     if (e != cudaSuccess) return (int)e;
-    e = launch_gemm_bf16_simple(a.A, h->workspace, a.residual, a.C, a.M, a.N, a.K, s);
+    e = launch_gemm_bf16_simple(a.A, h->workspace + skip, a.residual, a.C, a.M, a.N, a.K, s);
     h->launches += 1;
     return cuda_status(e);
 }
@@ -196,6 +198,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "decode_max_m")) {
         if (value < 0 || value > 16) return NVFP4_E_OPTION;
         h->decode_max_m = value;
+    } else if (!std::strcmp(name, "prefill_stream_k")) {
+        if (value < 0 || value > 1) return NVFP4_E_OPTION;
+        h->dev.prefill_stream_k = value;
     } else {
         return NVFP4_E_OPTION;
     }
@@ -207,6 +212,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     if (!std::strcmp(name, "decode_impl")) *value = h->decode_impl;
     else if (!std::strcmp(name, "prefill_impl")) *value = h->prefill_impl;
     else if (!std::strcmp(name, "decode_max_m")) *value = h->decode_max_m;
+    else if (!std::strcmp(name, "prefill_stream_k")) *value = h->dev.prefill_stream_k;
     else if (!std::strcmp(name, "sm_count")) *value = h->dev.sm_count;
     else return NVFP4_E_OPTION;
     return NVFP4_OK;

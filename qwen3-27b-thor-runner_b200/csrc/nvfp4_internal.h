@@ -25,7 +25,8 @@ struct nvfp4_device_info {
     int sm_count;
     int cc_major, cc_minor;
     size_t smem_optin;
-    unsigned int decode_epoch;   // bumped per GEMV launch; tags the cross-CTA flags in the scratch
+    unsigned int decode_epoch;   // bumped per launch; tags the cross-CTA flags in the scratch
+    int prefill_stream_k = 1;    // split the tiles left after whole waves by k over all CTAs
 };
 
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
@@ -51,9 +52,10 @@ cudaError_t configure_decode_mma();
 
 // --- prefill_umma.cu: fused dequant + tcgen05 BF16 GEMM with TMEM accumulators.
 bool prefill_umma_supported(const LinearArgs& a);
+size_t prefill_umma_reserved_bytes();   // flags + partial tiles at the start of the kernel's scratch
 size_t prefill_umma_scratch_bytes(int max_M, int max_N, int max_K);
 // scratch[0] is the handle's status word; the FP16 activation copy lives at scratch + offset.
-cudaError_t launch_prefill_umma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch,
+cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch,
                                 size_t scratch_bytes, size_t offset, int* launches, cudaStream_t s);
 
 // Sets the per-kernel attributes (dynamic shared memory opt-in) once per device.

@@ -2,7 +2,9 @@
 //
 //   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
 //
-// One persistent CTA per SM works on 128-token x 256-weight-row output tiles:
+// One persistent CTA per SM works on 128-token x 256-weight-row output tiles.  The (tile, 256-k
+// stage) units are split evenly over the CTAs (stream-K), so small token counts still fill the
+// GPU; a tile cut by a span boundary is summed from FP32 partial tiles in a fixed order.
 //   warp 0      TMA producer: activation tiles (128 tokens x 64 k, FP16, 128-byte swizzle) into a
 //               4-stage ring, raw weight stages (256 rows x 256 k of packed codes + scales, 36 KB)
 //               into a 2-stage ring.  Plain tiled TMA, never cluster multicast.
@@ -50,6 +52,8 @@ constexpr int kDequantWarps = 8, kEpiWarps = 4;
 constexpr int kSmemBytes = 1024 + kAStages * kABytes + kWStages * (kWPackedBytes + kWScaleBytes) +
                            kBBufs * kBBytes + 1024 /*table*/ + 256 /*barriers, tmem slot, abort*/;
 
+constexpr int kPartialVec = BM * BN / 4;      // float4 elements of one FP32 partial tile
+
 struct PrefillParams {
     const __nv_bfloat16* residual;
     __nv_bfloat16* C;
@@ -58,6 +62,50 @@ struct PrefillParams {
     float inv_gs;
     int M, N, K;
     int m_tiles, n_tiles;
+    // stream-K region: tiles [0, sk_tiles).  A tile cut by a span boundary is finished by the CTA
+    // holding its first stage, which adds the other CTAs' FP32 partial tiles in CTA order.
+    int sk_tiles;
+    float4* partials;          // [grid][2][64 column chunks][128 token rows] FP32 x 4
+    unsigned int* flags;       // [grid][2], launch epoch once that partial tile is stored
+    unsigned int epoch;
+};
+
+// Work of one CTA: first its share of the stream-K region (tiles [0, sk_tiles), cut into
+// (tile, stage) units and split evenly over the CTAs), then whole tiles sk_tiles + blockIdx.x +
+// i * gridDim.x.  The interleaved order keeps the CTAs that share a weight tile in step, so the
+// tile is fetched from HBM once and read from L2 by the others.  Every role walks the same list.
+struct Segment {
+    int tile, ks0, ks1;
+};
+struct Schedule {
+    long long u, u_end;
+    int dp_tile, num_tiles, kstages;
+    __device__ __forceinline__ Schedule(const PrefillParams& p, int kst) {
+        const long long sk_units = (long long)p.sk_tiles * kst;
+        u = (long long)blockIdx.x * sk_units / gridDim.x;
+        u_end = (long long)(blockIdx.x + 1) * sk_units / gridDim.x;
+        dp_tile = p.sk_tiles + blockIdx.x;
+        num_tiles = p.m_tiles * p.n_tiles;
+        kstages = kst;
+    }
+    __device__ __forceinline__ bool next(Segment& s) {
+        if (u < u_end) {
+            s.tile = (int)(u / kstages);
+            s.ks0 = (int)(u % kstages);
+            const long long room = u_end - u;
+            s.ks1 = (kstages - s.ks0) < room ? kstages : s.ks0 + (int)room;
+            u += s.ks1 - s.ks0;
+            return true;
+        }
+        if (dp_tile < num_tiles) {
+            s.tile = dp_tile;
+            s.ks0 = 0;
+            s.ks1 = kstages;
+            dp_tile += gridDim.x;
+            return true;
+        }
+        return false;
+    }
 };
 
 // ---------------------------------------------------------------- tcgen05 helpers
@@ -100,6 +148,85 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Split tiles this CTA holds a part of: [0] the one its span starts inside (partial slot 0),
+// [1] the one its span ends inside (slot 1); -1 = none.
+__device__ __forceinline__ void split_tiles_of_cta(const PrefillParams& p, int kstages, int out[2]) {
+    out[0] = out[1] = -1;
+    const long long sk_units = (long long)p.sk_tiles * kstages;
+    const long long u0 = (long long)blockIdx.x * sk_units / gridDim.x;
+    const long long u1 = (long long)(blockIdx.x + 1) * sk_units / gridDim.x;
+    if (u0 >= u1) return;
+    const int t0 = (int)(u0 / kstages), t1 = (int)((u1 - 1) / kstages);
+    if (u0 % kstages != 0) out[0] = t0;
+    else if (u1 - u0 < kstages) out[1] = t0;
+    if (t1 != t0 && u1 - (long long)t1 * kstages < kstages) out[1] = t1;
+}
+
+// Reduction of one split tile.  Every CTA holding a part of the tile calls this once its own
+// parts are stored: it waits (bounded) for the partial tiles of all P participants, sums them
+// in CTA order over its own 1/P of the tile and writes that part of the output.  All
+// participants add in the same order, so the result does not depend on timing.
+// t = 0..nthreads-1, nthreads a multiple of 128.
+__device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int tile, int kstages, int t, int nthreads,
+                                                  volatile int* s_abort) {
+    const long long sk_units = (long long)p.sk_tiles * kstages;
+    const long long tile_begin = (long long)tile * kstages, tile_end = tile_begin + kstages;
+    int first = blockIdx.x, last = blockIdx.x;
+    while (first > 0 && (long long)first * sk_units / gridDim.x > tile_begin) --first;
+    while (last + 1 < (int)gridDim.x && (long long)(last + 1) * sk_units / gridDim.x < tile_end) ++last;
+    if ((t & 31) == 0) {
+        const long long t0 = clock64();
+        for (int c = first; c <= last; ++c) {
+            const unsigned int* f = &p.flags[c * 2 + (c == first ? 1 : 0)];   // the first CTA holds the head of the tile
+            while (ptx::ld_acquire_gpu(f) != p.epoch) {
+                if (*s_abort) break;
+                if (clock64() - t0 > ptx::kWaitBudgetClocks) {
+                    *s_abort = 1;
+                    atomicCAS(p.status, 0u, 0x480u);
+                    break;
+                }
+            }
+        }
+    }
+    __syncwarp();
+    if (*s_abort) return;
+    const int P = last - first + 1, me = blockIdx.x - first;
+    const int j0 = (int)((long long)me * kPartialVec / P) & ~(BM - 1);
+    const int j1 = me + 1 == P ? kPartialVec : ((int)((long long)(me + 1) * kPartialVec / P) & ~(BM - 1));
+    const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
+    const int m = mt * BM + (t & (BM - 1));
+    const float mul = (m < p.M ? p.unscale[m] : 0.0f) * p.inv_gs;
+    const float4* head = p.partials + ((size_t)first * 2 + 1) * kPartialVec;
+    for (int j = j0 + t; j < j1; j += nthreads) {
+        float4 s = __ldcg(head + j);
+        for (int c = first + 1; c <= last; c += 8) {
+            float4 x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)      // eight loads in flight; absent participants add zero
+                x[i] = c + i <= last ? __ldcg(p.partials + (size_t)(c + i) * 2 * kPartialVec + j)
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { s.x += x[i].x; s.y += x[i].y; s.z += x[i].z; s.w += x[i].w; }
+        }
+        const int n = nt * BN + (j / BM) * 4;          // first of the 4 columns of this chunk
+        if (m < p.M && n < p.N) {                      // N % 8 == 0: a chunk of 4 is inside or outside
+            const size_t o = (size_t)m * p.N + n;
+            float f[4] = {s.x * mul, s.y * mul, s.z * mul, s.w * mul};
+            if (p.residual) {
+                const uint2 rr = *reinterpret_cast<const uint2*>(p.residual + o);
+                f[0] += bf16_bits_to_float(rr.x & 0xFFFFu);
+                f[1] += bf16_bits_to_float(rr.x >> 16);
+                f[2] += bf16_bits_to_float(rr.y & 0xFFFFu);
+                f[3] += bf16_bits_to_float(rr.y >> 16);
+            }
+            const __nv_bfloat162 b0 = __floats2bfloat162_rn(f[0], f[1]);
+            const __nv_bfloat162 b1 = __floats2bfloat162_rn(f[2], f[3]);
+            *reinterpret_cast<uint2*>(p.C + o) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_packed,
                     const __grid_constant__ CUtensorMap tm_scale, const PrefillParams p) {
@@ -123,8 +250,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int num_tiles = p.m_tiles * p.n_tiles;
     const int kstages = p.K / WK;
+    const bool all_reduce = p.sk_tiles == p.m_tiles * p.n_tiles;
 
     if (tid == 0) {
         for (int i = 0; i < kAStages; ++i) { ptx::mbar_init(&afull[i], 1); ptx::mbar_init(&aempty[i], 1); }
@@ -157,9 +284,11 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             const uint64_t pol_w = ptx::policy_evict_first(), pol_a = ptx::policy_evict_last();
             int sa = 0, sw = 0;
             uint32_t pa = 0, pw = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-                const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
-                for (int ks = 0; ks < kstages; ++ks) {
+            Schedule sched(p, kstages);
+            Segment sg;
+            while (sched.next(sg)) {
+                const int nt = sg.tile / p.m_tiles, mt = sg.tile % p.m_tiles;
+                for (int ks = sg.ks0; ks < sg.ks1; ++ks) {
                     ptx::mbar_wait(&wempty[sw], pw ^ 1u, s_abort, p.status, 0x410u + sw);
                     ptx::mbar_arrive_expect_tx(&wfull[sw], kWPackedBytes + kWScaleBytes);
                     ptx::tma_load_2d(s_wp + sw * kWPackedBytes, &tm_packed, &wfull[sw], ks * (WK / 2), nt * BN, pol_w);
@@ -179,11 +308,13 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         if (lane == 0) {
             int sa = 0, sb = 0, acc = 0;
             uint32_t pa = 0, pb = 0, pt = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            Schedule sched(p, kstages);
+            Segment sg;
+            while (sched.next(sg)) {
                 ptx::mbar_wait(&tempty[acc], pt ^ 1u, s_abort, p.status, 0x440u + acc);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
-                for (int kb = 0; kb < kstages * (WK / BK); ++kb) {
+                for (int kb = 0; kb < (sg.ks1 - sg.ks0) * (WK / BK); ++kb) {
                     ptx::mbar_wait(&afull[sa], pa, s_abort, p.status, 0x420u + sa);
                     ptx::mbar_wait(&bfull[sb], pb, s_abort, p.status, 0x430u + sb);
                     tc_fence_after();
@@ -209,8 +340,10 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         const int sw7 = row & 7;
         int sw = 0, sb = 0;
         uint32_t pw = 0, pb = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            for (int ks = 0; ks < kstages; ++ks) {
+        Schedule sched(p, kstages);
+        Segment sg;
+        while (sched.next(sg)) {
+            for (int ks = sg.ks0; ks < sg.ks1; ++ks) {
                 ptx::mbar_wait(&wfull[sw], pw, s_abort, p.status, 0x450u + sw);
                 const unsigned char* wp = s_wp + sw * kWPackedBytes + row * 128;
                 const uint4 sc16 = *reinterpret_cast<const uint4*>(s_ws + sw * kWScaleBytes + row * 16);
@@ -247,47 +380,74 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         const int ew = warp - 4;                          // TMEM lanes 32*ew .. 32*ew+31
         int acc = 0;
         uint32_t pt = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
-            const int m = mt * BM + ew * 32 + lane;
+        const int te = ew * 32 + lane;                        // 0..127: TMEM lane, token row of the tile
+        const long long sk_units = (long long)p.sk_tiles * kstages;
+        int pend[2] = {-1, -1};                               // split tiles whose partial this CTA has stored
+        Schedule sched(p, kstages);
+        Segment sg;
+        bool more = sched.next(sg);
+        while (more) {
+            const int nt = sg.tile / p.m_tiles, mt = sg.tile % p.m_tiles;
+            const int m = mt * BM + te;
+            const bool complete = sg.ks0 == 0 && sg.ks1 == kstages;
             ptx::mbar_wait(&tfull[acc], pt, s_abort, p.status, 0x470u + acc);
             tc_fence_after();
-            const float mul = (m < p.M ? p.unscale[m] : 0.0f) * p.inv_gs;
             const uint32_t t_addr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)acc * BN;
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(t_addr + c0, r);
-                const int n0 = nt * BN + c0;
-                if (m < p.M && n0 < p.N) {
-                    const size_t o = (size_t)m * p.N + n0;
-                    if (n0 + 32 <= p.N) {
+            if (!complete) {
+                // Part of a split tile: raw FP32 sums to this CTA's partial tile.  Layout
+                // [column chunk of 4][token row], so a warp's store covers 512 contiguous bytes.
+                const int which = sg.ks0 == 0 ? 1 : 0;        // head of a tile (span end) or tail (span start)
+                float4* slot = p.partials + ((size_t)blockIdx.x * 2 + which) * kPartialVec;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(t_addr + c0, r);
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            float f[8];
+                    for (int v = 0; v < 8; ++v)
+                        __stcg(slot + (c0 / 4 + v) * BM + te,
+                               make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                           __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+                }
+                __threadfence();
+                ptx::named_barrier_sync(1, kEpiWarps * 32);   // all 128 rows stored before the flag goes up
+                if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], p.epoch);
+                pend[which] = sg.tile;
+            } else {
+                const float mul = (m < p.M ? p.unscale[m] : 0.0f) * p.inv_gs;
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(t_addr + c0, r);
+                    const int n0 = nt * BN + c0;
+                    if (m < p.M && n0 < p.N) {
+                        const size_t o = (size_t)m * p.N + n0;
+                        if (n0 + 32 <= p.N) {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]) * mul;
-                            if (p.residual) {
-                                const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + o + v * 8);
-                                const uint32_t rv[4] = {rr.x, rr.y, rr.z, rr.w};
+                            for (int v = 0; v < 4; ++v) {
+                                float f[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]) * mul;
+                                if (p.residual) {
+                                    const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + o + v * 8);
+                                    const uint32_t rv[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        f[2 * i] += bf16_bits_to_float(rv[i] & 0xFFFFu);
+                                        f[2 * i + 1] += bf16_bits_to_float(rv[i] >> 16);
+                                    }
+                                }
+                                uint32_t ov[4];
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    f[2 * i] += bf16_bits_to_float(rv[i] & 0xFFFFu);
-                                    f[2 * i + 1] += bf16_bits_to_float(rv[i] >> 16);
+                                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                                    ov[i] = *reinterpret_cast<const uint32_t*>(&b2);
                                 }
+                                *reinterpret_cast<uint4*>(p.C + o + v * 8) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
                             }
-                            uint32_t ov[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                                ov[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                        } else {
+                            for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
+                                float f = __uint_as_float(r[i]) * mul;
+                                if (p.residual) f += __bfloat162float(p.residual[o + i]);
+                                p.C[o + i] = __float2bfloat16_rn(f);
                             }
-                            *reinterpret_cast<uint4*>(p.C + o + v * 8) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
-                            float f = __uint_as_float(r[i]) * mul;
-                            if (p.residual) f += __bfloat162float(p.residual[o + i]);
-                            p.C[o + i] = __float2bfloat16_rn(f);
                         }
                     }
                 }
@@ -296,6 +456,17 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tempty[acc]);
             if (++acc == kAccs) { acc = 0; pt ^= 1u; }
+            more = sched.next(sg);
+
+            // Whole tiles follow the stream-K region: these four warps reduce the split tiles now,
+            // behind the MMAs of the next tiles.  (With no whole tiles all warps do it at the end.)
+            if (!all_reduce && (pend[0] >= 0 || pend[1] >= 0) && (!more || sg.tile >= p.sk_tiles)) {
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    if (pend[w] >= 0) reduce_split_tile(p, pend[w], kstages, te, kEpiWarps * 32, s_abort);
+                    pend[w] = -1;
+                }
+            }
         }
     }
     tc_fence_before();
@@ -303,6 +474,14 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+    if (all_reduce) {
+        // Every tile was split and nothing else is left to do: all 16 warps reduce.
+        int split[2];
+        split_tiles_of_cta(p, kstages, split);
+#pragma unroll
+        for (int w = 0; w < 2; ++w)
+            if (split[w] >= 0) reduce_split_tile(p, split[w], kstages, tid, kThreads, s_abort);
     }
 }
 
@@ -378,22 +557,31 @@ bool prefill_umma_supported(const LinearArgs& a) {
     return true;
 }
 
-// FP16 copy of the activations + one FP32 per token.
+constexpr size_t kPartialTileBytes = (size_t)kPartialVec * 16;
+constexpr int kMaxPrefillGrid = 160;
+constexpr size_t kStreamKBytes = 4096 + 2 * kMaxPrefillGrid * kPartialTileBytes;
+
+size_t prefill_umma_reserved_bytes() { return kStreamKBytes; }
+
+// Stream-K flags and partial tiles (fixed place, so a flag word only ever holds launch epochs),
+// then the FP16 copy of the activations and one FP32 per token.
 size_t prefill_umma_scratch_bytes(int max_M, int /*max_N*/, int max_K) {
     if (max_M <= 16) return 0;
-    return act_bytes(max_M, max_K) + ((size_t)max_M * 4 + 255) / 256 * 256;
+    return kStreamKBytes + act_bytes(max_M, max_K) + ((size_t)max_M * 4 + 255) / 256 * 256;
 }
 
 cudaError_t configure_prefill_umma() {
     return cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
-// scratch: [0, 256) status word (shared with the GEMV kernel), then from `offset` the FP16 activations.
-cudaError_t launch_prefill_umma(const LinearArgs& a, const nvfp4_device_info& dev, void* scratch, size_t scratch_bytes,
+// scratch: [0, 256) status word (shared with the GEMV kernel); from `offset` the stream-K flags
+// (4 KB) and partial tiles, then the FP16 activations and the per-token factors.
+cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t scratch_bytes,
                                 size_t offset, int* launches, cudaStream_t s) {
     const size_t need = prefill_umma_scratch_bytes(a.M, a.N, a.K);
     if (offset + need > scratch_bytes) return cudaErrorMemoryAllocation;
-    char* base = static_cast<char*>(scratch) + offset;
+    char* sk = static_cast<char*>(scratch) + offset;
+    char* base = sk + kStreamKBytes;
     __half* ah = reinterpret_cast<__half*>(base);
     float* unscale = reinterpret_cast<float*>(base + act_bytes(a.M, a.K));
     CUtensorMap tma, tmp, tms;
@@ -416,8 +604,25 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, const nvfp4_device_info& de
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.m_tiles = (a.M + BM - 1) / BM;
     p.n_tiles = (a.N + BN - 1) / BN;
-    int grid = p.m_tiles * p.n_tiles;
-    if (grid > dev.sm_count) grid = dev.sm_count;
+    p.flags = reinterpret_cast<unsigned int*>(sk);
+    p.partials = reinterpret_cast<float4*>(sk + 4096);
+    p.epoch = ++dev.decode_epoch;
+    const int tiles = p.m_tiles * p.n_tiles;
+    int grid = dev.sm_count < kMaxPrefillGrid ? dev.sm_count : kMaxPrefillGrid;
+    const int kstages = a.K / WK;
+    if ((long long)tiles * kstages < grid) grid = tiles * kstages;   // then every tile is split, one stage per CTA
+    // Whole waves of tiles run tile by tile; the tiles left over are split by k over all CTAs when
+    // that is shorter than one more wave of whole tiles.  The split costs about six stage-times
+    // (partial tiles written, flags, reduction), measured on gate_up/down shapes at 64..8192 tokens.
+    p.sk_tiles = 0;
+    const int left = tiles % grid;
+    if (dev.prefill_stream_k && left > 0) {
+        int sk = left;
+        if (sk * kstages < grid) sk += tiles >= grid ? grid : 0;           // every CTA gets at least one stage
+        const long long whole = (long long)((tiles + grid - 1) / grid) * kstages;
+        const long long split = (long long)((tiles - sk) / grid) * kstages + ((long long)sk * kstages + grid - 1) / grid + 6;
+        if (split < whole && (long long)sk * kstages >= grid) p.sk_tiles = sk;
+    }
     prefill_umma_kernel<<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
     if (launches) *launches = 2;
     return cudaGetLastError();

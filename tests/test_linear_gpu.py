@@ -300,6 +300,30 @@ def test_prefill_small(handle, impl, M, N, K):
     assert ob.rel_frobenius(got, want) <= TOL
 
 
+@pytest.mark.parametrize("M,N,K,res", [(300, 15360, 3840, True),    # 180 tiles: one whole wave + 32 tiles split by k
+                                         (64, 5120, 4352, False),      # 20 tiles, each shared by ~7 CTAs
+                                         (40, 1000, 17408, True)])     # ragged N, deep K
+def test_prefill_split_tiles(handle, M, N, K, res):
+    """Tiles left over after whole waves are split along K over all CTAs and summed from FP32
+    partial tiles in a fixed order: same result as the oracle, run-to-run identical bits, and
+    the same as the whole-tile schedule up to FP32 summation order."""
+    packed, scale = util.make_weight(N, K, seed=M + 1, sigma=0.14)
+    A = util.make_bf16((M, K), seed=M + 2)
+    R = util.make_bf16((M, N), seed=M + 3) if res else None
+    got = run_linear(handle, A, packed, scale, 1.0, residual=R)
+    again = run_linear(handle, A, packed, scale, 1.0, residual=R)
+    assert np.array_equal(got, again)
+    handle.set_option("prefill_stream_k", 0)
+    try:
+        whole = run_linear(handle, A, packed, scale, 1.0, residual=R)
+    finally:
+        handle.set_option("prefill_stream_k", 1)
+    assert ob.rel_frobenius(got, whole) <= 5e-4   # FP32 summation order on deep K flips some BF16 roundings
+    want = ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMM, threads=8)
+    assert ob.rel_frobenius(got, want) <= TOL
+    assert handle.device_status() == 0
+
+
 @pytest.mark.parametrize("impl", [1, 2])
 def test_prefill_global_scale(handle, impl):
     """global_scale != 1: the library keeps FP32 block scales for every M (the reference's M<=8
