@@ -242,9 +242,13 @@ def main():
                     help="extra measurements to add to the JSON line")
     ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
     ap.add_argument("--prefill-ms", default="64,256,2048,8192", help="token counts of the prefill section")
+    ap.add_argument("--decode-ms", default="", help="token counts of the decode sweep (default: the five of configs[1]); "
+                                                    "a single value gives a profiler a known launch")
     ap.add_argument("--no-graph", action="store_true", help="time stream launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
+    if args.decode_ms:
+        globals()["DECODE_MS"] = tuple(int(x) for x in args.decode_ms.split(","))
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -323,7 +327,8 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc", "data": "synthetic",
             "config": {"workload": "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + down 5120x17408"
-                                   + (" (SMALL shapes)" if args.small else ""),
+                                   + (" (SMALL shapes)" if args.small else "")
+                                   + (f" (M restricted to {list(DECODE_MS)})" if args.decode_ms else ""),
                        "l2": f"weights rotate over {rot['gate_up'].n}/{rot['down'].n} distinct copies (> 2 x L2)",
                        "global_scale": 1.0, "scale_sigma": 0.02, "seed": 0,
                        "timing": "one CUDA-graph replay of the K steps" if use_graph else "K steps of stream launches",
