@@ -244,6 +244,8 @@ def main():
     ap.add_argument("--prefill-ms", default="64,256,2048,8192", help="token counts of the prefill section")
     ap.add_argument("--decode-ms", default="", help="token counts of the decode sweep (default: the five of configs[1]); "
                                                     "a single value gives a profiler a known launch")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="kernel-selection option set on the handle (nvfp4_set_option), e.g. skinny_min_m=1")
     ap.add_argument("--no-graph", action="store_true", help="time stream launches instead of a CUDA-graph replay")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
@@ -272,6 +274,9 @@ def main():
     if args.small:
         shapes = {"gate_up": (34816 // 4, 5120), "down": (5120, 17408 // 4), "qkv": (7168, 5120), "o": (5120, 6144)}
     h = nvfp4.Handle(0, 1 << 30)
+    for kv in args.option:
+        name, _, val = kv.partition("=")
+        h.set_option(name, int(val))
     stream = torch.cuda.current_stream()
 
     rot = {name: Rotating(*shapes[name], dev, seed=10 * i) for i, name in enumerate(("gate_up", "down"))}
@@ -332,7 +337,8 @@ def main():
                        "l2": f"weights rotate over {rot['gate_up'].n}/{rot['down'].n} distinct copies (> 2 x L2)",
                        "global_scale": 1.0, "scale_sigma": 0.02, "seed": 0,
                        "timing": "one CUDA-graph replay of the K steps" if use_graph else "K steps of stream launches",
-                       "decode_impl": h.get_option("decode_impl"), "prefill_impl": h.get_option("prefill_impl")},
+                       "decode_impl": h.get_option("decode_impl"), "prefill_impl": h.get_option("prefill_impl"),
+                       "options": args.option},
             "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "decode_sweep": sweep}
 
     if "e2e" in sections:

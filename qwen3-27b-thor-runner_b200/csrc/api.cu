@@ -20,6 +20,7 @@ struct nvfp4_handle {
     int decode_impl = 0;
     int prefill_impl = 0;
     int decode_max_m = 16;
+    int skinny_min_m = 17, skinny_max_m = 64;    // token counts routed to the weights-in-TMEM kernel
     unsigned long long launches = 0;
 };
 
@@ -57,6 +58,14 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
+    const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
+    if (fast_path_wanted && a.M >= h->skinny_min_m && a.M <= h->skinny_max_m && skinny_umma_supported(a) &&
+        kDecodeScratchBytes + prefill_umma_reserved_bytes() <= h->workspace_bytes) {
+        int nl = 0;
+        cudaError_t e = launch_skinny_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     if (a.M <= h->decode_max_m) {
         int impl = h->decode_impl;
         const bool fast_ok = decode_mma_supported(a) && decode_mma_fits(a, h->dev);
@@ -198,6 +207,15 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "decode_max_m")) {
         if (value < 0 || value > 16) return NVFP4_E_OPTION;
         h->decode_max_m = value;
+    } else if (!std::strcmp(name, "skinny_min_m")) {
+        if (value < 1 || value > 129) return NVFP4_E_OPTION;
+        h->skinny_min_m = value;
+    } else if (!std::strcmp(name, "skinny_max_m")) {
+        if (value < 0 || value > 128) return NVFP4_E_OPTION;
+        h->skinny_max_m = value;
+    } else if (!std::strcmp(name, "skinny_split_cost")) {
+        if (value < 0 || value > 1000) return NVFP4_E_OPTION;
+        h->dev.skinny_split_cost = value;
     } else if (!std::strcmp(name, "prefill_stream_k")) {
         if (value < 0 || value > 1) return NVFP4_E_OPTION;
         h->dev.prefill_stream_k = value;
@@ -213,6 +231,9 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "prefill_impl")) *value = h->prefill_impl;
     else if (!std::strcmp(name, "decode_max_m")) *value = h->decode_max_m;
     else if (!std::strcmp(name, "prefill_stream_k")) *value = h->dev.prefill_stream_k;
+    else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
+    else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
+    else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;
     else if (!std::strcmp(name, "sm_count")) *value = h->dev.sm_count;
     else return NVFP4_E_OPTION;
     return NVFP4_OK;

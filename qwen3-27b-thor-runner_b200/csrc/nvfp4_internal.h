@@ -27,6 +27,7 @@ struct nvfp4_device_info {
     size_t smem_optin;
     unsigned int decode_epoch;   // bumped per launch; tags the cross-CTA flags in the scratch
     int prefill_stream_k = 1;    // split the tiles left after whole waves by k over all CTAs
+    int skinny_split_cost = 12;  // stage-times charged to splitting row tiles by k in the few-token kernel
 };
 
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
@@ -50,6 +51,9 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
                               cudaStream_t s);
 cudaError_t configure_decode_mma();
 
+// --- act_f16.cu: BF16 activations -> FP16 copy with an exact per-token power-of-two scale; unscale[m] = 1/scale.
+cudaError_t launch_act_to_f16(const void* A, int M, int K, void* out_f16, float* unscale, cudaStream_t s);
+
 // --- prefill_umma.cu: fused dequant + tcgen05 BF16 GEMM with TMEM accumulators.
 bool prefill_umma_supported(const LinearArgs& a);
 size_t prefill_umma_reserved_bytes();   // flags + partial tiles at the start of the kernel's scratch
@@ -59,6 +63,12 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
                                 size_t scratch_bytes, size_t offset, int* launches, cudaStream_t s);
 
 // Sets the per-kernel attributes (dynamic shared memory opt-in) once per device.
+// --- skinny_umma.cu: 1 <= M <= 128, dequantised weights as the TMEM A operand of tcgen05.mma.
+bool skinny_umma_supported(const LinearArgs& a);
+cudaError_t configure_skinny_umma();
+cudaError_t launch_skinny_umma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t scratch_bytes,
+                               size_t offset, int* launches, cudaStream_t s);
+
 cudaError_t configure_kernels(const nvfp4_device_info& dev);
 
 }  // namespace nvfp4

@@ -34,9 +34,12 @@
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
+#include "umma.cuh"
 
 namespace nvfp4 {
 namespace {
+
+using namespace umma;
 
 constexpr int BM = 128;            // tokens per tile   (UMMA M)
 constexpr int BN = 256;            // weight rows per tile (UMMA N)
@@ -70,55 +73,7 @@ struct PrefillParams {
     unsigned int epoch;
 };
 
-// Work of one CTA: first its share of the stream-K region (tiles [0, sk_tiles), cut into
-// (tile, stage) units and split evenly over the CTAs), then whole tiles sk_tiles + blockIdx.x +
-// i * gridDim.x.  The interleaved order keeps the CTAs that share a weight tile in step, so the
-// tile is fetched from HBM once and read from L2 by the others.  Every role walks the same list.
-struct Segment {
-    int tile, ks0, ks1;
-};
-struct Schedule {
-    long long u, u_end;
-    int dp_tile, num_tiles, kstages;
-    __device__ __forceinline__ Schedule(const PrefillParams& p, int kst) {
-        const long long sk_units = (long long)p.sk_tiles * kst;
-        u = (long long)blockIdx.x * sk_units / gridDim.x;
-        u_end = (long long)(blockIdx.x + 1) * sk_units / gridDim.x;
-        dp_tile = p.sk_tiles + blockIdx.x;
-        num_tiles = p.m_tiles * p.n_tiles;
-        kstages = kst;
-    }
-    __device__ __forceinline__ bool next(Segment& s) {
-        if (u < u_end) {
-            s.tile = (int)(u / kstages);
-            s.ks0 = (int)(u % kstages);
-            const long long room = u_end - u;
-            s.ks1 = (kstages - s.ks0) < room ? kstages : s.ks0 + (int)room;
-            u += s.ks1 - s.ks0;
-            return true;
-        }
-        if (dp_tile < num_tiles) {
-            s.tile = dp_tile;
-            s.ks0 = 0;
-            s.ks1 = kstages;
-            dp_tile += gridDim.x;
-            return true;
-        }
-        return false;
-    }
-};
-
 // ---------------------------------------------------------------- tcgen05 helpers
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
-    // K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                              // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
-    return d;
-}
 // kind::f16, A = B = FP16, D = FP32, both operands K-major, M = 128, N = 256.
 constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
@@ -129,39 +84,6 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(ptx::smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Split tiles this CTA holds a part of: [0] the one its span starts inside (partial slot 0),
-// [1] the one its span ends inside (slot 1); -1 = none.
-__device__ __forceinline__ void split_tiles_of_cta(const PrefillParams& p, int kstages, int out[2]) {
-    out[0] = out[1] = -1;
-    const long long sk_units = (long long)p.sk_tiles * kstages;
-    const long long u0 = (long long)blockIdx.x * sk_units / gridDim.x;
-    const long long u1 = (long long)(blockIdx.x + 1) * sk_units / gridDim.x;
-    if (u0 >= u1) return;
-    const int t0 = (int)(u0 / kstages), t1 = (int)((u1 - 1) / kstages);
-    if (u0 % kstages != 0) out[0] = t0;
-    else if (u1 - u0 < kstages) out[1] = t0;
-    if (t1 != t0 && u1 - (long long)t1 * kstages < kstages) out[1] = t1;
-}
-
 // Reduction of one split tile.  Every CTA holding a part of the tile calls this once its own
 // parts are stored: it waits (bounded) for the partial tiles of all P participants, sums them
 // in CTA order over its own 1/P of the tile and writes that part of the output.  All
@@ -169,27 +91,9 @@ __device__ __forceinline__ void split_tiles_of_cta(const PrefillParams& p, int k
 // t = 0..nthreads-1, nthreads a multiple of 128.
 __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int tile, int kstages, int t, int nthreads,
                                                   volatile int* s_abort) {
-    const long long sk_units = (long long)p.sk_tiles * kstages;
-    const long long tile_begin = (long long)tile * kstages, tile_end = tile_begin + kstages;
-    int first = blockIdx.x, last = blockIdx.x;
-    while (first > 0 && (long long)first * sk_units / gridDim.x > tile_begin) --first;
-    while (last + 1 < (int)gridDim.x && (long long)(last + 1) * sk_units / gridDim.x < tile_end) ++last;
-    if ((t & 31) == 0) {
-        const long long t0 = clock64();
-        for (int c = first; c <= last; ++c) {
-            const unsigned int* f = &p.flags[c * 2 + (c == first ? 1 : 0)];   // the first CTA holds the head of the tile
-            while (ptx::ld_acquire_gpu(f) != p.epoch) {
-                if (*s_abort) break;
-                if (clock64() - t0 > ptx::kWaitBudgetClocks) {
-                    *s_abort = 1;
-                    atomicCAS(p.status, 0u, 0x480u);
-                    break;
-                }
-            }
-        }
-    }
-    __syncwarp();
-    if (*s_abort) return;
+    int first, last;
+    split_tile_participants(p.sk_tiles, kstages, tile, first, last);
+    if (!wait_split_tile_flags(p.flags, p.epoch, first, last, t, s_abort, p.status)) return;
     const int P = last - first + 1, me = blockIdx.x - first;
     const int j0 = (int)((long long)me * kPartialVec / P) & ~(BM - 1);
     const int j1 = me + 1 == P ? kPartialVec : ((int)((long long)(me + 1) * kPartialVec / P) & ~(BM - 1));
@@ -266,9 +170,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         s_table[tid] = b | (b << 16);
     }
     if (warp == 1) {   // one warp owns the TMEM allocation: 512 columns = two 128 x 256 FP32 accumulators
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(ptx::smem_u32(s_tmem)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tmem_alloc_512(s_tmem);
     }
     tc_fence_before();
     __syncthreads();
@@ -284,7 +186,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             const uint64_t pol_w = ptx::policy_evict_first(), pol_a = ptx::policy_evict_last();
             int sa = 0, sw = 0;
             uint32_t pa = 0, pw = 0;
-            Schedule sched(p, kstages);
+            Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
             Segment sg;
             while (sched.next(sg)) {
                 const int nt = sg.tile / p.m_tiles, mt = sg.tile % p.m_tiles;
@@ -308,7 +210,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         if (lane == 0) {
             int sa = 0, sb = 0, acc = 0;
             uint32_t pa = 0, pb = 0, pt = 0;
-            Schedule sched(p, kstages);
+            Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
             Segment sg;
             while (sched.next(sg)) {
                 ptx::mbar_wait(&tempty[acc], pt ^ 1u, s_abort, p.status, 0x440u + acc);
@@ -317,7 +219,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 for (int kb = 0; kb < (sg.ks1 - sg.ks0) * (WK / BK); ++kb) {
                     ptx::mbar_wait(&afull[sa], pa, s_abort, p.status, 0x420u + sa);
                     ptx::mbar_wait(&bfull[sb], pb, s_abort, p.status, 0x430u + sb);
-                    tc_fence_after();
+                    // Both operands arrive through shared memory (TMA, or generic stores followed by
+                    // fence.proxy.async before the arrive): no tcgen05 fence is needed per k-block.
                     const uint32_t a_addr = ptx::smem_u32(s_a + sa * kABytes);
                     const uint32_t b_addr = ptx::smem_u32(s_b + sb * kBBytes);
 #pragma unroll
@@ -340,7 +243,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         const int sw7 = row & 7;
         int sw = 0, sb = 0;
         uint32_t pw = 0, pb = 0;
-        Schedule sched(p, kstages);
+        Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
         Segment sg;
         while (sched.next(sg)) {
             for (int ks = sg.ks0; ks < sg.ks1; ++ks) {
@@ -383,7 +286,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         const int te = ew * 32 + lane;                        // 0..127: TMEM lane, token row of the tile
         const long long sk_units = (long long)p.sk_tiles * kstages;
         int pend[2] = {-1, -1};                               // split tiles whose partial this CTA has stored
-        Schedule sched(p, kstages);
+        Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
         Segment sg;
         bool more = sched.next(sg);
         while (more) {
@@ -473,78 +376,16 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        tmem_dealloc_512(tmem_base);
     }
     if (all_reduce) {
         // Every tile was split and nothing else is left to do: all 16 warps reduce.
         int split[2];
-        split_tiles_of_cta(p, kstages, split);
+        split_tiles_of_cta(p.sk_tiles, kstages, split);
 #pragma unroll
         for (int w = 0; w < 2; ++w)
             if (split[w] >= 0) reduce_split_tile(p, split[w], kstages, tid, kThreads, s_abort);
     }
-}
-
-// BF16 activations -> FP16 scaled by an exact per-token power of two; one CTA per token.
-__global__ void __launch_bounds__(256)
-act_to_f16_kernel(const __nv_bfloat16* __restrict__ A, __half* __restrict__ out, float* __restrict__ unscale, int K) {
-    __shared__ unsigned int s_max;
-    const int m = blockIdx.x;
-    const uint4* src = reinterpret_cast<const uint4*>(A + (size_t)m * K);
-    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)m * K);
-    if (threadIdx.x == 0) s_max = 0u;
-    __syncthreads();
-    unsigned int amax = 0;
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
-        const uint4 x = __ldg(src + i);
-        const uint32_t v[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) amax = max(amax, max(v[q] & 0x7FFFu, (v[q] >> 16) & 0x7FFFu));
-    }
-    amax = __reduce_max_sync(0xffffffffu, amax);
-    if ((threadIdx.x & 31) == 0 && amax) atomicMax(&s_max, amax);
-    __syncthreads();
-    int se = 268 - (int)(s_max >> 7);      // scale = 2^(141 - biased exponent): largest -> exponent 14
-    se = se < 1 ? 1 : (se > 254 ? 254 : se);
-    const float sc = __uint_as_float((uint32_t)se << 23);
-    if (threadIdx.x == 0) unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
-        const uint4 x = __ldg(src + i);
-        const uint32_t v[4] = {x.x, x.y, x.z, x.w};
-        uint32_t y[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            y[q] = ptx::pack_f16x2(__uint_as_float(v[q] << 16) * sc, __uint_as_float(v[q] & 0xFFFF0000u) * sc);
-        dst[i] = make_uint4(y[0], y[1], y[2], y[3]);
-    }
-}
-
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode() {
-    static EncodeFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeFn>(p);
-    }
-    return fn;
-}
-
-bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int esize, const void* base, uint64_t cols, uint64_t rows,
-              uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
-    EncodeFn enc = get_encode();
-    if (!enc) return false;
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * (uint64_t)esize};
-    const cuuint32_t box[2] = {box_cols, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 size_t act_bytes(int M, int K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }
@@ -592,8 +433,7 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
         !make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, BN,
                   CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
-    act_to_f16_kernel<<<a.M, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(a.A), ah, unscale, a.K);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_act_to_f16(a.A, a.M, a.K, ah, unscale, s);
     if (e != cudaSuccess) return e;
     PrefillParams p{};
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
@@ -631,6 +471,7 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
 cudaError_t configure_kernels(const nvfp4_device_info&) {
     cudaError_t e = configure_decode_mma();
     if (e == cudaSuccess) e = configure_prefill_umma();
+    if (e == cudaSuccess) e = configure_skinny_umma();
     return e;
 }
 
