@@ -22,23 +22,34 @@ def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
         mlps = make_mlp(M)
         X = torch.randn((M, H), device=dev).to(torch.bfloat16)
         Y = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
-        for i in range(3):
-            mlps[i % len(mlps)].forward(X, M, Y)
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(3, steps if M <= 256 else min(steps, 5))
-        e0.record()
-        for i in range(reps):
-            mlps[i % len(mlps)].forward(X, M, Y)
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
-        if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        out.append({"M": M, "ms": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1)})
+        def timed():
+            for i in range(3):
+                mlps[i % len(mlps)].forward(X, M, Y)
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(3, steps if M <= 256 else min(steps, 5))
+            e0.record()
+            for i in range(reps):
+                mlps[i % len(mlps)].forward(X, M, Y)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+            if dist is not None:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        ms = timed()
+        row = {"M": M, "ms": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1),
+               "reduction": "fused peer-memory kernel" if (M <= 16 and world > 1) else ("nccl all-reduce" if world > 1 else "none")}
+        if M <= 16 and world > 1:      # the same step with the library collective, for comparison
+            for m in mlps:
+                m.set_fused(False)
+            row["ms_nccl_allreduce"] = round(timed(), 4)
+            for m in mlps:
+                m.set_fused(True)
+        out.append(row)
         for m in mlps:
             m.close()
         del mlps
@@ -76,6 +87,7 @@ def main(args, world, rank, local_rank):
             gp, gs = bench.device_weight(2 * I, H, seed=100 + 2 * c, dev=dev)
             dp, ds = bench.device_weight(H, I, seed=101 + 2 * c, dev=dev)
             out.append(nvfp4_tp.TpMlp(h, comm, H, I, gp, gs, 1.0, dp, ds, 1.0, max_M))
+            out[-1].enable_p2p(dist, dev)          # M <= 16 sums through peer memory instead of NCCL
             del gp, gs, dp, ds
         torch.cuda.empty_cache()
         return out
@@ -94,13 +106,28 @@ def main(args, world, rank, local_rank):
         small = nvfp4_tp.TpMlp(h, comm, h_, i_, util.to_dev(gu_p).to(dev), util.to_dev(gu_s).to(dev), 1.0,
                                util.to_dev(dn_p).to(dev), util.to_dev(dn_s).to(dev), 1.0, m_)
         out = util.to_dev(Rs).to(dev)
-        small.forward(util.to_dev(Xs).to(dev), m_, out, residual=out)
+        small.forward(util.to_dev(Xs).to(dev), m_, out, residual=out)            # NCCL all-reduce of BF16 partials
+        small.enable_p2p(dist, dev)
+        out_f = util.to_dev(Rs).to(dev)
+        small.forward(util.to_dev(Xs).to(dev), m_, out_f, residual=out_f)        # fused FP32 push-and-sum
+        out_f2 = util.to_dev(Rs).to(dev)
+        small.forward(util.to_dev(Xs).to(dev), m_, out_f2, residual=out_f2)
         torch.cuda.synchronize()
+        xstatus = small.status()
+        same = torch.tensor([int(torch.equal(out_f, out_f2))], device=dev)
+        gathered = [torch.empty_like(out_f) for _ in range(world)]
+        dist.all_gather(gathered, out_f)
         if rank == 0:
-            want = ob.tp_mlp(Xs, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs, partial_bf16=True)
-            parity = {"rel_frobenius_vs_partition_aware_oracle": float(ob.rel_frobenius(util.to_host_u16(out), want)),
-                      "rel_frobenius_vs_unsplit_oracle": float(ob.rel_frobenius(
-                          util.to_host_u16(out), ob.mlp(Xs, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs)))}
+            want_bf16 = ob.tp_mlp(Xs, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs, partial_bf16=True)
+            want_f32 = ob.tp_mlp(Xs, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs, partial_bf16=False)
+            unsplit = ob.mlp(Xs, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs)
+            parity = {"nccl_path_vs_partition_aware_oracle_bf16_partials": float(ob.rel_frobenius(util.to_host_u16(out), want_bf16)),
+                      "nccl_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out), unsplit)),
+                      "fused_path_vs_partition_aware_oracle_f32_partials": float(ob.rel_frobenius(util.to_host_u16(out_f), want_f32)),
+                      "fused_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out_f), unsplit)),
+                      "fused_path_bitwise_repeatable": bool(same.item()),
+                      "fused_path_identical_on_all_ranks": all(torch.equal(g, gathered[0]) for g in gathered),
+                      "exchange_status": int(xstatus)}
         small.close()
     except Exception as e:  # the oracle is a checker only; the timing below does not depend on it
         parity = {"error": repr(e)}
@@ -131,7 +158,7 @@ def main(args, world, rank, local_rank):
     e1.record()
     torch.cuda.synchronize()
     dist.barrier()
-    launches = h.launch_count() - l0
+    launches = h.launch_count() - l0 + args.steps * len(bench.DECODE_MS)   # + one exchange kernel per forward
     t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())

@@ -116,6 +116,14 @@ int nvfp4_linear_decode_noalloc(const void* A_bf16, int M, const uint8_t* packed
                                 float global_scale, int N, int K, const void* residual_bf16_or_null,
                                 void* C_bf16, nvfp4_stream_t stream);
 
+/* C_f32[M,N] = A * W^T as unrounded FP32 (no residual, no BF16 rounding): a partial result for
+ * callers that sum several of them before rounding once, e.g. the K-split down projection of
+ * the tensor-parallel MLP.  No reference counterpart (the reference is single-GPU and always
+ * rounds, src/engine/dense_gemm_fp4_sm110.cu:137-140).  M <= 16 and K % 256 == 0, otherwise
+ * NVFP4_E_LIMIT. */
+int nvfp4_linear_f32(nvfp4_handle* h, const void* A_bf16, int M, const uint8_t* packed, const uint8_t* scale_ue4m3,
+                     float global_scale, int N, int K, void* C_f32, nvfp4_stream_t stream);
+
 /* Two linears sharing A: C1 = A*W1^T, C2 = A*W2^T, both [N,K].
  * Replaces invoke_fp4_dual_gemv (:395-416), generalised to any M. */
 int nvfp4_linear_dual(nvfp4_handle* h, const void* A_bf16, int M,

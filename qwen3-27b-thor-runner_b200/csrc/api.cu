@@ -58,6 +58,13 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
+    if (a.out_f32) {   // only the GEMV kernel stores unrounded sums
+        if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
+        int nl = 0;
+        cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
     if (fast_path_wanted && a.M >= h->skinny_min_m && a.M <= h->skinny_max_m && skinny_umma_supported(a) &&
         kDecodeScratchBytes + prefill_umma_reserved_bytes() <= h->workspace_bytes) {
@@ -260,6 +267,20 @@ int nvfp4_linear(nvfp4_handle* h, const void* A, int M, const uint8_t* packed, c
                  float global_scale, int N, int K, const void* residual, void* C, nvfp4_stream_t stream) {
     if (int e = validate_linear(h, A, M, packed, scale, global_scale, N, K, residual, C)) return e;
     LinearArgs a{A, packed, scale, 1.0f / global_scale, residual, C, M, N, K};
+    return run_linear(h, a, stream);
+}
+
+int nvfp4_linear_f32(nvfp4_handle* h, const void* A, int M, const uint8_t* packed, const uint8_t* scale,
+                     float global_scale, int N, int K, void* C_f32, nvfp4_stream_t stream) {
+    if (int e = validate_linear(h, A, M, packed, scale, global_scale, N, K, nullptr, C_f32)) return e;
+    if (M == 0) return NVFP4_OK;
+    {   // the output is twice as large as the BF16 one validate_linear assumed
+        const char* a0 = static_cast<const char*>(A);
+        const char* c0 = static_cast<const char*>(C_f32);
+        if (a0 < c0 + (size_t)M * N * 4 && c0 < a0 + (size_t)M * K * 2) return NVFP4_E_ALIAS;
+    }
+    LinearArgs a{A, packed, scale, 1.0f / global_scale, nullptr, C_f32, M, N, K};
+    a.out_f32 = true;
     return run_linear(h, a, stream);
 }
 

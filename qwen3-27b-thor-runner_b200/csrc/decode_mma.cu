@@ -77,6 +77,7 @@ struct DecodeParams {
     int stages;          // ring depth (each stage holds up to two half-units)
     int act_slots;       // activation slots (k-chunks of 256) held in shared memory
     int act_all;         // 1 = slot index is the k-chunk, 0 = position in the CTA's span
+    int out_f32;         // C is FP32 [M,N]: store the scaled sum unrounded (partial results for a later reduction)
     unsigned int epoch;
 };
 
@@ -453,6 +454,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     if (mm[i] >= p.M || n >= p.N) continue;
                     float x = (v[i] + pre[i]) * p.inv_gs;
                     const size_t o = (size_t)mm[i] * p.N + n;
+                    if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
                     if (p.residual) x += __bfloat162float(p.residual[o]);
                     p.C[o] = __float2bfloat16_rn(x);
                 }
@@ -527,6 +529,7 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     p.scratch = static_cast<unsigned char*>(scratch);
     p.inv_gs = a.inv_gs;
     p.M = m; p.N = a.N; p.K = a.K;
+    p.out_f32 = a.out_f32 ? 1 : 0;
     p.kchunks = a.K / kKC;
     const long long tiles = (a.N + kRT - 1) / kRT;
     p.units = (int)(tiles * p.kchunks);
@@ -584,7 +587,7 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         LinearArgs b = a;
         const int m = a.M - m0 < per ? a.M - m0 : per;
         b.A = static_cast<const char*>(a.A) + (size_t)m0 * a.K * 2;
-        b.C = static_cast<char*>(a.C) + (size_t)m0 * a.N * 2;
+        b.C = static_cast<char*>(a.C) + (size_t)m0 * a.N * (a.out_f32 ? 4 : 2);
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DecodePlan pl;
         if (!plan_decode(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;

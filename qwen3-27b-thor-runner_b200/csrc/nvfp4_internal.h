@@ -16,8 +16,9 @@ struct LinearArgs {
     const uint8_t* scale;   // [N,K/16]
     float inv_gs;           // 1.0f / global_scale, computed on the host in FP32
     const void* residual;   // [M,N] bf16 or nullptr
-    void* C;                // [M,N] bf16
+    void* C;                // [M,N] bf16 (fp32 when out_f32)
     int M, N, K;
+    bool out_f32 = false;   // unrounded FP32 sums, no residual: partial results a caller reduces itself
 };
 
 struct nvfp4_device_info {

@@ -1,6 +1,11 @@
-// Tensor-parallel NVFP4 MLP: per-rank shards, two linears + SwiGLU from the core library, one
-// NCCL all-reduce of the BF16 down-projection partials.  Host-side orchestration only; the
-// kernels are the core library's.
+// Tensor-parallel NVFP4 MLP: per-rank shards, two linears + SwiGLU from the core library, and
+// the sum of the down-projection partials over the ranks:
+//   * up to 16 tokens, once the ranks have exchanged their buffer handles: one kernel per rank
+//     pushes the rank's FP32 partial into every peer's exchange buffer with plain peer stores
+//     over NVLink, raises a flag there, waits (bounded) for the peers' flags on its own buffer,
+//     adds the P partials in rank order in FP32, adds the residual and rounds once.  No
+//     library collective, no multicast, deterministic, one rounding.
+//   * otherwise one NCCL all-reduce of the BF16 partials, the residual added in FP32 after it.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <nccl.h>
@@ -22,9 +27,112 @@ struct nvfp4_tp_mlp {
     float gu_gs = 1.0f, dn_gs = 1.0f;
     void *gate_up_out = nullptr, *act = nullptr;      // [max_M, 2*Ip], [max_M, Kp] (pad columns stay zero)
     void* res_copy = nullptr;                          // [max_M, H]: the residual of an in-place call
+    // Peer exchange (fused small-M reduction).  xbuf: this rank's buffer; peer[q]: rank q's buffer
+    // as mapped into this process (peer[rank] == xbuf).
+    unsigned char* xbuf = nullptr;
+    unsigned char* peer[NVFP4_TP_MAX_WORLD] = {};
+    float* partial = nullptr;                          // [kFusedMaxM, H] FP32: this rank's down-projection partial
+    bool attached = false;
+    int fused = 1;
 };
 
 namespace {
+
+// ---- peer exchange buffer layout (identical on every rank)
+constexpr int kFusedMaxM = 16;           // tokens the fused reduction takes (the GEMV regime)
+constexpr int kXCtas = 32;               // CTAs of the exchange kernel = flag columns
+constexpr size_t kXStatusOff = 0;        // sticky status word (0 = no wait ever ran out)
+constexpr size_t kXEpochOff = 64;        // launch counter, advanced by the kernel itself (graph replays stay valid)
+constexpr size_t kXDoneOff = 128;        // CTAs finished in the current launch
+constexpr size_t kXFlagsOff = 256;       // [2 sets][world <= 8][kXCtas] epoch flags, written by the peers
+constexpr size_t kXSlotsOff = 4096;      // [2 sets][world][kFusedMaxM * H] FP32 partials, written by the peers
+constexpr long long kXWaitClocks = 2000000000LL;   // about a second
+
+inline size_t xbuf_bytes(int world, int H) { return kXSlotsOff + 2ull * world * kFusedMaxM * H * 4; }
+
+struct ExchangeParams {
+    unsigned char* peer[NVFP4_TP_MAX_WORLD];
+    const float* partial;            // this rank's [M, H] FP32 partial
+    const __nv_bfloat16* residual;   // or null
+    __nv_bfloat16* out;
+    int rank, world, n4, H;          // n4 = M * H / 4
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// One launch per rank, the same grid on every rank.  CTA c owns the float4 elements c*256+t,
+// +gridDim*256, ...: it pushes them to slot [set][rank] of every rank's buffer, raises flag
+// [set][rank][c] there, waits for flags [set][q][c] of all ranks q on its own buffer and sums.
+// Only CTAs with the same index on different GPUs wait for each other; the two sets alternate
+// per launch, so a fast rank's next push never lands on data a slow rank still reads.
+__global__ void __launch_bounds__(256) exchange_reduce_kernel(const ExchangeParams p) {
+    __shared__ int s_fail;
+    unsigned char* mine = p.peer[p.rank];
+    const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(mine + kXEpochOff) + 1u;
+    const unsigned int set = epoch & 1u;
+    const size_t slot_floats = (size_t)kFusedMaxM * p.H;
+    const int tid = threadIdx.x, c = blockIdx.x;
+    if (tid == 0) s_fail = 0;
+    // push: 16-byte peer stores, consecutive threads -> consecutive addresses
+    for (int i = c * 256 + tid; i < p.n4; i += gridDim.x * 256) {
+        const float4 v = reinterpret_cast<const float4*>(p.partial)[i];
+        for (int q = 0; q < p.world; ++q) {
+            float4* dst = reinterpret_cast<float4*>(p.peer[q] + kXSlotsOff) + ((size_t)set * p.world + p.rank) * (slot_floats / 4);
+            dst[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.world) {
+        unsigned int* f = reinterpret_cast<unsigned int*>(p.peer[tid] + kXFlagsOff) + ((size_t)set * NVFP4_TP_MAX_WORLD + p.rank) * kXCtas + c;
+        st_release_sys(f, epoch);
+        // bounded wait for rank `tid`'s flag on this rank's own buffer
+        const unsigned int* w = reinterpret_cast<const unsigned int*>(mine + kXFlagsOff) + ((size_t)set * NVFP4_TP_MAX_WORLD + tid) * kXCtas + c;
+        const long long t0 = clock64();
+        while (ld_acquire_sys(w) != epoch) {
+            if (clock64() - t0 > kXWaitClocks) {
+                s_fail = 1;
+                atomicCAS(reinterpret_cast<unsigned int*>(mine + kXStatusOff), 0u, 0x700u + (unsigned)tid);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (!s_fail) {
+        const float4* slots = reinterpret_cast<const float4*>(mine + kXSlotsOff) + (size_t)set * p.world * (slot_floats / 4);
+        for (int i = c * 256 + tid; i < p.n4; i += gridDim.x * 256) {
+            float4 s = __ldcg(slots + i);                       // rank 0 first, then 1, 2, ...: the same order on every rank
+            for (int q = 1; q < p.world; ++q) {
+                const float4 x = __ldcg(slots + (size_t)q * (slot_floats / 4) + i);
+                s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+            }
+            if (p.residual) {
+                const uint2 r = reinterpret_cast<const uint2*>(p.residual)[i];
+                s.x += __uint_as_float(r.x << 16); s.y += __uint_as_float(r.x & 0xFFFF0000u);
+                s.z += __uint_as_float(r.y << 16); s.w += __uint_as_float(r.y & 0xFFFF0000u);
+            }
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+            reinterpret_cast<uint2*>(p.out)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        }
+    }
+    // the last CTA to finish advances the launch counter for the next launch
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        unsigned int* done = reinterpret_cast<unsigned int*>(mine + kXDoneOff);
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            *done = 0u;
+            *reinterpret_cast<volatile unsigned int*>(mine + kXEpochOff) = epoch;
+        }
+    }
+}
 
 // out = bf16(float(out) + float(residual)), 8 elements per thread; n % 8 == 0 (H % 256 == 0).
 __global__ void __launch_bounds__(256) add_residual_kernel(uint4* out, const uint4* residual, long long n8) {
@@ -85,6 +193,9 @@ int nvfp4_tp_mlp_destroy(nvfp4_tp_mlp* m) {
     if (!m) return NVFP4_E_NULL;
     cudaFree(m->gu_packed); cudaFree(m->gu_scale); cudaFree(m->dn_packed); cudaFree(m->dn_scale);
     cudaFree(m->gate_up_out); cudaFree(m->act); cudaFree(m->res_copy);
+    for (int q = 0; q < NVFP4_TP_MAX_WORLD; ++q)
+        if (m->peer[q] && m->peer[q] != m->xbuf) cudaIpcCloseMemHandle(m->peer[q]);
+    cudaFree(m->xbuf); cudaFree(m->partial);
     delete m;
     return NVFP4_OK;
 }
@@ -95,7 +206,7 @@ int nvfp4_tp_mlp_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int I, cons
     if (!h || !comm || !gup || !gus || !dnp || !dns || !out) return NVFP4_E_NULL;
     *out = nullptr;
     const int P = comm->world, r = comm->rank;
-    if (H <= 0 || I <= 0 || max_M <= 0 || (H % 256) != 0 || (I % (16 * P)) != 0) return NVFP4_E_SHAPE;
+    if (H <= 0 || I <= 0 || max_M <= 0 || (H % 256) != 0 || (I % (16 * P)) != 0 || P > NVFP4_TP_MAX_WORLD) return NVFP4_E_SHAPE;
     nvfp4_tp_mlp* m = new nvfp4_tp_mlp();
     m->h = h; m->comm = comm; m->H = H; m->I = I; m->max_M = max_M;
     m->Ip = I / P;
@@ -111,6 +222,9 @@ int nvfp4_tp_mlp_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int I, cons
     alloc(&m->gate_up_out, (size_t)max_M * gu_rows * 2);
     alloc(&m->act, (size_t)max_M * m->Kp * 2);
     alloc(&m->res_copy, (size_t)max_M * H * 2);
+    alloc((void**)&m->xbuf, xbuf_bytes(P, H));
+    alloc((void**)&m->partial, (size_t)kFusedMaxM * H * 4);
+    if (e == cudaSuccess) e = cudaMemset(m->xbuf, 0, xbuf_bytes(P, H));
     if (e == cudaSuccess) e = cudaMemset(m->dn_packed, 0, (size_t)H * m->Kp / 2);   // zero codes and zero scales
     if (e == cudaSuccess) e = cudaMemset(m->dn_scale, 0, (size_t)H * m->Kp / 16);   // in the K padding
     if (e == cudaSuccess) e = cudaMemset(m->act, 0, (size_t)max_M * m->Kp * 2);     // pad activations stay zero
@@ -123,6 +237,7 @@ int nvfp4_tp_mlp_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int I, cons
     // down columns [r*Ip, (r+1)*Ip) of every row, into rows of Kp elements.
     if (e == cudaSuccess) e = cudaMemcpy2D(m->dn_packed, (size_t)m->Kp / 2, dnp + (size_t)r * m->Ip / 2, (size_t)I / 2, (size_t)m->Ip / 2, H, cudaMemcpyDeviceToDevice);
     if (e == cudaSuccess) e = cudaMemcpy2D(m->dn_scale, (size_t)m->Kp / 16, dns + (size_t)r * m->Ip / 16, (size_t)I / 16, (size_t)m->Ip / 16, H, cudaMemcpyDeviceToDevice);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();   // the zeroed exchange buffer must be in place before a peer can push to it
     if (e != cudaSuccess) { nvfp4_tp_mlp_destroy(m); return (int)e; }
     *out = m;
     return NVFP4_OK;
@@ -144,7 +259,27 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     const char* gate = static_cast<const char*>(m->gate_up_out);
     st = nvfp4_swiglu_strided(m->h, gate, gate + (size_t)m->Ip * 2, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
     if (st) return st;
-    if (P == 1) return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
+    if (P == 1 && !(m->attached && m->fused))
+        return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
+    if (m->attached && m->fused && M <= kFusedMaxM) {
+        // FP32 partial -> peers -> ordered FP32 sum + residual -> one rounding; `out` may alias the
+        // residual (every element is read and written by the same thread).
+        st = nvfp4_linear_f32(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, m->partial, s);
+        if (st == NVFP4_OK) {
+            ExchangeParams xp{};
+            for (int q = 0; q < P; ++q) xp.peer[q] = m->peer[q];
+            xp.partial = m->partial;
+            xp.residual = static_cast<const __nv_bfloat16*>(residual);
+            xp.out = static_cast<__nv_bfloat16*>(out);
+            xp.rank = m->comm->rank; xp.world = P; xp.H = m->H;
+            xp.n4 = M * m->H / 4;
+            int grid = (xp.n4 + 255) / 256;
+            if (grid > kXCtas) grid = kXCtas;
+            exchange_reduce_kernel<<<grid, 256, 0, s>>>(xp);
+            return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_TP;
+        }
+        if (st != NVFP4_E_LIMIT) return st;      // a shape the FP32 GEMV does not take: use the collective below
+    }
     // The partials travel without the residual (a partial rounded to BF16 next to a residual ten
     // times its size would lose its low bits); it is added once, in FP32, after the sum.
     const void* res_src = residual;
@@ -165,6 +300,48 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
         if (cudaGetLastError() != cudaSuccess) return NVFP4_E_TP;
     }
     return NVFP4_OK;
+}
+
+int nvfp4_tp_mlp_p2p_handle(nvfp4_tp_mlp* m, void* out) {
+    if (!m || !out) return NVFP4_E_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == NVFP4_TP_P2P_HANDLE_BYTES, "IPC handle size");
+    cudaIpcMemHandle_t hd;
+    if (cudaIpcGetMemHandle(&hd, m->xbuf) != cudaSuccess) return NVFP4_E_TP;
+    std::memcpy(out, &hd, sizeof hd);
+    return NVFP4_OK;
+}
+
+int nvfp4_tp_mlp_p2p_attach(nvfp4_tp_mlp* m, const void* handles) {
+    if (!m) return NVFP4_E_NULL;
+    if (m->attached) return NVFP4_E_TP;
+    const int P = m->comm->world, r = m->comm->rank;
+    if (P > 1 && !handles) return NVFP4_E_NULL;
+    for (int q = 0; q < P; ++q) {
+        if (q == r) { m->peer[q] = m->xbuf; continue; }
+        cudaIpcMemHandle_t hd;
+        std::memcpy(&hd, static_cast<const char*>(handles) + (size_t)q * NVFP4_TP_P2P_HANDLE_BYTES, sizeof hd);
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, hd, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            for (int k = 0; k < q; ++k)
+                if (k != r && m->peer[k]) { cudaIpcCloseMemHandle(m->peer[k]); m->peer[k] = nullptr; }
+            return NVFP4_E_TP;
+        }
+        m->peer[q] = static_cast<unsigned char*>(ptr);
+    }
+    m->attached = true;
+    return NVFP4_OK;
+}
+
+int nvfp4_tp_mlp_set_fused(nvfp4_tp_mlp* m, int on) {
+    if (!m) return NVFP4_E_NULL;
+    m->fused = on ? 1 : 0;
+    return NVFP4_OK;
+}
+
+int nvfp4_tp_mlp_status(nvfp4_tp_mlp* m, unsigned int* status) {
+    if (!m || !status) return NVFP4_E_NULL;
+    if (cudaDeviceSynchronize() != cudaSuccess) return NVFP4_E_TP;
+    return cudaMemcpy(status, m->xbuf + kXStatusOff, 4, cudaMemcpyDeviceToHost) == cudaSuccess ? NVFP4_OK : NVFP4_E_TP;
 }
 
 }  // extern "C"

@@ -31,6 +31,7 @@ SIGNATURES = {
                              c_void_p, c_void_p, c_void_p]),
     "nvfp4_linear_decode_noalloc": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
                                             c_void_p, c_void_p]),
+    "nvfp4_linear_f32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
@@ -141,6 +142,10 @@ class Handle:
         v = ctypes.c_uint()
         self._check(self.lib.nvfp4_device_status(self.h, ctypes.byref(v)))
         return v.value
+
+    def linear_f32(self, A, M, packed, scale, global_scale, N, K, C_f32, stream=None):
+        self._check(self.lib.nvfp4_linear_f32(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,
+                                              _ptr(C_f32), _stream(stream)))
 
     def linear(self, A, M, packed, scale, global_scale, N, K, C, residual=None, stream=None, check=True):
         st = self.lib.nvfp4_linear(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,

@@ -12,6 +12,7 @@ import nvfp4
 _HERE = os.path.dirname(os.path.abspath(__file__))
 TP_LIB_PATH = os.path.join(_HERE, "lib", "libnvfp4_b200_tp.so")
 UNIQUE_ID_BYTES = 128
+P2P_HANDLE_BYTES = 64
 
 c_void_p, c_int, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
@@ -24,6 +25,10 @@ TP_SIGNATURES = {
     "nvfp4_tp_mlp_destroy": (c_int, [c_void_p]),
     "nvfp4_tp_mlp_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_tp_mlp_shard_bytes": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
+    "nvfp4_tp_mlp_p2p_handle": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_tp_mlp_p2p_attach": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_tp_mlp_set_fused": (c_int, [c_void_p, c_int]),
+    "nvfp4_tp_mlp_status": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint)]),
 }
 
 _lib = None
@@ -116,6 +121,43 @@ class TpMlp:
                                            out.data_ptr(), nvfp4._stream(stream))
         if st:
             raise nvfp4.Nvfp4Error(st)
+
+    def p2p_handle(self):
+        buf = ctypes.create_string_buffer(P2P_HANDLE_BYTES)
+        st = self.lib.nvfp4_tp_mlp_p2p_handle(self.m, buf)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        return bytes(buf.raw)
+
+    def p2p_attach(self, handles):
+        """handles: the ranks' p2p_handle() bytes concatenated in rank order (None for world 1).
+        Afterwards forward() sums up to 16 tokens with the fused peer-memory kernel."""
+        buf = None if handles is None else ctypes.create_string_buffer(bytes(handles), len(handles))
+        st = self.lib.nvfp4_tp_mlp_p2p_attach(self.m, buf)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def enable_p2p(self, dist=None, device=None):
+        """Collective: exchange the buffer handles over torch.distributed and attach."""
+        if dist is None or dist.get_world_size() == 1:
+            return self.p2p_attach(None)
+        import torch
+        mine = torch.tensor(list(self.p2p_handle()), dtype=torch.uint8, device=device)
+        allh = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(allh, mine)
+        self.p2p_attach(b"".join(bytes(t.cpu().tolist()) for t in allh))
+
+    def set_fused(self, on):
+        st = self.lib.nvfp4_tp_mlp_set_fused(self.m, 1 if on else 0)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def status(self):
+        v = ctypes.c_uint()
+        st = self.lib.nvfp4_tp_mlp_status(self.m, ctypes.byref(v))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        return v.value
 
     def shard_bytes(self):
         v = ctypes.c_size_t()

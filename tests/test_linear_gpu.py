@@ -437,3 +437,54 @@ def test_full_size_properties(handle, N, K):
     hp, hs = packed.cpu().numpy(), scale.cpu().numpy()
     sub = ob.linear(A, np.ascontiguousarray(hp[rows]), np.ascontiguousarray(hs[rows]), 1.0, mode=ob.GEMV)
     assert ob.rel_frobenius(np.ascontiguousarray(h1[:, rows]), sub) <= TOL
+
+
+# ---------------------------------------------------------------- FP32 partial output + fused TP reduction (one rank)
+
+def test_linear_f32_matches_bf16_path(handle):
+    """nvfp4_linear_f32 stores the same sums as nvfp4_linear, without the final rounding."""
+    import torch
+    M, N, K = 5, 640, 1024
+    packed, scale = util.make_weight(N, K, seed=31)
+    A = util.make_bf16((M, K), seed=32)
+    dC = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    handle.linear_f32(util.to_dev(A), M, util.to_dev(packed), util.to_dev(scale), 2.0, N, K, dC)
+    torch.cuda.synchronize()
+    got32 = dC.cpu().numpy()
+    got16 = run_linear(handle, A, packed, scale, 2.0)
+    assert np.array_equal(ob.f32_to_bf16(got32), got16)
+    with pytest.raises(nvfp4.Nvfp4Error):     # beyond the GEMV regime
+        handle.linear_f32(util.to_dev(util.make_bf16((17, K), seed=1)), 17, util.to_dev(packed), util.to_dev(scale), 1.0, N, K,
+                          torch.zeros((17, N), dtype=torch.float32, device="cuda"))
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_tp_mlp_fused_single_rank(handle, M):
+    """World of one: the fused push-and-sum kernel (self-push, own flag) must give what the plain
+    path gives, with and without an in-place residual."""
+    import torch
+    import nvfp4_tp
+    H, I = 512, 768
+    gu_p, gu_s = util.make_weight(2 * I, H, seed=41)
+    dn_p, dn_s = util.make_weight(H, I, seed=42)
+    X, R = util.make_bf16((M, H), seed=43), util.make_bf16((M, H), seed=44)
+    comm = nvfp4_tp.Comm(None, 0, 1)
+    mlp = nvfp4_tp.TpMlp(handle, comm, H, I, util.to_dev(gu_p), util.to_dev(gu_s), 1.0, util.to_dev(dn_p), util.to_dev(dn_s), 1.0, 16)
+    try:
+        plain = util.to_dev(R)
+        mlp.forward(util.to_dev(X), M, plain, residual=plain)
+        mlp.enable_p2p()
+        outs = []
+        for _ in range(3):                       # both flag sets and the launch counter get exercised
+            fused = util.to_dev(R)
+            mlp.forward(util.to_dev(X), M, fused, residual=fused)
+            torch.cuda.synchronize()
+            outs.append(util.to_host_u16(fused))
+        assert mlp.status() == 0
+        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+        assert np.array_equal(outs[0], util.to_host_u16(plain))
+        want = ob.mlp(X, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R)
+        assert ob.rel_frobenius(outs[0], want) <= TOL
+    finally:
+        mlp.close()
+        comm.close()
