@@ -22,31 +22,45 @@ def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
         mlps = make_mlp(M)
         X = torch.randn((M, H), device=dev).to(torch.bfloat16)
         Y = torch.empty((M, H), dtype=torch.bfloat16, device=dev)
+        state = {"i": 0}
+
+        def one():
+            state["i"] = (state["i"] + 1) % len(mlps)
+            mlps[state["i"]].forward(X, M, Y)
+
         def timed():
-            for i in range(3):
-                mlps[i % len(mlps)].forward(X, M, Y)
+            """Device time per forward, max over ranks.  Up to 256 tokens the forwards are captured
+            in one CUDA graph (a forward is shorter than the host's time to issue its launches);
+            if the capture is refused the launches are timed on the stream instead."""
+            import bench
+            for _ in range(3):
+                one()
             torch.cuda.synchronize()
             if dist is not None:
                 dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             reps = max(3, steps if M <= 256 else min(steps, 5))
-            e0.record()
-            for i in range(reps):
-                mlps[i % len(mlps)].forward(X, M, Y)
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+            mode = "stream"
+            ms = None
+            if M <= 256:
+                try:
+                    ms = bench.time_region(one, reps, torch, graph=True)
+                    mode = "graph"
+                except Exception:
+                    torch.cuda.synchronize()
+            if ms is None:
+                ms = bench.time_region(one, reps, torch, graph=False)
+            t = torch.tensor([ms], device=dev)
             if dist is not None:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
+            return float(t.item()), mode
 
-        ms = timed()
-        row = {"M": M, "ms": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1),
+        ms, mode = timed()
+        row = {"M": M, "ms": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1), "timing": mode,
                "reduction": "fused peer-memory kernel" if (M <= 16 and world > 1) else ("nccl all-reduce" if world > 1 else "none")}
         if M <= 16 and world > 1:      # the same step with the library collective, for comparison
             for m in mlps:
                 m.set_fused(False)
-            row["ms_nccl_allreduce"] = round(timed(), 4)
+            row["ms_nccl_allreduce"] = round(timed()[0], 4)
             for m in mlps:
                 m.set_fused(True)
         out.append(row)
@@ -115,8 +129,8 @@ def main(args, world, rank, local_rank):
         torch.cuda.synchronize()
         xstatus = small.status()
         same = torch.tensor([int(torch.equal(out_f, out_f2))], device=dev)
-        gathered = [torch.empty_like(out_f) for _ in range(world)]
-        dist.all_gather(gathered, out_f)
+        gathered = [torch.empty_like(out_f.view(torch.uint8)) for _ in range(world)]
+        dist.all_gather(gathered, out_f.view(torch.uint8))
         if rank == 0:
             want_bf16 = ob.tp_mlp(Xs, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs, partial_bf16=True)
             want_f32 = ob.tp_mlp(Xs, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=Rs, partial_bf16=False)

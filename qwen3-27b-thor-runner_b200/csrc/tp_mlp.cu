@@ -2,9 +2,9 @@
 // the sum of the down-projection partials over the ranks:
 //   * up to 16 tokens, once the ranks have exchanged their buffer handles: one kernel per rank
 //     pushes the rank's FP32 partial into every peer's exchange buffer with plain peer stores
-//     over NVLink, raises a flag there, waits (bounded) for the peers' flags on its own buffer,
-//     adds the P partials in rank order in FP32, adds the residual and rounds once.  No
-//     library collective, no multicast, deterministic, one rounding.
+//     over NVLink ({value, epoch} pairs, so the data is its own flag), polls (bounded) its own
+//     buffer for the peers' pairs, adds the P partials in rank order in FP32, adds the residual
+//     and rounds once.  No library collective, no multicast, deterministic, one rounding.
 //   * otherwise one NCCL all-reduce of the BF16 partials, the residual added in FP32 after it.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -40,15 +40,14 @@ namespace {
 
 // ---- peer exchange buffer layout (identical on every rank)
 constexpr int kFusedMaxM = 16;           // tokens the fused reduction takes (the GEMV regime)
-constexpr int kXCtas = 32;               // CTAs of the exchange kernel = flag columns
+constexpr int kXCtas = 32;               // most CTAs of the exchange kernel
 constexpr size_t kXStatusOff = 0;        // sticky status word (0 = no wait ever ran out)
 constexpr size_t kXEpochOff = 64;        // launch counter, advanced by the kernel itself (graph replays stay valid)
 constexpr size_t kXDoneOff = 128;        // CTAs finished in the current launch
-constexpr size_t kXFlagsOff = 256;       // [2 sets][world <= 8][kXCtas] epoch flags, written by the peers
-constexpr size_t kXSlotsOff = 4096;      // [2 sets][world][kFusedMaxM * H] FP32 partials, written by the peers
+constexpr size_t kXSlotsOff = 4096;      // [2 sets][world][kFusedMaxM * H] x {FP32 value, epoch}, written by the peers
 constexpr long long kXWaitClocks = 2000000000LL;   // about a second
 
-inline size_t xbuf_bytes(int world, int H) { return kXSlotsOff + 2ull * world * kFusedMaxM * H * 4; }
+inline size_t xbuf_bytes(int world, int H) { return kXSlotsOff + 2ull * world * kFusedMaxM * H * 8; }
 
 struct ExchangeParams {
     unsigned char* peer[NVFP4_TP_MAX_WORLD];
@@ -58,69 +57,67 @@ struct ExchangeParams {
     int rank, world, n4, H;          // n4 = M * H / 4
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ void st_volatile_v4(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
-// One launch per rank, the same grid on every rank.  CTA c owns the float4 elements c*256+t,
-// +gridDim*256, ...: it pushes them to slot [set][rank] of every rank's buffer, raises flag
-// [set][rank][c] there, waits for flags [set][q][c] of all ranks q on its own buffer and sums.
-// Only CTAs with the same index on different GPUs wait for each other; the two sets alternate
-// per launch, so a fast rank's next push never lands on data a slow rank still reads.
+// One launch per rank, the same grid on every rank.  Every FP32 value travels as an 8-byte
+// {value, launch epoch} pair (8-byte stores are single transactions), so the data is its own
+// arrival flag: no fence, no separate flag write, one NVLink traversal.  A thread pushes its
+// elements of the rank's partial into slot [set][rank] of every rank's buffer (16-byte stores
+// = two pairs), then polls slots [set][0..P-1] of its own buffer until the pairs carry this
+// launch's epoch (bounded), adds them in rank order, adds the residual and rounds once.  The
+// two sets alternate per launch: a fast rank's next push never lands on pairs a slow rank still
+// reads (it can only be two launches ahead after that rank has pushed the launch in between).
 __global__ void __launch_bounds__(256) exchange_reduce_kernel(const ExchangeParams p) {
-    __shared__ int s_fail;
     unsigned char* mine = p.peer[p.rank];
     const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(mine + kXEpochOff) + 1u;
     const unsigned int set = epoch & 1u;
-    const size_t slot_floats = (size_t)kFusedMaxM * p.H;
-    const int tid = threadIdx.x, c = blockIdx.x;
-    if (tid == 0) s_fail = 0;
-    // push: 16-byte peer stores, consecutive threads -> consecutive addresses
-    for (int i = c * 256 + tid; i < p.n4; i += gridDim.x * 256) {
+    const size_t slot_pairs = (size_t)kFusedMaxM * p.H;               // 8-byte pairs per slot
+    const int tid = threadIdx.x;
+    const size_t my_slot = ((size_t)set * p.world + p.rank) * slot_pairs * 8;
+    for (int i = blockIdx.x * 256 + tid; i < p.n4; i += gridDim.x * 256) {
         const float4 v = reinterpret_cast<const float4*>(p.partial)[i];
         for (int q = 0; q < p.world; ++q) {
-            float4* dst = reinterpret_cast<float4*>(p.peer[q] + kXSlotsOff) + ((size_t)set * p.world + p.rank) * (slot_floats / 4);
-            dst[i] = v;
+            unsigned char* dst = p.peer[q] + kXSlotsOff + my_slot + (size_t)i * 32;
+            st_volatile_v4(dst, __float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch);
+            st_volatile_v4(dst + 16, __float_as_uint(v.z), epoch, __float_as_uint(v.w), epoch);
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < p.world) {
-        unsigned int* f = reinterpret_cast<unsigned int*>(p.peer[tid] + kXFlagsOff) + ((size_t)set * NVFP4_TP_MAX_WORLD + p.rank) * kXCtas + c;
-        st_release_sys(f, epoch);
-        // bounded wait for rank `tid`'s flag on this rank's own buffer
-        const unsigned int* w = reinterpret_cast<const unsigned int*>(mine + kXFlagsOff) + ((size_t)set * NVFP4_TP_MAX_WORLD + tid) * kXCtas + c;
-        const long long t0 = clock64();
-        while (ld_acquire_sys(w) != epoch) {
-            if (clock64() - t0 > kXWaitClocks) {
-                s_fail = 1;
-                atomicCAS(reinterpret_cast<unsigned int*>(mine + kXStatusOff), 0u, 0x700u + (unsigned)tid);
-                break;
+    const long long t0 = clock64();
+    bool failed = false;
+    for (int i = blockIdx.x * 256 + tid; i < p.n4 && !failed; i += gridDim.x * 256) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < p.world; ++q) {                          // rank 0 first, then 1, 2, ...: the same order on every rank
+            const unsigned char* src = mine + kXSlotsOff + ((size_t)set * p.world + q) * slot_pairs * 8 + (size_t)i * 32;
+            uint4 a, b;
+            while (true) {
+                a = ld_volatile_v4(src);
+                b = ld_volatile_v4(src + 16);
+                if (a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch) break;
+                if (clock64() - t0 > kXWaitClocks) {
+                    atomicCAS(reinterpret_cast<unsigned int*>(mine + kXStatusOff), 0u, 0x700u + (unsigned)q);
+                    failed = true;
+                    break;
+                }
             }
+            if (failed) break;
+            s.x += __uint_as_float(a.x); s.y += __uint_as_float(a.z);
+            s.z += __uint_as_float(b.x); s.w += __uint_as_float(b.z);
         }
-    }
-    __syncthreads();
-    if (!s_fail) {
-        const float4* slots = reinterpret_cast<const float4*>(mine + kXSlotsOff) + (size_t)set * p.world * (slot_floats / 4);
-        for (int i = c * 256 + tid; i < p.n4; i += gridDim.x * 256) {
-            float4 s = __ldcg(slots + i);                       // rank 0 first, then 1, 2, ...: the same order on every rank
-            for (int q = 1; q < p.world; ++q) {
-                const float4 x = __ldcg(slots + (size_t)q * (slot_floats / 4) + i);
-                s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
-            }
-            if (p.residual) {
-                const uint2 r = reinterpret_cast<const uint2*>(p.residual)[i];
-                s.x += __uint_as_float(r.x << 16); s.y += __uint_as_float(r.x & 0xFFFF0000u);
-                s.z += __uint_as_float(r.y << 16); s.w += __uint_as_float(r.y & 0xFFFF0000u);
-            }
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
-            reinterpret_cast<uint2*>(p.out)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        if (failed) break;
+        if (p.residual) {
+            const uint2 r = reinterpret_cast<const uint2*>(p.residual)[i];
+            s.x += __uint_as_float(r.x << 16); s.y += __uint_as_float(r.x & 0xFFFF0000u);
+            s.z += __uint_as_float(r.y << 16); s.w += __uint_as_float(r.y & 0xFFFF0000u);
         }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(s.x, s.y), hi = __floats2bfloat162_rn(s.z, s.w);
+        reinterpret_cast<uint2*>(p.out)[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
     }
     // the last CTA to finish advances the launch counter for the next launch
     __syncthreads();
