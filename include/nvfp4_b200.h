@@ -72,7 +72,7 @@ const char* nvfp4_status_string(int status);
  *   "prefill_impl": 0 = auto, 1 = dequant-to-workspace + CUDA-core GEMM (debug),
  *                   2 = fused dequant + tcgen05 GEMM
  *   "decode_max_m": largest M routed to the GEMV path (default 16)
- *   "skinny_min_m", "skinny_max_m": token counts (default 17..64) routed to the few-token
+ *   "skinny_min_m", "skinny_max_m": token counts (default 9..64) routed to the few-token
  *                   kernel that keeps the dequantised weights in tensor memory; min 129 or
  *                   max 0 turns it off.  "skinny_split_cost": stage-times charged to
  *                   splitting row tiles along K when that kernel plans its work.

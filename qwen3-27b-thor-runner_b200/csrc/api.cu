@@ -20,7 +20,7 @@ struct nvfp4_handle {
     int decode_impl = 0;
     int prefill_impl = 0;
     int decode_max_m = 16;
-    int skinny_min_m = 17, skinny_max_m = 64;    // token counts routed to the weights-in-TMEM kernel
+    int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
     unsigned long long launches = 0;
 };
 

@@ -52,7 +52,8 @@ constexpr int kGroupWarps = 8;                    // warps that share one half-u
 // overlap the other CTA's streaming.
 constexpr int kPackedBytes = kRT * kKC / 2;       // 16384 per half-unit
 constexpr int kScaleBytes = kRT * kKC / 16;       // 2048 per half-unit
-constexpr int kActRowBytes = kKC * 2;             // 512 per token per half-unit (FP16)
+constexpr int kActBlockBytes = 128 + 16;          // 64 k of FP16 + 16 bytes of padding
+constexpr int kActRowBytes = 4 * kActBlockBytes;  // 576 per token per half-unit: four padded 64-k blocks
 constexpr int kMaxTokens = 8;                     // tokens per launch (one 8-column MMA tile)
 constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 output tile
 constexpr uint32_t kTxBytes = kPackedBytes + kScaleBytes;
@@ -81,12 +82,11 @@ struct DecodeParams {
     unsigned int epoch;
 };
 
-// 16-byte chunk c (0..31) of a 512-byte token row is stored at chunk position
-// (c & ~7) | ((c & 7) ^ ((c >> 3) | (tok & 1) << 2)): the consumers' 128-bit loads (lanes = 8 tokens
-// x 4 chunk groups) then hit 8 different bank groups.
-__device__ __forceinline__ int act_phys_chunk(int c, int tok) {
-    return (c & ~7) | ((c & 7) ^ (((c >> 3) & 3) | ((tok & 1) << 2)));
-}
+// Activation row of one (k-chunk, token): four 64-k blocks of 128 bytes, each followed by 16
+// bytes of padding.  Lane (g, t) of a consumer warp reads block t of token g, 16 bytes at a
+// time at immediate offsets; with the padding the 8 lanes of a quarter-warp (2 tokens x 4
+// blocks) hit 8 different 16-byte bank groups ((4*token + t + chunk) mod 8), no XOR needed.
+__device__ __forceinline__ int act_chunk_offset(int c) { return (c >> 3) * kActBlockBytes + (c & 7) * 16; }
 
 // Eight packed E2M1 codes (one 32-bit word, 8 consecutive k of one row) -> four f16x2 registers
 // holding e2m1 * block scale, in k order.  The hardware conversion is exact and the products
@@ -129,8 +129,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, G = gridDim.x;
-    const long long u_begin = (long long)cta * p.units / G;
-    const long long u_end = (long long)(cta + 1) * p.units / G;
+    const int u_begin = (int)((long long)cta * p.units / G);     // half-units [u_begin, u_end) of this CTA
+    const int u_end = (int)((long long)(cta + 1) * p.units / G);
     const int kc_begin = (int)(u_begin % p.kchunks);
 
     // The producer lane sets the ring up itself and starts streaming weights at once; the
@@ -156,12 +156,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             const uint64_t pol_stream = ptx::policy_evict_first();
             int stage = 0;
             uint32_t ph = 0;
-            long long hu = u_begin;
+            int hu = u_begin;
             int tile = (int)(u_begin / p.kchunks);
             int kc = kc_begin;                                // k-chunk of hu inside its row tile
             while (hu < u_end) {
-                const long long tile_end = hu - kc + p.kchunks;
-                const long long seg_end = tile_end < u_end ? tile_end : u_end;
+                const int tile_end = hu - kc + p.kchunks;
+                const int seg_end = tile_end < u_end ? tile_end : u_end;
                 const int row0 = tile * kRT;
                 while (hu < seg_end) {
                     const int cnt = (seg_end - hu) >= GROUPS ? GROUPS : 1;
@@ -197,7 +197,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     const int off_w1 = r0 * 128 + (((2 * t + 1) ^ g) << 4);   // row r0, chunk 2t+1
     const int off_s = r0 * 16 + 4 * t;                         // 4 scale bytes: blocks 4t..4t+3 of the row
     const int tok = g < p.M ? g : 0;                           // token feeding MMA column g (columns >= M are never stored)
-    const int act_sw = t | ((tok & 1) << 2);
 
     // Programmatic dependent launch: the next kernel of the stream may start its own weight
     // streaming while this grid drains; whatever depends on the previous grid (activations,
@@ -249,7 +248,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     int j, c;
                     const uint4* src = chunk_src(id, j, tk[u], c);
                     if (src) x[u] = __ldg(src);
-                    dst[u] = (j * p.M + tk[u]) * kActRowBytes + act_phys_chunk(c, tk[u]) * 16;
+                    dst[u] = (j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c);
                 }
             }
 #pragma unroll
@@ -274,13 +273,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             s_tokscale[8 + tid] = __uint_as_float((uint32_t)(254 - se) << 23);
         }
         ptx::named_barrier_sync(1, kConsumerThreads);
-        // Pass B: BF16 -> scaled FP16 in place (token rows are 512 bytes, so the token of a chunk
-        // is its row index modulo M).
-        const int nchunks = total;                            // 16-byte chunks in the resident area
+        // Pass B: BF16 -> scaled FP16 in place.  Chunk i of the data sits at row i/32 (row modulo M
+        // = its token), position act_chunk_offset(i mod 32) inside the padded row.
+        const int nchunks = total;                            // 16-byte data chunks in the resident area
         for (int i = tid; i < nchunks; i += kConsumerThreads) {
             const int row = i >> 5;
             const float sc = s_tokscale[row % p.M];
-            uint4* ptr = reinterpret_cast<uint4*>(s_act + (size_t)i * 16);
+            uint4* ptr = reinterpret_cast<uint4*>(s_act + row * kActRowBytes + act_chunk_offset(i & 31));
             const uint4 x = *ptr;
             const uint32_t v[4] = {x.x, x.y, x.z, x.w};
             uint32_t y[4];
@@ -294,20 +293,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 
     int stage = 0;
     uint32_t ph = 0;
-    long long hu = u_begin;
-    int tile = (int)(u_begin / p.kchunks);
+    int hu = u_begin;
+    int tile = u_begin / p.kchunks;
     int kc = kc_begin;                                         // k-chunk of hu inside its row tile
     int seg_parity = 0;
     while (hu < u_end) {
         const int kc_first = kc;
-        const long long tile_end = hu - kc + p.kchunks;
-        const long long seg_end = tile_end < u_end ? tile_end : u_end;
+        const int tile_end = hu - kc + p.kchunks;
+        const int seg_end = tile_end < u_end ? tile_end : u_end;
 
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-        // Segment bookkeeping known up front.  An owner whose contributors have already published
-        // their partials (the usual case: a contributor's share is the first thing it computes)
-        // fetches them now, off the critical path; otherwise it waits for them at the end.
+        // Segment bookkeeping known up front.
         const bool owner = (kc_first == 0);
         const bool complete = owner && (seg_end == tile_end);
         const int m0 = 2 * t, m1 = 2 * t + 1;
@@ -316,21 +313,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         int last = cta;                              // contributors are CTAs cta+1 .. last
         float pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         bool prefetched = complete;
-        if (grp == 0 && owner && !complete && !(PROBE & 32)) {
+        if (grp == 0 && owner && !complete && !(PROBE & 32))
             while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
-            int ready = 1;
-            if (lane == 0)
-                for (int c = cta + 1; c <= last; ++c) ready &= (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) == p.epoch);
-            ready = __shfl_sync(0xffffffffu, ready, 0);
-            if (ready) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (mm[i] < p.M)
-                        for (int c = cta + 1; c <= last; ++c)
-                            pre[i] += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
-                prefetched = true;
-            }
-        }
 
         while (hu < seg_end) {
             const int cnt = (seg_end - hu) >= GROUPS ? GROUPS : 1;
@@ -340,10 +324,29 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             // Every warp waits on every stage in order (an mbarrier waiter may not skip a phase);
             // group 1 has nothing to do in a stage that carries a single half-unit.
             ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0x200u + (unsigned)stage);
+            // Two stages before the end of an owner's segment: if the contributors have published
+            // their partials by now (the usual case: a contributor's share is the first thing it
+            // computes), fetch them behind the remaining math; otherwise wait for them at the end.
+            // (Looking at the start of the segment instead put two L2 round trips in front of the
+            // first stage of every owner: 1.8 us per launch on a B200.)
+            if (grp == 0 && owner && !prefetched && !(PROBE & 32) && seg_end - hu <= 2 * GROUPS) {
+                int ready = 1;
+                if (lane == 0)
+                    for (int c = cta + 1; c <= last; ++c) ready &= (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) == p.epoch);
+                ready = __shfl_sync(0xffffffffu, ready, 0);
+                if (ready) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (mm[i] < p.M)
+                            for (int c = cta + 1; c <= last; ++c)
+                                pre[i] += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
+                    prefetched = true;
+                }
+            }
             if (!(PROBE & 1) && grp < cnt) {
                 const unsigned char* wp = s_packed + (stage * GROUPS + grp) * kPackedBytes;
                 const unsigned char* sp = s_scale + (stage * GROUPS + grp) * kScaleBytes + off_s;
-                const unsigned char* ap = s_act + (size_t)(slot * p.M + tok) * kActRowBytes + t * 128;
+                const unsigned char* ap = s_act + (slot * p.M + tok) * kActRowBytes + t * kActBlockBytes;
                 const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
                 const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
                 const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + off_w0 + 8 * 128);
@@ -371,7 +374,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     expand_u32(qa[uu], Sa[uu >> 1], da);
                     expand_u32(qb[uu], Sb[uu >> 1], db);
                     uint4 x = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
-                    if (!(PROBE & 128)) x = *reinterpret_cast<const uint4*>(ap + ((uu ^ act_sw) << 4));
+                    if (!(PROBE & 128)) x = *reinterpret_cast<const uint4*>(ap + uu * 16);
                     const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // k 0..3 of this 8-group: rows g, g+8
                     const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // k 4..7
                     if (PROBE & 64) {   // measurement only: keep the conversions alive without the tensor core

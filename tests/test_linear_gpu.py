@@ -482,7 +482,8 @@ def test_tp_mlp_fused_single_rank(handle, M):
             outs.append(util.to_host_u16(fused))
         assert mlp.status() == 0
         assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
-        assert np.array_equal(outs[0], util.to_host_u16(plain))
+        # the plain path may use another kernel for this M (another FP32 summation order)
+        assert ob.rel_frobenius(outs[0], util.to_host_u16(plain)) <= 2e-4
         want = ob.mlp(X, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R)
         assert ob.rel_frobenius(outs[0], want) <= TOL
     finally:

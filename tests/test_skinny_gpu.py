@@ -17,7 +17,7 @@ def skinny(handle):
     handle.set_option("skinny_min_m", 1)
     handle.set_option("skinny_max_m", 128)
     yield handle
-    handle.set_option("skinny_min_m", 17)
+    handle.set_option("skinny_min_m", 9)
     handle.set_option("skinny_max_m", 64)
 
 
