@@ -13,10 +13,12 @@
 //   * Consumer group h works on half-unit h of every stage (two groups in a 17-warp CTA, one in a
 //     9-warp CTA, see GROUPS); each of a group's 8 warps owns 16 of the 128
 //     rows.  Codes are expanded in registers: cvt.rn.f16x2.e2m1x2 turns one packed byte into two
-//     exact FP16 values, one f16x2 multiply applies the block scale taken from a 256-entry
-//     shared-memory table.  Every product lut*scale is exact in FP16 (2 + 4 significant bits, all
-//     within [2^-10, 2880]).  The dot products run on the tensor cores (mma.sync m16n8k16, weights
-//     as the 16-row operand, the <= 8 tokens as the 8-column operand) with FP32 accumulators --
+//     exact FP16 values, one f16x2 multiply applies the block scale, formed without a table: the
+//     unsigned E4M3 byte shifted left by 7 IS the scale / 2^8 as an FP16 bit pattern (subnormal
+//     codes included).  Every product lut*scale/2^8 is exact in FP16 (2 + 4 significant bits, all
+//     within [2^-18, 11.25]); the 2^8 returns in the FP32 epilogue.  The dot products run on the
+//     tensor cores (mma.sync m16n8k16, weights as the 16-row operand, the <= 8 tokens as the
+//     8-column operand) with FP32 accumulators --
 //     CUDA cores alone cannot convert AND multiply-accumulate 0.56 B/element at HBM speed.
 //   * Activations: the CTA's whole k range stays resident in shared memory as FP16, converted
 //     once by the consumer warps with an exact per-token power-of-two scale (largest magnitude ->
@@ -116,8 +118,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     unsigned char* s_scale = s_packed + stages * GROUPS * kPackedBytes;   // stages x GROUPS x 2 KB
     unsigned char* s_act = s_scale + stages * GROUPS * kScaleBytes;       // slots x M x 512 B of FP16
     float* s_out = reinterpret_cast<float*>(s_act + p.act_slots * p.M * kActRowBytes);   // 2 FP32 exchange tiles
-    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_out + 2 * kMaxTokens * kOutLd);
-    float* s_tokscale = reinterpret_cast<float*>(s_table + 256);          // [0..7] scale, [8..15] 1/scale per token
+    float* s_tokscale = s_out + 2 * kMaxTokens * kOutLd;                  // [0..7] scale, [8..15] 1/scale per token
     unsigned int* s_amax = reinterpret_cast<unsigned int*>(s_tokscale + 16);   // [0..7] largest |activation| bits per token
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_amax + 16);
     uint64_t* empty_bar = full_bar + kMaxStages;
@@ -202,11 +203,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // streaming while this grid drains; whatever depends on the previous grid (activations,
     // residual, the outputs and the cross-CTA scratch) is only touched after griddep_wait().
     ptx::griddep_launch_dependents();
-    // Block-scale table: code byte -> f16x2 (both halves) of ue4m3(code); exact (4 significant bits).
-    if (tid < 256) {
-        const uint32_t b = (uint32_t)__half_as_ushort(__float2half_rn(ue4m3_to_float((uint32_t)tid)));
-        s_table[tid] = b | (b << 16);
-    }
     if (tid < 16) s_amax[tid] = 0u;
     ptx::named_barrier_sync(2, kThreads);            // mbarriers initialised (the producer only arrives)
     ptx::named_barrier_sync(1, kConsumerThreads);
@@ -356,15 +352,21 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #ifndef NVFP4_DM_VARIANT
 #define NVFP4_DM_VARIANT 0
 #endif
-                // The four block scales of each row (blocks 4t..4t+3 of the half-unit), looked up once.
+                // The four block scales of each row (blocks 4t..4t+3 of the half-unit) as f16x2.
+                // An unsigned E4M3 byte x (bit 7 ignored) equals the FP16 number with bit pattern
+                // x << 7, times 2^8 -- normal codes (exponent bias 7 vs 15), the subnormal codes
+                // (FP16 subnormals scale the same way) and 0x7F = 480 alike.  So the scale operand is
+                // one byte permute and one shift away, and the 2^8 is applied once in the epilogue.
+                // lut * (x << 7 as FP16) stays exact in FP16: at least 2^-18, 2 + 4 significant bits.
                 uint32_t Sa[4], Sb[4];
                 {
-                    const uint32_t ba = *reinterpret_cast<const uint32_t*>(sp);
-                    const uint32_t bb = *reinterpret_cast<const uint32_t*>(sp + 8 * 16);
+                    const uint32_t ba = *reinterpret_cast<const uint32_t*>(sp) & 0x7F7F7F7Fu;
+                    const uint32_t bb = *reinterpret_cast<const uint32_t*>(sp + 8 * 16) & 0x7F7F7F7Fu;
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
-                        Sa[b] = s_table[(ba >> (8 * b)) & 0xFFu];
-                        Sb[b] = s_table[(bb >> (8 * b)) & 0xFFu];
+                        const uint32_t sel = 0x4040u | (uint32_t)b | ((uint32_t)b << 8);   // bytes {b, zero, b, zero}
+                        Sa[b] = ptx::prmt(ba, 0u, sel) * 128u;
+                        Sb[b] = ptx::prmt(bb, 0u, sel) * 128u;
                     }
                 }
                 float acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // second accumulator: halves the MMA dependency chain
@@ -455,7 +457,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 for (int i = 0; i < 4; ++i) {
                     const int n = row_base + rr[i];
                     if (mm[i] >= p.M || n >= p.N) continue;
-                    float x = (v[i] + pre[i]) * p.inv_gs;
+                    float x = ((v[i] + pre[i]) * 256.0f) * p.inv_gs;      // 2^8: see the block scales above
                     const size_t o = (size_t)mm[i] * p.N + n;
                     if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
                     if (p.residual) x += __bfloat162float(p.residual[o]);
@@ -538,7 +540,7 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     p.units = (int)(tiles * p.kchunks);
     int grid = grid_cap < kMaxGrid ? grid_cap : kMaxGrid;
     if (grid > p.units) grid = p.units;
-    const int fixed = 1024 + 2 * kMaxTokens * kOutLd * 4 + 1024 + 128 + 2 * kMaxStages * 8 + 64;
+    const int fixed = 1024 + 2 * kMaxTokens * kOutLd * 4 + 128 + 2 * kMaxStages * 8 + 64;
     const int stage_w = groups * (kPackedBytes + kScaleBytes);
     const int budget = groups == 2 ? kSmemBudget : kSmemBudgetHalf;
     const int max_span = (p.units + grid - 1) / grid;
