@@ -112,7 +112,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     constexpr int kConsumerThreads = kConsumerWarps * 32;
     constexpr int kThreads = kConsumerThreads + 32;   // + producer warp
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment by an offset on the shared-memory array itself: the pointer keeps its
+    // address space, so every access below is a shared-memory instruction with a 32-bit address
+    // (rounding a generic 64-bit pointer instead turns them into generic loads and stores).
+    unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int stages = p.stages;
     unsigned char* s_packed = smem;                                       // stages x GROUPS x 16 KB, 1024-aligned
     unsigned char* s_scale = s_packed + stages * GROUPS * kPackedBytes;   // stages x GROUPS x 2 KB

@@ -154,7 +154,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_packed,
                    const __grid_constant__ CUtensorMap tm_scale, const SkinnyParams p) {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1024-byte alignment by an offset on the shared-memory array itself: the pointer keeps its
+    // address space, so every access below is a shared-memory instruction with a 32-bit address
+    // (rounding a generic 64-bit pointer instead turns them into generic loads and stores).
+    unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int xbytes = p.NT * (WK * 2);                               // one activation stage: 4 blocks of NT x 128 B
     unsigned char* s_x = smem;                                        // x_stages x xbytes
     unsigned char* s_wp = s_x + p.x_stages * xbytes;                  // w_stages x 16 KB packed codes
