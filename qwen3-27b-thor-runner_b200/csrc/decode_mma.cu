@@ -355,21 +355,16 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #ifndef NVFP4_DM_VARIANT
 #define NVFP4_DM_VARIANT 0
 #endif
-                // The four block scales of each row (blocks 4t..4t+3 of the half-unit) as f16x2.
-                // An unsigned E4M3 byte x (bit 7 ignored) equals the FP16 number with bit pattern
-                // x << 7, times 2^8 -- normal codes (exponent bias 7 vs 15), the subnormal codes
-                // (FP16 subnormals scale the same way) and 0x7F = 480 alike.  So the scale operand is
-                // one byte permute and one shift away, and the 2^8 is applied once in the epilogue.
-                // lut * (x << 7 as FP16) stays exact in FP16: at least 2^-18, 2 + 4 significant bits.
+                // The four block scales of each row (blocks 4t..4t+3 of the half-unit) as f16x2
+                // operands: scale / 2^8, formed from the byte without a table.
                 uint32_t Sa[4], Sb[4];
                 {
-                    const uint32_t ba = *reinterpret_cast<const uint32_t*>(sp) & 0x7F7F7F7Fu;
-                    const uint32_t bb = *reinterpret_cast<const uint32_t*>(sp + 8 * 16) & 0x7F7F7F7Fu;
+                    const uint32_t ba = mask_scale_bytes(*reinterpret_cast<const uint32_t*>(sp));
+                    const uint32_t bb = mask_scale_bytes(*reinterpret_cast<const uint32_t*>(sp + 8 * 16));
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
-                        const uint32_t sel = 0x4040u | (uint32_t)b | ((uint32_t)b << 8);   // bytes {b, zero, b, zero}
-                        Sa[b] = ptx::prmt(ba, 0u, sel) * 128u;
-                        Sb[b] = ptx::prmt(bb, 0u, sel) * 128u;
+                        Sa[b] = scale_byte_to_f16x2(ba, b);
+                        Sb[b] = scale_byte_to_f16x2(bb, b);
                     }
                 }
                 float acc2[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // second accumulator: halves the MMA dependency chain
@@ -460,7 +455,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 for (int i = 0; i < 4; ++i) {
                     const int n = row_base + rr[i];
                     if (mm[i] >= p.M || n >= p.N) continue;
-                    float x = ((v[i] + pre[i]) * 256.0f) * p.inv_gs;      // 2^8: see the block scales above
+                    float x = ((v[i] + pre[i]) * kBlockScaleUnfold) * p.inv_gs;
                     const size_t o = (size_t)mm[i] * p.N + n;
                     if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
                     if (p.residual) x += __bfloat162float(p.residual[o]);

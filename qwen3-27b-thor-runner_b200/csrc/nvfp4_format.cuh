@@ -35,4 +35,22 @@ __device__ __forceinline__ float ue4m3_to_float(uint32_t byte) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
+// Block scales for the f16x2 dequantisation, without a table.  An unsigned E4M3 byte x (bit 7
+// ignored) equals the FP16 number whose bit pattern is x << 7, times 2^8: normal codes because
+// the exponent bias moves from 7 to 15, the subnormal codes because FP16 subnormals scale the
+// same way, and 0x7F gives 480 like the reference's decoder (no NaN code).  Products
+// e2m1 * (x << 7 as FP16) are exact in FP16 (at least 2^-18, 2 + 4 significant bits), so the
+// kernels multiply by this operand and restore kBlockScaleUnfold once, in their FP32 epilogue.
+constexpr float kBlockScaleUnfold = 256.0f;
+
+__device__ __forceinline__ uint32_t mask_scale_bytes(uint32_t four_scale_bytes) { return four_scale_bytes & 0x7F7F7F7Fu; }
+
+// {s, s} as f16x2 with s = ue4m3(byte b of w) / 2^8; w holds four scale bytes, already masked.
+__device__ __forceinline__ uint32_t scale_byte_to_f16x2(uint32_t w_masked, int b) {
+    uint32_t d;
+    const uint32_t sel = 0x4040u | (uint32_t)b | ((uint32_t)b << 8);      // bytes {b, zero, b, zero}
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w_masked), "r"(0u), "r"(sel));
+    return d * 128u;                                                      // << 7 inside both halves
+}
+
 }  // namespace nvfp4

@@ -53,7 +53,7 @@ constexpr int kWScaleBytes = BN * WK / 16;    // 4 KB
 constexpr int kThreads = 512;
 constexpr int kDequantWarps = 8, kEpiWarps = 4;
 constexpr int kSmemBytes = 1024 + kAStages * kABytes + kWStages * (kWPackedBytes + kWScaleBytes) +
-                           kBBufs * kBBytes + 1024 /*table*/ + 256 /*barriers, tmem slot, abort*/;
+                           kBBufs * kBBytes + 256 /*barriers, tmem slot, abort*/;
 
 constexpr int kPartialVec = BM * BN / 4;      // float4 elements of one FP32 partial tile
 
@@ -99,7 +99,7 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int ti
     const int j1 = me + 1 == P ? kPartialVec : ((int)((long long)(me + 1) * kPartialVec / P) & ~(BM - 1));
     const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
     const int m = mt * BM + (t & (BM - 1));
-    const float mul = (m < p.M ? p.unscale[m] : 0.0f) * p.inv_gs;
+    const float mul = (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
     const float4* head = p.partials + ((size_t)first * 2 + 1) * kPartialVec;
     for (int j = j0 + t; j < j1; j += nthreads) {
         float4 s = __ldcg(head + j);
@@ -143,8 +143,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     unsigned char* s_b = s_a + kAStages * kABytes;                    // kBBufs x 32 KB
     unsigned char* s_wp = s_b + kBBufs * kBBytes;                     // kWStages x 32 KB packed codes
     unsigned char* s_ws = s_wp + kWStages * kWPackedBytes;            // kWStages x 4 KB scales
-    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_ws + kWStages * kWScaleBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_table + 256);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_ws + kWStages * kWScaleBytes);
     uint64_t* afull = bars;                  // [kAStages]
     uint64_t* aempty = afull + kAStages;     // [kAStages]
     uint64_t* wfull = aempty + kAStages;     // [kWStages]
@@ -167,10 +166,6 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         for (int i = 0; i < kAccs; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kEpiWarps); }
         *s_abort = 0;
         ptx::fence_mbar_init();
-    }
-    if (tid < 256) {
-        const uint32_t b = (uint32_t)__half_as_ushort(__float2half_rn(ue4m3_to_float((uint32_t)tid)));
-        s_table[tid] = b | (b << 16);
     }
     if (warp == 1) {   // one warp owns the TMEM allocation: 512 columns = two 128 x 256 FP32 accumulators
         tmem_alloc_512(s_tmem);
@@ -253,7 +248,8 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 ptx::mbar_wait(&wfull[sw], pw, s_abort, p.status, 0x450u + sw);
                 const unsigned char* wp = s_wp + sw * kWPackedBytes + row * 128;
                 const uint4 sc16 = *reinterpret_cast<const uint4*>(s_ws + sw * kWScaleBytes + row * 16);
-                const uint32_t scw[4] = {sc16.x, sc16.y, sc16.z, sc16.w};
+                const uint32_t scw[4] = {mask_scale_bytes(sc16.x), mask_scale_bytes(sc16.y), mask_scale_bytes(sc16.z),
+                                         mask_scale_bytes(sc16.w)};
 #pragma unroll
                 for (int j = 0; j < WK / BK; ++j) {
                     // packed bytes [32j, 32j+32) of the row = logical 16-byte chunks 2j, 2j+1
@@ -264,7 +260,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                     unsigned char* bp = s_b + sb * kBBytes + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {          // chunk c = 8 consecutive k = one 32-bit word of codes
-                        const uint32_t S = s_table[(scw[j] >> (8 * (c >> 1))) & 0xFFu];
+                        const uint32_t S = scale_byte_to_f16x2(scw[j], c >> 1);     // scale / 2^8, undone in the epilogue
                         uint32_t e[4];
                         ptx::cvt_e2m1x8_to_f16x2(q[c], e);
                         *reinterpret_cast<uint4*>(bp + ((c ^ sw7) << 4)) =
@@ -318,7 +314,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], p.epoch);
                 pend[which] = sg.tile;
             } else {
-                const float mul = (m < p.M ? p.unscale[m] : 0.0f) * p.inv_gs;
+                const float mul = (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld32(t_addr + c0, r);

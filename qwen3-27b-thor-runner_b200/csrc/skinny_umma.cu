@@ -118,7 +118,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // One token of one weight row: scale, residual, round, store.
 __device__ __forceinline__ void store_output(const SkinnyParams& p, int m, int n, float v) {
     const size_t o = (size_t)m * p.N + n;
-    float f = v * (p.unscale[m] * p.inv_gs);
+    float f = v * (p.unscale[m] * kBlockScaleUnfold * p.inv_gs);
     if (p.residual) f += __bfloat162float(p.residual[o]);
     p.C[o] = __float2bfloat16_rn(f);
 }
@@ -162,8 +162,7 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
     unsigned char* s_x = smem;                                        // x_stages x xbytes
     unsigned char* s_wp = s_x + p.x_stages * xbytes;                  // w_stages x 16 KB packed codes
     unsigned char* s_ws = s_wp + p.w_stages * kWPackedBytes;          // w_stages x 2 KB scales
-    uint32_t* s_table = reinterpret_cast<uint32_t*>(s_ws + p.w_stages * kWScaleBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_table + 256);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_ws + p.w_stages * kWScaleBytes);
     uint64_t* wfull = bars;                        // [kMaxWStages]
     uint64_t* wempty = wfull + kMaxWStages;        // [kMaxWStages]
     uint64_t* xfull = wempty + kMaxWStages;        // [kMaxXStages]
@@ -186,10 +185,6 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
         for (int i = 0; i < kAccs; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kEpiWarps); }
         *s_abort = 0;
         ptx::fence_mbar_init();
-    }
-    if (tid < 256) {
-        const uint32_t b = (uint32_t)__half_as_ushort(__float2half_rn(ue4m3_to_float((uint32_t)tid)));
-        s_table[tid] = b | (b << 16);
     }
     if (warp == 1) tmem_alloc_512(s_tmem);
     tc_fence_before();
@@ -300,9 +295,9 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {              // chunk c: 32 k = two block scales = 16 columns
                     const uint32_t w[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
-                    const uint32_t scw = c < 2 ? sc.x : sc.y;
-                    const uint32_t S0 = s_table[(scw >> (16 * (c & 1))) & 0xFFu];
-                    const uint32_t S1 = s_table[(scw >> (16 * (c & 1) + 8)) & 0xFFu];
+                    const uint32_t scw = mask_scale_bytes(c < 2 ? sc.x : sc.y);
+                    const uint32_t S0 = scale_byte_to_f16x2(scw, 2 * (c & 1));          // scale / 2^8, undone in the epilogue
+                    const uint32_t S1 = scale_byte_to_f16x2(scw, 2 * (c & 1) + 1);
                     uint32_t r[16];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -418,7 +413,7 @@ bool plan_skinny(const LinearArgs& a, const nvfp4_device_info& dev, SkinnyPlan* 
     if (ws > kMaxWStages) ws = kMaxWStages;
     if (ws < 2) return false;
     p.w_stages = ws;
-    out->smem = 1024 + p.x_stages * xbytes + ws * (kWPackedBytes + kWScaleBytes) + 1024 + 512;
+    out->smem = 1024 + p.x_stages * xbytes + ws * (kWPackedBytes + kWScaleBytes) + 512;
     // Tensor memory (512 columns): two accumulators, then as many 64-column A units as fit (even count).
     p.acc_cols = p.NT <= 64 ? 64 : 128;
     p.a_units = p.NT <= 64 ? 6 : 4;
