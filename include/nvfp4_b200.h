@@ -124,6 +124,27 @@ int nvfp4_linear_decode_noalloc(const void* A_bf16, int M, const uint8_t* packed
 int nvfp4_linear_f32(nvfp4_handle* h, const void* A_bf16, int M, const uint8_t* packed, const uint8_t* scale_ue4m3,
                      float global_scale, int N, int K, void* C_f32, nvfp4_stream_t stream);
 
+/* The K-split linear of a tensor-parallel group in ONE kernel: this rank's partial sums
+ * A * W^T (W = this rank's K columns) are pushed, unrounded, into the exchange buffers of all
+ * ranks of the group over peer memory (plain NVLink stores of {value, epoch} pairs), and the
+ * same kernel then adds the partials of all ranks in rank order in FP32, adds the residual and
+ * rounds once: C[M,N] is the full sum, identical on every rank.  `px` names the buffers:
+ * peer[q] is rank q's buffer as mapped into this process (peer[rank] is this rank's own; layout
+ * in csrc/exchange_layout.h, allocated zero-filled with room for 16 * N pairs per slot by
+ * libnvfp4_b200_tp).  Every rank of the group must make the same call (same M, N) in the same
+ * order; a peer whose data does not arrive within about a second sets the buffer's status word
+ * and leaves that part of C unwritten.  No reference counterpart (the reference is single-GPU).
+ * M <= 16, K % 256 == 0, world <= 8, otherwise NVFP4_E_LIMIT. */
+typedef struct nvfp4_peer_exchange {
+    void* peer[8];
+    int rank, world;
+    int slot_pairs;      /* pairs per slot of the buffers: at least M * N */
+} nvfp4_peer_exchange;
+int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A_bf16, int M, const uint8_t* packed,
+                              const uint8_t* scale_ue4m3, float global_scale, int N, int K,
+                              const void* residual_bf16_or_null, void* C_bf16, const nvfp4_peer_exchange* px,
+                              nvfp4_stream_t stream);
+
 /* Two linears sharing A: C1 = A*W1^T, C2 = A*W2^T, both [N,K].
  * Replaces invoke_fp4_dual_gemv (:395-416), generalised to any M. */
 int nvfp4_linear_dual(nvfp4_handle* h, const void* A_bf16, int M,

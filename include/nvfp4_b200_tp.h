@@ -54,11 +54,13 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* mlp, const void* X_bf16, int M, const voi
  * rank exports the 64-byte handle of its exchange buffer (cudaIpcGetMemHandle), the host ships
  * all of them to every rank (rank order, world x 64 bytes; any transport), every rank attaches
  * (cudaIpcOpenMemHandle; needs peer access, i.e. NVLink or PCIe P2P between the GPUs).  After
- * that nvfp4_tp_mlp_forward runs, per rank, the down projection to an FP32 partial and ONE
- * kernel that pushes the partial to all peers with plain stores, waits (bounded: about a
- * second, then the status word below becomes non-zero and `out` is left unwritten) for theirs
- * and adds them in rank order in FP32 with the residual.  world == 1 may attach with NULL.
- * nvfp4_tp_mlp_set_fused(mlp, 0) returns to the NCCL path.  All ranks must make the same
+ * that nvfp4_tp_mlp_forward's down projection pushes its FP32 sums to all peers with plain
+ * stores, waits (bounded: about a second, then the status word below becomes non-zero and that
+ * part of `out` is left unwritten) for theirs and adds them in rank order in FP32 with the
+ * residual, all in one kernel.  world == 1 may attach with NULL.
+ * nvfp4_tp_mlp_set_fused(mlp, 0) returns to the NCCL path; 1 (default once attached) fuses the
+ * push and the reduction into the down-projection kernel itself (nvfp4_linear_reduce_peers);
+ * 2 runs them as a separate kernel behind an FP32 down projection.  All ranks must make the same
  * sequence of forward calls (same M), as with any collective. */
 int nvfp4_tp_mlp_p2p_handle(nvfp4_tp_mlp* mlp, void* out_64_bytes);
 int nvfp4_tp_mlp_p2p_attach(nvfp4_tp_mlp* mlp, const void* handles_world_x_64_bytes);

@@ -58,7 +58,7 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
-    if (a.out_f32) {   // only the GEMV kernel stores unrounded sums
+    if (a.out_f32 || a.px) {   // only the GEMV kernel stores unrounded sums / reduces over a group
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
@@ -281,6 +281,21 @@ int nvfp4_linear_f32(nvfp4_handle* h, const void* A, int M, const uint8_t* packe
     }
     LinearArgs a{A, packed, scale, 1.0f / global_scale, nullptr, C_f32, M, N, K};
     a.out_f32 = true;
+    return run_linear(h, a, stream);
+}
+
+int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A, int M, const uint8_t* packed, const uint8_t* scale,
+                              float global_scale, int N, int K, const void* residual, void* C,
+                              const nvfp4_peer_exchange* px, nvfp4_stream_t stream) {
+    if (int e = validate_linear(h, A, M, packed, scale, global_scale, N, K, residual, C)) return e;
+    if (!px) return NVFP4_E_NULL;
+    if (px->world < 1 || px->world > 8 || px->rank < 0 || px->rank >= px->world) return NVFP4_E_TP;
+    for (int q = 0; q < px->world; ++q)
+        if (!px->peer[q] || (reinterpret_cast<uintptr_t>(px->peer[q]) & 15u)) return NVFP4_E_NULL;
+    if (M == 0) return NVFP4_OK;
+    if ((long long)M * N > px->slot_pairs) return NVFP4_E_LIMIT;
+    LinearArgs a{A, packed, scale, 1.0f / global_scale, residual, C, M, N, K};
+    a.px = px;
     return run_linear(h, a, stream);
 }
 

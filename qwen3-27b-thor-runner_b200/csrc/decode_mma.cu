@@ -38,6 +38,7 @@
 
 #include <mutex>
 
+#include "exchange_layout.h"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
@@ -82,6 +83,10 @@ struct DecodeParams {
     int act_all;         // 1 = slot index is the k-chunk, 0 = position in the CTA's span
     int out_f32;         // C is FP32 [M,N]: store the scaled sum unrounded (partial results for a later reduction)
     unsigned int epoch;
+    // Tensor-parallel K split: world > 0 = push the sums to the ranks' exchange buffers and reduce
+    // over the group at the end of this kernel (C then receives the full sum + residual).
+    unsigned char* xpeer[xchg::kMaxWorld];
+    int xrank, xworld, xslot_pairs;
 };
 
 // Activation row of one (k-chunk, token): four 64-k blocks of 128 bytes, each followed by 16
@@ -218,6 +223,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // and never overflows.  Pass B converts and stores in natural k order.  The scale is undone in
     // FP32 in the epilogue.
     ptx::griddep_wait();
+    // Group reduction: this launch's epoch and slot set (the counter was advanced by the previous
+    // launch that used the buffer, which has completed by now).
+    unsigned int xepoch = 0, xset = 0;
+    if (p.xworld > 0) {
+        xepoch = *reinterpret_cast<volatile unsigned int*>(p.xpeer[p.xrank] + xchg::kEpochOff) + 1u;
+        xset = xepoch & 1u;
+    }
     if (!(PROBE & 16)) {
         const int per_slot = p.M * 32;
         const int total = p.act_slots * per_slot;
@@ -458,12 +470,61 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     float x = ((v[i] + pre[i]) * kBlockScaleUnfold) * p.inv_gs;
                     const size_t o = (size_t)mm[i] * p.N + n;
                     if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
+                    if (p.xworld > 0) {   // the unrounded sum goes to slot [set][this rank] of every rank's buffer
+                        const size_t pair = ((size_t)xset * p.xworld + p.xrank) * p.xslot_pairs + o;
+                        for (int q = 0; q < p.xworld; ++q)
+                            ptx::st_volatile_v2(p.xpeer[q] + xchg::kSlotsOff + pair * 8, __float_as_uint(x), xepoch);
+                        continue;
+                    }
                     if (p.residual) x += __bfloat162float(p.residual[o]);
                     p.C[o] = __float2bfloat16_rn(x);
                 }
             }
         }
         if (kc >= p.kchunks) { kc = 0; ++tile; }
+    }
+
+    // ---------------------------------------------------------------- reduction over the group
+    // Every CTA takes 1/gridDim of the M x N outputs: it polls its own rank's buffer until the
+    // pairs of all ranks carry this launch's epoch (bounded), adds them in rank order, adds the
+    // residual and rounds once.  The pairs come from the tile owners on every rank, this GPU's
+    // own CTAs included: all CTAs of the grid are resident (one per SM) and an owner's push waits
+    // for nothing that happens after it, so these waits cannot form a cycle.
+    if (p.xworld > 0) {
+        unsigned char* mine = p.xpeer[p.xrank];
+        const int E = p.M * p.N;
+        const int e0 = (int)((long long)cta * E / G), e1 = (int)((long long)(cta + 1) * E / G);
+        const long long t0 = clock64();
+        bool failed = false;
+        for (int e = e0 + tid; e < e1 && !failed; e += kConsumerThreads) {
+            float sum = 0.0f;
+            for (int q = 0; q < p.xworld && !failed; ++q) {
+                const unsigned char* src = mine + xchg::kSlotsOff + (((size_t)xset * p.xworld + q) * p.xslot_pairs + e) * 8;
+                uint2 v = ptx::ld_volatile_v2(src);
+                while (v.y != xepoch) {
+                    if (clock64() - t0 > xchg::kWaitClocks) {
+                        atomicCAS(reinterpret_cast<unsigned int*>(mine + xchg::kStatusOff), 0u, 0x700u + (unsigned)q);
+                        failed = true;
+                        break;
+                    }
+                    v = ptx::ld_volatile_v2(src);
+                }
+                sum += __uint_as_float(v.x);
+            }
+            if (failed) break;
+            if (p.residual) sum += __bfloat162float(p.residual[e]);
+            p.C[e] = __float2bfloat16_rn(sum);
+        }
+        // the last CTA to get here advances the launch counter for the next launch
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        if (tid == 0) {
+            __threadfence();
+            unsigned int* done = reinterpret_cast<unsigned int*>(mine + xchg::kDoneOff);
+            if (atomicAdd(done, 1u) == (unsigned)G - 1u) {
+                *done = 0u;
+                *reinterpret_cast<volatile unsigned int*>(mine + xchg::kEpochOff) = xepoch;
+            }
+        }
     }
 }
 
@@ -533,6 +594,12 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     p.inv_gs = a.inv_gs;
     p.M = m; p.N = a.N; p.K = a.K;
     p.out_f32 = a.out_f32 ? 1 : 0;
+    if (a.px) {
+        for (int q = 0; q < a.px->world; ++q) p.xpeer[q] = static_cast<unsigned char*>(a.px->peer[q]);
+        p.xrank = a.px->rank;
+        p.xworld = a.px->world;
+        p.xslot_pairs = a.px->slot_pairs;
+    }
     p.kchunks = a.K / kKC;
     const long long tiles = (a.N + kRT - 1) / kRT;
     p.units = (int)(tiles * p.kchunks);

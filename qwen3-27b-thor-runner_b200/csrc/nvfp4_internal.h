@@ -19,6 +19,7 @@ struct LinearArgs {
     void* C;                // [M,N] bf16 (fp32 when out_f32)
     int M, N, K;
     bool out_f32 = false;   // unrounded FP32 sums, no residual: partial results a caller reduces itself
+    const nvfp4_peer_exchange* px = nullptr;   // push the sums to the peers and reduce over the group in the same kernel
 };
 
 struct nvfp4_device_info {

@@ -1,10 +1,12 @@
 // Tensor-parallel NVFP4 MLP: per-rank shards, two linears + SwiGLU from the core library, and
 // the sum of the down-projection partials over the ranks:
-//   * up to 16 tokens, once the ranks have exchanged their buffer handles: one kernel per rank
-//     pushes the rank's FP32 partial into every peer's exchange buffer with plain peer stores
-//     over NVLink ({value, epoch} pairs, so the data is its own flag), polls (bounded) its own
-//     buffer for the peers' pairs, adds the P partials in rank order in FP32, adds the residual
-//     and rounds once.  No library collective, no multicast, deterministic, one rounding.
+//   * up to 16 tokens, once the ranks have exchanged their buffer handles: the down-projection
+//     GEMV itself (nvfp4_linear_reduce_peers) pushes its unrounded FP32 sums into every rank's
+//     exchange buffer with plain peer stores over NVLink ({value, epoch} pairs, so the data is
+//     its own flag), polls (bounded) its own buffer for the peers' pairs, adds the P partials in
+//     rank order in FP32, adds the residual and rounds once.  No library collective, no
+//     multicast, deterministic, one rounding.  (Mode 2 does the same with a separate
+//     push-and-sum kernel behind an FP32 GEMV.)
 //   * otherwise one NCCL all-reduce of the BF16 partials, the residual added in FP32 after it.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -13,6 +15,7 @@
 #include <cstring>
 
 #include "../../include/nvfp4_b200_tp.h"
+#include "exchange_layout.h"
 
 struct nvfp4_tp_comm {
     ncclComm_t comm = nullptr;
@@ -38,16 +41,13 @@ struct nvfp4_tp_mlp {
 
 namespace {
 
-// ---- peer exchange buffer layout (identical on every rank)
-constexpr int kFusedMaxM = 16;           // tokens the fused reduction takes (the GEMV regime)
-constexpr int kXCtas = 32;               // most CTAs of the exchange kernel
-constexpr size_t kXStatusOff = 0;        // sticky status word (0 = no wait ever ran out)
-constexpr size_t kXEpochOff = 64;        // launch counter, advanced by the kernel itself (graph replays stay valid)
-constexpr size_t kXDoneOff = 128;        // CTAs finished in the current launch
-constexpr size_t kXSlotsOff = 4096;      // [2 sets][world][kFusedMaxM * H] x {FP32 value, epoch}, written by the peers
-constexpr long long kXWaitClocks = 2000000000LL;   // about a second
+using namespace nvfp4::xchg;
+constexpr int kFusedMaxM = kMaxTokens;
+constexpr int kXCtas = 32;               // most CTAs of the stand-alone exchange kernel
+constexpr size_t kXStatusOff = kStatusOff, kXEpochOff = kEpochOff, kXDoneOff = kDoneOff, kXSlotsOff = kSlotsOff;
+constexpr long long kXWaitClocks = kWaitClocks;
 
-inline size_t xbuf_bytes(int world, int H) { return kXSlotsOff + 2ull * world * kFusedMaxM * H * 8; }
+inline size_t xbuf_bytes(int world, int H) { return buffer_bytes(world, H); }
 
 struct ExchangeParams {
     unsigned char* peer[NVFP4_TP_MAX_WORLD];
@@ -258,9 +258,17 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     if (st) return st;
     if (P == 1 && !(m->attached && m->fused))
         return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
-    if (m->attached && m->fused && M <= kFusedMaxM) {
-        // FP32 partial -> peers -> ordered FP32 sum + residual -> one rounding; `out` may alias the
-        // residual (every element is read and written by the same thread).
+    if (m->attached && m->fused == 1 && M <= kFusedMaxM) {
+        // One kernel: the down projection pushes its unrounded sums to all ranks and reduces over
+        // the group (rank order, FP32, residual, one rounding).  `out` may alias the residual.
+        nvfp4_peer_exchange px{};
+        for (int q = 0; q < P; ++q) px.peer[q] = m->peer[q];
+        px.rank = m->comm->rank; px.world = P; px.slot_pairs = kFusedMaxM * m->H;
+        st = nvfp4_linear_reduce_peers(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, &px, s);
+        if (st != NVFP4_E_LIMIT) return st;      // a shape the GEMV kernel does not take: use the collective below
+    }
+    if (m->attached && m->fused == 2 && M <= kFusedMaxM) {
+        // Two kernels: FP32 partial, then the stand-alone push-and-sum kernel (kept for comparison).
         st = nvfp4_linear_f32(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, m->partial, s);
         if (st == NVFP4_OK) {
             ExchangeParams xp{};
@@ -275,7 +283,7 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
             exchange_reduce_kernel<<<grid, 256, 0, s>>>(xp);
             return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_TP;
         }
-        if (st != NVFP4_E_LIMIT) return st;      // a shape the FP32 GEMV does not take: use the collective below
+        if (st != NVFP4_E_LIMIT) return st;
     }
     // The partials travel without the residual (a partial rounded to BF16 next to a residual ten
     // times its size would lose its low bits); it is added once, in FP32, after the sum.
@@ -331,7 +339,7 @@ int nvfp4_tp_mlp_p2p_attach(nvfp4_tp_mlp* m, const void* handles) {
 
 int nvfp4_tp_mlp_set_fused(nvfp4_tp_mlp* m, int on) {
     if (!m) return NVFP4_E_NULL;
-    m->fused = on ? 1 : 0;
+    m->fused = on < 0 || on > 2 ? 1 : on;
     return NVFP4_OK;
 }
 

@@ -32,6 +32,8 @@ SIGNATURES = {
     "nvfp4_linear_decode_noalloc": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
                                             c_void_p, c_void_p]),
     "nvfp4_linear_f32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_linear_reduce_peers": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p,
+                                          c_void_p, c_void_p]),
     "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),

@@ -147,8 +147,10 @@ class TpMlp:
         dist.all_gather(allh, mine)
         self.p2p_attach(b"".join(bytes(t.cpu().tolist()) for t in allh))
 
-    def set_fused(self, on):
-        st = self.lib.nvfp4_tp_mlp_set_fused(self.m, 1 if on else 0)
+    def set_fused(self, mode):
+        """0/False = NCCL all-reduce, 1/True = reduction fused into the down-projection kernel,
+        2 = separate push-and-sum kernel."""
+        st = self.lib.nvfp4_tp_mlp_set_fused(self.m, int(mode))
         if st:
             raise nvfp4.Nvfp4Error(st)
 

@@ -475,13 +475,14 @@ def test_tp_mlp_fused_single_rank(handle, M):
         mlp.forward(util.to_dev(X), M, plain, residual=plain)
         mlp.enable_p2p()
         outs = []
-        for _ in range(3):                       # both flag sets and the launch counter get exercised
+        for mode in (1, 1, 1, 2, 2):             # in-kernel reduction, then the stand-alone kernel; both slot sets get used
+            mlp.set_fused(mode)
             fused = util.to_dev(R)
             mlp.forward(util.to_dev(X), M, fused, residual=fused)
             torch.cuda.synchronize()
             outs.append(util.to_host_u16(fused))
         assert mlp.status() == 0
-        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+        assert all(np.array_equal(outs[0], o) for o in outs[1:])
         # the plain path may use another kernel for this M (another FP32 summation order)
         assert ob.rel_frobenius(outs[0], util.to_host_u16(plain)) <= 2e-4
         want = ob.mlp(X, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R)
