@@ -145,6 +145,32 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A_bf16, int M, const 
                               const void* residual_bf16_or_null, void* C_bf16, const nvfp4_peer_exchange* px,
                               nvfp4_stream_t stream);
 
+/* The linear layer with its optional fusions, for M <= 16 and K % 256 == 0 (NVFP4_E_LIMIT
+ * otherwise; a descriptor that uses none of the options is the plain nvfp4_linear for any M):
+ *   swiglu_up     the activations are bf16(silu(A) * swiglu_up) (the reference's SwiGLU with its
+ *                 single rounding, src/engine/light_ops.cu:186-187), formed while the kernel
+ *                 stages them: A is the gate half, swiglu_up the up half of the gate/up output,
+ *                 so the [M, I] SwiGLU tensor of run_mlp (src/engine/layer.cu:87-99) is never written;
+ *   a_row_stride  elements between token rows of A and swiglu_up (2I for the merged gate/up layout);
+ *   k_valid       activation columns >= k_valid count as zero (a weight shard whose K was padded);
+ *   px            sum over a tensor-parallel group inside the kernel (see nvfp4_linear_reduce_peers).
+ * Zero / NULL fields mean "not used".  No reference counterpart for the fused forms. */
+typedef struct nvfp4_linear_desc {
+    const void* A;
+    const void* swiglu_up;
+    long long a_row_stride;
+    int k_valid;
+    int M;
+    const uint8_t* packed;
+    const uint8_t* scale;
+    float global_scale;
+    int N, K;
+    const void* residual;
+    void* C;
+    const nvfp4_peer_exchange* px;
+} nvfp4_linear_desc;
+int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* desc, nvfp4_stream_t stream);
+
 /* Two linears sharing A: C1 = A*W1^T, C2 = A*W2^T, both [N,K].
  * Replaces invoke_fp4_dual_gemv (:395-416), generalised to any M. */
 int nvfp4_linear_dual(nvfp4_handle* h, const void* A_bf16, int M,

@@ -58,7 +58,7 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
-    if (a.out_f32 || a.px) {   // only the GEMV kernel stores unrounded sums / reduces over a group
+    if (a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid) {   // options only the GEMV kernel implements
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
@@ -296,6 +296,29 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A, int M, const uint8
     if ((long long)M * N > px->slot_pairs) return NVFP4_E_LIMIT;
     LinearArgs a{A, packed, scale, 1.0f / global_scale, residual, C, M, N, K};
     a.px = px;
+    return run_linear(h, a, stream);
+}
+
+int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t stream) {
+    if (!d) return NVFP4_E_NULL;
+    if (int e = validate_linear(h, d->A, d->M, d->packed, d->scale, d->global_scale, d->N, d->K, d->residual, d->C)) return e;
+    const long long stride = d->a_row_stride ? d->a_row_stride : d->K;
+    const int k_valid = d->k_valid ? d->k_valid : d->K;
+    if (stride < k_valid || (stride & 7) || k_valid < 1 || k_valid > d->K || (k_valid & 7)) return NVFP4_E_SHAPE;
+    if (d->swiglu_up && !aligned16(d->swiglu_up)) return NVFP4_E_ALIGN;
+    if (d->px) {
+        if (d->px->world < 1 || d->px->world > 8 || d->px->rank < 0 || d->px->rank >= d->px->world) return NVFP4_E_TP;
+        for (int q = 0; q < d->px->world; ++q)
+            if (!d->px->peer[q] || (reinterpret_cast<uintptr_t>(d->px->peer[q]) & 15u)) return NVFP4_E_NULL;
+        if ((long long)d->M * d->N > d->px->slot_pairs) return NVFP4_E_LIMIT;
+    }
+    if (d->M == 0) return NVFP4_OK;
+    LinearArgs a{d->A, d->packed, d->scale, 1.0f / d->global_scale, d->residual, d->C, d->M, d->N, d->K};
+    a.px = d->px;
+    a.swiglu_up = d->swiglu_up;
+    a.a_stride = d->a_row_stride;
+    a.k_valid = d->k_valid;
+    if (!a.px && !a.swiglu_up && stride == d->K && k_valid == d->K) { a.a_stride = 0; a.k_valid = 0; }   // the plain call
     return run_linear(h, a, stream);
 }
 

@@ -71,7 +71,10 @@ constexpr size_t kPartialOffset = 16384;
 constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kGroupWarps));
 
 struct DecodeParams {
-    const __nv_bfloat16* A;
+    const __nv_bfloat16* A;         // activations, or the gate half when A_up is set
+    const __nv_bfloat16* A_up;      // null, or the up half: the activations are bf16(silu(gate) * up), formed while staging
+    long long a_stride;             // elements between token rows of A (and A_up)
+    int k_valid;                    // columns >= k_valid are zero (a K padded beyond the tensor)
     const __nv_bfloat16* residual;
     __nv_bfloat16* C;
     unsigned char* scratch;
@@ -242,29 +245,33 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             int kc = kc0 + j;
             if (kc >= p.kchunks) kc -= p.kchunks;
             const int k = kc * kKC + c * 8;
-            return k < p.K ? reinterpret_cast<const uint4*>(p.A + (size_t)tk * p.K + k) : nullptr;
+            return k < p.k_valid ? reinterpret_cast<const uint4*>(p.A + (size_t)tk * p.a_stride + k) : nullptr;
         };
         // Pass A: one trip to global memory, eight chunks in flight per thread; the raw BF16 chunk
         // goes to its final (swizzled) place, the magnitudes feed the per-token maximum.
         for (int base = tid; base < total; base += 8 * kConsumerThreads) {
-            uint4 x[8];
+            uint4 x[8], y[8];
             int tk[8], dst[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                x[u] = make_uint4(0u, 0u, 0u, 0u);
+                x[u] = y[u] = make_uint4(0u, 0u, 0u, 0u);
                 tk[u] = 0;
                 dst[u] = -1;
                 const int id = base + u * kConsumerThreads;
                 if (id < total) {
                     int j, c;
                     const uint4* src = chunk_src(id, j, tk[u], c);
-                    if (src) x[u] = __ldg(src);
+                    if (src) {
+                        x[u] = __ldg(src);
+                        if (p.A_up) y[u] = __ldg(src + (p.A_up - p.A) / 8);      // same row and column of the up half
+                    }
                     dst[u] = (j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c);
                 }
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 if (dst[u] < 0) continue;   // uniform across the warp: total is a multiple of 32
+                if (p.A_up) x[u] = swiglu_bf16x8(x[u], y[u]);   // zero chunks stay zero: silu(0) * 0
                 const uint32_t v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
                 uint32_t m = 0;
 #pragma unroll
@@ -588,6 +595,9 @@ struct DecodePlan {
 bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, void* scratch, DecodePlan* out) {
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16*>(a.A);
+    p.A_up = static_cast<const __nv_bfloat16*>(a.swiglu_up);
+    p.a_stride = a.a_stride ? a.a_stride : a.K;
+    p.k_valid = a.k_valid ? a.k_valid : a.K;
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.C = static_cast<__nv_bfloat16*>(a.C);
     p.scratch = static_cast<unsigned char*>(scratch);
@@ -656,7 +666,8 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
     for (int m0 = 0; m0 < a.M; m0 += per) {
         LinearArgs b = a;
         const int m = a.M - m0 < per ? a.M - m0 : per;
-        b.A = static_cast<const char*>(a.A) + (size_t)m0 * a.K * 2;
+        b.A = static_cast<const char*>(a.A) + (size_t)m0 * (a.a_stride ? a.a_stride : a.K) * 2;
+        if (a.swiglu_up) b.swiglu_up = static_cast<const char*>(a.swiglu_up) + (size_t)m0 * (a.a_stride ? a.a_stride : a.K) * 2;
         b.C = static_cast<char*>(a.C) + (size_t)m0 * a.N * (a.out_f32 ? 4 : 2);
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DecodePlan pl;

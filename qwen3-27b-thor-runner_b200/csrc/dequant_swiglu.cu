@@ -36,7 +36,6 @@ dequant_bf16_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
 // silu(x) = x / (1 + exp(-x)) in FP32, product rounded once to BF16
 // (src/engine/light_ops.cu:168-199 and :1542-1577).  gate and up rows are
 // row_stride_in elements apart (I for separate tensors, 2I for the merged layout).
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
@@ -48,16 +47,7 @@ swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __res
         const int m = (int)(v / vec_per_row), c = (int)(v % vec_per_row) * 8;
         const uint4 g4 = *reinterpret_cast<const uint4*>(gate + (size_t)m * row_stride_in + c);
         const uint4 u4 = *reinterpret_cast<const uint4*>(up + (size_t)m * row_stride_in + c);
-        const uint32_t gv[4] = {g4.x, g4.y, g4.z, g4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float g0 = bf16_bits_to_float(gv[j] & 0xFFFFu), g1 = bf16_bits_to_float(gv[j] >> 16);
-            const float u0 = bf16_bits_to_float(uv[j] & 0xFFFFu), u1 = bf16_bits_to_float(uv[j] >> 16);
-            const __nv_bfloat162 r = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
-            o[j] = *reinterpret_cast<const uint32_t*>(&r);
-        }
-        *reinterpret_cast<uint4*>(out + (size_t)m * row_stride_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(out + (size_t)m * row_stride_out + c) = swiglu_bf16x8(g4, u4);
     }
     // I % 8 tail columns, scalar.
     const int tail0 = vec_per_row * 8;

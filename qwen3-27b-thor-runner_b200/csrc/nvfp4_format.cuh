@@ -35,6 +35,24 @@ __device__ __forceinline__ float ue4m3_to_float(uint32_t byte) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
+// silu(x) = x / (1 + exp(-x)) in FP32 (src/engine/light_ops.cu:168-170).
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+
+// Eight BF16 gate values and eight BF16 up values -> eight BF16 bf16(silu(gate) * up), the
+// reference's SwiGLU with its single rounding (src/engine/light_ops.cu:186-187, :1566-1572).
+__device__ __forceinline__ uint4 swiglu_bf16x8(uint4 g4, uint4 u4) {
+    const uint32_t gv[4] = {g4.x, g4.y, g4.z, g4.w}, uv[4] = {u4.x, u4.y, u4.z, u4.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float g0 = bf16_bits_to_float(gv[j] & 0xFFFFu), g1 = bf16_bits_to_float(gv[j] >> 16);
+        const float u0 = bf16_bits_to_float(uv[j] & 0xFFFFu), u1 = bf16_bits_to_float(uv[j] >> 16);
+        const __nv_bfloat162 r = __floats2bfloat162_rn(silu(g0) * u0, silu(g1) * u1);
+        o[j] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // Block scales for the f16x2 dequantisation, without a table.  An unsigned E4M3 byte x (bit 7
 // ignored) equals the FP16 number whose bit pattern is x << 7, times 2^8: normal codes because
 // the exponent bias moves from 7 to 15, the subnormal codes because FP16 subnormals scale the

@@ -20,6 +20,9 @@ struct LinearArgs {
     int M, N, K;
     bool out_f32 = false;   // unrounded FP32 sums, no residual: partial results a caller reduces itself
     const nvfp4_peer_exchange* px = nullptr;   // push the sums to the peers and reduce over the group in the same kernel
+    const void* swiglu_up = nullptr;   // A is the gate half, this the up half: activations = bf16(silu(gate) * up)
+    long long a_stride = 0;            // elements between rows of A / swiglu_up (0 = K)
+    int k_valid = 0;                   // activation columns >= k_valid are zero (0 = K)
 };
 
 struct nvfp4_device_info {

@@ -254,20 +254,30 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     int st = nvfp4_linear(m->h, X, M, m->gu_packed, m->gu_scale, m->gu_gs, 2 * m->Ip, m->H, nullptr, m->gate_up_out, s);
     if (st) return st;
     const char* gate = static_cast<const char*>(m->gate_up_out);
-    st = nvfp4_swiglu_strided(m->h, gate, gate + (size_t)m->Ip * 2, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
-    if (st) return st;
-    if (P == 1 && !(m->attached && m->fused))
-        return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
-    if (m->attached && m->fused == 1 && M <= kFusedMaxM) {
-        // One kernel: the down projection pushes its unrounded sums to all ranks and reduces over
-        // the group (rank order, FP32, residual, one rounding).  `out` may alias the residual.
+    const char* up = gate + (size_t)m->Ip * 2;
+    const bool in_kernel = m->attached && m->fused == 1;     // group reduction inside the down-projection kernel
+    const bool standalone = m->attached && m->fused == 2;    // ... or by the separate push-and-sum kernel
+    if (M <= kFusedMaxM && (in_kernel || (P == 1 && !standalone))) {
+        // Two kernels in all.  The down projection forms bf16(silu(gate) * up) while it stages its
+        // activations (columns beyond I/P of the padded K count as zero) and, in a group, pushes
+        // its unrounded sums to all ranks and reduces over them (rank order, FP32, residual, one
+        // rounding) before it ends.  `out` may alias the residual.
         nvfp4_peer_exchange px{};
         for (int q = 0; q < P; ++q) px.peer[q] = m->peer[q];
         px.rank = m->comm->rank; px.world = P; px.slot_pairs = kFusedMaxM * m->H;
-        st = nvfp4_linear_reduce_peers(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, &px, s);
-        if (st != NVFP4_E_LIMIT) return st;      // a shape the GEMV kernel does not take: use the collective below
+        nvfp4_linear_desc d{};
+        d.A = gate; d.swiglu_up = up; d.a_row_stride = 2LL * m->Ip; d.k_valid = m->Ip; d.M = M;
+        d.packed = m->dn_packed; d.scale = m->dn_scale; d.global_scale = m->dn_gs; d.N = m->H; d.K = m->Kp;
+        d.residual = residual; d.C = out;
+        d.px = in_kernel ? &px : nullptr;
+        st = nvfp4_linear_ex(m->h, &d, s);
+        if (st != NVFP4_E_LIMIT) return st;      // a shape the GEMV kernel does not take: the general path below
     }
-    if (m->attached && m->fused == 2 && M <= kFusedMaxM) {
+    st = nvfp4_swiglu_strided(m->h, gate, up, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
+    if (st) return st;
+    if (P == 1 && !standalone)
+        return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
+    if (standalone && M <= kFusedMaxM) {
         // Two kernels: FP32 partial, then the stand-alone push-and-sum kernel (kept for comparison).
         st = nvfp4_linear_f32(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, m->partial, s);
         if (st == NVFP4_OK) {

@@ -13,6 +13,19 @@ LIB_PATH = os.path.join(_HERE, "lib", "libnvfp4_b200.so")
 c_void_p, c_int, c_float, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 
 
+class PeerExchange(ctypes.Structure):
+    """nvfp4_peer_exchange (include/nvfp4_b200.h)."""
+    _fields_ = [("peer", ctypes.c_void_p * 8), ("rank", ctypes.c_int), ("world", ctypes.c_int), ("slot_pairs", ctypes.c_int)]
+
+
+class LinearDesc(ctypes.Structure):
+    """nvfp4_linear_desc (include/nvfp4_b200.h)."""
+    _fields_ = [("A", ctypes.c_void_p), ("swiglu_up", ctypes.c_void_p), ("a_row_stride", ctypes.c_longlong),
+                ("k_valid", ctypes.c_int), ("M", ctypes.c_int), ("packed", ctypes.c_void_p), ("scale", ctypes.c_void_p),
+                ("global_scale", ctypes.c_float), ("N", ctypes.c_int), ("K", ctypes.c_int), ("residual", ctypes.c_void_p),
+                ("C", ctypes.c_void_p), ("px", ctypes.c_void_p)]
+
+
 class QuantizedWeight(ctypes.Structure):
     """Layout of qwen_thor::core::QuantizedWeight (reference src/engine/layer.h:197-204)."""
     _fields_ = [("packed", c_void_p), ("scale", c_void_p), ("global_scale", c_float),
@@ -34,6 +47,7 @@ SIGNATURES = {
     "nvfp4_linear_f32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_linear_reduce_peers": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p,
                                           c_void_p, c_void_p]),
+    "nvfp4_linear_ex": (c_int, [c_void_p, c_void_p, c_void_p]),
     "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
@@ -145,6 +159,14 @@ class Handle:
         self._check(self.lib.nvfp4_device_status(self.h, ctypes.byref(v)))
         return v.value
 
+    def linear_ex(self, A, M, packed, scale, global_scale, N, K, C, residual=None, swiglu_up=None, a_row_stride=0,
+                  k_valid=0, px=None, stream=None):
+        """nvfp4_linear_ex: the linear layer with SwiGLU formed while staging (A = gate half,
+        swiglu_up = up half), a row stride, a zero-padded K, and an optional peer exchange."""
+        d = LinearDesc(_ptr(A), _ptr(swiglu_up), a_row_stride, k_valid, M, _ptr(packed), _ptr(scale), global_scale, N, K,
+                       _ptr(residual), _ptr(C), None if px is None else ctypes.addressof(px))
+        self._check(self.lib.nvfp4_linear_ex(self.h, ctypes.byref(d), _stream(stream)))
+
     def linear_f32(self, A, M, packed, scale, global_scale, N, K, C_f32, stream=None):
         self._check(self.lib.nvfp4_linear_f32(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,
                                               _ptr(C_f32), _stream(stream)))
@@ -166,6 +188,10 @@ class Handle:
 
     def swiglu(self, gate, up, M, I, out, stream=None):
         self._check(self.lib.nvfp4_swiglu(self.h, _ptr(gate), _ptr(up), M, I, _ptr(out), _stream(stream)))
+
+    def swiglu_strided(self, gate, up, M, I, row_stride_in, out, row_stride_out, stream=None):
+        self._check(self.lib.nvfp4_swiglu_strided(self.h, _ptr(gate), _ptr(up), M, I, row_stride_in, _ptr(out),
+                                                  row_stride_out, _stream(stream)))
 
     def linear_host(self, A_host, M, packed, scale, global_scale, N, K, C_host, residual_host=None, stream=None):
         self._check(self.lib.nvfp4_linear_host(self.h, _ptr(A_host), M, _ptr(packed), _ptr(scale), global_scale,

@@ -490,3 +490,33 @@ def test_tp_mlp_fused_single_rank(handle, M):
     finally:
         mlp.close()
         comm.close()
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 13])
+def test_linear_ex_swiglu_prologue(handle, M):
+    """SwiGLU formed while the GEMV stages its activations (merged gate/up rows, K padded beyond
+    the tensor) gives the very bits of the separate SwiGLU kernel followed by the plain linear."""
+    import torch
+    I, Kp, N = 448, 512, 384                 # down-projection shard: 448 real columns in a K of 512
+    packed, scale = util.make_weight(N, Kp, seed=51)
+    packed[:, I // 2:] = 0                   # the padding of a shard carries zero codes and zero scales
+    scale[:, I // 16:] = 0
+    GU = util.make_bf16((M, 2 * I), seed=52)
+    R = util.make_bf16((M, N), seed=53)
+    dGU, dp, ds = util.to_dev(GU), util.to_dev(packed), util.to_dev(scale)
+    act = torch.zeros((M, Kp), dtype=torch.int16, device="cuda")
+    handle.swiglu_strided(dGU, dGU[:, I:], M, I, 2 * I, act, Kp)
+    want = ob.linear(util.pad_cols(ob.swiglu_merged(GU), Kp), packed, scale, 1.5, residual=R, mode=ob.GEMV, threads=4)
+    dC = util.to_dev(R)
+    handle.linear_ex(dGU, M, dp, ds, 1.5, N, Kp, dC, residual=dC, swiglu_up=dGU[:, I:], a_row_stride=2 * I, k_valid=I)
+    torch.cuda.synchronize()
+    got = util.to_host_u16(dC)
+    assert ob.rel_frobenius(got, want) <= TOL
+    dC2 = util.to_dev(R)
+    handle.set_option("skinny_min_m", 129)           # the plain linear through the same GEMV kernel
+    try:
+        handle.linear(act, M, dp, ds, 1.5, N, Kp, dC2, residual=dC2)
+    finally:
+        handle.set_option("skinny_min_m", 9)
+    torch.cuda.synchronize()
+    assert np.array_equal(got, util.to_host_u16(dC2))

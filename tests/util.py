@@ -40,3 +40,10 @@ def bf16_ulp_diff(a, b):
         x = x.astype(np.int32)
         return np.where(x & 0x8000, -(x & 0x7FFF), x & 0x7FFF)
     return int(np.abs(key(a) - key(b)).max()) if a.size else 0
+
+
+def pad_cols(a, cols):
+    """[M, c] -> [M, cols] with zero columns appended (BF16 bits: zero is +0.0)."""
+    out = np.zeros((a.shape[0], cols), a.dtype)
+    out[:, :a.shape[1]] = a
+    return out
