@@ -43,6 +43,7 @@ namespace {
 
 using namespace nvfp4::xchg;
 constexpr int kFusedMaxM = kMaxTokens;
+constexpr int kSwigluInStagingMaxM = 4;
 constexpr int kXCtas = 32;               // most CTAs of the stand-alone exchange kernel
 constexpr size_t kXStatusOff = kStatusOff, kXEpochOff = kEpochOff, kXDoneOff = kDoneOff, kXSlotsOff = kSlotsOff;
 constexpr long long kXWaitClocks = kWaitClocks;
@@ -257,24 +258,37 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     const char* up = gate + (size_t)m->Ip * 2;
     const bool in_kernel = m->attached && m->fused == 1;     // group reduction inside the down-projection kernel
     const bool standalone = m->attached && m->fused == 2;    // ... or by the separate push-and-sum kernel
+    // Up to kSwigluInStagingMaxM tokens the down projection forms bf16(silu(gate) * up) while it
+    // stages its activations, so the MLP is two kernels.  Every CTA of that kernel converts the
+    // activations of its own k range, i.e. the SwiGLU is recomputed once per row tile; beyond a few
+    // tokens that costs more than the separate SwiGLU launch it saves (measured: 8 tokens lose
+    // 2.8 us, 1 token gains 0.9 us on the 2-GPU shard shapes).
+    const bool swiglu_in_staging = M <= kSwigluInStagingMaxM;
+    if (!swiglu_in_staging) {
+        st = nvfp4_swiglu_strided(m->h, gate, up, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
+        if (st) return st;
+    }
     if (M <= kFusedMaxM && (in_kernel || (P == 1 && !standalone))) {
-        // Two kernels in all.  The down projection forms bf16(silu(gate) * up) while it stages its
-        // activations (columns beyond I/P of the padded K count as zero) and, in a group, pushes
-        // its unrounded sums to all ranks and reduces over them (rank order, FP32, residual, one
-        // rounding) before it ends.  `out` may alias the residual.
+        // In a group the down projection also pushes its unrounded sums to all ranks and reduces
+        // over them (rank order, FP32, residual, one rounding) before it ends.  `out` may alias
+        // the residual.  Columns beyond I/P of the padded K count as zero.
         nvfp4_peer_exchange px{};
         for (int q = 0; q < P; ++q) px.peer[q] = m->peer[q];
         px.rank = m->comm->rank; px.world = P; px.slot_pairs = kFusedMaxM * m->H;
         nvfp4_linear_desc d{};
-        d.A = gate; d.swiglu_up = up; d.a_row_stride = 2LL * m->Ip; d.k_valid = m->Ip; d.M = M;
+        if (swiglu_in_staging) { d.A = gate; d.swiglu_up = up; d.a_row_stride = 2LL * m->Ip; d.k_valid = m->Ip; }
+        else d.A = m->act;
+        d.M = M;
         d.packed = m->dn_packed; d.scale = m->dn_scale; d.global_scale = m->dn_gs; d.N = m->H; d.K = m->Kp;
         d.residual = residual; d.C = out;
         d.px = in_kernel ? &px : nullptr;
         st = nvfp4_linear_ex(m->h, &d, s);
         if (st != NVFP4_E_LIMIT) return st;      // a shape the GEMV kernel does not take: the general path below
     }
-    st = nvfp4_swiglu_strided(m->h, gate, up, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
-    if (st) return st;
+    if (swiglu_in_staging) {
+        st = nvfp4_swiglu_strided(m->h, gate, up, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
+        if (st) return st;
+    }
     if (P == 1 && !standalone)
         return nvfp4_linear(m->h, m->act, M, m->dn_packed, m->dn_scale, m->dn_gs, m->H, m->Kp, residual, out, s);
     if (standalone && M <= kFusedMaxM) {
