@@ -72,6 +72,8 @@ const char* nvfp4_status_string(int status);
  *   "prefill_impl": 0 = auto, 1 = dequant-to-workspace + CUDA-core GEMM (debug),
  *                   2 = fused dequant + tcgen05 GEMM
  *   "decode_max_m": largest M routed to the GEMV path (default 16)
+ *   "wide_gemv": 1 (default) = 9..16 tokens take one launch of the wide GEMV kernel (two
+ *                   8-token MMA tiles, activations streamed with the weights); 0 = off
  *   "skinny_min_m", "skinny_max_m": token counts (default 9..64) routed to the few-token
  *                   kernel that keeps the dequantised weights in tensor memory; min 129 or
  *                   max 0 turns it off.  "skinny_split_cost": stage-times charged to

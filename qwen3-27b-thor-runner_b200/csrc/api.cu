@@ -20,6 +20,7 @@ struct nvfp4_handle {
     int decode_impl = 0;
     int prefill_impl = 0;
     int decode_max_m = 16;
+    int wide_gemv = 1;                           // 9..16 tokens: one launch of the wide GEMV kernel
     int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
     unsigned long long launches = 0;
 };
@@ -66,6 +67,17 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
         return cuda_status(e);
     }
     const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
+    if (fast_path_wanted && h->wide_gemv && decode_wide_supported(a) &&
+        kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= h->workspace_bytes &&
+        decode_wide_scratch_bytes(h->dev.sm_count) <= kDecodeScratchBytes) {
+        // the FP16 activation copy and the per-token factors sit where the prefill kernel keeps its own
+        char* base = h->workspace + kDecodeScratchBytes + prefill_umma_reserved_bytes();
+        float* unscale = reinterpret_cast<float*>(base + ((size_t)a.M * a.K * 2 + 255) / 256 * 256);
+        int nl = 0;
+        cudaError_t e = launch_decode_wide(a, h->dev, h->workspace, base, unscale, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     if (fast_path_wanted && a.M >= h->skinny_min_m && a.M <= h->skinny_max_m && skinny_umma_supported(a) &&
         kDecodeScratchBytes + prefill_umma_reserved_bytes() <= h->workspace_bytes) {
         int nl = 0;
@@ -214,6 +226,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "decode_max_m")) {
         if (value < 0 || value > 16) return NVFP4_E_OPTION;
         h->decode_max_m = value;
+    } else if (!std::strcmp(name, "wide_gemv")) {
+        if (value < 0 || value > 1) return NVFP4_E_OPTION;
+        h->wide_gemv = value;
     } else if (!std::strcmp(name, "skinny_min_m")) {
         if (value < 1 || value > 129) return NVFP4_E_OPTION;
         h->skinny_min_m = value;
@@ -238,6 +253,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "prefill_impl")) *value = h->prefill_impl;
     else if (!std::strcmp(name, "decode_max_m")) *value = h->decode_max_m;
     else if (!std::strcmp(name, "prefill_stream_k")) *value = h->dev.prefill_stream_k;
+    else if (!std::strcmp(name, "wide_gemv")) *value = h->wide_gemv;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;

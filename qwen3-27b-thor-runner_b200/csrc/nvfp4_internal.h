@@ -68,6 +68,13 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
                                 size_t scratch_bytes, size_t offset, int* launches, cudaStream_t s);
 
 // Sets the per-kernel attributes (dynamic shared memory opt-in) once per device.
+// --- decode_wide.cu: 9..16 tokens in one GEMV launch, activations streamed through the ring.
+bool decode_wide_supported(const LinearArgs& a);
+size_t decode_wide_scratch_bytes(int sm_count);
+cudaError_t configure_decode_wide();
+cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, void* act_f16, float* unscale,
+                               int* launches, cudaStream_t s);
+
 // --- skinny_umma.cu: 1 <= M <= 128, dequantised weights as the TMEM A operand of tcgen05.mma.
 bool skinny_umma_supported(const LinearArgs& a);
 cudaError_t configure_skinny_umma();

@@ -471,6 +471,7 @@ cudaError_t configure_kernels(const nvfp4_device_info&) {
     cudaError_t e = configure_decode_mma();
     if (e == cudaSuccess) e = configure_prefill_umma();
     if (e == cudaSuccess) e = configure_skinny_umma();
+    if (e == cudaSuccess) e = configure_decode_wide();
     return e;
 }
 

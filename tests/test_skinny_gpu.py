@@ -16,7 +16,9 @@ TOL = 1e-3   # relative Frobenius error against the oracle
 def skinny(handle):
     handle.set_option("skinny_min_m", 1)
     handle.set_option("skinny_max_m", 128)
+    handle.set_option("wide_gemv", 0)
     yield handle
+    handle.set_option("wide_gemv", 1)
     handle.set_option("skinny_min_m", 9)
     handle.set_option("skinny_max_m", 64)
 
@@ -91,3 +93,36 @@ def test_skinny_matches_gemv_kernel(skinny):
     skinny.set_option("skinny_min_m", 17)
     b = run(skinny, A, packed, scale, 1.0)
     assert ob.rel_frobenius(a, b) <= 2e-4
+
+
+# ---------------------------------------------------------------- wide GEMV: 9..16 tokens in one launch
+
+@pytest.mark.parametrize("M,N,K,res", [
+    (9, 128, 256, False),         # one row tile, one half-unit
+    (12, 300, 1024, True),        # N not a multiple of the 128-row tile
+    (16, 5120, 4352, True),       # 40 row tiles split by k over all SMs (odd number of half-units per tile)
+    (16, 20000, 512, False),      # many row tiles, two half-units each
+    (11, 1000, 17408, True),      # deep K
+])
+def test_wide_gemv_vs_oracle(handle, M, N, K, res):
+    import oracle_binding as ob
+    assert handle.get_option("wide_gemv") == 1
+    packed, scale = util.make_weight(N, K, seed=M + N, sigma=0.14)
+    A = util.make_bf16((M, K), seed=M + 1)
+    R = util.make_bf16((M, N), seed=N + 2) if res else None
+    l0 = handle.launch_count()
+    got = run(handle, A, packed, scale, 1.7, residual=R)
+    assert handle.launch_count() - l0 == 2                  # the activation pre-pass + ONE GEMV launch
+    again = run(handle, A, packed, scale, 1.7, residual=R)
+    assert np.array_equal(got, again)                       # fixed summation order
+    want = ob.linear(A, packed, scale, 1.7, residual=R, mode=ob.GEMV, threads=8)
+    assert ob.rel_frobenius(got, want) <= TOL
+    handle.set_option("wide_gemv", 0)                       # the same through two launches of the 8-token kernel
+    handle.set_option("skinny_min_m", 129)
+    try:
+        two = run(handle, A, packed, scale, 1.7, residual=R)
+    finally:
+        handle.set_option("wide_gemv", 1)
+        handle.set_option("skinny_min_m", 9)
+    assert ob.rel_frobenius(got, two) <= 2e-4
+    assert handle.device_status() == 0
