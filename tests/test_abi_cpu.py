@@ -12,9 +12,10 @@ import nvfp4
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
+def declared_symbols(header=None):
+    """Function names declared in include/<header> (all headers when None)."""
     names = set()
-    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
+    for path in glob.glob(os.path.join(ROOT, "include", header or "*.h")):
         text = open(path).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names.update(re.findall(r"\b(nvfp4_[a-z0-9_]+)\s*\(", text))
@@ -23,12 +24,13 @@ def declared_symbols():
 
 def libs():
     out = [nvfp4.load()]
-    tp = os.path.join(os.path.dirname(nvfp4.LIB_PATH), "libnvfp4_b200_tp.so")
-    if os.path.exists(tp):
-        try:
-            out.append(ctypes.CDLL(tp))
-        except OSError:
-            pass
+    for name in ("libnvfp4_b200_tp.so", "libnvfp4_ckpt.so"):
+        path = os.path.join(os.path.dirname(nvfp4.LIB_PATH), name)
+        if os.path.exists(path):
+            try:
+                out.append(ctypes.CDLL(path))
+            except OSError:
+                pass
     return out
 
 
@@ -36,19 +38,20 @@ def test_library_exports_every_declared_symbol():
     loaded = libs()
     decl = declared_symbols()
     assert len(decl) >= 20
-    tp_built = len(loaded) > 1
+    assert len(loaded) == 3, "the tensor-parallel and the checkpoint library must be built"
     for name in sorted(decl):
-        if name.startswith("nvfp4_tp_") and not tp_built:
-            continue
         assert any(hasattr(l, name) for l in loaded), f"{name} declared in include/ but not exported"
 
 
 def test_binding_covers_header():
+    import nvfp4_ckpt
     import nvfp4_tp
-    decl = {n for n in declared_symbols() if not n.startswith("nvfp4_tp_")}
-    assert decl == set(nvfp4.SIGNATURES), decl ^ set(nvfp4.SIGNATURES)
-    tp = {n for n in declared_symbols() if n.startswith("nvfp4_tp_")}
+    core = declared_symbols("nvfp4_b200.h")
+    assert core == set(nvfp4.SIGNATURES), core ^ set(nvfp4.SIGNATURES)
+    tp = declared_symbols("nvfp4_b200_tp.h")
     assert tp == set(nvfp4_tp.TP_SIGNATURES), tp ^ set(nvfp4_tp.TP_SIGNATURES)
+    ck = declared_symbols("nvfp4_checkpoint.h")
+    assert ck == set(nvfp4_ckpt.CKPT_SIGNATURES), ck ^ set(nvfp4_ckpt.CKPT_SIGNATURES)
 
 
 def test_quantized_weight_layout():
