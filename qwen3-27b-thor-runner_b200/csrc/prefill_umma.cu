@@ -2,9 +2,10 @@
 //
 //   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
 //
-// One persistent CTA per SM works on 128-token x 256-weight-row output tiles.  The (tile, 256-k
-// stage) units are split evenly over the CTAs (stream-K), so small token counts still fill the
-// GPU; a tile cut by a span boundary is summed from FP32 partial tiles in a fixed order.
+// One persistent CTA per SM works on 128-token x 256-weight-row output tiles, two token tiles of
+// one weight tile at a time where the shape allows (both read the same dequantised B blocks, one
+// accumulator each), whole waves of such pairs first in an interleaved order; the tiles left over
+// are split along k over all CTAs (stream-K) and summed from FP32 partial tiles in a fixed order.
 //   warp 0      TMA producer: activation tiles (128 tokens x 64 k, FP16, 128-byte swizzle) into a
 //               4-stage ring, raw weight stages (256 rows x 256 k of packed codes + scales, 36 KB)
 //               into a 2-stage ring.  Plain tiled TMA, never cluster multicast.
@@ -68,6 +69,7 @@ struct PrefillParams {
     // stream-K region: tiles [0, sk_tiles).  A tile cut by a span boundary is finished by the CTA
     // holding its first stage, which adds the other CTAs' FP32 partial tiles in CTA order.
     int sk_tiles;
+    int sk_pairs;              // the same region counted in pairs of token tiles (see Schedule)
     float4* partials;          // [grid][2][64 column chunks][128 token rows] FP32 x 4
     unsigned int* flags;       // [grid][2], launch epoch once that partial tile is stored
     unsigned int epoch;
@@ -184,7 +186,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             const uint64_t pol_w = ptx::policy_evict_first(), pol_a = ptx::policy_evict_last();
             int sa = 0, sw = 0;
             uint32_t pa = 0, pw = 0;
-            Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
+            Schedule sched(p.sk_tiles, p.sk_pairs, p.m_tiles, p.n_tiles, kstages);
             Segment sg;
             while (sched.next(sg)) {
                 const int nt = sg.tile / p.m_tiles, mt = sg.tile % p.m_tiles;
@@ -195,10 +197,12 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                     ptx::tma_load_2d(s_ws + sw * kWScaleBytes, &tm_scale, &wfull[sw], ks * (WK / 16), nt * BN, pol_w);
                     if (++sw == kWStages) { sw = 0; pw ^= 1u; }
                     for (int j = 0; j < WK / BK; ++j) {
-                        ptx::mbar_wait(&aempty[sa], pa ^ 1u, s_abort, p.status, 0x400u + sa);
-                        ptx::mbar_arrive_expect_tx(&afull[sa], kABytes);
-                        ptx::tma_load_2d(s_a + sa * kABytes, &tm_act, &afull[sa], ks * WK + j * BK, mt * BM, pol_a);
-                        if (++sa == kAStages) { sa = 0; pa ^= 1u; }
+                        for (int i = 0; i < sg.pair; ++i) {       // one activation tile per token tile of the pair
+                            ptx::mbar_wait(&aempty[sa], pa ^ 1u, s_abort, p.status, 0x400u + sa);
+                            ptx::mbar_arrive_expect_tx(&afull[sa], kABytes);
+                            ptx::tma_load_2d(s_a + sa * kABytes, &tm_act, &afull[sa], ks * WK + j * BK, (mt + i) * BM, pol_a);
+                            if (++sa == kAStages) { sa = 0; pa ^= 1u; }
+                        }
                     }
                 }
             }
@@ -206,33 +210,43 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            int sa = 0, sb = 0, acc = 0;
-            uint32_t pa = 0, pb = 0, pt = 0;
-            Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
+            // A pair of token tiles shares every dequantised B block: eight MMAs per 64-k block instead
+            // of four for the same shared-memory fill, into both accumulators at once.  Single tiles
+            // alternate between the two accumulators so that the epilogue of one overlaps the next.
+            int sa = 0, sb = 0, next_acc = 0;
+            uint32_t pa = 0, pb = 0, ptbits = 0;      // bit a of ptbits: phase parity of accumulator a
+            Schedule sched(p.sk_tiles, p.sk_pairs, p.m_tiles, p.n_tiles, kstages);
             Segment sg;
             while (sched.next(sg)) {
-                ptx::mbar_wait(&tempty[acc], pt ^ 1u, s_abort, p.status, 0x440u + acc);
+                const int acc0 = sg.pair == 2 ? 0 : next_acc;
+                for (int i = 0; i < sg.pair; ++i)
+                    ptx::mbar_wait(&tempty[acc0 + i], ((ptbits >> (acc0 + i)) & 1u) ^ 1u, s_abort, p.status, 0x440u + acc0 + i);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
                 for (int kb = 0; kb < (sg.ks1 - sg.ks0) * (WK / BK); ++kb) {
-                    ptx::mbar_wait(&afull[sa], pa, s_abort, p.status, 0x420u + sa);
                     ptx::mbar_wait(&bfull[sb], pb, s_abort, p.status, 0x430u + sb);
                     // Both operands arrive through shared memory (TMA, or generic stores followed by
                     // fence.proxy.async before the arrive): no tcgen05 fence is needed per k-block.
-                    const uint32_t a_addr = ptx::smem_u32(s_a + sa * kABytes);
                     const uint32_t b_addr = ptx::smem_u32(s_b + sb * kBBytes);
+                    for (int i = 0; i < sg.pair; ++i) {
+                        ptx::mbar_wait(&afull[sa], pa, s_abort, p.status, 0x420u + sa);
+                        const uint32_t a_addr = ptx::smem_u32(s_a + sa * kABytes);
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(acc0 + i) * BN;
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < BK / 16; ++k) {
+                            umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
+                                     (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                        umma_commit(&aempty[sa]);  // operand buffers are free once these MMAs have read them
+                        if (++sa == kAStages) { sa = 0; pa ^= 1u; }
                     }
-                    umma_commit(&aempty[sa]);      // operand buffers are free once these MMAs have read them
                     umma_commit(&bempty[sb]);
-                    if (++sa == kAStages) { sa = 0; pa ^= 1u; }
                     if (++sb == kBBufs) { sb = 0; pb ^= 1u; }
                 }
-                umma_commit(&tfull[acc]);          // accumulator complete
-                if (++acc == kAccs) { acc = 0; pt ^= 1u; }
+                for (int i = 0; i < sg.pair; ++i) {
+                    umma_commit(&tfull[acc0 + i]);  // accumulator complete
+                    ptbits ^= 1u << (acc0 + i);
+                }
+                if (sg.pair == 1) next_acc ^= 1;
             }
         }
     } else if (warp >= 8) {
@@ -241,7 +255,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         const int sw7 = row & 7;
         int sw = 0, sb = 0;
         uint32_t pw = 0, pb = 0;
-        Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
+        Schedule sched(p.sk_tiles, p.sk_pairs, p.m_tiles, p.n_tiles, kstages);
         Segment sg;
         while (sched.next(sg)) {
             for (int ks = sg.ks0; ks < sg.ks1; ++ks) {
@@ -280,19 +294,22 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue: thread = token row
         const int ew = warp - 4;                          // TMEM lanes 32*ew .. 32*ew+31
-        int acc = 0;
-        uint32_t pt = 0;
+        int next_acc = 0;                                     // mirrors the MMA issuer's choice of accumulators
+        uint32_t ptbits = 0;                                  // bit a: phase parity of accumulator a
         const int te = ew * 32 + lane;                        // 0..127: TMEM lane, token row of the tile
         const long long sk_units = (long long)p.sk_tiles * kstages;
         int pend[2] = {-1, -1};                               // split tiles whose partial this CTA has stored
-        Schedule sched(p.sk_tiles, p.m_tiles * p.n_tiles, kstages);
+        Schedule sched(p.sk_tiles, p.sk_pairs, p.m_tiles, p.n_tiles, kstages);
         Segment sg;
         bool more = sched.next(sg);
         while (more) {
-            const int nt = sg.tile / p.m_tiles, mt = sg.tile % p.m_tiles;
+          for (int pi = 0; pi < sg.pair; ++pi) {              // the tiles of a pair one after the other
+            const int tile = sg.tile + pi;
+            const int acc = sg.pair == 2 ? pi : next_acc;
+            const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
             const int m = mt * BM + te;
             const bool complete = sg.ks0 == 0 && sg.ks1 == kstages;
-            ptx::mbar_wait(&tfull[acc], pt, s_abort, p.status, 0x470u + acc);
+            ptx::mbar_wait(&tfull[acc], (ptbits >> acc) & 1u, s_abort, p.status, 0x470u + acc);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)acc * BN;
             if (!complete) {
@@ -312,7 +329,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 __threadfence();
                 ptx::named_barrier_sync(1, kEpiWarps * 32);   // all 128 rows stored before the flag goes up
                 if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], p.epoch);
-                pend[which] = sg.tile;
+                pend[which] = tile;
             } else {
                 const float mul = (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -357,7 +374,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&tempty[acc]);
-            if (++acc == kAccs) { acc = 0; pt ^= 1u; }
+            ptbits ^= 1u << acc;
+          }
+            if (sg.pair == 1) next_acc ^= 1;
             more = sched.next(sg);
 
             // Whole tiles follow the stream-K region: these four warps reduce the split tiles now,
@@ -446,21 +465,29 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
     p.epoch = ++dev.decode_epoch;
-    const int tiles = p.m_tiles * p.n_tiles;
-    int grid = dev.sm_count < kMaxPrefillGrid ? dev.sm_count : kMaxPrefillGrid;
-    const int kstages = a.K / WK;
-    if ((long long)tiles * kstages < grid) grid = tiles * kstages;   // then every tile is split, one stage per CTA
-    // Whole waves of tiles run tile by tile; the tiles left over are split by k over all CTAs when
-    // that is shorter than one more wave of whole tiles.  The split costs about six stage-times
+    // Whole tiles are handed out in pairs of consecutive token tiles of one weight tile (a pair
+    // shares every dequantised B block, which is what the kernel is bound by); whole waves of
+    // pairs run pair by pair, the pairs left over are split tile by tile along k over all CTAs
+    // when that is shorter than one more wave.  Costs in stage-times: a pair's stage ~1.5 (eight
+    // MMAs instead of four on the same shared-memory fill), a single tile's 1, the split ~6
     // (partial tiles written, flags, reduction), measured on gate_up/down shapes at 64..8192 tokens.
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int ppn = (p.m_tiles + 1) / 2, pairs = p.n_tiles * ppn;
+    const int kstages = a.K / WK;
+    int grid = dev.sm_count < kMaxPrefillGrid ? dev.sm_count : kMaxPrefillGrid;
+    if ((long long)tiles * kstages < grid) grid = tiles * kstages;   // then every tile is split, one stage per CTA
+    auto tiles_of_pairs = [&](int np) { return (np / ppn) * p.m_tiles + ((np % ppn) * 2 < p.m_tiles ? (np % ppn) * 2 : p.m_tiles); };
+    const double pair_cost = p.m_tiles >= 2 ? 1.5 : 1.0;
     p.sk_tiles = 0;
-    const int left = tiles % grid;
+    p.sk_pairs = 0;
+    const int left = pairs % grid;
     if (dev.prefill_stream_k && left > 0) {
-        int sk = left;
-        if (sk * kstages < grid) sk += tiles >= grid ? grid : 0;           // every CTA gets at least one stage
-        const long long whole = (long long)((tiles + grid - 1) / grid) * kstages;
-        const long long split = (long long)((tiles - sk) / grid) * kstages + ((long long)sk * kstages + grid - 1) / grid + 6;
-        if (split < whole && (long long)sk * kstages >= grid) p.sk_tiles = sk;
+        int skp = left;
+        if ((long long)tiles_of_pairs(skp) * kstages < grid) skp += pairs >= grid ? grid : 0;   // every CTA gets at least one stage
+        const int skt = tiles_of_pairs(skp);
+        const double whole = (double)((pairs + grid - 1) / grid) * kstages * pair_cost;
+        const double split = (double)((pairs - skp) / grid) * kstages * pair_cost + (double)(((long long)skt * kstages + grid - 1) / grid) + 6.0;
+        if (split < whole && (long long)skt * kstages >= grid) { p.sk_pairs = skp; p.sk_tiles = skt; }
     }
     prefill_umma_kernel<<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
     if (launches) *launches = 2;

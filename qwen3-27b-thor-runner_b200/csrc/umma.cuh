@@ -12,21 +12,40 @@ namespace nvfp4 {
 namespace umma {
 
 // Work of one CTA: first its share of the stream-K region (tiles [0, sk_tiles), cut into
-// (tile, stage) units and split evenly over the CTAs), then whole tiles sk_tiles + blockIdx.x +
-// i * gridDim.x.  The interleaved order keeps the CTAs that share a weight tile in step, so the
-// tile is fetched from HBM once and read from L2 by the others.  Every role walks the same list.
+// (tile, stage) units and split evenly over the CTAs), then whole tiles (or pairs of tiles)
+// blockIdx.x + i * gridDim.x behind that region.  The interleaved order keeps the CTAs that share
+// a weight tile in step, so the tile is fetched from HBM once and read from L2 by the others.
+// Every role walks the same list.
 struct Segment {
     int tile, ks0, ks1;
+    int pair;     // 1, or 2: tiles `tile` and `tile + 1` (same weight rows, consecutive token tiles) over the whole k range
 };
 struct Schedule {
     long long u, u_end;
-    int dp_tile, num_tiles, kstages;
+    int dp, dp_end, kstages;
+    int m_tiles, pairs_per_nt;        // pairs_per_nt == 0: whole tiles are handed out one by one
+    // Whole tiles one by one: tiles [0, sk_tiles) are the stream-K region.
     __device__ __forceinline__ Schedule(int sk_tiles, int tiles, int kst) {
+        init_sk(sk_tiles, kst);
+        dp = sk_tiles + blockIdx.x;
+        dp_end = tiles;
+        m_tiles = 1;
+        pairs_per_nt = 0;
+    }
+    // Whole tiles in pairs of consecutive token tiles of one weight tile (the last pair of a
+    // weight tile is a single when m_tiles is odd); the pairs [0, sk_pairs) -- tiles [0, sk_tiles)
+    // -- are the stream-K region, handled tile by tile.
+    __device__ __forceinline__ Schedule(int sk_tiles, int sk_pairs, int m_tiles_, int n_tiles, int kst) {
+        init_sk(sk_tiles, kst);
+        m_tiles = m_tiles_;
+        pairs_per_nt = (m_tiles_ + 1) / 2;
+        dp = sk_pairs + blockIdx.x;
+        dp_end = n_tiles * pairs_per_nt;
+    }
+    __device__ __forceinline__ void init_sk(int sk_tiles, int kst) {
         const long long sk_units = (long long)sk_tiles * kst;
         u = (long long)blockIdx.x * sk_units / gridDim.x;
         u_end = (long long)(blockIdx.x + 1) * sk_units / gridDim.x;
-        dp_tile = sk_tiles + blockIdx.x;
-        num_tiles = tiles;
         kstages = kst;
     }
     __device__ __forceinline__ bool next(Segment& s) {
@@ -35,14 +54,22 @@ struct Schedule {
             s.ks0 = (int)(u % kstages);
             const long long room = u_end - u;
             s.ks1 = (kstages - s.ks0) < room ? kstages : s.ks0 + (int)room;
+            s.pair = 1;
             u += s.ks1 - s.ks0;
             return true;
         }
-        if (dp_tile < num_tiles) {
-            s.tile = dp_tile;
+        if (dp < dp_end) {
+            if (pairs_per_nt == 0) {
+                s.tile = dp;
+                s.pair = 1;
+            } else {
+                const int nt = dp / pairs_per_nt, mp = dp - nt * pairs_per_nt;
+                s.tile = nt * m_tiles + 2 * mp;
+                s.pair = m_tiles - 2 * mp >= 2 ? 2 : 1;
+            }
             s.ks0 = 0;
             s.ks1 = kstages;
-            dp_tile += gridDim.x;
+            dp += gridDim.x;
             return true;
         }
         return false;
