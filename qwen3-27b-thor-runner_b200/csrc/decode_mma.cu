@@ -41,34 +41,23 @@
 #include "exchange_layout.h"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
+#include "gemv_common.cuh"
 #include "ptx.cuh"
 
 namespace nvfp4 {
 namespace {
 
-constexpr int kRT = 128;                          // rows per half-unit
-constexpr int kKC = 256;                          // k elements per half-unit
-constexpr int kGroupWarps = 8;                    // warps that share one half-unit (16 rows each)
+using namespace gemv;
+
+
 // GROUPS consumer groups per CTA; group h takes half-unit h of every stage, so a stage carries
-// GROUPS half-units.  GROUPS = 2: one 17-warp CTA per SM.  GROUPS = 1: 9-warp CTAs, two per SM
-// when the activations are small -- the prologue and the epilogue chains of one CTA then
-// overlap the other CTA's streaming.
-constexpr int kPackedBytes = kRT * kKC / 2;       // 16384 per half-unit
-constexpr int kScaleBytes = kRT * kKC / 16;       // 2048 per half-unit
-constexpr int kActBlockBytes = 128 + 16;          // 64 k of FP16 + 16 bytes of padding
-constexpr int kActRowBytes = 4 * kActBlockBytes;  // 576 per token per half-unit: four padded 64-k blocks
+// GROUPS half-units.  GROUPS = 2: one 17-warp CTA per SM (what the library uses).  GROUPS = 1:
+// 9-warp CTAs, two per SM when the activations are small (measured slower).
 constexpr int kMaxTokens = 8;                     // tokens per launch (one 8-column MMA tile)
-constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 output tile
 constexpr uint32_t kTxBytes = kPackedBytes + kScaleBytes;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 227 * 1024;           // one CTA per SM
 constexpr int kSmemBudgetHalf = 113 * 1024;       // two CTAs per SM
-
-// Scratch layout (handle workspace): status word, per-CTA flags, per-CTA partial tiles.
-// A flag word holds the launch epoch once the CTA's partial for that 16-row slab is stored.
-constexpr size_t kFlagsOffset = 256;          // kGroupWarps flag words per CTA (one per 16-row slab)
-constexpr size_t kPartialOffset = 16384;
-constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kGroupWarps));
 
 struct DecodeParams {
     const __nv_bfloat16* A;         // activations, or the gate half when A_up is set
@@ -91,22 +80,6 @@ struct DecodeParams {
     unsigned char* xpeer[xchg::kMaxWorld];
     int xrank, xworld, xslot_pairs;
 };
-
-// Activation row of one (k-chunk, token): four 64-k blocks of 128 bytes, each followed by 16
-// bytes of padding.  Lane (g, t) of a consumer warp reads block t of token g, 16 bytes at a
-// time at immediate offsets; with the padding the 8 lanes of a quarter-warp (2 tokens x 4
-// blocks) hit 8 different 16-byte bank groups ((4*token + t + chunk) mod 8), no XOR needed.
-__device__ __forceinline__ int act_chunk_offset(int c) { return (c >> 3) * kActBlockBytes + (c & 7) * 16; }
-
-// Eight packed E2M1 codes (one 32-bit word, 8 consecutive k of one row) -> four f16x2 registers
-// holding e2m1 * block scale, in k order.  The hardware conversion is exact and the products
-// are exact in FP16 (2 x 4 significant bits; every value within [2^-10, 2880]).
-__device__ __forceinline__ void expand_u32(uint32_t q, uint32_t S, uint32_t (&d)[4]) {
-    uint32_t e[4];
-    ptx::cvt_e2m1x8_to_f16x2(q, e);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = ptx::mul_f16x2(e[i], S);
-}
 
 // PROBE selects measurement-only variants (the library instantiates PROBE = 0 only):
 //   bit 0: consumers skip the math (ring hand-shake only)   bit 3: producer moves no data
@@ -250,28 +223,46 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         // Pass A: one trip to global memory, eight chunks in flight per thread; the raw BF16 chunk
         // goes to its final (swizzled) place, the magnitudes feed the per-token maximum.
         for (int base = tid; base < total; base += 8 * kConsumerThreads) {
-            uint4 x[8], y[8];
-            int tk[8], dst[8];
+            uint4 x[8];
+            int tk[8], dst[8];      // dst: byte offset of the chunk; -1 = no chunk, <= -2 = a zero chunk (encodes -2 - offset)
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                x[u] = y[u] = make_uint4(0u, 0u, 0u, 0u);
+                x[u] = make_uint4(0u, 0u, 0u, 0u);
                 tk[u] = 0;
                 dst[u] = -1;
                 const int id = base + u * kConsumerThreads;
                 if (id < total) {
                     int j, c;
                     const uint4* src = chunk_src(id, j, tk[u], c);
-                    if (src) {
-                        x[u] = __ldg(src);
-                        if (p.A_up) y[u] = __ldg(src + (p.A_up - p.A) / 8);      // same row and column of the up half
+                    if (src) x[u] = __ldg(src);
+                    dst[u] = src ? (j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c) : -2 - ((j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c));
+                }
+            }
+            if (p.A_up) {
+                // SwiGLU on the fly: the up half sits (A_up - A) elements behind the gate half; four
+                // chunks at a time keep the registers in bounds.
+                const long long up_off = (p.A_up - p.A) / 8;
+#pragma unroll
+                for (int h4 = 0; h4 < 8; h4 += 4) {
+                    uint4 y[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        y[u] = make_uint4(0u, 0u, 0u, 0u);
+                        const int id = base + (h4 + u) * kConsumerThreads;
+                        if (id < total && dst[h4 + u] >= 0) {
+                            int j, tkk, c;
+                            y[u] = __ldg(chunk_src(id, j, tkk, c) + up_off);
+                        }
                     }
-                    dst[u] = (j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (dst[h4 + u] >= 0) x[h4 + u] = swiglu_bf16x8(x[h4 + u], y[u]);
                 }
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                if (dst[u] < 0) continue;   // uniform across the warp: total is a multiple of 32
-                if (p.A_up) x[u] = swiglu_bf16x8(x[u], y[u]);   // zero chunks stay zero: silu(0) * 0
+                if (dst[u] == -1) continue;   // uniform across the warp: total is a multiple of 32
+                if (dst[u] < 0) dst[u] = -2 - dst[u];           // a chunk beyond k_valid: stays zero
                 const uint32_t v[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
                 uint32_t m = 0;
 #pragma unroll
@@ -348,10 +339,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             // (Looking at the start of the segment instead put two L2 round trips in front of the
             // first stage of every owner: 1.8 us per launch on a B200.)
             if (grp == 0 && owner && !prefetched && !(PROBE & 32) && seg_end - hu <= 2 * GROUPS) {
-                int ready = 1;
-                if (lane == 0)
-                    for (int c = cta + 1; c <= last; ++c) ready &= (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) == p.epoch);
-                ready = __shfl_sync(0xffffffffu, ready, 0);
+                // one lane per contributor, so that the flag round trips overlap
+                int mine_ready = 1;
+                for (int c = cta + 1 + lane; c <= last; c += 32)
+                    mine_ready &= (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) == p.epoch);
+                const int ready = __all_sync(0xffffffffu, mine_ready);
                 if (ready) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -449,9 +441,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 if (lane == 0) ptx::st_release_gpu(&flags[cta * kGroupWarps + gw], p.epoch);
             } else {
                 if (!prefetched) {
-                    if (lane == 0) {
+                    {   // one lane per contributor, so that the flag round trips overlap
                         const long long t0 = clock64();
-                        for (int c = cta + 1; c <= last; ++c) {
+                        for (int c = cta + 1 + lane; c <= last; c += 32) {
                             while (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) != p.epoch) {
                                 if (*s_abort) break;
                                 if (clock64() - t0 > ptx::kWaitBudgetClocks) {

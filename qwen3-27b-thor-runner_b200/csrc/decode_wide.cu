@@ -1,5 +1,5 @@
-// Dequant-GEMV for 9..16 tokens in one launch: the GEMV kernel's skeleton (decode_mma.cu) with a
-// second 8-token MMA tile per weight fragment and the activations streamed through the ring.
+// Dequant-GEMV for 9..16 tokens in one launch: the GEMV kernel's consumer math (decode_mma.cu) with
+// a second 8-token MMA tile per weight fragment and the activations streamed through the ring.
 //
 //   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
 //
@@ -9,20 +9,23 @@
 // shared memory next to the ring (160 KB for K = 5120).  Here they travel with the weights:
 //   * a pre-pass (act_f16.cu) writes the FP16 copy of the activations, scaled per token by an
 //     exact power of two, into the handle workspace;
-//   * warp 16 streams the weight half-units (128 rows x 256 k: 16 KB of codes + 2 KB of scales),
-//     two per stage, with plain tiled TMA (no multicast); warp 17 copies the matching activations
-//     (16 token rows x 256 k) with 16-byte cp.async into the padded row layout of the GEMV kernel
-//     (four 64-k blocks of 128 + 16 bytes per token: the consumers' LDS.128 then use immediate
-//     offsets and hit all bank groups; the 128-byte TMA swizzle would give 4-way conflicts with
-//     this thread-to-k mapping), once the pre-pass has finished (programmatic dependent launch:
-//     the weight stream does not wait for it);
-//   * consumer group h (8 warps, 16 rows each) works on half-unit h of every stage: codes expanded
-//     in registers exactly as in the GEMV kernel, then mma.sync m16n8k16 against the two token
-//     tiles (tokens 0..7 and 8..15), FP32 accumulators;
-//   * stream-K over the half-units with the same deterministic fix-up: contributors store FP32
-//     partials and raise an epoch flag per 16-row slab, the CTA that holds a row tile's first
-//     half-unit adds them in CTA order, applies the token's unscale, 2^8 / global_scale and the
-//     residual in FP32 and rounds once.  Every wait is bounded and reports through the status word.
+//   * the work unit is 256 weight rows x 256 k (32 KB of codes + 4 KB of scales), one per ring
+//     stage; the units, row-pair-major, are split evenly over the CTAs (stream-K);
+//   * warp 16 streams the units with plain tiled TMA (no multicast); warp 17 copies the unit's
+//     activations (16 token rows x 256 k) with 16-byte cp.async into the padded row layout of the
+//     GEMV kernel (four 64-k blocks of 128 + 16 bytes per token: the consumers' LDS.128 then use
+//     immediate offsets and hit all bank groups; the 128-byte TMA swizzle would give 4-way
+//     conflicts with this thread-to-k mapping), once the pre-pass has finished (programmatic
+//     dependent launch: the weight stream does not wait for it);
+//   * each of the 16 consumer warps owns 16 of the unit's 256 rows over the whole k range of its
+//     CTA: codes expanded in registers exactly as in the GEMV kernel, then mma.sync m16n8k16
+//     against the two token tiles (tokens 0..7 and 8..15), FP32 accumulators.  All warps read the
+//     same 9 KB of activations, so a stage is 45 KB and five of them fit;
+//   * a row pair whose k range is split over several CTAs is finished warp by warp, without any
+//     CTA-wide step: contributors store FP32 partials and raise an epoch flag per 16-row slab, the
+//     CTA that holds the row pair's first unit adds them in CTA order, applies the token's unscale,
+//     2^8 / global_scale and the residual in FP32 and rounds once.  Every wait is bounded and
+//     reports through the status word.
 // Arithmetic: the reference's small-M kernel (src/engine/dense_gemm_fp4_sm110.cu:155-258) up to
 // FP32 summation order.
 #include <cuda.h>
@@ -30,33 +33,27 @@
 
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
+#include "gemv_common.cuh"
 #include "ptx.cuh"
 #include "umma.cuh"
 
 namespace nvfp4 {
 namespace {
 
-constexpr int kRT = 128;                          // rows per half-unit
-constexpr int kKC = 256;                          // k per half-unit
-constexpr int kGroupWarps = 8, kGroups = 2;
-constexpr int kConsumerWarps = kGroupWarps * kGroups;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 64;   // + weight producer warp + activation producer warp
+using namespace gemv;
+
+constexpr int kUnitRows = 2 * kRT;                // 256 weight rows per unit
+constexpr int kConsumerWarps = kUnitRows / 16;    // 16: one 16-row slab each
+constexpr int kThreads = kConsumerWarps * 32 + 64;   // + weight producer warp + activation producer warp
 constexpr int kTT = 2;                            // 8-token MMA tiles per launch
 constexpr int kTokens = 8 * kTT;
-constexpr int kPackedBytes = kRT * kKC / 2;       // 16384
-constexpr int kScaleBytes = kRT * kKC / 16;       // 2048
-constexpr int kActBlockBytes = 128 + 16;          // 64 k of FP16 + 16 bytes of padding
-constexpr int kActRowBytes = 4 * kActBlockBytes;  // 576 per token per half-unit
-constexpr int kActBytes = kTokens * kActRowBytes; // per half-unit: 9 KB
-constexpr int kStageBytes = kGroups * (kPackedBytes + kScaleBytes + kActBytes);   // 54 KB
-constexpr int kOutLd = kRT + 4;
-constexpr int kMaxStages = 4;
+constexpr int kUnitPackedBytes = kUnitRows * kKC / 2;     // 32 KB
+constexpr int kUnitScaleBytes = kUnitRows * kKC / 16;     // 4 KB
+constexpr int kActBytes = kTokens * kActRowBytes;         // 9 KB
+constexpr int kStageBytes = kUnitPackedBytes + kUnitScaleBytes + kActBytes;   // 45 KB
+constexpr int kMaxStages = 5;
 constexpr int kSmemBudget = 227 * 1024;
-// Scratch layout in the handle workspace, as in the GEMV kernel: status word, flags, partial tiles.
-constexpr size_t kFlagsOffset = 256;
-constexpr size_t kPartialOffset = 16384;
-constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kGroupWarps));
+constexpr int kWideMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kConsumerWarps));   // 16 flag words per CTA
 
 struct WideParams {
     const __nv_bfloat16* residual;
@@ -71,24 +68,16 @@ struct WideParams {
     unsigned int epoch;
 };
 
-__device__ __forceinline__ void expand_u32(uint32_t q, uint32_t S, uint32_t (&d)[4]) {
-    uint32_t e[4];
-    ptx::cvt_e2m1x8_to_f16x2(q, e);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = ptx::mul_f16x2(e[i], S);
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                    const WideParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int stages = p.stages;
-    unsigned char* s_packed = smem;                                        // stages x 2 x 16 KB
-    unsigned char* s_act = s_packed + stages * kGroups * kPackedBytes;     // stages x 2 x 9 KB
-    unsigned char* s_scale = s_act + stages * kGroups * kActBytes;         // stages x 2 x 2 KB
-    float* s_out = reinterpret_cast<float*>(s_scale + stages * kGroups * kScaleBytes);   // one FP32 exchange tile
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_out + kTokens * kOutLd);
+    unsigned char* s_packed = smem;                                   // stages x 32 KB, 1024-aligned
+    unsigned char* s_act = s_packed + stages * kUnitPackedBytes;      // stages x 9 KB
+    unsigned char* s_scale = s_act + stages * kActBytes;              // stages x 4 KB
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_scale + stages * kUnitScaleBytes);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
 
@@ -98,7 +87,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, G = gridDim.x;
-    const int u_begin = (int)((long long)cta * p.units / G);     // half-units [u_begin, u_end) of this CTA
+    const int u_begin = (int)((long long)cta * p.units / G);     // units [u_begin, u_end) of this CTA
     const int u_end = (int)((long long)(cta + 1) * p.units / G);
     const int kc_begin = u_begin % p.kchunks;
 
@@ -126,50 +115,35 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
         const uint64_t pol = ptx::policy_evict_first();
         int stage = 0;
         uint32_t ph = 0;
-        int hu = u_begin, tile = u_begin / p.kchunks, kc = kc_begin;
-        while (hu < u_end) {
-            const int tile_end = hu - kc + p.kchunks;
-            const int seg_end = tile_end < u_end ? tile_end : u_end;
-            const int row0 = tile * kRT;
-            while (hu < seg_end) {
-                const int cnt = (seg_end - hu) >= kGroups ? kGroups : 1;
-                ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, (acts ? 0x610u : 0x600u) + (unsigned)stage);
-                const int k0 = kc * kKC;
-                if (acts) {
-                    // chunk id = token * 32 + c: 16 bytes = 8 consecutive k of one token; token rows >= M are zero-filled
-                    for (int h = 0; h < cnt; ++h) {
-                        unsigned char* dst = s_act + (stage * kGroups + h) * kActBytes;
+        int pair = u_begin / p.kchunks, kc = kc_begin;
+        for (int u = u_begin; u < u_end; ++u) {
+            ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, (acts ? 0x610u : 0x600u) + (unsigned)stage);
+            const int k0 = kc * kKC;
+            if (acts) {
+                // chunk id = token * 32 + c: 16 bytes = 8 consecutive k of one token; token rows >= M are zero-filled
+                unsigned char* dst = s_act + stage * kActBytes;
 #pragma unroll 4
-                        for (int id = lane; id < kTokens * 32; id += 32) {
-                            const int tok = id >> 5, c = id & 31;
-                            const bool live = tok < p.M;
-                            const unsigned short* src = p.act + (size_t)(live ? tok : 0) * p.K + k0 + h * kKC + c * 8;
-                            ptx::cp_async_16(dst + tok * kActRowBytes + (c >> 3) * kActBlockBytes + (c & 7) * 16, src, live ? 16u : 0u);
-                        }
-                    }
-                    ptx::cp_async_mbar_arrive_noinc(&full_bar[stage]);
-                } else {
-                    ptx::mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)((kPackedBytes + kScaleBytes) * cnt));
-                    for (int h = 0; h < cnt; ++h) {
-                        ptx::tma_load_2d(s_packed + (stage * kGroups + h) * kPackedBytes, &tm_packed, &full_bar[stage],
-                                         (k0 + h * kKC) >> 1, row0, pol);
-                        ptx::tma_load_2d(s_scale + (stage * kGroups + h) * kScaleBytes, &tm_scale, &full_bar[stage],
-                                         (k0 + h * kKC) >> 4, row0, pol);
-                    }
+                for (int id = lane; id < kTokens * 32; id += 32) {
+                    const int tok = id >> 5, c = id & 31;
+                    const bool live = tok < p.M;
+                    const unsigned short* src = p.act + (size_t)(live ? tok : 0) * p.K + k0 + c * 8;
+                    ptx::cp_async_16(dst + tok * kActRowBytes + act_chunk_offset(c), src, live ? 16u : 0u);
                 }
-                hu += cnt;
-                kc += cnt;
-                if (++stage == stages) { stage = 0; ph ^= 1u; }
+                ptx::cp_async_mbar_arrive_noinc(&full_bar[stage]);
+            } else {
+                ptx::mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(kUnitPackedBytes + kUnitScaleBytes));
+                ptx::tma_load_2d(s_packed + stage * kUnitPackedBytes, &tm_packed, &full_bar[stage], k0 >> 1, pair * kUnitRows, pol);
+                ptx::tma_load_2d(s_scale + stage * kUnitScaleBytes, &tm_scale, &full_bar[stage], k0 >> 4, pair * kUnitRows, pol);
             }
-            if (kc >= p.kchunks) { kc = 0; ++tile; }
+            if (++kc == p.kchunks) { kc = 0; ++pair; }
+            if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
         return;
     }
 
     // ---------------------------------------------------------------------- consumer warps
-    const int grp = warp / kGroupWarps, gw = warp % kGroupWarps;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = gw * 16 + g;                                // tile rows r0 and r0 + 8
+    const int r0 = warp * 16 + g;                              // unit rows r0 and r0 + 8
     const int off_w0 = r0 * 128 + (((2 * t) ^ g) << 4);       // row r0, logical 16-byte chunk 2t (swizzle: chunk ^ (row & 7))
     const int off_w1 = r0 * 128 + (((2 * t + 1) ^ g) << 4);
     const int off_s = r0 * 16 + 4 * t;                         // 4 scale bytes: blocks 4t..4t+3 of the row
@@ -179,138 +153,119 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 
     int stage = 0;
     uint32_t ph = 0;
-    int hu = u_begin, tile = u_begin / p.kchunks, kc = kc_begin;
-    while (hu < u_end) {
+    int u = u_begin, pair = u_begin / p.kchunks, kc = kc_begin;
+    while (u < u_end) {
         const int kc_first = kc;
-        const int tile_end = hu - kc + p.kchunks;
-        const int seg_end = tile_end < u_end ? tile_end : u_end;
+        const int pair_end = u - kc + p.kchunks;               // first unit of the next row pair
+        const int seg_end = pair_end < u_end ? pair_end : u_end;
         float acc[kTT][4];
 #pragma unroll
         for (int j = 0; j < kTT; ++j)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-        while (hu < seg_end) {
-            const int cnt = (seg_end - hu) >= kGroups ? kGroups : 1;
-            hu += cnt;
-            kc += cnt;
-            // Every warp waits on every stage in order (an mbarrier waiter may not skip a phase);
-            // group 1 has nothing to do in a stage that carries a single half-unit.
+        for (; u < seg_end; ++u) {
             ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0x620u + (unsigned)stage);
-            if (grp < cnt) {
-                const unsigned char* wp = s_packed + (stage * kGroups + grp) * kPackedBytes;
-                const unsigned char* sp = s_scale + (stage * kGroups + grp) * kScaleBytes + off_s;
-                const unsigned char* ap = s_act + (stage * kGroups + grp) * kActBytes + off_a;
-                const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
-                const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
-                const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + off_w0 + 8 * 128);
-                const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + off_w1 + 8 * 128);
-                const uint32_t qa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
-                const uint32_t qb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-                uint32_t Sa[4], Sb[4];                         // block scales / 2^8 as f16x2, formed from the bytes
-                {
-                    const uint32_t ba = mask_scale_bytes(*reinterpret_cast<const uint32_t*>(sp));
-                    const uint32_t bb = mask_scale_bytes(*reinterpret_cast<const uint32_t*>(sp + 8 * 16));
+            const unsigned char* wp = s_packed + stage * kUnitPackedBytes;
+            const unsigned char* sp = s_scale + stage * kUnitScaleBytes + off_s;
+            const unsigned char* ap = s_act + stage * kActBytes + off_a;
+            const uint4 wa0 = *reinterpret_cast<const uint4*>(wp + off_w0);
+            const uint4 wa1 = *reinterpret_cast<const uint4*>(wp + off_w1);
+            const uint4 wb0 = *reinterpret_cast<const uint4*>(wp + off_w0 + 8 * 128);
+            const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + off_w1 + 8 * 128);
+            const uint32_t qa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
+            const uint32_t qb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
+            uint32_t Sa[4], Sb[4];                             // block scales / 2^8 as f16x2, formed from the bytes
+            {
+                const uint32_t ba = mask_scale_bytes(*reinterpret_cast<const uint32_t*>(sp));
+                const uint32_t bb = mask_scale_bytes(*reinterpret_cast<const uint32_t*>(sp + 8 * 16));
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        Sa[b] = scale_byte_to_f16x2(ba, b);
-                        Sb[b] = scale_byte_to_f16x2(bb, b);
-                    }
+                for (int b = 0; b < 4; ++b) {
+                    Sa[b] = scale_byte_to_f16x2(ba, b);
+                    Sb[b] = scale_byte_to_f16x2(bb, b);
                 }
-                float acc2[kTT][4];                            // second accumulators: halve the MMA dependency chains
-#pragma unroll
-                for (int j = 0; j < kTT; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc2[j][i] = 0.0f;
-#pragma unroll
-                for (int uu = 0; uu < 8; ++uu) {
-                    uint32_t da[4], db[4];
-                    expand_u32(qa[uu], Sa[uu >> 1], da);
-                    expand_u32(qb[uu], Sb[uu >> 1], db);
-                    const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // k 0..3 of this 8-group: rows g, g+8
-                    const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // k 4..7
-#pragma unroll
-                    for (int j = 0; j < kTT; ++j) {
-                        const uint4 x = *reinterpret_cast<const uint4*>(ap + j * (8 * kActRowBytes) + uu * 16);   // token tile j: tokens 8j..8j+7
-                        ptx::mma_f16_16x8x16(acc[j], a_lo, x.x, x.y);
-                        ptx::mma_f16_16x8x16(acc2[j], a_hi, x.z, x.w);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kTT; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[j][i] += acc2[j][i];
             }
+            float acc2[kTT][4];                                // second accumulators: halve the MMA dependency chains
+#pragma unroll
+            for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc2[j][i] = 0.0f;
+#pragma unroll
+            for (int uu = 0; uu < 8; ++uu) {
+                uint32_t da[4], db[4];
+                expand_u32(qa[uu], Sa[uu >> 1], da);
+                expand_u32(qb[uu], Sb[uu >> 1], db);
+                const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // k 0..3 of this 8-group: rows g, g+8
+                const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // k 4..7
+#pragma unroll
+                for (int j = 0; j < kTT; ++j) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(ap + j * (8 * kActRowBytes) + uu * 16);   // token tile j: tokens 8j..8j+7
+                    ptx::mma_f16_16x8x16(acc[j], a_lo, x.x, x.y);
+                    ptx::mma_f16_16x8x16(acc2[j], a_hi, x.z, x.w);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[j][i] += acc2[j][i];
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty_bar[stage]);
             if (++stage == stages) { stage = 0; ph ^= 1u; }
         }
+        kc += seg_end - (pair_end - p.kchunks + kc_first);     // units consumed in this segment
 
-        // ------------------------------------------------------------ segment epilogue
-        // Rows belong to warp pairs (warp gw of either group): group 1 hands its sums over through
-        // shared memory, group 0 finishes -- thread (g,t) holds rows r0, r0+8 x tokens 8j+2t, 8j+2t+1.
-        float* xchg = s_out;
+        // ------------------------------------------------------------ segment epilogue, warp by warp
+        // Thread (g,t) holds rows r0, r0+8 x tokens 8j+2t, 8j+2t+1 of the row pair.
         const bool owner = (kc_first == 0);
-        const bool complete = owner && (seg_end == tile_end);
-        if (grp == 1) {
-#pragma unroll
-            for (int j = 0; j < kTT; ++j) {
-                xchg[(8 * j + 2 * t) * kOutLd + r0] = acc[j][0];
-                xchg[(8 * j + 2 * t + 1) * kOutLd + r0] = acc[j][1];
-                xchg[(8 * j + 2 * t) * kOutLd + r0 + 8] = acc[j][2];
-                xchg[(8 * j + 2 * t + 1) * kOutLd + r0 + 8] = acc[j][3];
-            }
-        }
-        ptx::named_barrier_sync(4 + gw, 64);
-        if (grp == 0) {
-            int last = cta;                                    // contributors are CTAs cta+1 .. last
-            if (owner && !complete) {
-                while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
-                if (lane == 0) {
-                    const long long t0 = clock64();
-                    for (int c = cta + 1; c <= last; ++c) {
-                        while (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) != p.epoch) {
-                            if (*s_abort) break;
-                            if (clock64() - t0 > ptx::kWaitBudgetClocks) {
-                                *s_abort = 1;
-                                atomicCAS(status, 0u, 0x630u);
-                                break;
-                            }
+        const bool complete = owner && (seg_end == pair_end);
+        int last = cta;                                        // contributors are CTAs cta+1 .. last
+        if (owner && !complete) {
+            while (last + 1 < G && (long long)(last + 1) * p.units / G < pair_end) ++last;
+            // one lane per contributor (32 at a time), so that the flag round trips overlap
+            const long long t0 = clock64();
+            for (int c0 = cta + 1; c0 <= last; c0 += 32) {
+                const int c = c0 + lane;
+                if (c <= last) {
+                    while (ptx::ld_acquire_gpu(&flags[c * kConsumerWarps + warp]) != p.epoch) {
+                        if (*s_abort) break;
+                        if (clock64() - t0 > ptx::kWaitBudgetClocks) {
+                            *s_abort = 1;
+                            atomicCAS(status, 0u, 0x630u);
+                            break;
                         }
                     }
                 }
-                __syncwarp();
             }
-            const int row_base = tile * kRT;
+            __syncwarp();
+        }
+        const int row_base = pair * kUnitRows;
 #pragma unroll
-            for (int j = 0; j < kTT; ++j) {
-                const int mm[4] = {8 * j + 2 * t, 8 * j + 2 * t + 1, 8 * j + 2 * t, 8 * j + 2 * t + 1};
-                const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
+        for (int j = 0; j < kTT; ++j) {
+            const int mm[4] = {8 * j + 2 * t, 8 * j + 2 * t + 1, 8 * j + 2 * t, 8 * j + 2 * t + 1};
+            const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (mm[i] >= p.M) continue;
-                    float v = (acc[j][i] + xchg[mm[i] * kOutLd + rr[i]]) * p.unscale[mm[i]];
-                    if (!owner) {
-                        __stcg(partials + (size_t)cta * (kTokens * kRT) + mm[i] * kRT + rr[i], v);
-                        continue;
-                    }
-                    for (int c = cta + 1; c <= last; ++c)
-                        v += __ldcg(partials + (size_t)c * (kTokens * kRT) + mm[i] * kRT + rr[i]);
-                    const int n = row_base + rr[i];
-                    if (n >= p.N) continue;
-                    float x = (v * kBlockScaleUnfold) * p.inv_gs;
-                    const size_t o = (size_t)mm[i] * p.N + n;
-                    if (p.residual) x += __bfloat162float(p.residual[o]);
-                    p.C[o] = __float2bfloat16_rn(x);
+            for (int i = 0; i < 4; ++i) {
+                if (mm[i] >= p.M) continue;
+                float v = acc[j][i] * p.unscale[mm[i]];
+                if (!owner) {
+                    __stcg(partials + (size_t)cta * (kTokens * kUnitRows) + mm[i] * kUnitRows + rr[i], v);
+                    continue;
                 }
-            }
-            if (!owner) {
-                __syncwarp();
-                if (lane == 0) ptx::st_release_gpu(&flags[cta * kGroupWarps + gw], p.epoch);
+                for (int c = cta + 1; c <= last; ++c)
+                    v += __ldcg(partials + (size_t)c * (kTokens * kUnitRows) + mm[i] * kUnitRows + rr[i]);
+                const int n = row_base + rr[i];
+                if (n >= p.N) continue;
+                float x = (v * kBlockScaleUnfold) * p.inv_gs;
+                const size_t o = (size_t)mm[i] * p.N + n;
+                if (p.residual) x += __bfloat162float(p.residual[o]);
+                p.C[o] = __float2bfloat16_rn(x);
             }
         }
-        ptx::named_barrier_sync(4 + gw, 64);      // the pair's rows of the exchange tile are free for the next segment
-        if (kc >= p.kchunks) { kc = 0; ++tile; }
+        if (!owner) {
+            __syncwarp();
+            if (lane == 0) ptx::st_release_gpu(&flags[cta * kConsumerWarps + warp], p.epoch);
+        }
+        if (kc >= p.kchunks) { kc = 0; ++pair; }
     }
 }
 
@@ -322,7 +277,7 @@ bool decode_wide_supported(const LinearArgs& a) {
     return !a.out_f32 && !a.px && !a.swiglu_up && !a.a_stride && !a.k_valid;
 }
 
-size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kRT * 4; }
+size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kUnitRows * 4; }
 
 cudaError_t configure_decode_wide() {
     return cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
@@ -333,9 +288,9 @@ cudaError_t configure_decode_wide() {
 cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, void* act_f16, float* unscale,
                                int* launches, cudaStream_t s) {
     CUtensorMap tmp, tms;
-    if (!umma::make_map(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT,
+    if (!umma::make_map(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kUnitRows,
                         CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !umma::make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kRT,
+        !umma::make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kUnitRows,
                         CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     cudaError_t e = launch_act_to_f16(a.A, a.M, a.K, act_f16, unscale, s);
@@ -349,10 +304,10 @@ cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void
     p.inv_gs = a.inv_gs;
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.kchunks = a.K / kKC;
-    p.units = (int)(((long long)a.N + kRT - 1) / kRT * p.kchunks);
-    int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
+    p.units = (int)(((long long)a.N + kUnitRows - 1) / kUnitRows * p.kchunks);
+    int grid = dev.sm_count < kWideMaxGrid ? dev.sm_count : kWideMaxGrid;
     if (grid > p.units) grid = p.units;
-    const int fixed = 1024 + kTokens * kOutLd * 4 + 2 * kMaxStages * 8 + 64;
+    const int fixed = 1024 + 2 * kMaxStages * 8 + 64;
     int stages = (kSmemBudget - fixed) / kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
