@@ -139,20 +139,19 @@ __device__ __forceinline__ void split_tile_participants(int sk_tiles, int kstage
     while (last + 1 < (int)gridDim.x && (long long)(last + 1) * sk_units / gridDim.x < tile_end) ++last;
 }
 
-// Bounded wait (one lane per warp polls) until every participant's flag carries this launch's epoch.
+// Bounded wait until every participant's flag carries this launch's epoch.  Each lane of a warp
+// polls another participant, so the flag round trips overlap.
 __device__ __forceinline__ bool wait_split_tile_flags(const unsigned int* flags, unsigned int epoch, int first, int last,
                                                       int t, volatile int* s_abort, unsigned int* status) {
-    if ((t & 31) == 0) {
-        const long long t0 = clock64();
-        for (int c = first; c <= last; ++c) {
-            const unsigned int* f = &flags[c * 2 + (c == first ? 1 : 0)];
-            while (ptx::ld_acquire_gpu(f) != epoch) {
-                if (*s_abort) break;
-                if (clock64() - t0 > ptx::kWaitBudgetClocks) {
-                    *s_abort = 1;
-                    atomicCAS(status, 0u, 0x480u);
-                    break;
-                }
+    const long long t0 = clock64();
+    for (int c = first + (t & 31); c <= last; c += 32) {
+        const unsigned int* f = &flags[c * 2 + (c == first ? 1 : 0)];
+        while (ptx::ld_acquire_gpu(f) != epoch) {
+            if (*s_abort) break;
+            if (clock64() - t0 > ptx::kWaitBudgetClocks) {
+                *s_abort = 1;
+                atomicCAS(status, 0u, 0x480u);
+                break;
             }
         }
     }
