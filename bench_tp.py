@@ -74,6 +74,129 @@ def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
     return out
 
 
+QKV = dict(q_rows=6144, kv_rows=512, n_kv_heads=2, o_in=6144)   # merged qkv [7168, 5120], o [5120, 6144]
+
+
+def run_tp_layer_stream(torch, dist, h, comm, dev, world, layers=64, tokens=(1, 2, 4)):
+    """configs[3] over the group: 64 layers x {qkv (split by KV-head groups), o (split by K, summed
+    over the ranks inside its kernel), gate_up, SwiGLU, down (likewise)}; every tensor distinct;
+    one shared peer exchange; the attention between qkv and o is a stub (o reads the first columns
+    of this rank's q in place).  Time per token-step, max over ranks, CUDA-graph replay."""
+    import bench
+    import nvfp4_tp
+    H, I = bench.H, bench.I
+    x = nvfp4_tp.Exchange(comm, H)
+    x.enable(dist if world > 1 else None, dev)
+    attns, mlps = [], []
+    for l in range(layers):
+        qp, qs = bench.device_weight(QKV["q_rows"] + 2 * QKV["kv_rows"], H, seed=2000 + 4 * l, dev=dev)
+        op, os_ = bench.device_weight(H, QKV["o_in"], seed=2001 + 4 * l, dev=dev)
+        a = nvfp4_tp.TpAttn(h, comm, H, QKV["q_rows"], QKV["kv_rows"], QKV["n_kv_heads"], QKV["o_in"], qp, qs, 1.0, op, os_, 1.0, 4)
+        a.use_exchange(x)
+        attns.append(a)
+        del qp, qs, op, os_
+        gp, gs = bench.device_weight(2 * I, H, seed=2002 + 4 * l, dev=dev)
+        dp, ds = bench.device_weight(H, I, seed=2003 + 4 * l, dev=dev)
+        m = nvfp4_tp.TpMlp(h, comm, H, I, gp, gs, 1.0, dp, ds, 1.0, 4)
+        m.use_exchange(x)
+        mlps.append(m)
+        del gp, gs, dp, ds
+    torch.cuda.empty_cache()
+    width = attns[0].q_local + 2 * attns[0].kv_local
+    full_bytes = lambda M: layers * (bench.alg_bytes(QKV["q_rows"] + 2 * QKV["kv_rows"], H, M) + bench.alg_bytes(H, QKV["o_in"], M)
+                                     + bench.alg_bytes(2 * I, H, M) + bench.alg_bytes(H, I, M))
+    rows = []
+    for M in tokens:
+        hid = bench.device_acts(M, H, seed=M, dev=dev)
+        hid2 = torch.empty_like(hid)
+        qkv = torch.empty((M, width), dtype=torch.bfloat16, device=dev)
+
+        def token_step():
+            for l in range(layers):
+                attns[l].qkv(hid, M, qkv)
+                attns[l].out(qkv, M, hid2, residual=hid, row_stride=width)
+                mlps[l].forward(hid2, M, hid, residual=hid2)
+
+        token_step()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        ms = bench.time_region(token_step, 3, torch, graph=True)
+        t = torch.tensor([ms], device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        rows.append({"M": M, "ms_per_token_step": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1),
+                     "aggregate_GBps_unsplit_bytes": round(full_bytes(M) / (ms * 1e-3) / 1e9, 1),
+                     "launch_mode": "CUDA-graph replay of 3 token-steps", "reductions_per_token_step": 2 * layers})
+    status = x.status()
+    for b in attns + mlps:
+        b.close()
+    x.close()
+    torch.cuda.empty_cache()
+    return {"layers": layers, "shapes": "qkv 7168x5120 (q 6144 + k 512 + v 512, 2 KV heads), o 5120x6144, gate_up 34816x5120, down 5120x17408",
+            "rows": rows, "exchange_status": int(status)}
+
+
+def attn_parity(torch, dist, h, comm, dev, world, rank):
+    """A small attention-projection block against the unsplit CPU oracle (rank 0 checks)."""
+    import nvfp4_tp
+    import oracle_binding as ob
+    import util
+    H, M = 512, 4
+    q_rows, kv_rows, n_kv, o_in = 256 * world, 64 * 2, 2, 256 * world
+    qkv_p, qkv_s = util.make_weight(q_rows + 2 * kv_rows, H, seed=11)
+    o_p, o_s = util.make_weight(H, o_in, seed=12)
+    X, R = util.make_bf16((M, H), seed=13), util.make_bf16((M, H), seed=14)
+    blk = nvfp4_tp.TpAttn(h, comm, H, q_rows, kv_rows, n_kv, o_in, util.to_dev(qkv_p).to(dev), util.to_dev(qkv_s).to(dev), 1.0,
+                          util.to_dev(o_p).to(dev), util.to_dev(o_s).to(dev), 1.0, M)
+    x = nvfp4_tp.Exchange(comm, H)
+    x.enable(dist if world > 1 else None, dev)
+    width = blk.q_local + 2 * blk.kv_local
+    qkv = torch.empty((M, width), dtype=torch.bfloat16, device=dev)
+    blk.qkv(util.to_dev(X).to(dev), M, qkv)
+    out_n = util.to_dev(R).to(dev)
+    blk.out(qkv, M, out_n, residual=out_n, row_stride=width)      # NCCL path (no exchange yet)
+    blk.use_exchange(x)
+    out_f = util.to_dev(R).to(dev)
+    blk.out(qkv, M, out_f, residual=out_f, row_stride=width)      # reduction inside the kernel
+    torch.cuda.synchronize()
+    rows = nvfp4_tp.qkv_rows(q_rows, kv_rows, n_kv, rank, world)
+    full_qkv = ob.linear(X, qkv_p, qkv_s, 1.0)
+    mine = util.to_host_u16(qkv)
+    ok_rows = torch.tensor([int(np_equal(mine, full_qkv[:, rows]))], device=dev)
+    if dist is not None:
+        dist.all_reduce(ok_rows, op=dist.ReduceOp.MIN)
+    gathered = [torch.empty_like(out_f.view(torch.uint8)) for _ in range(world)]
+    if dist is not None:
+        dist.all_gather(gathered, out_f.view(torch.uint8))
+    else:
+        gathered = [out_f.view(torch.uint8)]
+    res = None
+    if rank == 0:
+        want = ob.linear(np_ascontig(full_qkv[:, :q_rows]), o_p, o_s, 1.0, residual=R)   # stub attention: the q columns
+        res = {"qkv_shards_equal_unsplit_oracle_rows": bool(ok_rows.item()),
+               "o_nccl_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out_n), want)),
+               "o_fused_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out_f), want)),
+               "o_fused_identical_on_all_ranks": all(torch.equal(g, gathered[0]) for g in gathered),
+               "exchange_status": int(x.status())}
+    else:
+        x.status()
+    blk.close()
+    x.close()
+    return res
+
+
+def np_equal(a, b):
+    import numpy as np
+    return np.array_equal(a, b)
+
+
+def np_ascontig(a):
+    import numpy as np
+    return np.ascontiguousarray(a)
+
+
 def main(args, world, rank, local_rank):
     import torch
     import torch.distributed as dist
@@ -216,6 +339,11 @@ def main(args, world, rank, local_rank):
     del mlps
     torch.cuda.empty_cache()
 
+    try:
+        attn_par = attn_parity(torch, dist, h, comm, dev, world, rank)
+    except Exception as e:
+        attn_par = {"error": repr(e)}
+    stream = run_tp_layer_stream(torch, dist, h, comm, dev, world)
     table = run_tp_mlp_table(torch, dist, lambda M: make_mlp_set(M, copies=(None if M <= 256 else 2)), H, dev, world,
                              args.steps)
     if rank == 0:
@@ -231,7 +359,8 @@ def main(args, world, rank, local_rank):
                 "roofline": {"bound": "hbm", "kernel": "whole MLP forward (gate_up, SwiGLU, down + group reduction), aggregate over ranks",
                              "achieved": round(value, 1), "peak": agg_peak, "peak_source": peaks["source"], "unit": "GB/s",
                              "frac": round(value / agg_peak, 4), "traffic": None},
-                "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "tp_mlp": table, "parity": parity}
+                "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "tp_mlp": table, "parity": parity,
+                "tp_layer_stream": stream, "attn_parity": attn_par}
         print(json.dumps(line))
     comm.close()
     dist.destroy_process_group()

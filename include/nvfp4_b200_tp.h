@@ -1,5 +1,6 @@
 /*
- * nvfp4_b200_tp — tensor-parallel NVFP4 MLP across the GPUs of one node (one process per GPU).
+ * nvfp4_b200_tp — tensor-parallel NVFP4 MLP and attention projections across the GPUs of one
+ * node (one process per GPU).
  *
  * New work: the reference engine is single-GPU (its link line carries no communication
  * library).  The block reproduces the reference's MLP sequence (run_mlp,
@@ -23,6 +24,8 @@ extern "C" {
 
 typedef struct nvfp4_tp_comm nvfp4_tp_comm;
 typedef struct nvfp4_tp_mlp nvfp4_tp_mlp;
+typedef struct nvfp4_tp_attn nvfp4_tp_attn;
+typedef struct nvfp4_tp_exchange nvfp4_tp_exchange;
 
 #define NVFP4_TP_UNIQUE_ID_BYTES 128
 #define NVFP4_TP_P2P_HANDLE_BYTES 64
@@ -70,6 +73,48 @@ int nvfp4_tp_mlp_status(nvfp4_tp_mlp* mlp, unsigned int* status);
 
 /* Bytes this rank streams per forward (its weight shards incl. padding). */
 int nvfp4_tp_mlp_shard_bytes(nvfp4_tp_mlp* mlp, size_t* bytes);
+
+/* The peer exchange as an object of its own: one per rank serves every block whose output is
+ * [M, H] (the MLP blocks and the attention blocks of all layers), as long as all ranks call the
+ * blocks in the same order -- the two slot sets alternate per reduction, whichever block runs
+ * it.  handle / attach / status as for nvfp4_tp_mlp_p2p_* above (collective: every rank attaches
+ * the handles of all ranks, in rank order).  The exchange must outlive the blocks that use it. */
+int nvfp4_tp_exchange_create(nvfp4_tp_comm* comm, int H, nvfp4_tp_exchange** out);
+int nvfp4_tp_exchange_destroy(nvfp4_tp_exchange* x);
+int nvfp4_tp_exchange_handle(nvfp4_tp_exchange* x, void* out_64_bytes);
+int nvfp4_tp_exchange_attach(nvfp4_tp_exchange* x, const void* handles_world_x_64_bytes);
+int nvfp4_tp_exchange_status(nvfp4_tp_exchange* x, unsigned int* status);
+/* The MLP block reduces through `x` instead of its own exchange (NULL: back to its own). */
+int nvfp4_tp_mlp_use_exchange(nvfp4_tp_mlp* mlp, nvfp4_tp_exchange* x);
+
+/* Attention-side projections as a tensor-parallel block.  New work like the MLP block; the
+ * single-GPU sequence it splits is src/engine/layer.cu:190-217 (merged FP4 QKV projection) and
+ * :404-409 (output projection).  The merged QKV tensor [q_rows + 2*kv_rows, H] (q rows, k rows,
+ * v rows) is split by output rows in whole KV-head groups: rank r owns q rows
+ * [r*q_rows/P, (r+1)*q_rows/P) and the k and v rows of its KV heads (n_kv_heads % P == 0), or,
+ * with more ranks than KV heads (P % n_kv_heads == 0), of KV head r / (P / n_kv_heads).  The
+ * output projection [H, o_in] is split by K columns [r*o_in/P, (r+1)*o_in/P); its partial sums
+ * are added over the ranks exactly as the MLP's down projection (inside the GEMV kernel for
+ * M <= 16 once nvfp4_tp_attn_use_exchange gave it an attached exchange, NCCL otherwise).
+ * Built from the FULL device-resident tensors, which may be freed afterwards.
+ * H % 256 == 0, q_rows % (8*P) == 0, o_in % (16*P) == 0. */
+int nvfp4_tp_attn_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int q_rows, int kv_rows, int n_kv_heads, int o_in,
+                         const uint8_t* qkv_packed, const uint8_t* qkv_scale, float qkv_global_scale,
+                         const uint8_t* o_packed, const uint8_t* o_scale, float o_global_scale,
+                         int max_M, nvfp4_tp_attn** out);
+int nvfp4_tp_attn_destroy(nvfp4_tp_attn* attn);
+/* This rank's widths: q rows, k rows (= v rows), output-projection input columns. */
+int nvfp4_tp_attn_dims(nvfp4_tp_attn* attn, int* q_local, int* kv_local, int* o_local);
+int nvfp4_tp_attn_shard_bytes(nvfp4_tp_attn* attn, size_t* bytes);
+int nvfp4_tp_attn_use_exchange(nvfp4_tp_attn* attn, nvfp4_tp_exchange* x);
+int nvfp4_tp_attn_set_fused(nvfp4_tp_attn* attn, int mode);   /* 0, 1, 2 as nvfp4_tp_mlp_set_fused */
+/* qkv_out[M, q_local + 2*kv_local] = X[M,H] * shard^T: this rank's q | k | v, no exchange. */
+int nvfp4_tp_attn_qkv(nvfp4_tp_attn* attn, const void* X_bf16, int M, void* qkv_out_bf16, nvfp4_stream_t stream);
+/* out[M,H] = sum over ranks of attn_r[M, o_local] * o_shard_r^T (+ residual), identical on every
+ * rank.  attn rows are row_stride elements apart (0 = o_local; a multiple of 8): the attention
+ * output may be read in place from a wider buffer.  residual may be NULL and may alias out. */
+int nvfp4_tp_attn_out(nvfp4_tp_attn* attn, const void* attn_bf16, long long row_stride, int M,
+                      const void* residual_bf16_or_null, void* out_bf16, nvfp4_stream_t stream);
 
 #ifdef __cplusplus
 }

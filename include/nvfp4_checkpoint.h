@@ -80,6 +80,14 @@ int nvfp4_tp_shard_gate_up(const nvfp4_host_weight* merged, int rank, int world,
                            nvfp4_host_weight* shard);
 int nvfp4_tp_shard_down(const nvfp4_host_weight* down, int rank, int world, uint8_t* packed_out, uint8_t* scale_out,
                         nvfp4_host_weight* shard);
+/* Attention side: merged QKV [q_rows + 2*kv_rows, H] (q rows, k rows, v rows) -> rank r's q rows
+ * [r*q_rows/P, (r+1)*q_rows/P) and the k and v rows of its KV heads (n_kv_heads % P == 0), or of KV
+ * head r / (P / n_kv_heads) when the ranks outnumber the KV heads (P % n_kv_heads == 0): shard
+ * [q_rows/P + 2*kv_local, H].  The output projection [H, o_in] splits by K like the down projection
+ * (nvfp4_tp_shard_down).  q_rows % (8 * world) == 0. */
+int nvfp4_tp_shard_qkv(const nvfp4_host_weight* merged, int q_rows, int kv_rows, int n_kv_heads, int rank, int world,
+                       uint8_t* packed_out, uint8_t* scale_out, nvfp4_host_weight* shard);
+int nvfp4_tp_shard_qkv_rows(int q_rows, int kv_rows, int n_kv_heads, int world);   /* rows of a QKV shard, or < 0 */
 int nvfp4_tp_shard_down_k(int I, int world);                       /* padded K of a down shard, or < 0 */
 
 /* Minimal safetensors writer: n tensors, names[i], tensors[i] (data, nbytes, dtype, rank, shape). */

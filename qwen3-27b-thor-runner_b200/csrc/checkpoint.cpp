@@ -323,6 +323,41 @@ int nvfp4_tp_shard_down(const nvfp4_host_weight* d, int rank, int world, uint8_t
     return NVFP4_CKPT_OK;
 }
 
+int nvfp4_tp_shard_qkv_rows(int q_rows, int kv_rows, int n_kv_heads, int world) {
+    if (q_rows <= 0 || kv_rows <= 0 || n_kv_heads <= 0 || world < 1) return NVFP4_CKPT_E_SHAPE;
+    if ((q_rows % (8 * world)) != 0 || (kv_rows % n_kv_heads) != 0) return NVFP4_CKPT_E_SHAPE;
+    if (world <= n_kv_heads ? (n_kv_heads % world) != 0 : (world % n_kv_heads) != 0) return NVFP4_CKPT_E_SHAPE;
+    const int kv_local = world <= n_kv_heads ? kv_rows / world : kv_rows / n_kv_heads;
+    if ((kv_local % 8) != 0) return NVFP4_CKPT_E_SHAPE;
+    return q_rows / world + 2 * kv_local;
+}
+
+int nvfp4_tp_shard_qkv(const nvfp4_host_weight* m, int q_rows, int kv_rows, int n_kv_heads, int rank, int world,
+                       uint8_t* packed_out, uint8_t* scale_out, nvfp4_host_weight* shard) {
+    if (!m || !m->packed || !m->scale || !packed_out || !scale_out || !shard) return NVFP4_CKPT_E_NULL;
+    const int rows = nvfp4_tp_shard_qkv_rows(q_rows, kv_rows, n_kv_heads, world);
+    if (rows < 0) return rows;
+    if (rank < 0 || rank >= world || m->N != q_rows + 2 * kv_rows) return NVFP4_CKPT_E_SHAPE;
+    const int head = kv_rows / n_kv_heads;
+    const size_t q_local = (size_t)(q_rows / world);
+    const size_t kv_local = world <= n_kv_heads ? (size_t)(kv_rows / world) : (size_t)head;
+    const size_t kv_first = world <= n_kv_heads ? (size_t)rank * kv_local : (size_t)(rank / (world / n_kv_heads)) * head;
+    const size_t prow = (size_t)m->K / 2, srow = (size_t)m->K / 16;
+    const size_t src[3] = {(size_t)rank * q_local, (size_t)q_rows + kv_first, (size_t)q_rows + kv_rows + kv_first};
+    const size_t cnt[3] = {q_local, kv_local, kv_local};
+    size_t dst = 0;
+    for (int b = 0; b < 3; ++b) {           // q, k, v: three contiguous row blocks
+        std::memcpy(packed_out + dst * prow, m->packed + src[b] * prow, cnt[b] * prow);
+        std::memcpy(scale_out + dst * srow, m->scale + src[b] * srow, cnt[b] * srow);
+        dst += cnt[b];
+    }
+    *shard = *m;
+    shard->packed = packed_out;
+    shard->scale = scale_out;
+    shard->N = rows;
+    return NVFP4_CKPT_OK;
+}
+
 int nvfp4_ckpt_write(const char* path, const char* const* names, const nvfp4_ckpt_tensor* t, int n) {
     if (!path || !names || !t || n < 0) return NVFP4_CKPT_E_NULL;
     std::string h = "{";

@@ -1,0 +1,44 @@
+// Shared between the tensor-parallel blocks (tp_common.cu, tp_mlp.cu, tp_attn.cu): the
+// communicator, the peer-exchange object of the fused small-M reduction, and the row-split linear
+// (K columns split over the ranks, partial sums added over the group) both blocks end with.
+#pragma once
+#include <cuda_runtime.h>
+#include <nccl.h>
+
+#include "../../include/nvfp4_b200_tp.h"
+#include "exchange_layout.h"
+
+struct nvfp4_tp_comm {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+// One rank's end of the peer exchange.  xbuf: this rank's buffer; peer[q]: rank q's buffer as
+// mapped into this process (peer[rank] == xbuf).  One exchange serves any number of blocks with
+// the same output width H, as long as every rank calls them in the same order.
+struct nvfp4_tp_exchange {
+    nvfp4_tp_comm* comm = nullptr;
+    int H = 0;
+    unsigned char* xbuf = nullptr;
+    unsigned char* peer[NVFP4_TP_MAX_WORLD] = {};
+    float* partial = nullptr;          // [16, H] FP32: this rank's partial for the stand-alone exchange kernel
+    bool attached = false;
+};
+
+namespace nvfp4 {
+namespace tp {
+
+constexpr int kFusedMaxM = xchg::kMaxTokens;
+
+// C[M,H] = sum over ranks of A_r[M,K_r] * W_r[H,K_r]^T (+ residual), identical on every rank.
+// `d` describes this rank's share (A, shard, residual, C; optionally the strided / SwiGLU /
+// k_valid forms of nvfp4_linear_ex).  mode: 0 = NCCL, 1 = reduction inside the GEMV kernel,
+// 2 = FP32 GEMV + stand-alone exchange kernel; 1 and 2 need an attached exchange and M <= 16.
+// Returns NVFP4_E_LIMIT when `d` uses nvfp4_linear_ex options and the fused path cannot take
+// it: the caller then materialises plain [M, K] activations and calls again.
+// res_copy: [max_M, H] BF16 scratch for an in-place residual on the NCCL path.
+int rowsplit_linear(nvfp4_handle* h, nvfp4_tp_comm* comm, nvfp4_tp_exchange* x, int mode, const nvfp4_linear_desc& d,
+                    void* res_copy, cudaStream_t s);
+
+}  // namespace tp
+}  // namespace nvfp4

@@ -33,6 +33,9 @@ CKPT_SIGNATURES = {
     "nvfp4_tp_shard_gate_up": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_down": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_down_k": (c_int, [c_int, c_int]),
+    "nvfp4_tp_shard_qkv": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                   ctypes.POINTER(HostWeight)]),
+    "nvfp4_tp_shard_qkv_rows": (c_int, [c_int, c_int, c_int, c_int]),
     "nvfp4_ckpt_write": (c_int, [c_char_p, ctypes.POINTER(c_char_p), ctypes.POINTER(CkptTensor), c_int]),
     "nvfp4_ckpt_status_string": (c_char_p, [c_int]),
 }
@@ -133,6 +136,20 @@ def shard_gate_up(packed, scale, gs, rank, world):
     po, so = np.empty((rows, K // 2), np.uint8), np.empty((rows, K // 16), np.uint8)
     out = HostWeight()
     _check(lib.nvfp4_tp_shard_gate_up(ctypes.byref(w), rank, world, po.ctypes.data, so.ctypes.data, ctypes.byref(out)))
+    return po, so
+
+
+def shard_qkv(packed, scale, gs, q_rows, kv_rows, n_kv_heads, rank, world):
+    lib = load()
+    packed, scale = np.ascontiguousarray(packed), np.ascontiguousarray(scale)
+    w = _host_weight(packed, scale, gs)
+    rows = lib.nvfp4_tp_shard_qkv_rows(q_rows, kv_rows, n_kv_heads, world)
+    _check(rows if rows < 0 else 0)
+    K = packed.shape[1] * 2
+    po, so = np.empty((rows, K // 2), np.uint8), np.empty((rows, K // 16), np.uint8)
+    out = HostWeight()
+    _check(lib.nvfp4_tp_shard_qkv(ctypes.byref(w), q_rows, kv_rows, n_kv_heads, rank, world, po.ctypes.data, so.ctypes.data,
+                                  ctypes.byref(out)))
     return po, so
 
 

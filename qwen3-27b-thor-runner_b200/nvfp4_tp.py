@@ -1,4 +1,4 @@
-"""Host side of the tensor-parallel NVFP4 MLP: ctypes binding of libnvfp4_b200_tp.so
+"""Host side of the tensor-parallel NVFP4 blocks (MLP, attention projections): ctypes binding of libnvfp4_b200_tp.so
 (include/nvfp4_b200_tp.h) and the numpy statement of its sharding rule, which the CPU
 (gloo) tests run against the oracle.  One process per GPU; the communicator id travels over
 whatever channel the caller has (the benchmark broadcasts it with torch.distributed)."""
@@ -29,6 +29,21 @@ TP_SIGNATURES = {
     "nvfp4_tp_mlp_p2p_attach": (c_int, [c_void_p, c_void_p]),
     "nvfp4_tp_mlp_set_fused": (c_int, [c_void_p, c_int]),
     "nvfp4_tp_mlp_status": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint)]),
+    "nvfp4_tp_mlp_use_exchange": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_tp_exchange_create": (c_int, [c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "nvfp4_tp_exchange_destroy": (c_int, [c_void_p]),
+    "nvfp4_tp_exchange_handle": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_tp_exchange_attach": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_tp_exchange_status": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint)]),
+    "nvfp4_tp_attn_create": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                     c_void_p, c_void_p, c_float, c_int, ctypes.POINTER(c_void_p)]),
+    "nvfp4_tp_attn_destroy": (c_int, [c_void_p]),
+    "nvfp4_tp_attn_dims": (c_int, [c_void_p, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
+    "nvfp4_tp_attn_shard_bytes": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
+    "nvfp4_tp_attn_use_exchange": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_tp_attn_set_fused": (c_int, [c_void_p, c_int]),
+    "nvfp4_tp_attn_qkv": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "nvfp4_tp_attn_out": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None
@@ -73,6 +88,28 @@ def shard_down(packed, scale, rank, world):
     return p, s
 
 
+def qkv_rows(q_rows, kv_rows, n_kv_heads, rank, world):
+    """Row indices of the merged [q_rows + 2*kv_rows, H] tensor (q, k, v) that rank r keeps: its share
+    of the q rows and the k and v rows of its KV heads (of KV head r // (P // n_kv) when the ranks
+    outnumber the KV heads)."""
+    assert q_rows % (8 * world) == 0 and kv_rows % n_kv_heads == 0
+    ql = q_rows // world
+    head = kv_rows // n_kv_heads
+    if world <= n_kv_heads:
+        assert n_kv_heads % world == 0
+        kvl, kv0 = kv_rows // world, rank * (kv_rows // world)
+    else:
+        assert world % n_kv_heads == 0
+        kvl, kv0 = head, (rank // (world // n_kv_heads)) * head
+    return np.r_[rank * ql:(rank + 1) * ql, q_rows + kv0:q_rows + kv0 + kvl,
+                 q_rows + kv_rows + kv0:q_rows + kv_rows + kv0 + kvl]
+
+
+def shard_qkv(packed, scale, q_rows, kv_rows, n_kv_heads, rank, world):
+    rows = qkv_rows(q_rows, kv_rows, n_kv_heads, rank, world)
+    return np.ascontiguousarray(packed[rows]), np.ascontiguousarray(scale[rows])
+
+
 def pad_activation(act, kp):
     """[M, I/P] BF16 bits -> [M, kp] with zero padding."""
     out = np.zeros((act.shape[0], kp), act.dtype)
@@ -104,6 +141,103 @@ def unique_id():
     if st:
         raise nvfp4.Nvfp4Error(st)
     return bytes(buf.raw)
+
+
+class Exchange:
+    """A rank's peer-exchange buffer for the fused small-M reduction, shared by any number of blocks."""
+
+    def __init__(self, comm, H):
+        self.lib = load()
+        x = c_void_p()
+        st = self.lib.nvfp4_tp_exchange_create(comm.c, H, ctypes.byref(x))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        self.x = x
+
+    def handle(self):
+        buf = ctypes.create_string_buffer(P2P_HANDLE_BYTES)
+        st = self.lib.nvfp4_tp_exchange_handle(self.x, buf)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        return bytes(buf.raw)
+
+    def attach(self, handles):
+        buf = None if handles is None else ctypes.create_string_buffer(bytes(handles), len(handles))
+        st = self.lib.nvfp4_tp_exchange_attach(self.x, buf)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def enable(self, dist=None, device=None):
+        """Collective: exchange the buffer handles over torch.distributed and attach."""
+        if dist is None or dist.get_world_size() == 1:
+            return self.attach(None)
+        import torch
+        mine = torch.tensor(list(self.handle()), dtype=torch.uint8, device=device)
+        allh = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(allh, mine)
+        self.attach(b"".join(bytes(t.cpu().tolist()) for t in allh))
+
+    def status(self):
+        v = ctypes.c_uint()
+        st = self.lib.nvfp4_tp_exchange_status(self.x, ctypes.byref(v))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        return v.value
+
+    def close(self):
+        if getattr(self, "x", None):
+            self.lib.nvfp4_tp_exchange_destroy(self.x)
+            self.x = None
+
+
+class TpAttn:
+    """Tensor-parallel attention projections (QKV split by KV-head groups, output projection split by K)."""
+
+    def __init__(self, handle, comm, H, q_rows, kv_rows, n_kv_heads, o_in, qkv_packed, qkv_scale, qkv_gs, o_packed,
+                 o_scale, o_gs, max_M):
+        self.lib = load()
+        a = c_void_p()
+        st = self.lib.nvfp4_tp_attn_create(handle.h, comm.c, H, q_rows, kv_rows, n_kv_heads, o_in, qkv_packed.data_ptr(),
+                                           qkv_scale.data_ptr(), qkv_gs, o_packed.data_ptr(), o_scale.data_ptr(), o_gs,
+                                           max_M, ctypes.byref(a))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        self.a, self.H = a, H
+        q, kv, o = c_int(), c_int(), c_int()
+        self.lib.nvfp4_tp_attn_dims(a, ctypes.byref(q), ctypes.byref(kv), ctypes.byref(o))
+        self.q_local, self.kv_local, self.o_local = q.value, kv.value, o.value
+
+    def qkv(self, X, M, qkv_out, stream=None):
+        st = self.lib.nvfp4_tp_attn_qkv(self.a, X.data_ptr(), M, qkv_out.data_ptr(), nvfp4._stream(stream))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def out(self, attn, M, out, residual=None, row_stride=0, stream=None):
+        ptr = attn if isinstance(attn, int) else attn.data_ptr()
+        st = self.lib.nvfp4_tp_attn_out(self.a, ptr, row_stride, M, None if residual is None else residual.data_ptr(),
+                                        out.data_ptr(), nvfp4._stream(stream))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def use_exchange(self, x):
+        st = self.lib.nvfp4_tp_attn_use_exchange(self.a, None if x is None else x.x)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def set_fused(self, mode):
+        st = self.lib.nvfp4_tp_attn_set_fused(self.a, int(mode))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def shard_bytes(self):
+        v = ctypes.c_size_t()
+        self.lib.nvfp4_tp_attn_shard_bytes(self.a, ctypes.byref(v))
+        return v.value
+
+    def close(self):
+        if getattr(self, "a", None):
+            self.lib.nvfp4_tp_attn_destroy(self.a)
+            self.a = None
 
 
 class TpMlp:
@@ -146,6 +280,11 @@ class TpMlp:
         allh = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
         dist.all_gather(allh, mine)
         self.p2p_attach(b"".join(bytes(t.cpu().tolist()) for t in allh))
+
+    def use_exchange(self, x):
+        st = self.lib.nvfp4_tp_mlp_use_exchange(self.m, None if x is None else x.x)
+        if st:
+            raise nvfp4.Nvfp4Error(st)
 
     def set_fused(self, mode):
         """0/False = NCCL all-reduce, 1/True = reduction fused into the down-projection kernel,

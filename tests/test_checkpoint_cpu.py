@@ -169,6 +169,46 @@ def test_shard_tool_end_to_end(tmp_path):
     assert bad.returncode == 1 and "no tensor of that name" in bad.stderr
 
 
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_qkv_shard_rule_matches_numpy_statement(world):
+    H, q_rows, kv_rows, n_kv = 256, 768, 128, 2
+    p, s = util.make_weight(q_rows + 2 * kv_rows, H, seed=7)
+    for r in range(world):
+        cp, cs = nvfp4_ckpt.shard_qkv(p, s, 1.0, q_rows, kv_rows, n_kv, r, world)
+        wp, ws = nvfp4_tp.shard_qkv(p, s, q_rows, kv_rows, n_kv, r, world)
+        assert np.array_equal(cp, wp) and np.array_equal(cs, ws)
+    with pytest.raises(nvfp4_ckpt.CkptError):
+        nvfp4_ckpt.shard_qkv(p, s, 1.0, q_rows, kv_rows, n_kv, 0, 3)             # 3 ranks and 2 KV heads do not divide
+
+
+def test_shard_tool_attention_projections(tmp_path):
+    """The tool's attn form: q, k, v merged by rows, then every rank file holds the QKV rows of its
+    KV-head group and its K columns of the output projection."""
+    H, q_rows, kv_rows, n_kv, world = 256, 512, 128, 2, 4
+    p = "model.language_model.layers.3.self_attn."
+    tq, qp, qs = linear_tensors(p + "q_proj", q_rows, H, 21, 2.0)
+    tk, kp, ks = linear_tensors(p + "k_proj", kv_rows, H, 22, 2.0)
+    tv, vp, vs = linear_tensors(p + "v_proj", kv_rows, H, 23, 2.0)
+    to, op, os_ = linear_tensors(p + "o_proj", H, q_rows, 24, 1.0)
+    src = tmp_path / "model.safetensors"
+    py_write_safetensors(src, {**tq, **tk, **tv, **to}, metadata={"format": "pt"})
+    out = subprocess.run([nvfp4_ckpt.SHARD_TOOL_PATH, "attn", str(src), str(tmp_path / "attn3"), str(world), str(n_kv),
+                          p + "q_proj", p + "k_proj", p + "v_proj", p + "o_proj"], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    mp, ms = np.concatenate([qp, kp, vp]), np.concatenate([qs, ks, vs])
+    for r in range(world):
+        c = nvfp4_ckpt.Checkpoint(str(tmp_path / f"attn3.rank{r}.safetensors"))
+        try:
+            packed, scale, g, _ = c.linear("qkv")
+            wp, ws = nvfp4_tp.shard_qkv(mp, ms, q_rows, kv_rows, n_kv, r, world)
+            assert np.array_equal(packed, wp) and np.array_equal(scale, ws) and g == 2.0
+            packed, scale, g, _ = c.linear("o")
+            wp, ws = nvfp4_tp.shard_down(op, os_, r, world)
+            assert np.array_equal(packed, wp) and np.array_equal(scale, ws) and g == 1.0
+        finally:
+            c.close()
+
+
 def test_writer_roundtrip(tmp_path):
     a = np.arange(24, dtype=np.uint8).reshape(2, 12)
     b = np.array([1.5], np.float32)

@@ -492,6 +492,53 @@ def test_tp_mlp_fused_single_rank(handle, M):
         comm.close()
 
 
+@pytest.mark.parametrize("M,o_in", [(1, 768), (4, 768), (16, 768), (40, 768), (3, 800)])
+def test_tp_attn_single_rank(handle, M, o_in):
+    """World of one: the QKV projection equals the unsplit oracle; the output projection reads the
+    attention output in place from the wider QKV buffer (row stride, K padded beyond o_in when o_in
+    is not a multiple of 256) and, through an attached exchange, reduces over the group of one."""
+    import torch
+    import nvfp4_tp
+    H, q_rows, kv_rows, n_kv = 512, o_in, 128, 2
+    qkv_p, qkv_s = util.make_weight(q_rows + 2 * kv_rows, H, seed=51)
+    o_p, o_s = util.make_weight(H, o_in, seed=52)
+    X, R = util.make_bf16((M, H), seed=53), util.make_bf16((M, H), seed=54)
+    comm = nvfp4_tp.Comm(None, 0, 1)
+    blk = nvfp4_tp.TpAttn(handle, comm, H, q_rows, kv_rows, n_kv, o_in, util.to_dev(qkv_p), util.to_dev(qkv_s), 1.0,
+                          util.to_dev(o_p), util.to_dev(o_s), 1.0, 64)
+    x = nvfp4_tp.Exchange(comm, H)
+    try:
+        assert (blk.q_local, blk.kv_local, blk.o_local) == (q_rows, kv_rows, o_in)
+        width = q_rows + 2 * kv_rows
+        qkv = torch.empty((M, width), dtype=torch.int16, device="cuda")
+        blk.qkv(util.to_dev(X), M, qkv)
+        torch.cuda.synchronize()
+        got_qkv = util.to_host_u16(qkv)
+        want_qkv = ob.linear(X, qkv_p, qkv_s, 1.0, mode=ob.GEMV if M <= 16 else ob.AUTO)
+        assert ob.rel_frobenius(got_qkv, want_qkv) <= TOL
+        attn = np.ascontiguousarray(got_qkv[:, :o_in])                # stub attention: the q columns
+        want = ob.linear(attn, o_p, o_s, 1.0, residual=R, mode=ob.GEMV if M <= 16 else ob.AUTO)
+        outs = []
+        x.attach(None)
+        for use_x, mode in ((False, 1), (True, 1), (True, 1), (True, 2), (True, 0)):
+            blk.use_exchange(x if use_x else None)
+            blk.set_fused(mode)
+            out = util.to_dev(R)
+            blk.out(qkv, M, out, residual=out, row_stride=width)
+            torch.cuda.synchronize()
+            outs.append(util.to_host_u16(out))
+            assert ob.rel_frobenius(outs[-1], want) <= (TOL if M <= 16 else 3e-3)
+        assert x.status() == 0
+        if M <= 16:
+            assert np.array_equal(outs[1], outs[2])
+            for o in outs:
+                assert ob.rel_frobenius(o, outs[0]) <= 2e-4
+    finally:
+        blk.close()
+        x.close()
+        comm.close()
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 13])
 def test_linear_ex_swiglu_prologue(handle, M):
     """SwiGLU formed while the GEMV stages its activations (merged gate/up rows, K padded beyond

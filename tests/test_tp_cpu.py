@@ -45,6 +45,54 @@ def test_padding_contributes_nothing():
             assert ob.rel_frobenius(got, want) < 1e-6
 
 
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_qkv_split_follows_the_kv_heads(world):
+    """Every q row lands on exactly one rank; every KV head on one rank, or, with more ranks than
+    KV heads, on world / n_kv ranks -- and always on the rank that holds its query heads."""
+    q_rows, kv_rows, n_kv = 6144, 512, 2
+    head = kv_rows // n_kv
+    q_per_kv = q_rows // n_kv
+    seen_q = np.zeros(q_rows, int)
+    seen_kv = np.zeros(kv_rows, int)
+    for r in range(world):
+        rows = nvfp4_tp.qkv_rows(q_rows, kv_rows, n_kv, r, world)
+        q = rows[rows < q_rows]
+        k = rows[(rows >= q_rows) & (rows < q_rows + kv_rows)] - q_rows
+        v = rows[rows >= q_rows + kv_rows] - q_rows - kv_rows
+        assert np.array_equal(k, v) and len(q) == q_rows // world
+        seen_q[q] += 1
+        seen_kv[k] += 1
+        # the KV heads of this rank's query rows are the KV heads it holds
+        assert set(q // q_per_kv) == set(k // head)
+    assert (seen_q == 1).all()
+    assert (seen_kv == max(1, world // n_kv)).all()
+
+
+def test_attention_projections_split_matches_unsplit():
+    """Column-split QKV + row-split output projection with the oracle as the kernel: the shards'
+    outputs are slices of the unsplit projection, and the partial sums add up to the unsplit
+    output projection (FP32 partials: the fused path's arithmetic)."""
+    M, H, world = 3, 256, 4
+    q_rows, kv_rows, n_kv, o_in = 1024, 128, 2, 1024
+    qkv_p, qkv_s = util.make_weight(q_rows + 2 * kv_rows, H, seed=21)
+    o_p, o_s = util.make_weight(H, o_in, seed=22)
+    X = util.make_bf16((M, H), seed=23)
+    full = ob.linear(X, qkv_p, qkv_s, 1.0)
+    attn_full = np.ascontiguousarray(full[:, :q_rows])          # stub attention: the q columns
+    want = ob.bf16_to_f32(ob.linear(attn_full, o_p, o_s, 1.0))
+    total = np.zeros((M, H), np.float64)
+    for r in range(world):
+        p, s = nvfp4_tp.shard_qkv(qkv_p, qkv_s, q_rows, kv_rows, n_kv, r, world)
+        mine = ob.linear(X, p, s, 1.0)
+        assert np.array_equal(mine, full[:, nvfp4_tp.qkv_rows(q_rows, kv_rows, n_kv, r, world)])
+        ol = o_in // world
+        dp, ds = nvfp4_tp.shard_down(o_p, o_s, r, world)        # the output projection splits like the down projection
+        a = nvfp4_tp.pad_activation(np.ascontiguousarray(mine[:, :ol]), dp.shape[1] * 2)
+        total += ob.bf16_to_f32(ob.linear(a, dp, ds, 1.0)).astype(np.float64)
+    # each partial carries one BF16 rounding here (the oracle's output type); the fused kernel keeps FP32
+    assert np.linalg.norm(total - want) / np.linalg.norm(want) < 5e-3
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
