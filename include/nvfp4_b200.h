@@ -155,7 +155,14 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A_bf16, int M, const 
  *                 so the [M, I] SwiGLU tensor of run_mlp (src/engine/layer.cu:87-99) is never written;
  *   a_row_stride  elements between token rows of A and swiglu_up (2I for the merged gate/up layout);
  *   k_valid       activation columns >= k_valid count as zero (a weight shard whose K was padded);
- *   px            sum over a tensor-parallel group inside the kernel (see nvfp4_linear_reduce_peers).
+ *   px            sum over a tensor-parallel group inside the kernel (see nvfp4_linear_reduce_peers);
+ *   norm_weight   [K] BF16: the activations are rmsnorm(A) with the centred weight,
+ *                 bf16((A * rsqrt(mean(A^2) + norm_eps)) * (1 + norm_weight)) per token row, formed
+ *                 while the kernel stages them: the bits nvfp4_rmsnorm would store, up to the FP32
+ *                 summation order of mean(A^2), without the kernel or the round trip (the
+ *                 reference fuses the norm into its BF16 GEMV only, src/engine/layer.cu:217-222; its
+ *                 FP4 path runs invoke_rmsnorm first, :190-193).  Not together with swiglu_up or
+ *                 k_valid.  Every CTA normalises for itself, so this pays for a few tokens only.
  * Zero / NULL fields mean "not used".  No reference counterpart for the fused forms. */
 typedef struct nvfp4_linear_desc {
     const void* A;
@@ -170,6 +177,8 @@ typedef struct nvfp4_linear_desc {
     const void* residual;
     void* C;
     const nvfp4_peer_exchange* px;
+    const void* norm_weight;
+    float norm_eps;
 } nvfp4_linear_desc;
 int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* desc, nvfp4_stream_t stream);
 
@@ -191,6 +200,17 @@ int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* sc
  * (invoke_swiglu_merged, src/engine/light_ops.cu:1542-1587). */
 int nvfp4_swiglu(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16_or_null,
                  int M, int I, void* out_bf16, nvfp4_stream_t stream);
+
+/* out[M,K] = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + weight) ) per token row, FP32 inside
+ * (invoke_rmsnorm, src/engine/light_ops.cu:65-112; the centred weight of the reference's model).
+ * K % 8 == 0; out may alias x. */
+int nvfp4_rmsnorm(nvfp4_handle* h, const void* x_bf16, const void* weight_bf16, float eps, int M, int K,
+                  void* out_bf16, nvfp4_stream_t stream);
+/* residual += bias (rounded once to BF16, in place), norm_out = rmsnorm of the unrounded sum
+ * (invoke_fused_add_rmsnorm, src/engine/light_ops.cu:270-328: the step in front of the MLP,
+ * src/engine/layer.cu:47-50). */
+int nvfp4_add_rmsnorm(nvfp4_handle* h, void* residual_bf16, const void* bias_bf16, const void* weight_bf16, float eps,
+                      int M, int K, void* norm_out_bf16, nvfp4_stream_t stream);
 
 /* Same with explicit row strides (in elements): gate and up rows are in_stride apart, output
  * rows out_stride apart.  Used where the SwiGLU output feeds a K-padded weight shard. */

@@ -209,6 +209,48 @@ void nvfp4_oracle_swiglu_merged(const uint16_t* merged, int T, int I, uint16_t* 
                             (size_t)I, out + (size_t)t * I);
 }
 
+/* src/engine/light_ops.cu:30-57 (blockReduceSum with 256 threads) over per-thread partial sums */
+static float block_reduce_256(float* v) {
+    float w[8];
+    for (int wid = 0; wid < 8; ++wid) {
+        float* l = v + 32 * wid;
+        for (int off = 16; off > 0; off >>= 1)
+            for (int lane = 0; lane + off < 32; ++lane) l[lane] += l[lane + off];   /* lane reads the old value of lane+off: ascending order keeps it old */
+        w[wid] = l[0];
+    }
+    float l[32];
+    for (int lane = 0; lane < 32; ++lane) l[lane] = lane < 8 ? w[lane] : 0.0f;
+    for (int off = 16; off > 0; off >>= 1)
+        for (int lane = 0; lane + off < 32; ++lane) l[lane] += l[lane + off];
+    return l[0];
+}
+
+/* src/engine/light_ops.cu:65-106 and :270-318 */
+void nvfp4_oracle_rmsnorm(const uint16_t* x, const uint16_t* bias, const uint16_t* weight, float eps,
+                          int M, int K, uint16_t* out, uint16_t* residual_out) {
+    float* r = (float*)malloc((size_t)K * sizeof(float));
+    for (int m = 0; m < M; ++m) {
+        const uint16_t* xr = x + (size_t)m * K;
+        float part[256];
+        for (int t = 0; t < 256; ++t) part[t] = 0.0f;
+        for (int i = 0; i < K; ++i) {
+            float v = nvfp4_oracle_bf2f(xr[i]);
+            if (bias) v = v + nvfp4_oracle_bf2f(bias[(size_t)m * K + i]);
+            r[i] = v;
+        }
+        for (int t = 0; t < 256; ++t)
+            for (int i = t; i < K; i += 256) part[t] = fmaf(r[i], r[i], part[t]);
+        const float sum_sq = block_reduce_256(part);
+        const float inv_rms = 1.0f / sqrtf(sum_sq / (float)K + eps);
+        for (int i = 0; i < K; ++i) {
+            if (bias && residual_out) residual_out[(size_t)m * K + i] = nvfp4_oracle_f2bf(r[i]);
+            const float w = nvfp4_oracle_bf2f(weight[i]);
+            out[(size_t)m * K + i] = nvfp4_oracle_f2bf(r[i] * inv_rms * (1.0f + w));
+        }
+    }
+    free(r);
+}
+
 void nvfp4_oracle_mlp(const uint16_t* X, int M, int H, int I,
                       const uint8_t* gu_packed, const uint8_t* gu_scale, float gu_gs,
                       const uint8_t* dn_packed, const uint8_t* dn_scale, float dn_gs,

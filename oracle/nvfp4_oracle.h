@@ -77,6 +77,17 @@ void nvfp4_oracle_swiglu(const uint16_t* gate, const uint16_t* up, size_t n, uin
  * Follows src/engine/light_ops.cu:1542-1577. */
 void nvfp4_oracle_swiglu_merged(const uint16_t* merged, int T, int I, uint16_t* out);
 
+/* RMSNorm with the centred weight, one row per token:
+ *   out = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + w) ), FP32 throughout.
+ * Follows rmsnorm_kernel, src/engine/light_ops.cu:65-106, including its summation order (256
+ * threads, thread t sums elements t, t+256, ... with fused multiply-adds, then the shuffle-down
+ * trees of blockReduceSum, :30-57).  The device's rsqrtf is an approximation; 1/sqrtf stands
+ * in for it here, so outputs may differ from the device's in the last BF16 bit of a few elements.
+ * K % 256 == 0.  bias != NULL: x = residual + bias first (FP32), and bf16(x) is written back to
+ * `residual_out` (fused_add_rmsnorm_kernel, :270-318; the norm uses the unrounded sum). */
+void nvfp4_oracle_rmsnorm(const uint16_t* x, const uint16_t* bias, const uint16_t* weight, float eps,
+                          int M, int K, uint16_t* out, uint16_t* residual_out);
+
 /* The MLP sequence of src/engine/layer.cu:62-110 with merged gate/up:
  * gate_up linear -> BF16 -> SwiGLU -> BF16 -> down linear (+residual) -> BF16.
  * gate_up weight is [2I, H] (gate rows then up rows), down weight is [H, I]. */

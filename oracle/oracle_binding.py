@@ -53,6 +53,8 @@ def load():
         lib.nvfp4_oracle_swiglu.argtypes = [_u16p, _u16p, ctypes.c_size_t, _u16p]
         lib.nvfp4_oracle_swiglu_merged.restype = None
         lib.nvfp4_oracle_swiglu_merged.argtypes = [_u16p, c_int, c_int, _u16p]
+        lib.nvfp4_oracle_rmsnorm.restype = None
+        lib.nvfp4_oracle_rmsnorm.argtypes = [_u16p, c_void_p, _u16p, c_float, c_int, c_int, _u16p, c_void_p]
         lib.nvfp4_oracle_mlp.restype = None
         lib.nvfp4_oracle_mlp.argtypes = [_u16p, c_int, c_int, c_int, _u8p, _u8p, c_float, _u8p, _u8p, c_float,
                                          c_void_p, _u16p, c_int, c_int]
@@ -109,6 +111,21 @@ def swiglu_merged(merged):
     out = np.empty((T, I2 // 2), np.uint16)
     load().nvfp4_oracle_swiglu_merged(merged, T, I2 // 2, out)
     return out
+
+
+def rmsnorm(x, weight, eps, bias=None):
+    """x, bias: uint16 [M,K] BF16 bits; weight [K].  Returns the normalised rows; with `bias`
+    (x + bias normalised) also the updated residual."""
+    M, K = x.shape
+    out = np.empty((M, K), np.uint16)
+    if bias is None:
+        load().nvfp4_oracle_rmsnorm(np.ascontiguousarray(x), None, np.ascontiguousarray(weight), eps, M, K, out, None)
+        return out
+    bias = np.ascontiguousarray(bias)
+    res = np.empty((M, K), np.uint16)
+    load().nvfp4_oracle_rmsnorm(np.ascontiguousarray(x), bias.ctypes.data, np.ascontiguousarray(weight), eps, M, K, out,
+                                res.ctypes.data)
+    return out, res
 
 
 def mlp(X, gu_packed, gu_scale, gu_gs, dn_packed, dn_scale, dn_gs, residual=None, mode=AUTO, threads=1):
@@ -193,5 +210,9 @@ def load_ref():
         for n in ("ref_fp4_gemv", "ref_fp4_gemv_add", "ref_fp4_dual_gemv", "ref_fp4_gemm", "ref_fp4_gemm_add",
                   "ref_swiglu", "ref_swiglu_merged"):
             getattr(lib, n).restype = None
+        if hasattr(lib, "ref_rmsnorm"):
+            lib.ref_rmsnorm.argtypes = [vp, vp, vp, c_float, c_int, c_int, vp]
+            lib.ref_fused_add_rmsnorm.argtypes = [vp, vp, vp, vp, c_float, c_int, c_int, vp]
+            lib.ref_rmsnorm.restype = lib.ref_fused_add_rmsnorm.restype = None
         _ref = lib
     return _ref

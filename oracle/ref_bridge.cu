@@ -73,6 +73,16 @@ void ref_swiglu_merged(void* out, const void* merged, int T, int I, cudaStream_t
     qwen_thor::ops::invoke_swiglu_merged((__nv_bfloat16*)out, (const __nv_bfloat16*)merged, T, I, s);
 }
 
+void ref_rmsnorm(void* out, const void* x, const void* weight, float eps, int T, int hs, cudaStream_t s) {
+    qwen_thor::ops::invoke_rmsnorm((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)weight, eps, T, hs, s);
+}
+
+void ref_fused_add_rmsnorm(void* norm_out, void* residual, const void* bias, const void* weight, float eps, int T,
+                           int hs, cudaStream_t s) {
+    qwen_thor::ops::invoke_fused_add_rmsnorm((__nv_bfloat16*)norm_out, (__nv_bfloat16*)residual,
+                                             (const __nv_bfloat16*)bias, (const __nv_bfloat16*)weight, eps, T, hs, s);
+}
+
 }  // extern "C"
 
 // light_ops.cu (compiled for its two SwiGLU launchers) also references the

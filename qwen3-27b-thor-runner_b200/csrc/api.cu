@@ -59,7 +59,7 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
-    if (a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid) {   // options only the GEMV kernel implements
+    if (a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w) {   // options only the GEMV kernel implements
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
@@ -322,6 +322,10 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
     const int k_valid = d->k_valid ? d->k_valid : d->K;
     if (stride < k_valid || (stride & 7) || k_valid < 1 || k_valid > d->K || (k_valid & 7)) return NVFP4_E_SHAPE;
     if (d->swiglu_up && !aligned16(d->swiglu_up)) return NVFP4_E_ALIGN;
+    if (d->norm_weight) {
+        if (!aligned16(d->norm_weight)) return NVFP4_E_ALIGN;
+        if (d->swiglu_up || k_valid != d->K || !(d->norm_eps >= 0.0f)) return NVFP4_E_SHAPE;   // the norm runs over all K columns of A itself
+    }
     if (d->px) {
         if (d->px->world < 1 || d->px->world > 8 || d->px->rank < 0 || d->px->rank >= d->px->world) return NVFP4_E_TP;
         for (int q = 0; q < d->px->world; ++q)
@@ -334,6 +338,8 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
     a.swiglu_up = d->swiglu_up;
     a.a_stride = d->a_row_stride;
     a.k_valid = d->k_valid;
+    a.norm_w = d->norm_weight;
+    a.norm_eps = d->norm_eps;
     if (!a.px && !a.swiglu_up && stride == d->K && k_valid == d->K) { a.a_stride = 0; a.k_valid = 0; }   // the plain call
     return run_linear(h, a, stream);
 }
@@ -382,6 +388,28 @@ int nvfp4_swiglu(nvfp4_handle* h, const void* gate, const void* up, int M, int I
     const bool merged = (up == nullptr);
     if (merged) up = static_cast<const char*>(gate) + (size_t)I * 2;
     return nvfp4_swiglu_strided(h, gate, up, M, I, merged ? 2LL * I : (long long)I, out, I, stream);
+}
+
+int nvfp4_rmsnorm(nvfp4_handle* h, const void* x, const void* weight, float eps, int M, int K, void* out,
+                  nvfp4_stream_t stream) {
+    if (!h || !x || !weight || !out) return NVFP4_E_NULL;
+    if (M < 0 || K <= 0 || (K & 7) != 0) return NVFP4_E_SHAPE;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(out)) return NVFP4_E_ALIGN;
+    if (M == 0) return NVFP4_OK;
+    cudaError_t e = launch_rmsnorm(out, const_cast<void*>(x), nullptr, weight, eps, M, K, stream);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
+int nvfp4_add_rmsnorm(nvfp4_handle* h, void* residual, const void* bias, const void* weight, float eps, int M, int K,
+                      void* norm_out, nvfp4_stream_t stream) {
+    if (!h || !residual || !bias || !weight || !norm_out) return NVFP4_E_NULL;
+    if (M < 0 || K <= 0 || (K & 7) != 0) return NVFP4_E_SHAPE;
+    if (!aligned16(residual) || !aligned16(bias) || !aligned16(weight) || !aligned16(norm_out)) return NVFP4_E_ALIGN;
+    if (M == 0) return NVFP4_OK;
+    cudaError_t e = launch_rmsnorm(norm_out, residual, bias, weight, eps, M, K, stream);
+    h->launches += 1;
+    return cuda_status(e);
 }
 
 int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M, const uint8_t* packed, const uint8_t* scale,

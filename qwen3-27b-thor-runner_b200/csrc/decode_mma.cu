@@ -64,6 +64,8 @@ struct DecodeParams {
     const __nv_bfloat16* A_up;      // null, or the up half: the activations are bf16(silu(gate) * up), formed while staging
     long long a_stride;             // elements between token rows of A (and A_up)
     int k_valid;                    // columns >= k_valid are zero (a K padded beyond the tensor)
+    const __nv_bfloat16* norm_w;    // null, or [K]: the activations are rmsnorm(A) with the centred weight, formed while staging
+    float norm_eps;
     const __nv_bfloat16* residual;
     __nv_bfloat16* C;
     unsigned char* scratch;
@@ -206,6 +208,69 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         xepoch = *reinterpret_cast<volatile unsigned int*>(p.xpeer[p.xrank] + xchg::kEpochOff) + 1u;
         xset = xepoch & 1u;
     }
+    if (p.norm_w) {
+        // RMSNorm on the fly (rmsnorm_kernel, src/engine/light_ops.cu:65-106): every CTA reads the
+        // whole rows once for the sum of squares and for the largest |x (1 + w)| -- that times
+        // 1/rms bounds the normalised row, which is what the FP16 scale needs.  A warp's 32 lanes
+        // hold 32 consecutive chunks of one token; warp w adds its share of token t into
+        // s_part[w][t] in loop order, so the sum has a fixed order.
+        float* s_part = s_out;                                // [kConsumerWarps][8], free until the first epilogue
+        if (tid < kConsumerWarps * 8) s_part[tid] = 0.0f;
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        const int row_chunks = p.K >> 3;                      // a multiple of 32
+        const int total = p.M * row_chunks;
+        for (int base = tid; base < total; base += 4 * kConsumerThreads) {
+            uint4 x[4], w[4];
+            int tk[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int id = base + u * kConsumerThreads;
+                x[u] = w[u] = make_uint4(0u, 0u, 0u, 0u);
+                tk[u] = -1;
+                if (id < total) {
+                    tk[u] = id / row_chunks;
+                    const int c = id - tk[u] * row_chunks;
+                    x[u] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)tk[u] * p.a_stride) + c);
+                    w[u] = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + c);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (tk[u] < 0) continue;                      // uniform across the warp
+                const uint32_t xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w}, wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+                float ss = 0.0f, mt = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float x0 = __uint_as_float(xv[i] << 16), x1 = __uint_as_float(xv[i] & 0xFFFF0000u);
+                    const float w0 = 1.0f + __uint_as_float(wv[i] << 16), w1 = 1.0f + __uint_as_float(wv[i] & 0xFFFF0000u);
+                    ss = fmaf(x0, x0, ss);
+                    ss = fmaf(x1, x1, ss);
+                    mt = fmaxf(mt, fmaxf(fabsf(x0 * w0), fabsf(x1 * w1)));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+                }
+                if (lane == 0) {
+                    s_part[warp * 8 + tk[u]] += ss;
+                    atomicMax(&s_amax[tk[u]], __float_as_uint(mt));
+                }
+            }
+        }
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        if (tid < p.M) {
+            float ss = 0.0f;
+            for (int w = 0; w < kConsumerWarps; ++w) ss += s_part[w * 8 + tid];
+            const float inv = 1.0f / sqrtf(ss / (float)p.K + p.norm_eps);
+            s_amax[8 + tid] = __float_as_uint(inv);
+            // the bound of the normalised row, in the BF16 bit pattern the scale selection below reads
+            float b = __uint_as_float(s_amax[tid]) * inv;
+            b = b < 3.0e38f ? b : 3.0e38f;                    // also catches a NaN row: the scale stays finite
+            s_amax[tid] = __float_as_uint(b) >> 16;
+        }
+        // the staging passes below end with barriers of their own before s_amax[8..] is read
+    }
     if (!(PROBE & 16)) {
         const int per_slot = p.M * 32;
         const int total = p.act_slots * per_slot;
@@ -269,7 +334,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 for (int i = 0; i < 4; ++i) m = max(m, max(v[i] & 0x7FFFu, (v[i] >> 16) & 0x7FFFu));
                 // the 32 lanes of a warp hold the 32 chunks of one (slot, token) row
                 m = __reduce_max_sync(0xffffffffu, m);
-                if (lane == 0 && m) atomicMax(&s_amax[tk[u]], m);
+                if (lane == 0 && m && !p.norm_w) atomicMax(&s_amax[tk[u]], m);
                 *reinterpret_cast<uint4*>(s_act + dst[u]) = x[u];
             }
         }
@@ -290,7 +355,23 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             const float sc = s_tokscale[row % p.M];
             uint4* ptr = reinterpret_cast<uint4*>(s_act + row * kActRowBytes + act_chunk_offset(i & 31));
             const uint4 x = *ptr;
-            const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+            uint32_t v[4] = {x.x, x.y, x.z, x.w};
+            if (p.norm_w) {
+                // bf16( (x / rms) * (1 + w) ), the bits the separate RMSNorm kernel would have stored
+                const int tkn = row % p.M;
+                int kc = kc0 + row / p.M;
+                if (kc >= p.kchunks) kc -= p.kchunks;
+                const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(p.norm_w + kc * kKC) + (i & 31));
+                const uint32_t wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                const float inv = __uint_as_float(s_amax[8 + tkn]);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float y0 = __uint_as_float(v[q] << 16) * inv * (1.0f + __uint_as_float(wv[q] << 16));
+                    const float y1 = __uint_as_float(v[q] & 0xFFFF0000u) * inv * (1.0f + __uint_as_float(wv[q] & 0xFFFF0000u));
+                    const __nv_bfloat162 yb = __floats2bfloat162_rn(y0, y1);
+                    v[q] = *reinterpret_cast<const uint32_t*>(&yb);
+                }
+            }
             uint32_t y[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q)
@@ -590,6 +671,8 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     p.A_up = static_cast<const __nv_bfloat16*>(a.swiglu_up);
     p.a_stride = a.a_stride ? a.a_stride : a.K;
     p.k_valid = a.k_valid ? a.k_valid : a.K;
+    p.norm_w = static_cast<const __nv_bfloat16*>(a.norm_w);
+    p.norm_eps = a.norm_eps;
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.C = static_cast<__nv_bfloat16*>(a.C);
     p.scratch = static_cast<unsigned char*>(scratch);

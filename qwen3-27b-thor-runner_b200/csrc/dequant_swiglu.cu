@@ -1,4 +1,4 @@
-// Whole-matrix dequantisation and SwiGLU: the two small bandwidth kernels beside
+// Whole-matrix dequantisation, SwiGLU and RMSNorm: the small bandwidth kernels beside
 // the linear layer.
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
@@ -77,6 +77,110 @@ cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, flo
     const long long groups = (long long)N * (K >> 4);
     dequant_bf16_kernel<<<grid_for(groups, 256), 256, 0, s>>>(packed, scale, static_cast<__nv_bfloat16*>(out),
                                                             inv_gs, groups);
+    return cudaGetLastError();
+}
+
+namespace {
+
+// RMSNorm with the centred weight, one CTA per token:
+//   out = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + w) ), FP32 throughout
+// (rmsnorm_kernel, src/engine/light_ops.cu:65-106).  With `bias` the row is x + bias first, kept
+// unrounded for the norm, and bf16(x + bias) goes back to x (fused_add_rmsnorm_kernel, :270-318).
+// 16-byte chunks; a thread keeps up to kNormCache chunks in registers between the two passes and
+// reads the row again beyond that.  1/sqrtf and a true division, not the fast-math forms.
+constexpr int kNormThreads = 256;
+constexpr int kNormCache = 6;                 // x 256 threads x 8 elements = 12288 columns from registers
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_kernel(__nv_bfloat16* out, __nv_bfloat16* x, const __nv_bfloat16* __restrict__ bias,
+               const __nv_bfloat16* __restrict__ weight, float eps, int K) {
+    __shared__ float s_part[kNormThreads / 32];
+    __shared__ float s_inv;
+    const int tid = threadIdx.x;
+    const size_t row = (size_t)blockIdx.x * K;
+    const int chunks = K >> 3;
+    auto load = [&](int c, float (&v)[8]) {
+        const uint4 a = *reinterpret_cast<const uint4*>(x + row + (size_t)c * 8);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(aw[i] << 16);
+            v[2 * i + 1] = __uint_as_float(aw[i] & 0xFFFF0000u);
+        }
+        if (bias) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias + row + (size_t)c * 8));
+            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] += __uint_as_float(bw[i] << 16);
+                v[2 * i + 1] += __uint_as_float(bw[i] & 0xFFFF0000u);
+            }
+        }
+    };
+    float cache[kNormCache][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kNormCache; ++j) {
+        const int c = tid + j * kNormThreads;
+        if (c < chunks) {
+            load(c, cache[j]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(cache[j][i], cache[j][i], ss);
+        }
+    }
+    for (int c = tid + kNormCache * kNormThreads; c < chunks; c += kNormThreads) {
+        float v[8];
+        load(c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kNormThreads / 32; ++i) t += s_part[i];
+        s_inv = 1.0f / sqrtf(t / (float)K + eps);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    auto store = [&](int c, const float (&v)[8]) {
+        const uint4 w4 = __ldg(reinterpret_cast<const uint4*>(weight + (size_t)c * 8));
+        const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+        uint32_t o[4], r[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float w0 = 1.0f + __uint_as_float(ww[i] << 16), w1 = 1.0f + __uint_as_float(ww[i] & 0xFFFF0000u);
+            const __nv_bfloat162 y = __floats2bfloat162_rn(v[2 * i] * inv * w0, v[2 * i + 1] * inv * w1);
+            o[i] = *reinterpret_cast<const uint32_t*>(&y);
+            const __nv_bfloat162 q = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            r[i] = *reinterpret_cast<const uint32_t*>(&q);
+        }
+        if (bias) *reinterpret_cast<uint4*>(x + row + (size_t)c * 8) = make_uint4(r[0], r[1], r[2], r[3]);
+        *reinterpret_cast<uint4*>(out + row + (size_t)c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    };
+    // the uncached tail first: with a bias its x is still the old value only until it is stored
+    for (int c = tid + kNormCache * kNormThreads; c < chunks; c += kNormThreads) {
+        float v[8];
+        load(c, v);
+        store(c, v);
+    }
+#pragma unroll
+    for (int j = 0; j < kNormCache; ++j) {
+        const int c = tid + j * kNormThreads;
+        if (c < chunks) store(c, cache[j]);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm(void* out, void* x, const void* bias, const void* weight, float eps, int M, int K,
+                           cudaStream_t s) {
+    rmsnorm_kernel<<<M, kNormThreads, 0, s>>>(static_cast<__nv_bfloat16*>(out), static_cast<__nv_bfloat16*>(x),
+                                              static_cast<const __nv_bfloat16*>(bias),
+                                              static_cast<const __nv_bfloat16*>(weight), eps, K);
     return cudaGetLastError();
 }
 

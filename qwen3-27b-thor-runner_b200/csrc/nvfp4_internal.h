@@ -23,6 +23,8 @@ struct LinearArgs {
     const void* swiglu_up = nullptr;   // A is the gate half, this the up half: activations = bf16(silu(gate) * up)
     long long a_stride = 0;            // elements between rows of A / swiglu_up (0 = K)
     int k_valid = 0;                   // activation columns >= k_valid are zero (0 = K)
+    const void* norm_w = nullptr;      // [K] BF16: activations = rmsnorm(A) with the centred weight (1 + w)
+    float norm_eps = 0.0f;
 };
 
 struct nvfp4_device_info {
@@ -43,6 +45,9 @@ cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, flo
                                 void* out, cudaStream_t s);
 cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
                           void* out, long long row_stride_out, cudaStream_t s);
+// out = rmsnorm(x (+ bias)) with the centred weight; with a bias, x is updated in place.  One CTA per token.
+cudaError_t launch_rmsnorm(void* out, void* x, const void* bias, const void* weight, float eps, int M, int K,
+                           cudaStream_t s);
 
 // --- prefill_simple.cu: C = A * Wdq^T with Wdq bf16 [N,K] already dequantised (debug path).
 cudaError_t launch_gemm_bf16_simple(const void* A, const void* Wdq, const void* residual, void* C,

@@ -23,7 +23,8 @@ class LinearDesc(ctypes.Structure):
     _fields_ = [("A", ctypes.c_void_p), ("swiglu_up", ctypes.c_void_p), ("a_row_stride", ctypes.c_longlong),
                 ("k_valid", ctypes.c_int), ("M", ctypes.c_int), ("packed", ctypes.c_void_p), ("scale", ctypes.c_void_p),
                 ("global_scale", ctypes.c_float), ("N", ctypes.c_int), ("K", ctypes.c_int), ("residual", ctypes.c_void_p),
-                ("C", ctypes.c_void_p), ("px", ctypes.c_void_p)]
+                ("C", ctypes.c_void_p), ("px", ctypes.c_void_p), ("norm_weight", ctypes.c_void_p),
+                ("norm_eps", ctypes.c_float)]
 
 
 class QuantizedWeight(ctypes.Structure):
@@ -54,6 +55,8 @@ SIGNATURES = {
     "nvfp4_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_swiglu_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p,
                                      ctypes.c_longlong, c_void_p]),
+    "nvfp4_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_invoke_fp4_gemv": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p]),
     "nvfp4_invoke_fp4_gemv_add": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p,
                                          c_void_p]),
@@ -160,11 +163,12 @@ class Handle:
         return v.value
 
     def linear_ex(self, A, M, packed, scale, global_scale, N, K, C, residual=None, swiglu_up=None, a_row_stride=0,
-                  k_valid=0, px=None, stream=None):
-        """nvfp4_linear_ex: the linear layer with SwiGLU formed while staging (A = gate half,
-        swiglu_up = up half), a row stride, a zero-padded K, and an optional peer exchange."""
+                  k_valid=0, px=None, norm_weight=None, norm_eps=0.0, stream=None):
+        """nvfp4_linear_ex: the linear layer with SwiGLU (A = gate half, swiglu_up = up half) or
+        RMSNorm (norm_weight) formed while staging, a row stride, a zero-padded K, and an
+        optional peer exchange."""
         d = LinearDesc(_ptr(A), _ptr(swiglu_up), a_row_stride, k_valid, M, _ptr(packed), _ptr(scale), global_scale, N, K,
-                       _ptr(residual), _ptr(C), None if px is None else ctypes.addressof(px))
+                       _ptr(residual), _ptr(C), None if px is None else ctypes.addressof(px), _ptr(norm_weight), norm_eps)
         self._check(self.lib.nvfp4_linear_ex(self.h, ctypes.byref(d), _stream(stream)))
 
     def linear_f32(self, A, M, packed, scale, global_scale, N, K, C_f32, stream=None):
@@ -192,6 +196,13 @@ class Handle:
     def swiglu_strided(self, gate, up, M, I, row_stride_in, out, row_stride_out, stream=None):
         self._check(self.lib.nvfp4_swiglu_strided(self.h, _ptr(gate), _ptr(up), M, I, row_stride_in, _ptr(out),
                                                   row_stride_out, _stream(stream)))
+
+    def rmsnorm(self, x, weight, eps, M, K, out, stream=None):
+        self._check(self.lib.nvfp4_rmsnorm(self.h, _ptr(x), _ptr(weight), eps, M, K, _ptr(out), _stream(stream)))
+
+    def add_rmsnorm(self, residual, bias, weight, eps, M, K, norm_out, stream=None):
+        self._check(self.lib.nvfp4_add_rmsnorm(self.h, _ptr(residual), _ptr(bias), _ptr(weight), eps, M, K, _ptr(norm_out),
+                                               _stream(stream)))
 
     def linear_host(self, A_host, M, packed, scale, global_scale, N, K, C_host, residual_host=None, stream=None):
         self._check(self.lib.nvfp4_linear_host(self.h, _ptr(A_host), M, _ptr(packed), _ptr(scale), global_scale,

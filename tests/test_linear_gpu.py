@@ -4,6 +4,7 @@ own kernels run side by side.  Tolerance: dequantised weights bit-exact; linear 
 relative Frobenius error <= 1e-3 against the FP32-accumulate, single-rounding oracle."""
 import ctypes
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -537,6 +538,103 @@ def test_tp_attn_single_rank(handle, M, o_in):
         blk.close()
         x.close()
         comm.close()
+
+
+# ---------------------------------------------------------------- RMSNorm: the kernel and the GEMV prologue
+
+NORM_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_b200_rmsnorm.npz")
+
+
+def _close_bits(got, want, frac=0.02):
+    """Same BF16 bits except a last-bit difference in at most `frac` of the elements (the sum of
+    squares is added in another order, rsqrt is evaluated another way)."""
+    assert util.bf16_ulp_diff(got, want) <= 1
+    assert (got != want).mean() <= frac
+
+
+@pytest.mark.parametrize("M,K,add", [(1, 256, False), (5, 5120, False), (300, 5120, True), (3, 13312, True), (2, 13312, False)])
+def test_rmsnorm_vs_oracle(handle, M, K, add):
+    import torch
+    x, w = util.make_bf16((M, K), seed=61, std=1.5), util.make_bf16((K,), seed=62, std=0.3)
+    out = torch.zeros((M, K), dtype=torch.int16, device="cuda")
+    if add:
+        b = util.make_bf16((M, K), seed=63, std=0.7)
+        dx = util.to_dev(x)
+        handle.add_rmsnorm(dx, util.to_dev(b), util.to_dev(w), 1e-6, M, K, out)
+        torch.cuda.synchronize()
+        want, want_res = ob.rmsnorm(x, w, 1e-6, bias=b)
+        assert np.array_equal(util.to_host_u16(dx), want_res)          # residual += bias, one rounding: exact
+    else:
+        handle.rmsnorm(util.to_dev(x), util.to_dev(w), 1e-6, M, K, out)
+        torch.cuda.synchronize()
+        want = ob.rmsnorm(x, w, 1e-6)
+    _close_bits(util.to_host_u16(out), want)
+
+
+@pytest.mark.skipif(not os.path.exists(NORM_GOLDEN), reason="golden file not generated")
+def test_rmsnorm_against_committed_reference_outputs(handle):
+    """The kernel against what the reference's own rmsnorm / fused add+rmsnorm kernels stored on a B200."""
+    import torch
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_reference_rmsnorm_golden as g
+    gold = np.load(NORM_GOLDEN)
+    for name, c in g.cases().items():
+        T, hs = c["x"].shape
+        out = torch.zeros((T, hs), dtype=torch.int16, device="cuda")
+        if c["add"]:
+            dx = util.to_dev(c["x"])
+            handle.add_rmsnorm(dx, util.to_dev(c["bias"]), util.to_dev(c["w"]), g.EPS, T, hs, out)
+            torch.cuda.synchronize()
+            assert np.array_equal(util.to_host_u16(dx), gold[name + "_residual"]), name
+        else:
+            handle.rmsnorm(util.to_dev(c["x"]), util.to_dev(c["w"]), g.EPS, T, hs, out)
+            torch.cuda.synchronize()
+        _close_bits(util.to_host_u16(out), gold[name])
+
+
+@pytest.mark.parametrize("M,N,K,res,stride", [
+    (1, 640, 1024, False, 0),          # every CTA holds the whole k range
+    (3, 5120, 5120, True, 0),
+    (8, 1024, 5120, False, 5376),      # rows of a wider buffer
+    (2, 128, 17408, True, 0),          # one row tile over all CTAs: a CTA stages a slice of k but norms the whole row
+    (13, 384, 2048, True, 0),          # two launches of the 8-token kernel
+])
+def test_linear_ex_rmsnorm_prologue(handle, M, N, K, res, stride):
+    """RMSNorm formed while the GEMV stages its activations against the separate RMSNorm kernel
+    followed by the plain linear, and against the oracle's rmsnorm -> linear."""
+    import torch
+    packed, scale = util.make_weight(N, K, seed=71)
+    w = util.make_bf16((K,), seed=72, std=0.3)
+    ld = stride or K
+    Xw = util.make_bf16((M, ld), seed=73, std=2.0)
+    X = np.ascontiguousarray(Xw[:, :K])
+    R = util.make_bf16((M, N), seed=74) if res else None
+    dp, ds, dw = util.to_dev(packed), util.to_dev(scale), util.to_dev(w)
+    fused = util.to_dev(R) if res else torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    handle.linear_ex(util.to_dev(Xw), M, dp, ds, 1.3, N, K, fused, residual=fused if res else None, a_row_stride=stride,
+                     norm_weight=dw, norm_eps=1e-6)
+    again = util.to_dev(R) if res else torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    handle.linear_ex(util.to_dev(Xw), M, dp, ds, 1.3, N, K, again, residual=again if res else None, a_row_stride=stride,
+                     norm_weight=dw, norm_eps=1e-6)
+    normed = torch.zeros((M, K), dtype=torch.int16, device="cuda")
+    handle.rmsnorm(util.to_dev(X), dw, 1e-6, M, K, normed)
+    plain = util.to_dev(R) if res else torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    handle.set_option("wide_gemv", 0)
+    handle.set_option("skinny_min_m", 129)
+    try:
+        handle.linear(normed, M, dp, ds, 1.3, N, K, plain, residual=plain if res else None)
+    finally:
+        handle.set_option("wide_gemv", 1)
+        handle.set_option("skinny_min_m", 9)
+    torch.cuda.synchronize()
+    got = util.to_host_u16(fused)
+    assert np.array_equal(got, util.to_host_u16(again))                 # fixed summation order
+    assert ob.rel_frobenius(got, util.to_host_u16(plain)) <= 5e-4
+    want = ob.linear(ob.rmsnorm(X, w, 1e-6), packed, scale, 1.3, residual=R, mode=ob.GEMV, threads=8)
+    assert ob.rel_frobenius(got, want) <= TOL
+    assert handle.device_status() == 0
+    with pytest.raises(nvfp4.Nvfp4Error):                               # the norm needs the whole row: no padded K
+        handle.linear_ex(util.to_dev(Xw), M, dp, ds, 1.3, N, K, fused, k_valid=K - 16, norm_weight=dw, norm_eps=1e-6)
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 13])

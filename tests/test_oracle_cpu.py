@@ -2,6 +2,7 @@
 the structural facts of the reference formula, and the golden vectors produced by the
 reference's own kernels on a B200 (tests/golden/reference_b200.npz)."""
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -191,3 +192,38 @@ def test_oracle_against_reference_golden():
             # result sits one extra BF16 rounding away from the FP32-accumulate formula (measured
             # 1.15e-3 on this case; the oracle matches the float64 evaluation exactly).
             assert ob.rel_frobenius(got, want) <= 3e-3, name
+
+
+# ---------------------------------------------------------------- RMSNorm
+
+def test_rmsnorm_oracle_against_float64():
+    M, K = 4, 5120
+    x, w, b = util.make_bf16((M, K), seed=1, std=1.5), util.make_bf16((K,), seed=2, std=0.3), util.make_bf16((M, K), seed=3)
+    xf, wf = ob.bf16_to_f32(x).astype(np.float64), ob.bf16_to_f32(w).astype(np.float64)
+    want = ob.f32_to_bf16((xf / np.sqrt((xf ** 2).mean(1, keepdims=True) + 1e-6) * (1 + wf)).astype(np.float32))
+    got = ob.rmsnorm(x, w, 1e-6)
+    assert util.bf16_ulp_diff(got, want) <= 1 and (got != want).mean() < 0.02
+    s = xf + ob.bf16_to_f32(b)
+    want = ob.f32_to_bf16((s / np.sqrt((s ** 2).mean(1, keepdims=True) + 1e-6) * (1 + wf)).astype(np.float32))
+    got, res = ob.rmsnorm(x, w, 1e-6, bias=b)
+    assert np.array_equal(res, ob.f32_to_bf16(s.astype(np.float32)))
+    assert util.bf16_ulp_diff(got, want) <= 1 and (got != want).mean() < 0.02
+
+
+NORM_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_b200_rmsnorm.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(NORM_GOLDEN), reason="golden file not generated")
+def test_rmsnorm_oracle_against_committed_reference_outputs():
+    """The oracle against what the reference's own kernels stored on a B200: the updated residual
+    bit for bit, the normalised rows up to the last bit of a few elements (the reference is
+    compiled with fast-math rsqrt and division)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_reference_rmsnorm_golden as g
+    gold = np.load(NORM_GOLDEN)
+    for name, c in g.cases().items():
+        norm, res = g.oracle_output(c)
+        if c["add"]:
+            assert np.array_equal(res, gold[name + "_residual"]), name
+        assert util.bf16_ulp_diff(norm, gold[name]) <= 1, name
+        assert (norm != gold[name]).mean() <= 0.02, name
