@@ -239,7 +239,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--sections", default="decode,prefill,stream,e2e,cpu,refkernel,tp",
+    ap.add_argument("--sections", default="decode,prefill,stream,mlp,e2e,cpu,refkernel,tp",
                     help="extra measurements to add to the JSON line")
     ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
     ap.add_argument("--prefill-ms", default="64,256,2048,8192", help="token counts of the prefill section")
@@ -357,6 +357,9 @@ def main():
     if "stream" in sections and not args.small:
         import bench_sections
         line["layer_stream"] = bench_sections.layer_stream(h, SHAPES, peaks, torch, alg_bytes)
+    if "mlp" in sections and not args.small:
+        import bench_sections
+        line["mlp_block"] = bench_sections.mlp_block(h, shapes, rot, torch)
     if "refkernel" in sections:
         import bench_sections
         line["reference_kernels_on_this_gpu"] = bench_sections.reference_kernels(shapes, rot, acts, outs, torch,
@@ -376,6 +379,7 @@ def main():
             return out
 
         line["tp_mlp"] = bench_tp.run_tp_mlp_table(torch, None, make_one, H, dev, 1, args.steps)
+        line["tp_layer_stream"] = bench_tp.run_tp_layer_stream(torch, None, h, comm1, dev, 1)
         comm1.close()
     if "cpu" in sections:
         line["cpu_baseline"], _ = cpu_baseline_sweep(15.0)

@@ -127,6 +127,50 @@ def layer_stream(h, SHAPES, peaks, torch, alg_bytes, layers=64):
     return res
 
 
+def mlp_block(h, shapes, rot, torch, tokens=(1, 2, 4, 8)):
+    """One decode MLP block of a layer, src/engine/layer.cu:47-110: RMSNorm -> gate_up -> SwiGLU -> down
+    + residual, as four launches (the reference's sequence) and with the norm formed in the gate_up
+    GEMV's staging and, up to four tokens, the SwiGLU in the down GEMV's (two launches).
+    CUDA-graph timed; the weights rotate over copies larger than L2."""
+    import bench
+    dev = torch.device("cuda:0")
+    (N1, K1), (N2, K2) = shapes["gate_up"], shapes["down"]
+    I = N1 // 2
+    w = bench.device_acts(1, K1, seed=77, dev=dev).reshape(-1)
+    out = []
+    for M in tokens:
+        X = bench.device_acts(M, K1, seed=M, dev=dev)
+        Xn = torch.empty_like(X)
+        gu = torch.empty((M, N1), dtype=torch.bfloat16, device=dev)
+        act = torch.empty((M, I), dtype=torch.bfloat16, device=dev)
+        Y = torch.empty((M, N2), dtype=torch.bfloat16, device=dev)
+
+        def separate():
+            p1, s1 = rot["gate_up"].next()
+            p2, s2 = rot["down"].next()
+            h.rmsnorm(X, w, 1e-6, M, K1, Xn)
+            h.linear(Xn, M, p1, s1, 1.0, N1, K1, gu)
+            h.swiglu(gu, None, M, I, act)
+            h.linear(act, M, p2, s2, 1.0, N2, K2, Y, residual=X)
+
+        def fused():
+            p1, s1 = rot["gate_up"].next()
+            p2, s2 = rot["down"].next()
+            h.linear_ex(X, M, p1, s1, 1.0, N1, K1, gu, norm_weight=w, norm_eps=1e-6)
+            if M <= 4:
+                h.linear_ex(gu, M, p2, s2, 1.0, N2, K2, Y, residual=X, swiglu_up=gu[:, I:], a_row_stride=2 * I)
+            else:
+                h.swiglu(gu, None, M, I, act)
+                h.linear(act, M, p2, s2, 1.0, N2, K2, Y, residual=X)
+
+        row = {"M": M}
+        for name, fn in (("ms_four_launches", separate), ("ms_fused_prologues", fused)):
+            fn(); fn()
+            row[name] = round(bench.time_region(fn, 6, torch, graph=True), 5)
+        out.append(row)
+    return out
+
+
 def reference_kernels(shapes, rot, acts, outs, torch, alg_bytes, decode_ms):
     """The reference engine's kernels (its own source compiled for sm_100a into oracle/_ref) on the
     same device buffers: what the reference would do on this GPU, beside ours."""

@@ -205,6 +205,10 @@ def main(args, world, rank, local_rank):
     import nvfp4
     import nvfp4_tp
 
+    # The communication library prints its version banner on stdout; keep stdout for the one JSON line.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local_rank)
     dev = torch.device(f"cuda:{local_rank}")
     dist.init_process_group("nccl", device_id=dev)
@@ -361,6 +365,9 @@ def main(args, world, rank, local_rank):
                              "frac": round(value / agg_peak, 4), "traffic": None},
                 "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "tp_mlp": table, "parity": parity,
                 "tp_layer_stream": stream, "attn_parity": attn_par}
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     comm.close()
     dist.destroy_process_group()

@@ -100,7 +100,7 @@ int nvfp4_linear(nvfp4_handle* h, const void* A_bf16, int M,
 
 /* The GEMV for callers that must not allocate device memory (no counterpart in the reference:
  * there the scratch is a lazily grown global buffer).  Same arguments and result as nvfp4_linear
- * without a handle: the cross-CTA scratch of the GEMV kernel sits in a fixed ~656 KB array inside
+ * without a handle: the cross-CTA scratch of the GEMV kernel sits in a fixed ~1.3 MB array inside
  * the library's device image (held by every GPU that loads the library, until the process exits),
  * so the call performs no cudaMalloc / cudaFree of any kind.  It serves hosts whose device memory
  * is fully planned before they start calling -- e.g. an engine that gives all remaining HBM to its

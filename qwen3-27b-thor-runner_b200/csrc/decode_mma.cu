@@ -25,9 +25,11 @@
 //     [2^14, 2^15)), so BF16's wider exponent range costs nothing; the scale is undone in FP32.
 //     More than 8 tokens, or activations too large for shared memory, run as several launches.
 //   * A row tile whose K range is split over several CTAs is finished by the CTA that holds its
-//     first half-unit: the others store FP32 partials to the handle's scratch and raise a flag;
-//     the owner adds them in a fixed order (deterministic), applies 2^32/global_scale and the
-//     residual in FP32 and rounds once to BF16.  Its wait on the flags is bounded.
+//     first half-unit: the others store their FP32 partials to the handle's scratch as 8-byte
+//     {value, launch epoch} pairs (one transaction each, so a pair is its own arrival flag: no
+//     fence, no flag write, one L2 round trip for the reader); the owner adds them in a fixed
+//     order (deterministic), applies 2^8/global_scale and the residual in FP32 and rounds once
+//     to BF16.  Its wait on the pairs is bounded.
 //
 // Arithmetic: group products are summed in FP32 by the MMA, block scales are applied exactly
 // before the sum (they are exact), 1/global_scale once at the end.  This is the reference's
@@ -69,6 +71,7 @@ struct DecodeParams {
     const __nv_bfloat16* residual;
     __nv_bfloat16* C;
     unsigned char* scratch;
+    unsigned char* pairs;  // split-tile partials as {FP32 value, epoch} pairs: [CTA][8 tokens][128 rows] x 8 bytes
     float inv_gs;        // 1 / global_scale
     int M, N, K;         // M <= 8 tokens in this launch
     int units, kchunks;  // total half-units, half-units per row tile
@@ -111,8 +114,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
-    unsigned int* flags = reinterpret_cast<unsigned int*>(p.scratch + kFlagsOffset);
-    float* partials = reinterpret_cast<float*>(p.scratch + kPartialOffset);
+    unsigned char* pairs = p.pairs;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, G = gridDim.x;
@@ -405,6 +407,47 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         bool prefetched = complete;
         if (grp == 0 && owner && !complete && !(PROBE & 32))
             while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
+        // The contributors' pairs for this thread's (up to four) outputs, added in CTA order (a fixed
+        // summation order).  Two contributors at a time: their eight loads are issued before any
+        // is looked at, so they share one L2 round trip.  blocking: wait (bounded) for pairs that
+        // do not carry this launch's epoch yet; otherwise give up at the first such pair.
+        auto gather_pairs = [&](float (&sum)[4], bool blocking) -> bool {
+            const long long t0 = clock64();
+            for (int c0 = cta + 1; c0 <= last; c0 += 2) {
+                const bool two = c0 + 1 <= last;
+                const unsigned char* src = pairs + ((size_t)c0 * (kMaxTokens * kRT)) * 8;
+                while (true) {
+                    uint2 v[2][4];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            v[j][i] = make_uint2(0u, p.epoch);
+                            if (mm[i] < p.M && (j == 0 || two))
+                                v[j][i] = ptx::ld_volatile_v2(src + ((size_t)j * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]) * 8);
+                        }
+                    bool ready = true;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == p.epoch);
+                    if (ready) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) sum[i] += __uint_as_float(v[j][i].x);
+                        break;
+                    }
+                    if (!blocking) return false;
+                    if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
+                        *s_abort = 1;
+                        atomicCAS(status, 0u, 0x300u);
+                        return false;
+                    }
+                }
+            }
+            return true;
+        };
 
         while (hu < seg_end) {
             const int cnt = (seg_end - hu) >= GROUPS ? GROUPS : 1;
@@ -420,17 +463,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             // (Looking at the start of the segment instead put two L2 round trips in front of the
             // first stage of every owner: 1.8 us per launch on a B200.)
             if (grp == 0 && owner && !prefetched && !(PROBE & 32) && seg_end - hu <= 2 * GROUPS) {
-                // one lane per contributor, so that the flag round trips overlap
-                int mine_ready = 1;
-                for (int c = cta + 1 + lane; c <= last; c += 32)
-                    mine_ready &= (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) == p.epoch);
-                const int ready = __all_sync(0xffffffffu, mine_ready);
-                if (ready) {
+                float got[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (__all_sync(0xffffffffu, gather_pairs(got, false))) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (mm[i] < p.M)
-                            for (int c = cta + 1; c <= last; ++c)
-                                pre[i] += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
+                    for (int i = 0; i < 4; ++i) pre[i] = got[i];
                     prefetched = true;
                 }
             }
@@ -514,33 +550,15 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             }
             float v[4] = {acc[0] * us0, acc[1] * us1, acc[2] * us0, acc[3] * us1};
             if (!owner) {
-                float* slot = partials + (size_t)cta * (kMaxTokens * kRT);
+                // the pair is its own flag: an aligned 8-byte store is one transaction
+                unsigned char* slot = pairs + (size_t)cta * (kMaxTokens * kRT) * 8;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (mm[i] < p.M) __stcg(slot + mm[i] * kRT + rr[i], v[i]);
-                __syncwarp();
-                if (lane == 0) ptx::st_release_gpu(&flags[cta * kGroupWarps + gw], p.epoch);
+                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), p.epoch);
             } else {
                 if (!prefetched) {
-                    {   // one lane per contributor, so that the flag round trips overlap
-                        const long long t0 = clock64();
-                        for (int c = cta + 1 + lane; c <= last; c += 32) {
-                            while (ptx::ld_acquire_gpu(&flags[c * kGroupWarps + gw]) != p.epoch) {
-                                if (*s_abort) break;
-                                if (clock64() - t0 > ptx::kWaitBudgetClocks) {
-                                    *s_abort = 1;
-                                    atomicCAS(status, 0u, 0x300u);
-                                    break;
-                                }
-                            }
-                        }
-                    }
+                    gather_pairs(pre, true);
                     __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (mm[i] < p.M)
-                            for (int c = cta + 1; c <= last; ++c)
-                                pre[i] += __ldcg(partials + (size_t)c * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]);
                 }
                 const int row_base = tile * kRT;
 #pragma unroll
@@ -649,7 +667,7 @@ bool decode_mma_supported(const LinearArgs& a) {
 }
 
 size_t decode_mma_scratch_bytes(const LinearArgs&, const nvfp4_device_info& dev) {
-    return kPartialOffset + (size_t)dev.sm_count * kMaxTokens * kRT * 4;
+    return dev.gemv_pairs_offset + (size_t)dev.sm_count * kMaxTokens * kRT * 8;
 }
 
 cudaError_t configure_decode_mma() {
@@ -665,7 +683,8 @@ struct DecodePlan {
     int grid, smem, groups;
 };
 
-bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, void* scratch, DecodePlan* out) {
+bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, void* scratch, size_t pairs_offset,
+                        DecodePlan* out) {
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16*>(a.A);
     p.A_up = static_cast<const __nv_bfloat16*>(a.swiglu_up);
@@ -676,6 +695,7 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.C = static_cast<__nv_bfloat16*>(a.C);
     p.scratch = static_cast<unsigned char*>(scratch);
+    p.pairs = p.scratch + pairs_offset;
     p.inv_gs = a.inv_gs;
     p.M = m; p.N = a.N; p.K = a.K;
     p.out_f32 = a.out_f32 ? 1 : 0;
@@ -711,7 +731,7 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
 // One 17-warp CTA per SM.  (Two 9-warp CTAs per SM, GROUPS = 1, measured 1-2 us slower per launch
 // on the MLP shapes: both CTAs of an SM start and end together, so nothing overlaps.)
 bool plan_decode(const LinearArgs& a, int m, const nvfp4_device_info& dev, void* scratch, DecodePlan* out) {
-    return plan_decode_groups(a, m, 2, dev.sm_count, scratch, out);
+    return plan_decode_groups(a, m, 2, dev.sm_count, scratch, dev.gemv_pairs_offset, out);
 }
 
 // Largest token count per launch (<= 8) whose activations fit beside the ring; 0 if none.
@@ -776,10 +796,10 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
 // reference engine does) has nothing to give later, so an allocation made by a plug-in can
 // fail or push the engine over its own budget; code running under a fixed memory plan is in
 // the same position.  For them the GEMV is offered without a handle: the cross-CTA scratch
-// (flags + FP32 partial tiles) that nvfp4_linear takes from the handle workspace lives in a
+// (the partial tiles) that nvfp4_linear takes from the handle workspace lives in a
 // fixed array in the library's device image instead.
 //
-// The array costs kNoAllocScratchBytes (about 656 KB) on every GPU that loads the library, for
+// The array costs kNoAllocScratchBytes (about 1.3 MB) on every GPU that loads the library, for
 // the life of the process.  Limits that follow from its fixed size and from the absence of a
 // workspace: at most 160 CTAs (the grid is capped there), M <= 16, K % 256 == 0, and the
 // activations of 8 tokens or fewer must fit in shared memory beside the weight ring; anything
@@ -788,7 +808,7 @@ namespace nvfp4 {
 namespace {
 
 constexpr int kNoAllocMaxGrid = 160;
-constexpr size_t kNoAllocScratchBytes = kPartialOffset + (size_t)kNoAllocMaxGrid * kMaxTokens * kRT * 4;
+constexpr size_t kNoAllocScratchBytes = kPartialOffset + (size_t)kNoAllocMaxGrid * kMaxTokens * kRT * 8;
 
 // File-scope device array: in HOST code this name is only a handle for the runtime, not an
 // address a kernel can use.  noalloc_setup() asks the runtime for the real device address
@@ -824,6 +844,7 @@ int noalloc_setup(int device, NoAllocState** out) {
         st.dev.sm_count = sms < kNoAllocMaxGrid ? sms : kNoAllocMaxGrid;   // the grid never exceeds the scratch
         st.dev.cc_major = major;
         st.dev.decode_epoch = 0;
+        st.dev.gemv_pairs_offset = kPartialOffset;     // no other kernel shares this scratch
         st.ready = true;
     }
     *out = &st;

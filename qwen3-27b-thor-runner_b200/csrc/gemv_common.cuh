@@ -22,6 +22,10 @@ constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 exch
 // word holds the launch epoch once the CTA's partial for that 16-row slab is stored.
 constexpr size_t kFlagsOffset = 256;              // kGroupWarps flag words per CTA (one per 16-row slab)
 constexpr size_t kPartialOffset = 16384;
+// The 8-token kernel's partials travel as 8-byte {FP32 value, launch epoch} pairs (the data is its
+// own arrival flag), [CTA][8 tokens][128 rows], in a region of their own behind the wide kernel's
+// FP32 partial slabs (a float there could otherwise be read as an epoch).
+constexpr size_t kPairOffset = 2560u << 10;
 constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kGroupWarps));
 
 // Activation row of one (k-chunk, token): four 64-k blocks of 128 bytes, each followed by 16
