@@ -27,7 +27,7 @@ struct nvfp4_handle {
 
 namespace {
 
-constexpr size_t kDecodeScratchBytes = 4u << 20;   // split-K partials + tile counters of the GEMV kernel
+constexpr size_t kDecodeScratchBytes = 8u << 20;   // status word + the split-tile partial pairs of the two GEMV kernels
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -69,7 +69,7 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
     if (fast_path_wanted && h->wide_gemv && decode_wide_supported(a) &&
         kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= h->workspace_bytes &&
-        decode_wide_scratch_bytes(h->dev.sm_count) <= kDecodeScratchBytes) {
+        decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset) {
         // the FP16 activation copy and the per-token factors sit where the prefill kernel keeps its own
         char* base = h->workspace + kDecodeScratchBytes + prefill_umma_reserved_bytes();
         float* unscale = reinterpret_cast<float*>(base + ((size_t)a.M * a.K * 2 + 255) / 256 * 256);

@@ -22,10 +22,10 @@
 //     against the two token tiles (tokens 0..7 and 8..15), FP32 accumulators.  All warps read the
 //     same 9 KB of activations, so a stage is 45 KB and five of them fit;
 //   * a row pair whose k range is split over several CTAs is finished warp by warp, without any
-//     CTA-wide step: contributors store FP32 partials and raise an epoch flag per 16-row slab, the
-//     CTA that holds the row pair's first unit adds them in CTA order, applies the token's unscale,
-//     2^8 / global_scale and the residual in FP32 and rounds once.  Every wait is bounded and
-//     reports through the status word.
+//     CTA-wide step: contributors store their FP32 partials as 8-byte {value, launch epoch} pairs
+//     (one transaction each: the pair is its own arrival flag), the CTA that holds the row pair's
+//     first unit adds them in CTA order, applies 2^8 / global_scale and the residual in FP32 and
+//     rounds once.  Every wait is bounded and reports through the status word.
 // Arithmetic: the reference's small-M kernel (src/engine/dense_gemm_fp4_sm110.cu:155-258) up to
 // FP32 summation order.
 #include <cuda.h>
@@ -53,7 +53,8 @@ constexpr int kActBytes = kTokens * kActRowBytes;         // 9 KB
 constexpr int kStageBytes = kUnitPackedBytes + kUnitScaleBytes + kActBytes;   // 45 KB
 constexpr int kMaxStages = 5;
 constexpr int kSmemBudget = 227 * 1024;
-constexpr int kWideMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kConsumerWarps));   // 16 flag words per CTA
+constexpr int kWideMaxGrid = 160;                 // CTAs whose partial slabs fit in front of the 8-token kernel's pairs
+static_assert(kPartialOffset + (size_t)kWideMaxGrid * kTokens * kUnitRows * 8 <= kPairOffset, "scratch layout");
 
 struct WideParams {
     const __nv_bfloat16* residual;
@@ -82,8 +83,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
-    unsigned int* flags = reinterpret_cast<unsigned int*>(p.scratch + kFlagsOffset);
-    float* partials = reinterpret_cast<float*>(p.scratch + kPartialOffset);
+    unsigned char* pairs = p.scratch + kPartialOffset;     // [CTA][16 tokens][256 rows] x {FP32 value, epoch}
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, G = gridDim.x;
@@ -219,51 +219,78 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
         const bool owner = (kc_first == 0);
         const bool complete = owner && (seg_end == pair_end);
         int last = cta;                                        // contributors are CTAs cta+1 .. last
-        if (owner && !complete) {
+        if (owner && !complete)
             while (last + 1 < G && (long long)(last + 1) * p.units / G < pair_end) ++last;
-            // one lane per contributor (32 at a time), so that the flag round trips overlap
+        const int row_base = pair * kUnitRows;
+        const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
+        float v[kTT][4];
+#pragma unroll
+        for (int j = 0; j < kTT; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int m = 8 * j + 2 * t + (i & 1);
+                v[j][i] = m < p.M ? acc[j][i] * p.unscale[m] : 0.0f;
+            }
+        if (!owner) {
+            // the pair is its own arrival flag: an aligned 8-byte store is one transaction
+            unsigned char* slot = pairs + (size_t)cta * (kTokens * kUnitRows) * 8;
+#pragma unroll
+            for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int m = 8 * j + 2 * t + (i & 1);
+                    if (m < p.M) ptx::st_volatile_v2(slot + (m * kUnitRows + rr[i]) * 8, __float_as_uint(v[j][i]), p.epoch);
+                }
+        } else {
+            // contributors in CTA order (a fixed summation order); the eight loads of one contributor
+            // are issued before any is looked at; the wait for an old epoch is bounded
             const long long t0 = clock64();
-            for (int c0 = cta + 1; c0 <= last; c0 += 32) {
-                const int c = c0 + lane;
-                if (c <= last) {
-                    while (ptx::ld_acquire_gpu(&flags[c * kConsumerWarps + warp]) != p.epoch) {
-                        if (*s_abort) break;
-                        if (clock64() - t0 > ptx::kWaitBudgetClocks) {
-                            *s_abort = 1;
-                            atomicCAS(status, 0u, 0x630u);
-                            break;
+            bool failed = false;
+            for (int c = cta + 1; c <= last && !failed; ++c) {
+                const unsigned char* src = pairs + (size_t)c * (kTokens * kUnitRows) * 8;
+                while (true) {
+                    uint2 x[kTT][4];
+#pragma unroll
+                    for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int m = 8 * j + 2 * t + (i & 1);
+                            x[j][i] = make_uint2(0u, p.epoch);
+                            if (m < p.M) x[j][i] = ptx::ld_volatile_v2(src + (m * kUnitRows + rr[i]) * 8);
                         }
+                    bool ready = true;
+#pragma unroll
+                    for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == p.epoch);
+                    if (ready) {
+#pragma unroll
+                        for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) v[j][i] += __uint_as_float(x[j][i].x);
+                        break;
+                    }
+                    if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
+                        *s_abort = 1;
+                        atomicCAS(status, 0u, 0x630u);
+                        failed = true;
+                        break;
                     }
                 }
             }
             __syncwarp();
-        }
-        const int row_base = pair * kUnitRows;
 #pragma unroll
-        for (int j = 0; j < kTT; ++j) {
-            const int mm[4] = {8 * j + 2 * t, 8 * j + 2 * t + 1, 8 * j + 2 * t, 8 * j + 2 * t + 1};
-            const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
+            for (int j = 0; j < kTT; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (mm[i] >= p.M) continue;
-                float v = acc[j][i] * p.unscale[mm[i]];
-                if (!owner) {
-                    __stcg(partials + (size_t)cta * (kTokens * kUnitRows) + mm[i] * kUnitRows + rr[i], v);
-                    continue;
+                for (int i = 0; i < 4; ++i) {
+                    const int m = 8 * j + 2 * t + (i & 1);
+                    const int n = row_base + rr[i];
+                    if (m >= p.M || n >= p.N) continue;
+                    float x = (v[j][i] * kBlockScaleUnfold) * p.inv_gs;
+                    const size_t o = (size_t)m * p.N + n;
+                    if (p.residual) x += __bfloat162float(p.residual[o]);
+                    p.C[o] = __float2bfloat16_rn(x);
                 }
-                for (int c = cta + 1; c <= last; ++c)
-                    v += __ldcg(partials + (size_t)c * (kTokens * kUnitRows) + mm[i] * kUnitRows + rr[i]);
-                const int n = row_base + rr[i];
-                if (n >= p.N) continue;
-                float x = (v * kBlockScaleUnfold) * p.inv_gs;
-                const size_t o = (size_t)mm[i] * p.N + n;
-                if (p.residual) x += __bfloat162float(p.residual[o]);
-                p.C[o] = __float2bfloat16_rn(x);
-            }
-        }
-        if (!owner) {
-            __syncwarp();
-            if (lane == 0) ptx::st_release_gpu(&flags[cta * kConsumerWarps + warp], p.epoch);
         }
         if (kc >= p.kchunks) { kc = 0; ++pair; }
     }
@@ -277,13 +304,13 @@ bool decode_wide_supported(const LinearArgs& a) {
     return !a.out_f32 && !a.px && !a.swiglu_up && !a.a_stride && !a.k_valid;
 }
 
-size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kUnitRows * 4; }
+size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kUnitRows * 8; }
 
 cudaError_t configure_decode_wide() {
     return cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
 }
 
-// scratch: the handle workspace ([0, 16 KB) status word and flags, then the partial tiles);
+// scratch: the handle workspace ([0, 16 KB) status word, then the partial pairs);
 // act_f16 / unscale: room for the FP16 activation copy (M * K * 2 bytes) and M floats.
 cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, void* act_f16, float* unscale,
                                int* launches, cudaStream_t s) {

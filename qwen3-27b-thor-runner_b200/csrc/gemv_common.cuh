@@ -18,15 +18,13 @@ constexpr int kActBlockBytes = 128 + 16;          // 64 k of FP16 + 16 bytes of 
 constexpr int kActRowBytes = 4 * kActBlockBytes;  // 576 per token per half-unit: four padded 64-k blocks
 constexpr int kOutLd = kRT + 4;                   // padded row of the FP32 exchange tile
 
-// Scratch layout (handle workspace): status word, per-CTA flags, per-CTA partial tiles.  A flag
-// word holds the launch epoch once the CTA's partial for that 16-row slab is stored.
-constexpr size_t kFlagsOffset = 256;              // kGroupWarps flag words per CTA (one per 16-row slab)
+// Scratch layout (handle workspace): status word, then the per-CTA partial tiles.
 constexpr size_t kPartialOffset = 16384;
-// The 8-token kernel's partials travel as 8-byte {FP32 value, launch epoch} pairs (the data is its
-// own arrival flag), [CTA][8 tokens][128 rows], in a region of their own behind the wide kernel's
-// FP32 partial slabs (a float there could otherwise be read as an epoch).
-constexpr size_t kPairOffset = 2560u << 10;
-constexpr int kMaxGrid = (int)((kPartialOffset - kFlagsOffset) / (4 * kGroupWarps));
+// Split-tile partials travel as 8-byte {FP32 value, launch epoch} pairs (the data is its own arrival
+// flag).  The wide kernel's, [CTA][16 tokens][256 rows], start at kPartialOffset (32 KB per CTA); the
+// 8-token kernel's, [CTA][8 tokens][128 rows], at kPairOffset (8 KB per CTA).
+constexpr size_t kPairOffset = 6u << 20;
+constexpr int kMaxGrid = 256;                     // CTAs of the 8-token kernel whose pairs fit its 2 MB of scratch
 
 // Activation row of one (k-chunk, token): four 64-k blocks of 128 bytes, each followed by 16
 // bytes of padding.  Lane (g, t) of a consumer warp reads block t of token g, 16 bytes at a

@@ -35,7 +35,7 @@ struct nvfp4_device_info {
     unsigned int decode_epoch;   // bumped per launch; tags the cross-CTA flags in the scratch
     int prefill_stream_k = 1;    // split the tiles left after whole waves by k over all CTAs
     int skinny_split_cost = 12;  // stage-times charged to splitting row tiles by k in the few-token kernel
-    size_t gemv_pairs_offset = 2560u << 10;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
+    size_t gemv_pairs_offset = 6u << 20;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
 };
 
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
