@@ -239,7 +239,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--sections", default="decode,prefill,stream,mlp,e2e,cpu,refkernel,tp",
+    ap.add_argument("--sections", default="decode,prefill,stream,mlp,dense,e2e,cpu,refkernel,tp",
                     help="extra measurements to add to the JSON line")
     ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
     ap.add_argument("--prefill-ms", default="64,256,2048,8192", help="token counts of the prefill section")
@@ -360,6 +360,9 @@ def main():
     if "mlp" in sections and not args.small:
         import bench_sections
         line["mlp_block"] = bench_sections.mlp_block(h, shapes, rot, torch)
+    if "dense" in sections and not args.small:
+        import bench_sections
+        line["dense_bf16_gemv"] = bench_sections.dense_bf16(h, peaks, torch)
     if "refkernel" in sections:
         import bench_sections
         line["reference_kernels_on_this_gpu"] = bench_sections.reference_kernels(shapes, rot, acts, outs, torch,

@@ -171,6 +171,36 @@ def mlp_block(h, shapes, rot, torch, tokens=(1, 2, 4, 8)):
     return out
 
 
+def dense_bf16(h, peaks, torch, tokens=(1, 4, 8)):
+    """BF16-weight GEMV (the tensors a quantised checkpoint keeps in BF16): the lm_head [248320, 5120]
+    (2.54 GB, far larger than L2) and a 5120 x 5120 projection rotating over copies larger than L2.
+    CUDA-graph timed; GB/s counts weight + activation + output bytes."""
+    import bench
+    dev = torch.device("cuda:0")
+    out = []
+    for name, N, K, copies in (("lm_head", 248320, 5120, 1), ("proj_5120", 5120, 5120, 6)):
+        ws = [(torch.randn((N, K), device=dev, generator=torch.Generator(device=dev).manual_seed(40 + i)) * 0.02).to(torch.bfloat16)
+              for i in range(copies)]
+        for M in tokens:
+            A = bench.device_acts(M, K, seed=M, dev=dev)
+            C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            st = {"i": 0}
+
+            def go():
+                st["i"] = (st["i"] + 1) % copies
+                h.linear_bf16(A, M, ws[st["i"]], N, K, C)
+
+            go(); go()
+            ms = bench.time_region(go, 6, torch, graph=True)
+            nbytes = 2 * N * K + 2 * M * K + 2 * M * N
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(ms * 1e3, 2), "GBps": round(gbs, 1),
+                        "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)})
+        del ws
+        torch.cuda.empty_cache()
+    return out
+
+
 def reference_kernels(shapes, rot, acts, outs, torch, alg_bytes, decode_ms):
     """The reference engine's kernels (its own source compiled for sm_100a into oracle/_ref) on the
     same device buffers: what the reference would do on this GPU, beside ours."""

@@ -201,6 +201,15 @@ int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* sc
 int nvfp4_swiglu(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16_or_null,
                  int M, int I, void* out_bf16, nvfp4_stream_t stream);
 
+/* C[M,N] = A[M,K] * W^T (+ residual) for a weight that stayed BF16 in the checkpoint (lm_head, the
+ * linear-attention projections): W is [N,K] row-major BF16, the reference's "[K,N] column major".
+ * Replaces invoke_dense_gemv / invoke_dense_gemv_add / invoke_dense_gemm(_add)
+ * (src/engine/dense_gemm.h:44-115).  Up to 16 tokens (K % 128 == 0) run the HBM-bound GEMV kernel
+ * (TMA ring + mma.sync BF16, FP32 accumulation, residual added before the only rounding); more tokens
+ * fall back to a plain CUDA-core GEMM: correct, not fast.  residual may alias C. */
+int nvfp4_linear_bf16(nvfp4_handle* h, const void* A_bf16, int M, const void* W_bf16, int N, int K,
+                      const void* residual_bf16_or_null, void* C_bf16, nvfp4_stream_t stream);
+
 /* out[M,K] = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + weight) ) per token row, FP32 inside
  * (invoke_rmsnorm, src/engine/light_ops.cu:65-112; the centred weight of the reference's model).
  * K % 8 == 0; out may alias x. */

@@ -209,6 +209,23 @@ void nvfp4_oracle_swiglu_merged(const uint16_t* merged, int T, int I, uint16_t* 
                             (size_t)I, out + (size_t)t * I);
 }
 
+/* src/engine/dense_gemm.h:64-95 */
+void nvfp4_oracle_dense_linear(const uint16_t* A, int M, const uint16_t* W, int N, int K,
+                               const uint16_t* residual, uint16_t* C) {
+    float* a = (float*)malloc((size_t)K * sizeof(float));
+    for (int m = 0; m < M; ++m) {
+        for (int k = 0; k < K; ++k) a[k] = nvfp4_oracle_bf2f(A[(size_t)m * K + k]);
+        for (int n = 0; n < N; ++n) {
+            const uint16_t* w = W + (size_t)n * K;
+            float acc = 0.0f;
+            for (int k = 0; k < K; ++k) acc += a[k] * nvfp4_oracle_bf2f(w[k]);
+            if (residual) acc += nvfp4_oracle_bf2f(residual[(size_t)m * N + n]);
+            C[(size_t)m * N + n] = nvfp4_oracle_f2bf(acc);
+        }
+    }
+    free(a);
+}
+
 /* src/engine/light_ops.cu:30-57 (blockReduceSum with 256 threads) over per-thread partial sums */
 static float block_reduce_256(float* v) {
     float w[8];

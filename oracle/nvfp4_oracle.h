@@ -77,6 +77,13 @@ void nvfp4_oracle_swiglu(const uint16_t* gate, const uint16_t* up, size_t n, uin
  * Follows src/engine/light_ops.cu:1542-1577. */
 void nvfp4_oracle_swiglu_merged(const uint16_t* merged, int T, int I, uint16_t* out);
 
+/* C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ) for a BF16 weight: exact BF16 products added in
+ * FP32 in k order, residual added in FP32 before the only rounding.  The semantics of the
+ * reference's dense GEMV family (invoke_dense_gemv / _add, src/engine/dense_gemm.h:64-95) up to
+ * the FP32 summation order. */
+void nvfp4_oracle_dense_linear(const uint16_t* A, int M, const uint16_t* W, int N, int K,
+                               const uint16_t* residual, uint16_t* C);
+
 /* RMSNorm with the centred weight, one row per token:
  *   out = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + w) ), FP32 throughout.
  * Follows rmsnorm_kernel, src/engine/light_ops.cu:65-106, including its summation order (256

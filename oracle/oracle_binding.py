@@ -53,6 +53,8 @@ def load():
         lib.nvfp4_oracle_swiglu.argtypes = [_u16p, _u16p, ctypes.c_size_t, _u16p]
         lib.nvfp4_oracle_swiglu_merged.restype = None
         lib.nvfp4_oracle_swiglu_merged.argtypes = [_u16p, c_int, c_int, _u16p]
+        lib.nvfp4_oracle_dense_linear.restype = None
+        lib.nvfp4_oracle_dense_linear.argtypes = [_u16p, c_int, _u16p, c_int, c_int, c_void_p, _u16p]
         lib.nvfp4_oracle_rmsnorm.restype = None
         lib.nvfp4_oracle_rmsnorm.argtypes = [_u16p, c_void_p, _u16p, c_float, c_int, c_int, _u16p, c_void_p]
         lib.nvfp4_oracle_mlp.restype = None
@@ -111,6 +113,16 @@ def swiglu_merged(merged):
     out = np.empty((T, I2 // 2), np.uint16)
     load().nvfp4_oracle_swiglu_merged(merged, T, I2 // 2, out)
     return out
+
+
+def dense_linear(A, W, residual=None):
+    """A [M,K], W [N,K]: uint16 BF16 bits; returns uint16 [M,N]."""
+    M, K = A.shape
+    N = W.shape[0]
+    assert W.shape[1] == K
+    C = np.empty((M, N), np.uint16)
+    load().nvfp4_oracle_dense_linear(np.ascontiguousarray(A), M, np.ascontiguousarray(W), N, K, _res_ptr(residual), C)
+    return C
 
 
 def rmsnorm(x, weight, eps, bias=None):

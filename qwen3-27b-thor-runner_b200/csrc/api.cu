@@ -390,6 +390,28 @@ int nvfp4_swiglu(nvfp4_handle* h, const void* gate, const void* up, int M, int I
     return nvfp4_swiglu_strided(h, gate, up, M, I, merged ? 2LL * I : (long long)I, out, I, stream);
 }
 
+int nvfp4_linear_bf16(nvfp4_handle* h, const void* A, int M, const void* W, int N, int K, const void* residual, void* C,
+                      nvfp4_stream_t stream) {
+    if (!h || !A || !W || !C) return NVFP4_E_NULL;
+    if (M < 0 || N <= 0 || K <= 0 || (K & 7) != 0) return NVFP4_E_SHAPE;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(C) || (residual && !aligned16(residual))) return NVFP4_E_ALIGN;
+    const char* a0 = static_cast<const char*>(A);
+    const char* c0 = static_cast<const char*>(C);
+    if (M > 0 && a0 < c0 + (size_t)M * N * 2 && c0 < a0 + (size_t)M * K * 2) return NVFP4_E_ALIAS;
+    if (M == 0) return NVFP4_OK;
+    DenseArgs a{A, W, residual, C, M, N, K};
+    if (dense_gemv_supported(a, h->dev)) {
+        int nl = 0;
+        cudaError_t e = launch_dense_gemv(a, h->dev, h->workspace, &nl, stream);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
+    // more than 16 tokens, or K not a multiple of 128: the plain CUDA-core GEMM (no tensor-core kernel for BF16 weights yet)
+    cudaError_t e = launch_gemm_bf16_simple(A, W, residual, C, M, N, K, stream);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
 int nvfp4_rmsnorm(nvfp4_handle* h, const void* x, const void* weight, float eps, int M, int K, void* out,
                   nvfp4_stream_t stream) {
     if (!h || !x || !weight || !out) return NVFP4_E_NULL;

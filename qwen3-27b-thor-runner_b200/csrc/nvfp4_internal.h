@@ -54,6 +54,18 @@ cudaError_t launch_rmsnorm(void* out, void* x, const void* bias, const void* wei
 cudaError_t launch_gemm_bf16_simple(const void* A, const void* Wdq, const void* residual, void* C,
                                     int M, int N, int K, cudaStream_t s);
 
+// --- dense_gemv.cu: BF16 weights [N,K], up to 16 tokens (8 per launch), the NVFP4 GEMV's skeleton without dequantisation.
+struct DenseArgs {
+    const void* A;          // [M,K] BF16
+    const void* W;          // [N,K] BF16 row-major
+    const void* residual;   // [M,N] BF16 or null
+    void* C;                // [M,N] BF16
+    int M, N, K;
+};
+bool dense_gemv_supported(const DenseArgs& a, const nvfp4_device_info& dev);
+cudaError_t configure_dense_gemv();
+cudaError_t launch_dense_gemv(const DenseArgs& a, nvfp4_device_info& dev, void* scratch, int* launches, cudaStream_t s);
+
 // --- decode_mma.cu: TMA-fed shared-memory ring + register dequant + warp MMA GEMV (M <= 16).
 bool decode_mma_supported(const LinearArgs& a);
 bool decode_mma_fits(const LinearArgs& a, const nvfp4_device_info& dev);   // activations fit in shared memory

@@ -55,6 +55,7 @@ SIGNATURES = {
     "nvfp4_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_swiglu_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p,
                                      ctypes.c_longlong, c_void_p]),
+    "nvfp4_linear_bf16": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_invoke_fp4_gemv": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p]),
@@ -196,6 +197,9 @@ class Handle:
     def swiglu_strided(self, gate, up, M, I, row_stride_in, out, row_stride_out, stream=None):
         self._check(self.lib.nvfp4_swiglu_strided(self.h, _ptr(gate), _ptr(up), M, I, row_stride_in, _ptr(out),
                                                   row_stride_out, _stream(stream)))
+
+    def linear_bf16(self, A, M, W, N, K, C, residual=None, stream=None):
+        self._check(self.lib.nvfp4_linear_bf16(self.h, _ptr(A), M, _ptr(W), N, K, _ptr(residual), _ptr(C), _stream(stream)))
 
     def rmsnorm(self, x, weight, eps, M, K, out, stream=None):
         self._check(self.lib.nvfp4_rmsnorm(self.h, _ptr(x), _ptr(weight), eps, M, K, _ptr(out), _stream(stream)))

@@ -227,3 +227,11 @@ def test_rmsnorm_oracle_against_committed_reference_outputs():
             assert np.array_equal(res, gold[name + "_residual"]), name
         assert util.bf16_ulp_diff(norm, gold[name]) <= 1, name
         assert (norm != gold[name]).mean() <= 0.02, name
+
+
+def test_dense_linear_oracle_against_float64():
+    M, N, K = 3, 200, 768
+    A, W, R = util.make_bf16((M, K), seed=31), util.make_bf16((N, K), seed=32, std=0.05), util.make_bf16((M, N), seed=33)
+    want = ob.bf16_to_f32(A).astype(np.float64) @ ob.bf16_to_f32(W).astype(np.float64).T + ob.bf16_to_f32(R)
+    got = ob.dense_linear(A, W, residual=R)
+    assert util.bf16_ulp_diff(got, ob.f32_to_bf16(want.astype(np.float32))) <= 1
