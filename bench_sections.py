@@ -171,7 +171,7 @@ def mlp_block(h, shapes, rot, torch, tokens=(1, 2, 4, 8)):
     return out
 
 
-def dense_bf16(h, peaks, torch, tokens=(1, 4, 8)):
+def dense_bf16(h, peaks, torch, tokens=(1, 4, 8), gemm_tokens=(256, 2048)):
     """BF16-weight GEMV (the tensors a quantised checkpoint keeps in BF16): the lm_head [248320, 5120]
     (2.54 GB, far larger than L2) and a 5120 x 5120 projection rotating over copies larger than L2.
     CUDA-graph timed; GB/s counts weight + activation + output bytes."""
@@ -196,6 +196,21 @@ def dense_bf16(h, peaks, torch, tokens=(1, 4, 8)):
             gbs = nbytes / (ms * 1e-3) / 1e9
             out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(ms * 1e3, 2), "GBps": round(gbs, 1),
                         "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4)})
+        if name == "proj_5120":
+            for M in gemm_tokens:          # the tcgen05 GEMM on the same weights
+                A = bench.device_acts(M, K, seed=M, dev=dev)
+                C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+                st = {"i": 0}
+
+                def go():
+                    st["i"] = (st["i"] + 1) % copies
+                    h.linear_bf16(A, M, ws[st["i"]], N, K, C)
+
+                go(); go()
+                ms = bench.time_region(go, 6, torch, graph=True)
+                tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+                out.append({"shape": name, "N": N, "K": K, "M": M, "us": round(ms * 1e3, 2), "TFLOPs": round(tf, 1),
+                            "frac_of_measured_bf16_burst": round(tf / peaks["bf16_tflops"], 4)})
         del ws
         torch.cuda.empty_cache()
     return out

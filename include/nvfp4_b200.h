@@ -206,7 +206,9 @@ int nvfp4_swiglu(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16_or_
  * Replaces invoke_dense_gemv / invoke_dense_gemv_add / invoke_dense_gemm(_add)
  * (src/engine/dense_gemm.h:44-115).  Up to 16 tokens (K % 128 == 0) run the HBM-bound GEMV kernel
  * (TMA ring + mma.sync BF16, FP32 accumulation, residual added before the only rounding); more tokens
- * fall back to a plain CUDA-core GEMM: correct, not fast.  residual may alias C. */
+ * (K % 256 == 0, N % 8 == 0) run the tcgen05 GEMM of the quantised path with the weight blocks loaded
+ * straight into the operand buffers; other shapes fall back to a plain CUDA-core GEMM: correct,
+ * not fast.  residual may alias C. */
 int nvfp4_linear_bf16(nvfp4_handle* h, const void* A_bf16, int M, const void* W_bf16, int N, int K,
                       const void* residual_bf16_or_null, void* C_bf16, nvfp4_stream_t stream);
 

@@ -406,7 +406,13 @@ int nvfp4_linear_bf16(nvfp4_handle* h, const void* A, int M, const void* W, int 
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
-    // more than 16 tokens, or K not a multiple of 128: the plain CUDA-core GEMM (no tensor-core kernel for BF16 weights yet)
+    if (M > 16 && dense_umma_supported(a) && kDecodeScratchBytes + dense_umma_scratch_bytes() <= h->workspace_bytes) {
+        int nl = 0;
+        cudaError_t e = launch_dense_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, stream);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
+    // shapes neither kernel takes (K % 256, N % 8): the plain CUDA-core GEMM
     cudaError_t e = launch_gemm_bf16_simple(A, W, residual, C, M, N, K, stream);
     h->launches += 1;
     return cuda_status(e);

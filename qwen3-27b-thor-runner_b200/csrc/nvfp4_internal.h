@@ -65,6 +65,11 @@ struct DenseArgs {
 bool dense_gemv_supported(const DenseArgs& a, const nvfp4_device_info& dev);
 cudaError_t configure_dense_gemv();
 cudaError_t launch_dense_gemv(const DenseArgs& a, nvfp4_device_info& dev, void* scratch, int* launches, cudaStream_t s);
+// --- prefill_umma.cu, BF16 weights: the tcgen05 GEMM without the dequantisation (K % 256 == 0, N % 8 == 0).
+bool dense_umma_supported(const DenseArgs& a);
+size_t dense_umma_scratch_bytes();
+cudaError_t launch_dense_umma(const DenseArgs& a, nvfp4_device_info& dev, void* scratch, size_t scratch_bytes, size_t offset,
+                              int* launches, cudaStream_t s);
 
 // --- decode_mma.cu: TMA-fed shared-memory ring + register dequant + warp MMA GEMV (M <= 16).
 bool decode_mma_supported(const LinearArgs& a);

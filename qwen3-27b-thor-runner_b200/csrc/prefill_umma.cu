@@ -47,6 +47,7 @@ constexpr int BN = 256;            // weight rows per tile (UMMA N)
 constexpr int BK = 64;             // k per MMA operand block (128 bytes of FP16: one swizzle row)
 constexpr int WK = 256;            // k per raw weight stage (4 operand blocks)
 constexpr int kAStages = 4, kWStages = 2, kBBufs = 2, kAccs = 2;
+constexpr int kBBufsDense = 4;     // BF16 weights: the raw-weight ring is not needed and holds two more B blocks
 constexpr int kABytes = BM * BK * 2;          // 16 KB
 constexpr int kBBytes = BN * BK * 2;          // 32 KB
 constexpr int kWPackedBytes = BN * WK / 2;    // 32 KB
@@ -73,17 +74,19 @@ struct PrefillParams {
     float4* partials;          // [grid][2][64 column chunks][128 token rows] FP32 x 4
     unsigned int* flags;       // [grid][2], launch epoch once that partial tile is stored
     unsigned int epoch;
+    int dense;                 // 1 = BF16 weights and activations as they are: no token scale, no 2^8, no global scale
 };
 
 // ---------------------------------------------------------------- tcgen05 helpers
 // kind::f16, A = B = FP16, D = FP32, both operands K-major, M = 128, N = 256.
 constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t kInstrDescBf16 = kInstrDesc | (1u << 7) | (1u << 10);   // A and B formats: BF16
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Reduction of one split tile.  Every CTA holding a part of the tile calls this once its own
@@ -101,7 +104,7 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int ti
     const int j1 = me + 1 == P ? kPartialVec : ((int)((long long)(me + 1) * kPartialVec / P) & ~(BM - 1));
     const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
     const int m = mt * BM + (t & (BM - 1));
-    const float mul = (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
+    const float mul = p.dense ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
     const float4* head = p.partials + ((size_t)first * 2 + 1) * kPartialVec;
     for (int j = j0 + t; j < j1; j += nthreads) {
         float4 s = __ldcg(head + j);
@@ -133,6 +136,10 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int ti
     }
 }
 
+// DENSE: the weight is BF16 [N,K] (tm_packed is its tensor map, boxes of 64 k x 256 rows; tm_scale is
+// unused) and the activations are the caller's BF16 rows: the producer loads the B blocks straight
+// into the operand buffers, the dequantisation warps have nothing to do.
+template <bool DENSE>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_packed,
                     const __grid_constant__ CUtensorMap tm_scale, const PrefillParams p) {
@@ -150,9 +157,10 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     uint64_t* aempty = afull + kAStages;     // [kAStages]
     uint64_t* wfull = aempty + kAStages;     // [kWStages]
     uint64_t* wempty = wfull + kWStages;     // [kWStages]
-    uint64_t* bfull = wempty + kWStages;     // [kBBufs]
-    uint64_t* bempty = bfull + kBBufs;       // [kBBufs]
-    uint64_t* tfull = bempty + kBBufs;       // [kAccs]
+    constexpr int NB = DENSE ? kBBufsDense : kBBufs;   // B operand buffers (DENSE: s_b runs on into the raw-weight ring)
+    uint64_t* bfull = wempty + kWStages;     // [NB]
+    uint64_t* bempty = bfull + kBBufsDense;  // [NB]
+    uint64_t* tfull = bempty + kBBufsDense;  // [kAccs]
     uint64_t* tempty = tfull + kAccs;        // [kAccs]
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + kAccs);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
@@ -164,7 +172,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     if (tid == 0) {
         for (int i = 0; i < kAStages; ++i) { ptx::mbar_init(&afull[i], 1); ptx::mbar_init(&aempty[i], 1); }
         for (int i = 0; i < kWStages; ++i) { ptx::mbar_init(&wfull[i], 1); ptx::mbar_init(&wempty[i], kDequantWarps); }
-        for (int i = 0; i < kBBufs; ++i) { ptx::mbar_init(&bfull[i], kDequantWarps); ptx::mbar_init(&bempty[i], 1); }
+        for (int i = 0; i < NB; ++i) { ptx::mbar_init(&bfull[i], DENSE ? 1 : kDequantWarps); ptx::mbar_init(&bempty[i], 1); }
         for (int i = 0; i < kAccs; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kEpiWarps); }
         *s_abort = 0;
         ptx::fence_mbar_init();
@@ -184,19 +192,27 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             ptx::prefetch_tensormap(&tm_packed);
             ptx::prefetch_tensormap(&tm_scale);
             const uint64_t pol_w = ptx::policy_evict_first(), pol_a = ptx::policy_evict_last();
-            int sa = 0, sw = 0;
-            uint32_t pa = 0, pw = 0;
+            int sa = 0, sw = 0, sb = 0;
+            uint32_t pa = 0, pw = 0, pb = 0;
             Schedule sched(p.sk_tiles, p.sk_pairs, p.m_tiles, p.n_tiles, kstages);
             Segment sg;
             while (sched.next(sg)) {
                 const int nt = sg.tile / p.m_tiles, mt = sg.tile % p.m_tiles;
                 for (int ks = sg.ks0; ks < sg.ks1; ++ks) {
-                    ptx::mbar_wait(&wempty[sw], pw ^ 1u, s_abort, p.status, 0x410u + sw);
-                    ptx::mbar_arrive_expect_tx(&wfull[sw], kWPackedBytes + kWScaleBytes);
-                    ptx::tma_load_2d(s_wp + sw * kWPackedBytes, &tm_packed, &wfull[sw], ks * (WK / 2), nt * BN, pol_w);
-                    ptx::tma_load_2d(s_ws + sw * kWScaleBytes, &tm_scale, &wfull[sw], ks * (WK / 16), nt * BN, pol_w);
-                    if (++sw == kWStages) { sw = 0; pw ^= 1u; }
+                    if (!DENSE) {
+                        ptx::mbar_wait(&wempty[sw], pw ^ 1u, s_abort, p.status, 0x410u + sw);
+                        ptx::mbar_arrive_expect_tx(&wfull[sw], kWPackedBytes + kWScaleBytes);
+                        ptx::tma_load_2d(s_wp + sw * kWPackedBytes, &tm_packed, &wfull[sw], ks * (WK / 2), nt * BN, pol_w);
+                        ptx::tma_load_2d(s_ws + sw * kWScaleBytes, &tm_scale, &wfull[sw], ks * (WK / 16), nt * BN, pol_w);
+                        if (++sw == kWStages) { sw = 0; pw ^= 1u; }
+                    }
                     for (int j = 0; j < WK / BK; ++j) {
+                        if (DENSE) {      // the B block of this 64-k step, as the tensor core wants it
+                            ptx::mbar_wait(&bempty[sb], pb ^ 1u, s_abort, p.status, 0x410u + sb);
+                            ptx::mbar_arrive_expect_tx(&bfull[sb], kBBytes);
+                            ptx::tma_load_2d(s_b + sb * kBBytes, &tm_packed, &bfull[sb], ks * WK + j * BK, nt * BN, pol_w);
+                            if (++sb == NB) { sb = 0; pb ^= 1u; }
+                        }
                         for (int i = 0; i < sg.pair; ++i) {       // one activation tile per token tile of the pair
                             ptx::mbar_wait(&aempty[sa], pa ^ 1u, s_abort, p.status, 0x400u + sa);
                             ptx::mbar_arrive_expect_tx(&afull[sa], kABytes);
@@ -234,13 +250,13 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k) {
                             umma_f16(d_tmem, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(b_addr + k * 32),
-                                     (kb > 0 || k > 0) ? 1u : 0u);
+                                     (kb > 0 || k > 0) ? 1u : 0u, DENSE ? kInstrDescBf16 : kInstrDesc);
                         }
                         umma_commit(&aempty[sa]);  // operand buffers are free once these MMAs have read them
                         if (++sa == kAStages) { sa = 0; pa ^= 1u; }
                     }
                     umma_commit(&bempty[sb]);
-                    if (++sb == kBBufs) { sb = 0; pb ^= 1u; }
+                    if (++sb == NB) { sb = 0; pb ^= 1u; }
                 }
                 for (int i = 0; i < sg.pair; ++i) {
                     umma_commit(&tfull[acc0 + i]);  // accumulator complete
@@ -249,7 +265,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 if (sg.pair == 1) next_acc ^= 1;
             }
         }
-    } else if (warp >= 8) {
+    } else if (warp >= 8 && !DENSE) {
         // ------------------------------------------------------------------ dequantise: thread = weight row
         const int row = tid - 8 * 32;                     // 0..255
         const int sw7 = row & 7;
@@ -291,7 +307,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 if (++sw == kWStages) { sw = 0; pw ^= 1u; }
             }
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 8) {
         // ------------------------------------------------------------------ epilogue: thread = token row
         const int ew = warp - 4;                          // TMEM lanes 32*ew .. 32*ew+31
         int next_acc = 0;                                     // mirrors the MMA issuer's choice of accumulators
@@ -331,7 +347,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], p.epoch);
                 pend[which] = tile;
             } else {
-                const float mul = (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
+                const float mul = DENSE ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld32(t_addr + c0, r);
@@ -430,7 +446,38 @@ size_t prefill_umma_scratch_bytes(int max_M, int /*max_N*/, int max_K) {
 }
 
 cudaError_t configure_prefill_umma() {
-    return cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(prefill_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(prefill_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+// Plans the tiles of one launch (fills sk_tiles / sk_pairs) and returns the grid.
+static int plan_tiles(PrefillParams& p, const nvfp4_device_info& dev) {
+    // Whole tiles are handed out in pairs of consecutive token tiles of one weight tile (a pair
+    // shares every dequantised B block, which is what the kernel is bound by); whole waves of
+    // pairs run pair by pair, the pairs left over are split tile by tile along k over all CTAs
+    // when that is shorter than one more wave.  Costs in stage-times: a pair's stage ~1.5 (eight
+    // MMAs instead of four on the same shared-memory fill), a single tile's 1, the split ~6
+    // (partial tiles written, flags, reduction), measured on gate_up/down shapes at 64..8192 tokens.
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int ppn = (p.m_tiles + 1) / 2, pairs = p.n_tiles * ppn;
+    const int kstages = p.K / WK;
+    int grid = dev.sm_count < kMaxPrefillGrid ? dev.sm_count : kMaxPrefillGrid;
+    if ((long long)tiles * kstages < grid) grid = tiles * kstages;   // then every tile is split, one stage per CTA
+    auto tiles_of_pairs = [&](int np) { return (np / ppn) * p.m_tiles + ((np % ppn) * 2 < p.m_tiles ? (np % ppn) * 2 : p.m_tiles); };
+    const double pair_cost = p.m_tiles >= 2 ? 1.5 : 1.0;
+    p.sk_tiles = 0;
+    p.sk_pairs = 0;
+    const int left = pairs % grid;
+    if (dev.prefill_stream_k && left > 0) {
+        int skp = left;
+        if ((long long)tiles_of_pairs(skp) * kstages < grid) skp += pairs >= grid ? grid : 0;   // every CTA gets at least one stage
+        const int skt = tiles_of_pairs(skp);
+        const double whole = (double)((pairs + grid - 1) / grid) * kstages * pair_cost;
+        const double split = (double)((pairs - skp) / grid) * kstages * pair_cost + (double)(((long long)skt * kstages + grid - 1) / grid) + 6.0;
+        if (split < whole && (long long)skt * kstages >= grid) { p.sk_pairs = skp; p.sk_tiles = skt; }
+    }
+    return grid;
 }
 
 // scratch: [0, 256) status word (shared with the GEMV kernel); from `offset` the stream-K flags
@@ -465,32 +512,47 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
     p.epoch = ++dev.decode_epoch;
-    // Whole tiles are handed out in pairs of consecutive token tiles of one weight tile (a pair
-    // shares every dequantised B block, which is what the kernel is bound by); whole waves of
-    // pairs run pair by pair, the pairs left over are split tile by tile along k over all CTAs
-    // when that is shorter than one more wave.  Costs in stage-times: a pair's stage ~1.5 (eight
-    // MMAs instead of four on the same shared-memory fill), a single tile's 1, the split ~6
-    // (partial tiles written, flags, reduction), measured on gate_up/down shapes at 64..8192 tokens.
-    const int tiles = p.m_tiles * p.n_tiles;
-    const int ppn = (p.m_tiles + 1) / 2, pairs = p.n_tiles * ppn;
-    const int kstages = a.K / WK;
-    int grid = dev.sm_count < kMaxPrefillGrid ? dev.sm_count : kMaxPrefillGrid;
-    if ((long long)tiles * kstages < grid) grid = tiles * kstages;   // then every tile is split, one stage per CTA
-    auto tiles_of_pairs = [&](int np) { return (np / ppn) * p.m_tiles + ((np % ppn) * 2 < p.m_tiles ? (np % ppn) * 2 : p.m_tiles); };
-    const double pair_cost = p.m_tiles >= 2 ? 1.5 : 1.0;
-    p.sk_tiles = 0;
-    p.sk_pairs = 0;
-    const int left = pairs % grid;
-    if (dev.prefill_stream_k && left > 0) {
-        int skp = left;
-        if ((long long)tiles_of_pairs(skp) * kstages < grid) skp += pairs >= grid ? grid : 0;   // every CTA gets at least one stage
-        const int skt = tiles_of_pairs(skp);
-        const double whole = (double)((pairs + grid - 1) / grid) * kstages * pair_cost;
-        const double split = (double)((pairs - skp) / grid) * kstages * pair_cost + (double)(((long long)skt * kstages + grid - 1) / grid) + 6.0;
-        if (split < whole && (long long)skt * kstages >= grid) { p.sk_pairs = skp; p.sk_tiles = skt; }
-    }
-    prefill_umma_kernel<<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
+    const int grid = plan_tiles(p, dev);
+    prefill_umma_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
     if (launches) *launches = 2;
+    return cudaGetLastError();
+}
+
+bool dense_umma_supported(const DenseArgs& a) {
+    if (a.M < 1 || (a.K % WK) != 0 || (a.N % 8) != 0) return false;
+    return (reinterpret_cast<uintptr_t>(a.W) & 15u) == 0;
+}
+
+size_t dense_umma_scratch_bytes() { return kStreamKBytes; }
+
+// The same kernel on a BF16 weight [N,K] and the caller's BF16 activations: no pre-pass, the B
+// blocks come straight from the weight by TMA.  scratch as above (status word at 0, stream-K flags
+// and partial tiles from `offset`).
+cudaError_t launch_dense_umma(const DenseArgs& a, nvfp4_device_info& dev, void* scratch, size_t scratch_bytes, size_t offset,
+                              int* launches, cudaStream_t s) {
+    if (offset + kStreamKBytes > scratch_bytes) return cudaErrorMemoryAllocation;
+    char* sk = static_cast<char*>(scratch) + offset;
+    CUtensorMap tma, tmw;
+    if (!make_map(&tma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, (uint64_t)a.K, (uint64_t)a.M, BK, BM,
+                  CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tmw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.W, (uint64_t)a.K, (uint64_t)a.N, BK, BN,
+                  CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorInvalidValue;
+    PrefillParams p{};
+    p.residual = static_cast<const __nv_bfloat16*>(a.residual);
+    p.C = static_cast<__nv_bfloat16*>(a.C);
+    p.status = static_cast<unsigned int*>(scratch);
+    p.inv_gs = 1.0f;
+    p.dense = 1;
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.m_tiles = (a.M + BM - 1) / BM;
+    p.n_tiles = (a.N + BN - 1) / BN;
+    p.flags = reinterpret_cast<unsigned int*>(sk);
+    p.partials = reinterpret_cast<float4*>(sk + 4096);
+    p.epoch = ++dev.decode_epoch;
+    const int grid = plan_tiles(p, dev);
+    prefill_umma_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(tma, tmw, tmw, p);
+    if (launches) *launches = 1;
     return cudaGetLastError();
 }
 

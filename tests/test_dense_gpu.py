@@ -60,8 +60,31 @@ def test_dense_lm_head_shape_sample(handle):
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 3e-3   # BF16 output rounding
 
 
-def test_dense_fallback_beyond_16_tokens(handle):
-    M, N, K = 24, 256, 512
+@pytest.mark.parametrize("M,N,K,res", [
+    (17, 256, 256, False),         # one tile, one stage
+    (24, 256, 512, True),
+    (128, 1000, 1024, True),       # N not a multiple of the 256-row tile
+    (300, 2048, 1280, False),      # three token tiles: a pair and a single
+    (1000, 640, 5120, True),       # few tiles, deep K: split along k over the CTAs
+    (130, 40000, 256, True),       # more tiles than CTAs: whole waves of pairs + a split remainder
+])
+def test_dense_gemm_vs_oracle(handle, M, N, K, res):
+    """More than 16 tokens: the tcgen05 GEMM with the BF16 weight blocks loaded straight into the
+    operand buffers."""
+    W = util.make_bf16((N, K), seed=N + K + 1, std=0.05)
+    A = util.make_bf16((M, K), seed=M + 3)
+    R = util.make_bf16((M, N), seed=N + 4) if res else None
+    l0 = handle.launch_count()
+    got = run(handle, A, W, residual=R)
+    assert handle.launch_count() - l0 == 1
+    assert np.array_equal(got, run(handle, A, W, residual=R))          # fixed summation order
+    assert ob.rel_frobenius(got, ob.dense_linear(A, W, residual=R)) <= TOL
+    assert handle.device_status() == 0
+
+
+def test_dense_fallback_shapes(handle):
+    """K not a multiple of 256 beyond 16 tokens: the plain CUDA-core GEMM."""
+    M, N, K = 24, 256, 384
     W = util.make_bf16((N, K), seed=7, std=0.05)
     A = util.make_bf16((M, K), seed=8)
     R = util.make_bf16((M, N), seed=9)
