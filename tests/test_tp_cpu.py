@@ -151,3 +151,53 @@ def test_two_rank_gloo_matches_partition_aware_oracle(world):
     # BF16 partials: close to the partition-aware oracle, a BF16 rounding away from the unsplit MLP
     assert ob.rel_frobenius(outs[0], aware) < 5e-3
     assert ob.rel_frobenius(outs[0], full) < 1e-2
+
+
+def _attn_rank_main(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, H, q_rows, kv_rows, n_kv, o_in = 3, 256, 512, 128, 2, 512
+        qkv_p, qkv_s = util.make_weight(q_rows + 2 * kv_rows, H, seed=41)
+        o_p, o_s = util.make_weight(H, o_in, seed=42)
+        X, R = util.make_bf16((M, H), seed=43), util.make_bf16((M, H), seed=44)
+        # what nvfp4_tp_attn_qkv / nvfp4_tp_attn_out do on one rank, with the oracle as the kernel
+        p, s = nvfp4_tp.shard_qkv(qkv_p, qkv_s, q_rows, kv_rows, n_kv, rank, world)
+        qkv = ob.linear(X, p, s, 1.0)
+        ol = o_in // world
+        attn = np.ascontiguousarray(qkv[:, :ol])               # stub attention: this rank's q columns
+        dp, ds = nvfp4_tp.shard_down(o_p, o_s, rank, world)
+        part = ob.linear(nvfp4_tp.pad_activation(attn, dp.shape[1] * 2), dp, ds, 1.0)
+        t = torch.from_numpy(ob.bf16_to_f32(part).copy())
+        dist.all_reduce(t)                                     # one sum all-reduce of the [M, H] partials
+        got = ob.f32_to_bf16(ob.bf16_to_f32(ob.f32_to_bf16(t.numpy())) + ob.bf16_to_f32(R))
+        q.put((rank, qkv, got))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_attention_block():
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_attn_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = {r: (a, b) for r, a, b in (q.get(timeout=120) for _ in range(world))}
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    M, H, q_rows, kv_rows, n_kv, o_in = 3, 256, 512, 128, 2, 512
+    qkv_p, qkv_s = util.make_weight(q_rows + 2 * kv_rows, H, seed=41)
+    o_p, o_s = util.make_weight(H, o_in, seed=42)
+    X, R = util.make_bf16((M, H), seed=43), util.make_bf16((M, H), seed=44)
+    full = ob.linear(X, qkv_p, qkv_s, 1.0)
+    for r in range(world):                                     # every rank's q | k | v = rows of the unsplit projection
+        assert np.array_equal(res[r][0], full[:, nvfp4_tp.qkv_rows(q_rows, kv_rows, n_kv, r, world)])
+    assert np.array_equal(res[0][1], res[1][1])                # every rank ends with the same tensor
+    want = ob.linear(np.ascontiguousarray(full[:, :q_rows]), o_p, o_s, 1.0, residual=R)
+    assert ob.rel_frobenius(res[0][1], want) < 1e-2            # BF16 partials: a rounding away from the unsplit projection
