@@ -129,8 +129,9 @@ def layer_stream(h, SHAPES, peaks, torch, alg_bytes, layers=64):
 
 def mlp_block(h, shapes, rot, torch, tokens=(1, 2, 4, 8)):
     """One decode MLP block of a layer, src/engine/layer.cu:47-110: RMSNorm -> gate_up -> SwiGLU -> down
-    + residual, as four launches (the reference's sequence) and with the norm formed in the gate_up
-    GEMV's staging and, up to four tokens, the SwiGLU in the down GEMV's (two launches).
+    + residual, as four launches (the reference's sequence), with the norm formed in the gate_up
+    GEMV's staging and, up to four tokens, the SwiGLU in the down GEMV's (two launches), and with the
+    SwiGLU in the gate_up GEMV's epilogue (gate/up rows interleaved at load time; two launches).
     CUDA-graph timed; the weights rotate over copies larger than L2."""
     import bench
     dev = torch.device("cuda:0")
@@ -163,8 +164,16 @@ def mlp_block(h, shapes, rot, torch, tokens=(1, 2, 4, 8)):
                 h.swiglu(gu, None, M, I, act)
                 h.linear(act, M, p2, s2, 1.0, N2, K2, Y, residual=X)
 
+        def fused_epilogue():
+            # gate/up rows interleaved at load time: SwiGLU in the gate_up epilogue, two launches for any M <= 8
+            p1, s1 = rot["gate_up"].next()          # timing only: the row order does not change the work
+            p2, s2 = rot["down"].next()
+            h.linear_ex(X, M, p1, s1, 1.0, N1, K1, act, norm_weight=w, norm_eps=1e-6, swiglu_epilogue=True)
+            h.linear(act, M, p2, s2, 1.0, N2, K2, Y, residual=X)
+
         row = {"M": M}
-        for name, fn in (("ms_four_launches", separate), ("ms_fused_prologues", fused)):
+        for name, fn in (("ms_four_launches", separate), ("ms_fused_prologues", fused),
+                         ("ms_norm_prologue_swiglu_epilogue", fused_epilogue)):
             fn(); fn()
             row[name] = round(bench.time_region(fn, 6, torch, graph=True), 5)
         out.append(row)

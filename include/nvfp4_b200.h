@@ -163,6 +163,12 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A_bf16, int M, const 
  *                 reference fuses the norm into its BF16 GEMV only, src/engine/layer.cu:217-222; its
  *                 FP4 path runs invoke_rmsnorm first, :190-193).  Not together with swiglu_up or
  *                 k_valid.  Every CTA normalises for itself, so this pays for a few tokens only.
+ *   swiglu_epilogue  non-zero: the weight is a merged gate/up tensor whose rows were interleaved in
+ *                 slabs of 16 (rows 16s..16s+7 = gate rows 8s..8s+7, rows 16s+8..16s+15 = their up rows:
+ *                 nvfp4_interleave_gate_up in nvfp4_checkpoint.h does it at load time); C is then
+ *                 [M, N/2] = bf16(silu(gate) * up) with gate and up rounded to BF16 first, i.e. the bits
+ *                 of nvfp4_linear followed by nvfp4_swiglu, without the [M, N] round trip and the second
+ *                 kernel.  N % 16 == 0, no residual, no px.
  * Zero / NULL fields mean "not used".  No reference counterpart for the fused forms. */
 typedef struct nvfp4_linear_desc {
     const void* A;
@@ -179,6 +185,7 @@ typedef struct nvfp4_linear_desc {
     const nvfp4_peer_exchange* px;
     const void* norm_weight;
     float norm_eps;
+    int swiglu_epilogue;
 } nvfp4_linear_desc;
 int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* desc, nvfp4_stream_t stream);
 

@@ -71,6 +71,13 @@ int nvfp4_ckpt_linear(const nvfp4_ckpt* c, const char* prefix, nvfp4_host_weight
 int nvfp4_merge_rows(const nvfp4_host_weight* parts, int n, uint8_t* packed_out, uint8_t* scale_out,
                      nvfp4_host_weight* merged);
 
+/* Merged gate/up [2I, H] (gate rows, then up rows) -> rows interleaved in slabs of 16: rows 16s..16s+7 =
+ * gate rows 8s..8s+7, rows 16s+8..16s+15 = up rows 8s..8s+7.  That is the layout the swiglu_epilogue form
+ * of nvfp4_linear_ex reads: a thread of the GEMV kernel then holds a gate value and its up value.
+ * I % 8 == 0; works on a shard of nvfp4_tp_shard_gate_up as well. */
+int nvfp4_interleave_gate_up(const nvfp4_host_weight* merged, uint8_t* packed_out, uint8_t* scale_out,
+                             nvfp4_host_weight* out);
+
 /* Tensor-parallel shards of the MLP, rank r of `world`:
  *   gate_up: merged [2I, H] -> gate rows and up rows [r*I/P, (r+1)*I/P), merged again [2I/P, H];
  *   down:    [H, I] -> K columns [r*I/P, (r+1)*I/P), K zero-padded (zero codes, zero scales) to a

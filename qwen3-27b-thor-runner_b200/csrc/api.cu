@@ -37,7 +37,7 @@ int check_scale(float gs) {
 }
 
 int validate_linear(const nvfp4_handle* h, const void* A, int M, const uint8_t* packed, const uint8_t* scale,
-                    float gs, int N, int K, const void* residual, const void* C) {
+                    float gs, int N, int K, const void* residual, const void* C, int c_cols = 0) {
     if (!h || !A || !packed || !scale || !C) return NVFP4_E_NULL;
     if (M < 0 || N <= 0 || K <= 0 || (K & 15) != 0) return NVFP4_E_SHAPE;
     if ((long long)N * K / 2 > (1LL << 40)) return NVFP4_E_SHAPE;
@@ -49,7 +49,7 @@ int validate_linear(const nvfp4_handle* h, const void* A, int M, const uint8_t* 
     const char* a0 = static_cast<const char*>(A);
     const char* a1 = a0 + (size_t)M * K * 2;
     const char* c0 = static_cast<const char*>(C);
-    const char* c1 = c0 + (size_t)M * N * 2;
+    const char* c1 = c0 + (size_t)M * (c_cols ? c_cols : N) * 2;
     if (M > 0 && a0 < c1 && c0 < a1) return NVFP4_E_ALIAS;
     return NVFP4_OK;
 }
@@ -59,7 +59,7 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
-    if (a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w) {   // options only the GEMV kernel implements
+    if (a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w || a.swiglu_out) {   // options only the GEMV kernel implements
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
@@ -317,7 +317,9 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A, int M, const uint8
 
 int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t stream) {
     if (!d) return NVFP4_E_NULL;
-    if (int e = validate_linear(h, d->A, d->M, d->packed, d->scale, d->global_scale, d->N, d->K, d->residual, d->C)) return e;
+    if (int e = validate_linear(h, d->A, d->M, d->packed, d->scale, d->global_scale, d->N, d->K, d->residual, d->C,
+                                d->swiglu_epilogue ? d->N / 2 : 0))
+        return e;
     const long long stride = d->a_row_stride ? d->a_row_stride : d->K;
     const int k_valid = d->k_valid ? d->k_valid : d->K;
     if (stride < k_valid || (stride & 7) || k_valid < 1 || k_valid > d->K || (k_valid & 7)) return NVFP4_E_SHAPE;
@@ -325,6 +327,9 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
     if (d->norm_weight) {
         if (!aligned16(d->norm_weight)) return NVFP4_E_ALIGN;
         if (d->swiglu_up || k_valid != d->K || !(d->norm_eps >= 0.0f)) return NVFP4_E_SHAPE;   // the norm runs over all K columns of A itself
+    }
+    if (d->swiglu_epilogue) {
+        if ((d->N & 15) != 0 || d->residual || d->px) return NVFP4_E_SHAPE;   // whole 16-row slabs; the output is the activation of the next linear
     }
     if (d->px) {
         if (d->px->world < 1 || d->px->world > 8 || d->px->rank < 0 || d->px->rank >= d->px->world) return NVFP4_E_TP;
@@ -340,6 +345,7 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
     a.k_valid = d->k_valid;
     a.norm_w = d->norm_weight;
     a.norm_eps = d->norm_eps;
+    a.swiglu_out = d->swiglu_epilogue != 0;
     if (!a.px && !a.swiglu_up && stride == d->K && k_valid == d->K) { a.a_stride = 0; a.k_valid = 0; }   // the plain call
     return run_linear(h, a, stream);
 }

@@ -323,6 +323,22 @@ int nvfp4_tp_shard_down(const nvfp4_host_weight* d, int rank, int world, uint8_t
     return NVFP4_CKPT_OK;
 }
 
+int nvfp4_interleave_gate_up(const nvfp4_host_weight* m, uint8_t* packed_out, uint8_t* scale_out, nvfp4_host_weight* out) {
+    if (!m || !m->packed || !m->scale || !packed_out || !scale_out || !out) return NVFP4_CKPT_E_NULL;
+    if ((m->N % 16) != 0) return NVFP4_CKPT_E_SHAPE;
+    const size_t I = (size_t)m->N / 2, prow = (size_t)m->K / 2, srow = (size_t)m->K / 16;
+    for (size_t s = 0; s < I / 8; ++s) {          // slab s: 8 gate rows, then their 8 up rows
+        std::memcpy(packed_out + (16 * s) * prow, m->packed + (8 * s) * prow, 8 * prow);
+        std::memcpy(packed_out + (16 * s + 8) * prow, m->packed + (I + 8 * s) * prow, 8 * prow);
+        std::memcpy(scale_out + (16 * s) * srow, m->scale + (8 * s) * srow, 8 * srow);
+        std::memcpy(scale_out + (16 * s + 8) * srow, m->scale + (I + 8 * s) * srow, 8 * srow);
+    }
+    *out = *m;
+    out->packed = packed_out;
+    out->scale = scale_out;
+    return NVFP4_CKPT_OK;
+}
+
 int nvfp4_tp_shard_qkv_rows(int q_rows, int kv_rows, int n_kv_heads, int world) {
     if (q_rows <= 0 || kv_rows <= 0 || n_kv_heads <= 0 || world < 1) return NVFP4_CKPT_E_SHAPE;
     if ((q_rows % (8 * world)) != 0 || (kv_rows % n_kv_heads) != 0) return NVFP4_CKPT_E_SHAPE;

@@ -78,6 +78,7 @@ struct DecodeParams {
     int stages;          // ring depth (each stage holds up to two half-units)
     int act_slots;       // activation slots (k-chunks of 256) held in shared memory
     int act_all;         // 1 = slot index is the k-chunk, 0 = position in the CTA's span
+    int swiglu_out;      // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
     int out_f32;         // C is FP32 [M,N]: store the scaled sum unrounded (partial results for a later reduction)
     unsigned int epoch;
     // Tensor-parallel K split: world > 0 = push the sums to the ranks' exchange buffers and reduce
@@ -86,11 +87,7 @@ struct DecodeParams {
     int xrank, xworld, xslot_pairs;
 };
 
-// PROBE selects measurement-only variants (the library instantiates PROBE = 0 only):
-//   bit 0: consumers skip the math (ring hand-shake only)   bit 3: producer moves no data
-//   bit 4: no activation staging                            bit 5: no epilogue
-//   bit 6: XOR instead of the MMAs                          bit 7: no activation loads in the loop
-template <int GROUPS, int PROBE = 0>
+template <int GROUPS>
 __global__ void __launch_bounds__((kGroupWarps * GROUPS + 1) * 32, 3 - GROUPS)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const DecodeParams p) {
@@ -156,16 +153,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     const int cnt = (seg_end - hu) >= GROUPS ? GROUPS : 1;
                     ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0x100u + (unsigned)stage);
                     const int k0 = kc * kKC;
-                    if (PROBE & 8) {
-                        ptx::mbar_arrive(&full_bar[stage]);
-                    } else {
-                        ptx::mbar_arrive_expect_tx(&full_bar[stage], kTxBytes * cnt);
-                        for (int h = 0; h < cnt; ++h) {
-                            ptx::tma_load_2d(s_packed + (stage * GROUPS + h) * kPackedBytes, &tm_packed, &full_bar[stage],
-                                             (k0 + h * kKC) >> 1, row0, pol_stream);
-                            ptx::tma_load_2d(s_scale + (stage * GROUPS + h) * kScaleBytes, &tm_scale, &full_bar[stage],
-                                             (k0 + h * kKC) >> 4, row0, pol_stream);
-                        }
+                    ptx::mbar_arrive_expect_tx(&full_bar[stage], kTxBytes * cnt);
+                    for (int h = 0; h < cnt; ++h) {
+                        ptx::tma_load_2d(s_packed + (stage * GROUPS + h) * kPackedBytes, &tm_packed, &full_bar[stage],
+                                         (k0 + h * kKC) >> 1, row0, pol_stream);
+                        ptx::tma_load_2d(s_scale + (stage * GROUPS + h) * kScaleBytes, &tm_scale, &full_bar[stage],
+                                         (k0 + h * kKC) >> 4, row0, pol_stream);
                     }
                     hu += cnt;
                     kc += cnt;
@@ -273,7 +266,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         }
         // the staging passes below end with barriers of their own before s_amax[8..] is read
     }
-    if (!(PROBE & 16)) {
+    {
         const int per_slot = p.M * 32;
         const int total = p.act_slots * per_slot;
         const int kc0 = p.act_all ? 0 : kc_begin;
@@ -405,7 +398,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         int last = cta;                              // contributors are CTAs cta+1 .. last
         float pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         bool prefetched = complete;
-        if (grp == 0 && owner && !complete && !(PROBE & 32))
+        if (grp == 0 && owner && !complete)
             while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
         // The contributors' pairs for this thread's (up to four) outputs, added in CTA order (a fixed
         // summation order).  Two contributors at a time: their eight loads are issued before any
@@ -462,7 +455,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             // computes), fetch them behind the remaining math; otherwise wait for them at the end.
             // (Looking at the start of the segment instead put two L2 round trips in front of the
             // first stage of every owner: 1.8 us per launch on a B200.)
-            if (grp == 0 && owner && !prefetched && !(PROBE & 32) && seg_end - hu <= 2 * GROUPS) {
+            if (grp == 0 && owner && !prefetched && seg_end - hu <= 2 * GROUPS) {
                 float got[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 if (__all_sync(0xffffffffu, gather_pairs(got, false))) {
 #pragma unroll
@@ -470,7 +463,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     prefetched = true;
                 }
             }
-            if (!(PROBE & 1) && grp < cnt) {
+            if (grp < cnt) {
                 const unsigned char* wp = s_packed + (stage * GROUPS + grp) * kPackedBytes;
                 const unsigned char* sp = s_scale + (stage * GROUPS + grp) * kScaleBytes + off_s;
                 const unsigned char* ap = s_act + (slot * p.M + tok) * kActRowBytes + t * kActBlockBytes;
@@ -480,9 +473,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 const uint4 wb1 = *reinterpret_cast<const uint4*>(wp + off_w1 + 8 * 128);
                 const uint32_t qa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
                 const uint32_t qb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-#ifndef NVFP4_DM_VARIANT
-#define NVFP4_DM_VARIANT 0
-#endif
                 // The four block scales of each row (blocks 4t..4t+3 of the half-unit) as f16x2
                 // operands: scale / 2^8, formed from the byte without a table.
                 uint32_t Sa[4], Sb[4];
@@ -501,19 +491,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     uint32_t da[4], db[4];
                     expand_u32(qa[uu], Sa[uu >> 1], da);
                     expand_u32(qb[uu], Sb[uu >> 1], db);
-                    uint4 x = make_uint4(0x3c003c00u, 0x3c003c00u, 0x3c003c00u, 0x3c003c00u);
-                    if (!(PROBE & 128)) x = *reinterpret_cast<const uint4*>(ap + uu * 16);
+                    const uint4 x = *reinterpret_cast<const uint4*>(ap + uu * 16);
                     const uint32_t a_lo[4] = {da[0], db[0], da[1], db[1]};   // k 0..3 of this 8-group: rows g, g+8
                     const uint32_t a_hi[4] = {da[2], db[2], da[3], db[3]};   // k 4..7
-                    if (PROBE & 64) {   // measurement only: keep the conversions alive without the tensor core
-                        acc[0] = __uint_as_float(__float_as_uint(acc[0]) ^ da[0] ^ db[1] ^ x.x);
-                        acc[1] = __uint_as_float(__float_as_uint(acc[1]) ^ da[1] ^ db[2] ^ x.y);
-                        acc[2] = __uint_as_float(__float_as_uint(acc[2]) ^ da[2] ^ db[3] ^ x.z);
-                        acc[3] = __uint_as_float(__float_as_uint(acc[3]) ^ da[3] ^ db[0] ^ x.w);
-                    } else {
-                        ptx::mma_f16_16x8x16(acc, a_lo, x.x, x.y);
-                        ptx::mma_f16_16x8x16(acc2, a_hi, x.z, x.w);
-                    }
+                    ptx::mma_f16_16x8x16(acc, a_lo, x.x, x.y);
+                    ptx::mma_f16_16x8x16(acc2, a_hi, x.z, x.w);
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
@@ -530,7 +512,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         // thread (g,t) holds rows r0, r0+8 x tokens 2t, 2t+1.  The other warps keep streaming.
         float* xchg = s_out + (seg_parity ? kMaxTokens * kOutLd : 0);
         seg_parity ^= 1;
-        if (PROBE & 32) { if (kc >= p.kchunks) { kc = 0; ++tile; } continue; }
         if (GROUPS == 2) {
             if (grp == 1) {
                 xchg[(2 * t) * kOutLd + r0] = acc[0];
@@ -561,6 +542,19 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     __syncwarp();
                 }
                 const int row_base = tile * kRT;
+                if (p.swiglu_out) {
+                    // Thread (g,t) holds gate row 8 gw + g of this tile's 64 pairs (i = 0, 1) and its up row
+                    // (i = 2, 3) for tokens 2t, 2t+1: the projection's outputs are rounded to BF16 as the
+                    // separate kernels would store them, then silu(gate) * up, one more rounding.
+                    const int n_out = tile * (kRT / 2) + gw * 8 + g;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        if (mm[i] >= p.M || row_base + rr[i] >= p.N) continue;
+                        const float gate = __bfloat162float(__float2bfloat16_rn(((v[i] + pre[i]) * kBlockScaleUnfold) * p.inv_gs));
+                        const float up = __bfloat162float(__float2bfloat16_rn(((v[i + 2] + pre[i + 2]) * kBlockScaleUnfold) * p.inv_gs));
+                        p.C[(size_t)mm[i] * (p.N / 2) + n_out] = __float2bfloat16_rn(silu(gate) * up);
+                    }
+                } else
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int n = row_base + rr[i];
@@ -671,7 +665,7 @@ size_t decode_mma_scratch_bytes(const LinearArgs&, const nvfp4_device_info& dev)
 }
 
 cudaError_t configure_decode_mma() {
-    return cudaFuncSetAttribute(decode_mma_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    return cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
 }
 
 namespace {
@@ -699,6 +693,7 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     p.inv_gs = a.inv_gs;
     p.M = m; p.N = a.N; p.K = a.K;
     p.out_f32 = a.out_f32 ? 1 : 0;
+    p.swiglu_out = a.swiglu_out ? 1 : 0;
     if (a.px) {
         for (int q = 0; q < a.px->world; ++q) p.xpeer[q] = static_cast<unsigned char*>(a.px->peer[q]);
         p.xrank = a.px->rank;
@@ -763,11 +758,11 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         const int m = a.M - m0 < per ? a.M - m0 : per;
         b.A = static_cast<const char*>(a.A) + (size_t)m0 * (a.a_stride ? a.a_stride : a.K) * 2;
         if (a.swiglu_up) b.swiglu_up = static_cast<const char*>(a.swiglu_up) + (size_t)m0 * (a.a_stride ? a.a_stride : a.K) * 2;
-        b.C = static_cast<char*>(a.C) + (size_t)m0 * a.N * (a.out_f32 ? 4 : 2);
+        b.C = static_cast<char*>(a.C) + (size_t)m0 * (a.swiglu_out ? a.N / 2 : a.N) * (a.out_f32 ? 4 : 2);
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DecodePlan pl;
         if (!plan_decode(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
-        pl.p.epoch = ++dev.decode_epoch;
+        pl.p.epoch = next_epoch(dev);
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(pl.grid);
         cfg.blockDim = dim3((2 * kGroupWarps + 1) * 32);
@@ -778,7 +773,7 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<2, 0>, tmp, tms, pl.p);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<2>, tmp, tms, pl.p);
         ++n;
         if (e != cudaSuccess) { if (launches) *launches = n; return e; }
     }

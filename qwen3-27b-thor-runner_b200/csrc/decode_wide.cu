@@ -338,7 +338,7 @@ cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void
     int stages = (kSmemBudget - fixed) / kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
-    p.epoch = ++dev.decode_epoch;
+    p.epoch = next_epoch(dev);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);

@@ -337,7 +337,7 @@ cudaError_t launch_dense_gemv(const DenseArgs& a, nvfp4_device_info& dev, void* 
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DensePlan pl;
         if (!plan_dense(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
-        pl.p.epoch = ++dev.decode_epoch;
+        pl.p.epoch = next_epoch(dev);
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(pl.grid);
         cfg.blockDim = dim3(kDenseThreads);

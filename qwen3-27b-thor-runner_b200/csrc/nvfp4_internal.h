@@ -23,6 +23,7 @@ struct LinearArgs {
     const void* swiglu_up = nullptr;   // A is the gate half, this the up half: activations = bf16(silu(gate) * up)
     long long a_stride = 0;            // elements between rows of A / swiglu_up (0 = K)
     int k_valid = 0;                   // activation columns >= k_valid are zero (0 = K)
+    bool swiglu_out = false;           // weight rows interleaved (8 gate, 8 up per 16): C is [M, N/2] = bf16(silu(gate) * up)
     const void* norm_w = nullptr;      // [K] BF16: activations = rmsnorm(A) with the centred weight (1 + w)
     float norm_eps = 0.0f;
 };
@@ -37,6 +38,13 @@ struct nvfp4_device_info {
     int skinny_split_cost = 12;  // stage-times charged to splitting row tiles by k in the few-token kernel
     size_t gemv_pairs_offset = 6u << 20;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
 };
+
+// The tag of one launch in the cross-CTA scratch (flags, {value, epoch} pairs).  Zero is what freshly
+// cleared scratch holds, so it is never handed out, also not when the counter wraps.
+inline unsigned int next_epoch(nvfp4_device_info& dev) {
+    if (++dev.decode_epoch == 0u) ++dev.decode_epoch;
+    return dev.decode_epoch;
+}
 
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
 cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);

@@ -511,7 +511,7 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.n_tiles = (a.N + BN - 1) / BN;
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
-    p.epoch = ++dev.decode_epoch;
+    p.epoch = next_epoch(dev);
     const int grid = plan_tiles(p, dev);
     prefill_umma_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
     if (launches) *launches = 2;
@@ -549,7 +549,7 @@ cudaError_t launch_dense_umma(const DenseArgs& a, nvfp4_device_info& dev, void* 
     p.n_tiles = (a.N + BN - 1) / BN;
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
-    p.epoch = ++dev.decode_epoch;
+    p.epoch = next_epoch(dev);
     const int grid = plan_tiles(p, dev);
     prefill_umma_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(tma, tmw, tmw, p);
     if (launches) *launches = 1;

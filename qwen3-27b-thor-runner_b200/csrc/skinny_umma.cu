@@ -480,7 +480,7 @@ cudaError_t launch_skinny_umma(const LinearArgs& a, nvfp4_device_info& dev, void
     pl.p.inv_gs = a.inv_gs;
     pl.p.flags = reinterpret_cast<unsigned int*>(sk);
     pl.p.partials = reinterpret_cast<float*>(sk + 4096);
-    pl.p.epoch = ++dev.decode_epoch;
+    pl.p.epoch = next_epoch(dev);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.grid);
     cfg.blockDim = dim3(kThreads);

@@ -24,7 +24,7 @@ class LinearDesc(ctypes.Structure):
                 ("k_valid", ctypes.c_int), ("M", ctypes.c_int), ("packed", ctypes.c_void_p), ("scale", ctypes.c_void_p),
                 ("global_scale", ctypes.c_float), ("N", ctypes.c_int), ("K", ctypes.c_int), ("residual", ctypes.c_void_p),
                 ("C", ctypes.c_void_p), ("px", ctypes.c_void_p), ("norm_weight", ctypes.c_void_p),
-                ("norm_eps", ctypes.c_float)]
+                ("norm_eps", ctypes.c_float), ("swiglu_epilogue", ctypes.c_int)]
 
 
 class QuantizedWeight(ctypes.Structure):
@@ -164,12 +164,12 @@ class Handle:
         return v.value
 
     def linear_ex(self, A, M, packed, scale, global_scale, N, K, C, residual=None, swiglu_up=None, a_row_stride=0,
-                  k_valid=0, px=None, norm_weight=None, norm_eps=0.0, stream=None):
+                  k_valid=0, px=None, norm_weight=None, norm_eps=0.0, swiglu_epilogue=False, stream=None):
         """nvfp4_linear_ex: the linear layer with SwiGLU (A = gate half, swiglu_up = up half) or
         RMSNorm (norm_weight) formed while staging, a row stride, a zero-padded K, and an
         optional peer exchange."""
         d = LinearDesc(_ptr(A), _ptr(swiglu_up), a_row_stride, k_valid, M, _ptr(packed), _ptr(scale), global_scale, N, K,
-                       _ptr(residual), _ptr(C), None if px is None else ctypes.addressof(px), _ptr(norm_weight), norm_eps)
+                       _ptr(residual), _ptr(C), None if px is None else ctypes.addressof(px), _ptr(norm_weight), norm_eps, int(bool(swiglu_epilogue)))
         self._check(self.lib.nvfp4_linear_ex(self.h, ctypes.byref(d), _stream(stream)))
 
     def linear_f32(self, A, M, packed, scale, global_scale, N, K, C_f32, stream=None):

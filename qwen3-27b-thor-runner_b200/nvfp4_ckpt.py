@@ -33,6 +33,7 @@ CKPT_SIGNATURES = {
     "nvfp4_tp_shard_gate_up": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_down": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_down_k": (c_int, [c_int, c_int]),
+    "nvfp4_interleave_gate_up": (c_int, [ctypes.POINTER(HostWeight), c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_qkv": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                    ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_qkv_rows": (c_int, [c_int, c_int, c_int, c_int]),
@@ -136,6 +137,17 @@ def shard_gate_up(packed, scale, gs, rank, world):
     po, so = np.empty((rows, K // 2), np.uint8), np.empty((rows, K // 16), np.uint8)
     out = HostWeight()
     _check(lib.nvfp4_tp_shard_gate_up(ctypes.byref(w), rank, world, po.ctypes.data, so.ctypes.data, ctypes.byref(out)))
+    return po, so
+
+
+def interleave_gate_up(packed, scale, gs):
+    """Merged gate/up rows -> slabs of 8 gate rows + their 8 up rows (the swiglu_epilogue layout)."""
+    lib = load()
+    packed, scale = np.ascontiguousarray(packed), np.ascontiguousarray(scale)
+    w = _host_weight(packed, scale, gs)
+    po, so = np.empty_like(packed), np.empty_like(scale)
+    out = HostWeight()
+    _check(lib.nvfp4_interleave_gate_up(ctypes.byref(w), po.ctypes.data, so.ctypes.data, ctypes.byref(out)))
     return po, so
 
 

@@ -110,6 +110,13 @@ def shard_qkv(packed, scale, q_rows, kv_rows, n_kv_heads, rank, world):
     return np.ascontiguousarray(packed[rows]), np.ascontiguousarray(scale[rows])
 
 
+def interleave_rows(I):
+    """Row order of the swiglu_epilogue layout for a merged gate/up tensor of 2I rows."""
+    assert I % 8 == 0
+    s = np.arange(I // 8)[:, None] * 8 + np.arange(8)[None, :]
+    return np.concatenate([s, I + s], axis=1).reshape(-1)
+
+
 def pad_activation(act, kp):
     """[M, I/P] BF16 bits -> [M, kp] with zero padding."""
     out = np.zeros((act.shape[0], kp), act.dtype)

@@ -209,6 +209,19 @@ def test_shard_tool_attention_projections(tmp_path):
             c.close()
 
 
+def test_interleave_gate_up_matches_numpy_statement():
+    """Slabs of 8 gate rows followed by their 8 up rows; a shard of the tensor-parallel split works the same."""
+    H, I = 256, 272
+    p, s = util.make_weight(2 * I, H, seed=9)
+    order = nvfp4_tp.interleave_rows(I)
+    assert sorted(order) == list(range(2 * I))
+    assert list(order[:16]) == list(range(8)) + list(range(I, I + 8))
+    cp, cs = nvfp4_ckpt.interleave_gate_up(p, s, 1.0)
+    assert np.array_equal(cp, p[order]) and np.array_equal(cs, s[order])
+    with pytest.raises(nvfp4_ckpt.CkptError):
+        nvfp4_ckpt.interleave_gate_up(p[:2 * I - 8], s[:2 * I - 8], 1.0)          # 2I not a multiple of 16
+
+
 def test_writer_roundtrip(tmp_path):
     a = np.arange(24, dtype=np.uint8).reshape(2, 12)
     b = np.array([1.5], np.float32)

@@ -637,6 +637,53 @@ def test_linear_ex_rmsnorm_prologue(handle, M, N, K, res, stride):
         handle.linear_ex(util.to_dev(Xw), M, dp, ds, 1.3, N, K, fused, k_valid=K - 16, norm_weight=dw, norm_eps=1e-6)
 
 
+@pytest.mark.parametrize("M,I,K,norm", [
+    (1, 64, 256, False),           # one tile
+    (3, 2176, 5120, True),         # row tiles split over the CTAs, RMSNorm in front
+    (8, 17408 // 8, 1024, False),
+    (13, 520, 2048, True),         # two launches; I not a multiple of the 64 pairs of a tile
+])
+def test_linear_ex_swiglu_epilogue(handle, M, I, K, norm):
+    """gate/up rows interleaved in slabs of 16: the GEMV's epilogue forms bf16(silu(gate) * up) itself;
+    the bits of the plain linear on the merged tensor followed by the SwiGLU kernel."""
+    import torch
+    import nvfp4_tp
+    packed, scale = util.make_weight(2 * I, K, seed=81)
+    order = nvfp4_tp.interleave_rows(I)
+    ip, isc = np.ascontiguousarray(packed[order]), np.ascontiguousarray(scale[order])
+    X = util.make_bf16((M, K), seed=82, std=1.5)
+    w = util.make_bf16((K,), seed=83, std=0.3)
+    dX, dw = util.to_dev(X), util.to_dev(w)
+    fused = torch.full((M, I), 0x7FC0, dtype=torch.int16, device="cuda")
+    handle.linear_ex(dX, M, util.to_dev(ip), util.to_dev(isc), 1.7, 2 * I, K, fused, swiglu_epilogue=True,
+                     norm_weight=dw if norm else None, norm_eps=1e-6)
+    # the separate kernels on the merged (not interleaved) tensor
+    gu = torch.empty((M, 2 * I), dtype=torch.int16, device="cuda")
+    handle.set_option("wide_gemv", 0)
+    handle.set_option("skinny_min_m", 129)
+    try:
+        handle.linear_ex(dX, M, util.to_dev(packed), util.to_dev(scale), 1.7, 2 * I, K, gu,
+                         norm_weight=dw if norm else None, norm_eps=1e-6)
+    finally:
+        handle.set_option("wide_gemv", 1)
+        handle.set_option("skinny_min_m", 9)
+    sep = torch.empty((M, I), dtype=torch.int16, device="cuda")
+    handle.swiglu(gu, None, M, I, sep)
+    torch.cuda.synchronize()
+    got = util.to_host_u16(fused)
+    # same kernel and roundings; the rows sit in other tiles, so where a tile is split over CTAs the FP32
+    # sums are added in another order: a last-bit difference in a few outputs
+    assert ob.rel_frobenius(got, util.to_host_u16(sep)) <= 5e-4
+    if 2 * I <= 128:
+        assert np.array_equal(got, util.to_host_u16(sep))             # one tile: the very same sums
+    xin = ob.rmsnorm(X, w, 1e-6) if norm else X
+    want = ob.swiglu_merged(ob.linear(xin, packed, scale, 1.7, mode=ob.GEMV, threads=8))
+    assert ob.rel_frobenius(got, want) <= 2e-3                        # SwiGLU amplifies the last-bit differences of its inputs
+    assert handle.device_status() == 0
+    with pytest.raises(nvfp4.Nvfp4Error):                             # the output feeds the next linear: no residual here
+        handle.linear_ex(dX, M, util.to_dev(ip), util.to_dev(isc), 1.7, 2 * I, K, fused, residual=fused, swiglu_epilogue=True)
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 13])
 def test_linear_ex_swiglu_prologue(handle, M):
     """SwiGLU formed while the GEMV stages its activations (merged gate/up rows, K padded beyond
