@@ -234,6 +234,11 @@ int nvfp4_add_rmsnorm(nvfp4_handle* h, void* residual_bf16, const void* bias_bf1
  * rows out_stride apart.  Used where the SwiGLU output feeds a K-padded weight shard. */
 int nvfp4_swiglu_strided(nvfp4_handle* h, const void* gate_bf16, const void* up_bf16, int M, int I,
                          long long in_stride, void* out_bf16, long long out_stride, nvfp4_stream_t stream);
+/* The same on the output of a linear whose gate/up weight rows were interleaved in slabs of 16
+ * (nvfp4_interleave_gate_up): gate_up rows hold 8 gate values, their 8 up values, 8 gate values, ...;
+ * out[M,I].  I % 8 == 0; row strides in elements. */
+int nvfp4_swiglu_interleaved(nvfp4_handle* h, const void* gate_up_bf16, int M, int I, long long in_stride,
+                             void* out_bf16, long long out_stride, nvfp4_stream_t stream);
 
 /* ---- reference-shaped entry points --------------------------------------
  * Same argument meaning as the reference functions of the same name (void

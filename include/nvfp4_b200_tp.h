@@ -10,7 +10,9 @@
  * push-and-sum kernel over peer memory (FP32, rank order) for up to 16 tokens.
  * Rank r owns gate rows and up rows [r*I/P, (r+1)*I/P) and down columns [r*I/P, (r+1)*I/P);
  * a shard is a pure slice of the reference layout (no re-quantisation); the down shard's K is
- * zero-padded to a multiple of 256 so that its scale rows stay 16-byte multiples.
+ * zero-padded to a multiple of 256 so that its scale rows stay 16-byte multiples, and the block's
+ * own copy of the gate/up shard has its rows interleaved in slabs of 16 (8 gate rows, their 8 up
+ * rows) so that up to 8 tokens get their SwiGLU in the gate_up kernel's epilogue.
  * Library: libnvfp4_b200_tp.so (needs libnvfp4_b200.so and libnccl.so.2).
  */
 #ifndef NVFP4_B200_TP_H

@@ -387,6 +387,17 @@ int nvfp4_swiglu_strided(nvfp4_handle* h, const void* gate, const void* up, int 
     return cuda_status(e);
 }
 
+int nvfp4_swiglu_interleaved(nvfp4_handle* h, const void* gate_up, int M, int I, long long in_stride, void* out,
+                             long long out_stride, nvfp4_stream_t stream) {
+    if (!h || !gate_up || !out) return NVFP4_E_NULL;
+    if (M < 0 || I <= 0 || (I & 7) != 0 || in_stride < 2LL * I || out_stride < I) return NVFP4_E_SHAPE;
+    if (!aligned16(gate_up) || !aligned16(out) || (in_stride & 7) || (out_stride & 7)) return NVFP4_E_ALIGN;
+    if (M == 0) return NVFP4_OK;
+    cudaError_t e = launch_swiglu(gate_up, static_cast<const char*>(gate_up) + 16, in_stride, M, I, out, out_stride, stream, true);
+    h->launches += 1;
+    return cuda_status(e);
+}
+
 int nvfp4_swiglu(nvfp4_handle* h, const void* gate, const void* up, int M, int I, void* out,
                  nvfp4_stream_t stream) {
     if (!h || !gate || !out) return NVFP4_E_NULL;

@@ -35,18 +35,22 @@ dequant_bf16_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
 
 // silu(x) = x / (1 + exp(-x)) in FP32, product rounded once to BF16
 // (src/engine/light_ops.cu:168-199 and :1542-1577).  gate and up rows are
-// row_stride_in elements apart (I for separate tensors, 2I for the merged layout).
+// row_stride_in elements apart (I for separate tensors, 2I for the merged layout).  interleaved:
+// the input row holds slabs of 16 columns, 8 gate values followed by their 8 up values (the
+// output of a linear on row-interleaved gate/up weights); gate points at column 0, up at column 8.
 
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
-              __nv_bfloat16* __restrict__ out, long long row_stride_in, long long row_stride_out, int M, int I) {
+              __nv_bfloat16* __restrict__ out, long long row_stride_in, long long row_stride_out, int M, int I,
+              int interleaved) {
     const int vec_per_row = I >> 3;
     const long long total = (long long)M * vec_per_row;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += stride) {
         const int m = (int)(v / vec_per_row), c = (int)(v % vec_per_row) * 8;
-        const uint4 g4 = *reinterpret_cast<const uint4*>(gate + (size_t)m * row_stride_in + c);
-        const uint4 u4 = *reinterpret_cast<const uint4*>(up + (size_t)m * row_stride_in + c);
+        const int cin = interleaved ? 2 * c : c;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(gate + (size_t)m * row_stride_in + cin);
+        const uint4 u4 = *reinterpret_cast<const uint4*>(up + (size_t)m * row_stride_in + cin);
         *reinterpret_cast<uint4*>(out + (size_t)m * row_stride_out + c) = swiglu_bf16x8(g4, u4);
     }
     // I % 8 tail columns, scalar.
@@ -185,11 +189,12 @@ cudaError_t launch_rmsnorm(void* out, void* x, const void* bias, const void* wei
 }
 
 cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
-                          void* out, long long row_stride_out, cudaStream_t s) {
+                          void* out, long long row_stride_out, cudaStream_t s, bool interleaved) {
     const long long vecs = (long long)M * ((I + 7) >> 3);
     swiglu_kernel<<<grid_for(vecs, 256), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gate),
                                                     static_cast<const __nv_bfloat16*>(up),
-                                                    static_cast<__nv_bfloat16*>(out), row_stride_in, row_stride_out, M, I);
+                                                    static_cast<__nv_bfloat16*>(out), row_stride_in, row_stride_out, M, I,
+                                                    interleaved ? 1 : 0);
     return cudaGetLastError();
 }
 

@@ -53,7 +53,7 @@ cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);
 cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, float inv_gs, int N, int K,
                                 void* out, cudaStream_t s);
 cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
-                          void* out, long long row_stride_out, cudaStream_t s);
+                          void* out, long long row_stride_out, cudaStream_t s, bool interleaved = false);
 // out = rmsnorm(x (+ bias)) with the centred weight; with a bias, x is updated in place.  One CTA per token.
 cudaError_t launch_rmsnorm(void* out, void* x, const void* bias, const void* weight, float eps, int M, int K,
                            cudaStream_t s);

@@ -8,13 +8,14 @@
 // src/engine/model.cpp:456-514) and writes, for every rank r, <out_prefix>.rank<r>.safetensors with
 //   gate_up.weight_packed [2I/P, H/2]   gate_up.weight_scale [2I/P, H/16]   gate_up.weight_global_scale
 //   down.weight_packed    [H, Kp/2]     down.weight_scale    [H, Kp/16]     down.weight_global_scale
-// Kp = I/P rounded up to a multiple of 256, the padding zero: exactly the shards
-// nvfp4_tp_mlp_create cuts on the device, so a rank can load its file and skip that step.
+// Kp = I/P rounded up to a multiple of 256, the padding zero: the row and column split
+// nvfp4_tp_mlp_create makes on the device (which then also interleaves the gate and up rows of its
+// own copy in slabs of 16 for the fused SwiGLU epilogue; nvfp4_interleave_gate_up does that on the host).
 // The attn form merges q, k and v by rows (src/engine/model.cpp:296-350), gives rank r its q rows and the
 // k and v rows of its KV heads, and cuts the output projection by K like the down projection:
 //   qkv.weight_packed [q/P + 2 kv_local, H/2]   qkv.weight_scale   qkv.weight_global_scale
 //   o.weight_packed   [H, Kp/2]                 o.weight_scale     o.weight_global_scale
-// exactly the shards nvfp4_tp_attn_create cuts on the device.
+// the shards nvfp4_tp_attn_create cuts on the device.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>

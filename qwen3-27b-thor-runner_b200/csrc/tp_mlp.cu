@@ -21,7 +21,7 @@ struct nvfp4_tp_mlp {
 };
 
 namespace {
-constexpr int kSwigluInStagingMaxM = 4;
+constexpr int kSwigluInEpilogueMaxM = 8;   // one launch of the 8-token GEMV kernel
 }
 
 extern "C" {
@@ -60,12 +60,16 @@ int nvfp4_tp_mlp_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int I, cons
     if (e == cudaSuccess) e = cudaMemset(m->dn_packed, 0, (size_t)H * m->Kp / 2);   // zero codes and zero scales
     if (e == cudaSuccess) e = cudaMemset(m->dn_scale, 0, (size_t)H * m->Kp / 16);   // in the K padding
     if (e == cudaSuccess) e = cudaMemset(m->act, 0, (size_t)max_M * m->Kp * 2);     // pad activations stay zero
-    // gate rows [r*Ip, (r+1)*Ip) then up rows I + [r*Ip, (r+1)*Ip): contiguous row blocks of the merged tensor.
+    // gate rows [r*Ip, (r+1)*Ip) and up rows I + [r*Ip, (r+1)*Ip) of the merged tensor, interleaved in
+    // slabs of 16 rows (8 gate rows, their 8 up rows): a thread of the GEMV kernel then holds a gate
+    // value next to its up value and the SwiGLU moves into the gate_up epilogue.  One strided copy
+    // per half: blocks of 8 rows land 16 rows apart.
     const size_t prow = (size_t)H / 2, srow = (size_t)H / 16;
-    if (e == cudaSuccess) e = cudaMemcpy(m->gu_packed, gup + (size_t)r * m->Ip * prow, m->Ip * prow, cudaMemcpyDeviceToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(m->gu_packed + m->Ip * prow, gup + ((size_t)I + (size_t)r * m->Ip) * prow, m->Ip * prow, cudaMemcpyDeviceToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(m->gu_scale, gus + (size_t)r * m->Ip * srow, m->Ip * srow, cudaMemcpyDeviceToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(m->gu_scale + m->Ip * srow, gus + ((size_t)I + (size_t)r * m->Ip) * srow, m->Ip * srow, cudaMemcpyDeviceToDevice);
+    const size_t slabs = (size_t)m->Ip / 8;
+    if (e == cudaSuccess) e = cudaMemcpy2D(m->gu_packed, 16 * prow, gup + (size_t)r * m->Ip * prow, 8 * prow, 8 * prow, slabs, cudaMemcpyDeviceToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy2D(m->gu_packed + 8 * prow, 16 * prow, gup + ((size_t)I + (size_t)r * m->Ip) * prow, 8 * prow, 8 * prow, slabs, cudaMemcpyDeviceToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy2D(m->gu_scale, 16 * srow, gus + (size_t)r * m->Ip * srow, 8 * srow, 8 * srow, slabs, cudaMemcpyDeviceToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy2D(m->gu_scale + 8 * srow, 16 * srow, gus + ((size_t)I + (size_t)r * m->Ip) * srow, 8 * srow, 8 * srow, slabs, cudaMemcpyDeviceToDevice);
     // down columns [r*Ip, (r+1)*Ip) of every row, into rows of Kp elements.
     if (e == cudaSuccess) e = cudaMemcpy2D(m->dn_packed, (size_t)m->Kp / 2, dnp + (size_t)r * m->Ip / 2, (size_t)I / 2, (size_t)m->Ip / 2, H, cudaMemcpyDeviceToDevice);
     if (e == cudaSuccess) e = cudaMemcpy2D(m->dn_scale, (size_t)m->Kp / 16, dns + (size_t)r * m->Ip / 16, (size_t)I / 16, (size_t)m->Ip / 16, H, cudaMemcpyDeviceToDevice);
@@ -87,27 +91,39 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     if (!m || !X || !out) return NVFP4_E_NULL;
     if (M < 0 || M > m->max_M) return NVFP4_E_SHAPE;
     if (M == 0) return NVFP4_OK;
-    int st = nvfp4_linear(m->h, X, M, m->gu_packed, m->gu_scale, m->gu_gs, 2 * m->Ip, m->H, nullptr, m->gate_up_out, s);
-    if (st) return st;
-    const char* gate = static_cast<const char*>(m->gate_up_out);
-    const char* up = gate + (size_t)m->Ip * 2;
     nvfp4_linear_desc d{};
     d.M = M;
     d.packed = m->dn_packed; d.scale = m->dn_scale; d.global_scale = m->dn_gs; d.N = m->H; d.K = m->Kp;
     d.residual = residual; d.C = out;
-    // Up to kSwigluInStagingMaxM tokens the down projection forms bf16(silu(gate) * up) while it
-    // stages its activations, so the MLP is two kernels.  Every CTA of that kernel converts the
-    // activations of its own k range, i.e. the SwiGLU is recomputed once per row tile; beyond a few
-    // tokens that costs more than the separate SwiGLU launch it saves (measured: 8 tokens lose
-    // 2.8 us, 1 token gains 0.9 us on the 2-GPU shard shapes).  Columns beyond I/P of the padded
-    // K count as zero.
-    if (M <= kSwigluInStagingMaxM) {
-        d.A = gate; d.swiglu_up = up; d.a_row_stride = 2LL * m->Ip; d.k_valid = m->Ip;
-        st = nvfp4::tp::rowsplit_linear(m->h, m->comm, m->x, m->fused, d, m->res_copy, s);
-        if (st != NVFP4_E_LIMIT) return st;
-        d.swiglu_up = nullptr; d.a_row_stride = 0; d.k_valid = 0;
+    int st;
+    if (M <= kSwigluInEpilogueMaxM) {
+        // Up to 8 tokens the gate_up GEMV forms bf16(silu(gate) * up) in its epilogue (the shard's rows
+        // are interleaved for that), so the MLP is two kernels and the [M, 2 I/P] tensor never exists.
+        // The down projection reads the [M, I/P] result in place; columns beyond I/P of its padded K
+        // count as zero.
+        nvfp4_linear_desc g{};
+        g.A = X; g.M = M;
+        g.packed = m->gu_packed; g.scale = m->gu_scale; g.global_scale = m->gu_gs; g.N = 2 * m->Ip; g.K = m->H;
+        g.C = m->gate_up_out;
+        g.swiglu_epilogue = 1;
+        st = nvfp4_linear_ex(m->h, &g, s);
+        if (st == NVFP4_OK) {
+            d.A = m->gate_up_out;
+            if (m->Kp != m->Ip) { d.a_row_stride = m->Ip; d.k_valid = m->Ip; }
+            st = nvfp4::tp::rowsplit_linear(m->h, m->comm, m->x, m->fused, d, m->res_copy, s);
+            if (st != NVFP4_E_LIMIT) return st;
+            // the general kernels want plain [M, Kp] rows: copy (the pad columns of `act` stay zero)
+            if (cudaMemcpy2DAsync(m->act, (size_t)m->Kp * 2, m->gate_up_out, (size_t)m->Ip * 2, (size_t)m->Ip * 2, M,
+                                  cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+                return NVFP4_E_TP;
+            d.A = m->act; d.a_row_stride = 0; d.k_valid = 0;
+            return nvfp4::tp::rowsplit_linear(m->h, m->comm, m->x, m->fused, d, m->res_copy, s);
+        }
+        if (st != NVFP4_E_LIMIT) return st;      // a shape the GEMV kernel does not take: the general path below
     }
-    st = nvfp4_swiglu_strided(m->h, gate, up, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
+    st = nvfp4_linear(m->h, X, M, m->gu_packed, m->gu_scale, m->gu_gs, 2 * m->Ip, m->H, nullptr, m->gate_up_out, s);
+    if (st) return st;
+    st = nvfp4_swiglu_interleaved(m->h, m->gate_up_out, M, m->Ip, 2LL * m->Ip, m->act, m->Kp, s);
     if (st) return st;
     d.A = m->act;
     return nvfp4::tp::rowsplit_linear(m->h, m->comm, m->x, m->fused, d, m->res_copy, s);

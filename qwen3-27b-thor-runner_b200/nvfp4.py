@@ -58,6 +58,8 @@ SIGNATURES = {
     "nvfp4_linear_bf16": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_swiglu_interleaved": (c_int, [c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p, ctypes.c_longlong,
+                                         c_void_p]),
     "nvfp4_invoke_fp4_gemv": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p]),
     "nvfp4_invoke_fp4_gemv_add": (None, [c_void_p, ctypes.POINTER(QuantizedWeight), c_void_p, c_void_p,
                                          c_void_p]),
@@ -207,6 +209,10 @@ class Handle:
     def add_rmsnorm(self, residual, bias, weight, eps, M, K, norm_out, stream=None):
         self._check(self.lib.nvfp4_add_rmsnorm(self.h, _ptr(residual), _ptr(bias), _ptr(weight), eps, M, K, _ptr(norm_out),
                                                _stream(stream)))
+
+    def swiglu_interleaved(self, gate_up, M, I, row_stride_in, out, row_stride_out, stream=None):
+        self._check(self.lib.nvfp4_swiglu_interleaved(self.h, _ptr(gate_up), M, I, row_stride_in, _ptr(out), row_stride_out,
+                                                      _stream(stream)))
 
     def linear_host(self, A_host, M, packed, scale, global_scale, N, K, C_host, residual_host=None, stream=None):
         self._check(self.lib.nvfp4_linear_host(self.h, _ptr(A_host), M, _ptr(packed), _ptr(scale), global_scale,
