@@ -12,7 +12,7 @@
  * a shard is a pure slice of the reference layout (no re-quantisation); the down shard's K is
  * zero-padded to a multiple of 256 so that its scale rows stay 16-byte multiples, and the block's
  * own copy of the gate/up shard has its rows interleaved in slabs of 16 (8 gate rows, their 8 up
- * rows) so that up to 8 tokens get their SwiGLU in the gate_up kernel's epilogue.
+ * rows) so that up to 16 tokens get their SwiGLU in the gate_up kernel's epilogue.
  * Library: libnvfp4_b200_tp.so (needs libnvfp4_b200.so and libnccl.so.2).
  */
 #ifndef NVFP4_B200_TP_H

@@ -59,17 +59,20 @@ int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 // One linear call on device buffers.
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (a.M == 0) return NVFP4_OK;
-    if (a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w || a.swiglu_out) {   // options only the GEMV kernel implements
+    const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
+    const bool wide_ok = fast_path_wanted && h->wide_gemv && decode_wide_supported(a) &&
+                         kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= h->workspace_bytes &&
+                         decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset;
+    // options only the GEMV kernels implement (the SwiGLU epilogue exists in the wide one too)
+    const bool other_options = a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
+    if (other_options || (a.swiglu_out && !wide_ok)) {
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
-    const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
-    if (fast_path_wanted && h->wide_gemv && decode_wide_supported(a) &&
-        kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= h->workspace_bytes &&
-        decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset) {
+    if (wide_ok) {
         // the FP16 activation copy and the per-token factors sit where the prefill kernel keeps its own
         char* base = h->workspace + kDecodeScratchBytes + prefill_umma_reserved_bytes();
         float* unscale = reinterpret_cast<float*>(base + ((size_t)a.M * a.K * 2 + 255) / 256 * 256);

@@ -66,6 +66,7 @@ struct WideParams {
     int M, N, K;
     int units, kchunks;
     int stages;
+    int swiglu_out;            // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
     unsigned int epoch;
 };
 
@@ -279,6 +280,21 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
                 }
             }
             __syncwarp();
+            if (p.swiglu_out) {
+                // the warp's slab is one gate/up slab: row r0 is a gate row (i = 0, 1), row r0 + 8 its up row
+                // (i = 2, 3); both rounded to BF16 as the separate kernels would store them, then SwiGLU
+                const int n_out = (row_base >> 1) + warp * 8 + g;
+#pragma unroll
+                for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int m = 8 * j + 2 * t + i;
+                        if (m >= p.M || row_base + r0 >= p.N) continue;
+                        const float gate = __bfloat162float(__float2bfloat16_rn((v[j][i] * kBlockScaleUnfold) * p.inv_gs));
+                        const float up = __bfloat162float(__float2bfloat16_rn((v[j][i + 2] * kBlockScaleUnfold) * p.inv_gs));
+                        p.C[(size_t)m * (p.N / 2) + n_out] = __float2bfloat16_rn(silu(gate) * up);
+                    }
+            } else
 #pragma unroll
             for (int j = 0; j < kTT; ++j)
 #pragma unroll
@@ -301,7 +317,8 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 bool decode_wide_supported(const LinearArgs& a) {
     if (a.M < 9 || a.M > kTokens || (a.K % kKC) != 0) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
-    return !a.out_f32 && !a.px && !a.swiglu_up && !a.a_stride && !a.k_valid;
+    if (a.swiglu_out && a.residual) return false;
+    return !a.out_f32 && !a.px && !a.swiglu_up && !a.a_stride && !a.k_valid && !a.norm_w;
 }
 
 size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kUnitRows * 8; }
@@ -330,6 +347,7 @@ cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void
     p.scratch = static_cast<unsigned char*>(scratch);
     p.inv_gs = a.inv_gs;
     p.M = a.M; p.N = a.N; p.K = a.K;
+    p.swiglu_out = a.swiglu_out ? 1 : 0;
     p.kchunks = a.K / kKC;
     p.units = (int)(((long long)a.N + kUnitRows - 1) / kUnitRows * p.kchunks);
     int grid = dev.sm_count < kWideMaxGrid ? dev.sm_count : kWideMaxGrid;

@@ -21,7 +21,7 @@ struct nvfp4_tp_mlp {
 };
 
 namespace {
-constexpr int kSwigluInEpilogueMaxM = 8;   // one launch of the 8-token GEMV kernel
+constexpr int kSwigluInEpilogueMaxM = 16;  // the GEMV kernels (8 tokens per launch, or the wide one for 9..16)
 }
 
 extern "C" {
@@ -97,7 +97,7 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     d.residual = residual; d.C = out;
     int st;
     if (M <= kSwigluInEpilogueMaxM) {
-        // Up to 8 tokens the gate_up GEMV forms bf16(silu(gate) * up) in its epilogue (the shard's rows
+        // Up to 16 tokens the gate_up GEMV forms bf16(silu(gate) * up) in its epilogue (the shard's rows
         // are interleaved for that), so the MLP is two kernels and the [M, 2 I/P] tensor never exists.
         // The down projection reads the [M, I/P] result in place; columns beyond I/P of its padded K
         // count as zero.

@@ -641,7 +641,9 @@ def test_linear_ex_rmsnorm_prologue(handle, M, N, K, res, stride):
     (1, 64, 256, False),           # one tile
     (3, 2176, 5120, True),         # row tiles split over the CTAs, RMSNorm in front
     (8, 17408 // 8, 1024, False),
-    (13, 520, 2048, True),         # two launches; I not a multiple of the 64 pairs of a tile
+    (13, 520, 2048, True),         # two launches (the norm keeps it on the 8-token kernel); I not a multiple of the 64 pairs of a tile
+    (11, 520, 2048, False),        # 9..16 tokens without other options: the wide GEMV's epilogue
+    (16, 2176, 5120, False),
 ])
 def test_linear_ex_swiglu_epilogue(handle, M, I, K, norm):
     """gate/up rows interleaved in slabs of 16: the GEMV's epilogue forms bf16(silu(gate) * up) itself;
