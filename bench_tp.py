@@ -248,7 +248,7 @@ def main(args, world, rank, local_rank):
         dn_p, dn_s = util.make_weight(h_, i_, seed=2)
         Xs, Rs = util.make_bf16((m_, h_), seed=3), util.make_bf16((m_, h_), seed=4)
         small = nvfp4_tp.TpMlp(h, comm, h_, i_, util.to_dev(gu_p).to(dev), util.to_dev(gu_s).to(dev), 1.0,
-                               util.to_dev(dn_p).to(dev), util.to_dev(dn_s).to(dev), 1.0, m_)
+                               util.to_dev(dn_p).to(dev), util.to_dev(dn_s).to(dev), 1.0, 16)
         out = util.to_dev(Rs).to(dev)
         small.forward(util.to_dev(Xs).to(dev), m_, out, residual=out)            # NCCL all-reduce of BF16 partials
         small.enable_p2p(dist, dev)
@@ -256,6 +256,10 @@ def main(args, world, rank, local_rank):
         small.forward(util.to_dev(Xs).to(dev), m_, out_f, residual=out_f)        # fused FP32 push-and-sum
         out_f2 = util.to_dev(Rs).to(dev)
         small.forward(util.to_dev(Xs).to(dev), m_, out_f2, residual=out_f2)
+        # twelve tokens: the wide GEMV on both projections, its own in-kernel reduction
+        X12, R12 = util.make_bf16((12, h_), seed=5), util.make_bf16((12, h_), seed=6)
+        out12 = util.to_dev(R12).to(dev)
+        small.forward(util.to_dev(X12).to(dev), 12, out12, residual=out12)
         torch.cuda.synchronize()
         xstatus = small.status()
         same = torch.tensor([int(torch.equal(out_f, out_f2))], device=dev)
@@ -269,6 +273,8 @@ def main(args, world, rank, local_rank):
                       "nccl_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out), unsplit)),
                       "fused_path_vs_partition_aware_oracle_f32_partials": float(ob.rel_frobenius(util.to_host_u16(out_f), want_f32)),
                       "fused_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out_f), unsplit)),
+                      "fused_path_12_tokens_vs_unsplit_oracle": float(ob.rel_frobenius(
+                          util.to_host_u16(out12), ob.mlp(X12, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R12))),
                       "fused_path_bitwise_repeatable": bool(same.item()),
                       "fused_path_identical_on_all_ranks": all(torch.equal(g, gathered[0]) for g in gathered),
                       "exchange_status": int(xstatus)}

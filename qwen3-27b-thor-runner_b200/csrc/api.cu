@@ -63,9 +63,9 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     const bool wide_ok = fast_path_wanted && h->wide_gemv && decode_wide_supported(a) &&
                          kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= h->workspace_bytes &&
                          decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset;
-    // options only the GEMV kernels implement (the SwiGLU epilogue exists in the wide one too)
-    const bool other_options = a.out_f32 || a.px || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
-    if (other_options || (a.swiglu_out && !wide_ok)) {
+    // options only the GEMV kernels implement (the SwiGLU epilogue and the group reduction exist in the wide one too)
+    const bool other_options = a.out_f32 || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
+    if (other_options || ((a.swiglu_out || a.px) && !wide_ok)) {
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);

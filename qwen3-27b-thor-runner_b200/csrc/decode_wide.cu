@@ -26,6 +26,9 @@
 //     (one transaction each: the pair is its own arrival flag), the CTA that holds the row pair's
 //     first unit adds them in CTA order, applies 2^8 / global_scale and the residual in FP32 and
 //     rounds once.  Every wait is bounded and reports through the status word.
+// Options shared with the 8-token kernel: the SwiGLU epilogue on row-interleaved gate/up weights and
+// the sum over a tensor-parallel group inside the kernel ({value, epoch} pairs pushed to every
+// rank's exchange buffer, reduced in rank order once the CTA has no weight left to stream).
 // Arithmetic: the reference's small-M kernel (src/engine/dense_gemm_fp4_sm110.cu:155-258) up to
 // FP32 summation order.
 #include <cuda.h>
@@ -34,6 +37,7 @@
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "gemv_common.cuh"
+#include "exchange_layout.h"
 #include "ptx.cuh"
 #include "umma.cuh"
 
@@ -66,6 +70,10 @@ struct WideParams {
     int M, N, K;
     int units, kchunks;
     int stages;
+    // Tensor-parallel K split: world > 0 = push the sums to the ranks' exchange buffers and reduce over
+    // the group at the end of this kernel, exactly as the 8-token kernel does (decode_mma.cu).
+    unsigned char* xpeer[xchg::kMaxWorld];
+    int xrank, xworld, xslot_pairs;
     int swiglu_out;            // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
     unsigned int epoch;
 };
@@ -151,6 +159,11 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
     const int off_a = g * kActRowBytes + t * kActBlockBytes;   // token g (second tile: g + 8), 64-k block t; chunks at immediate offsets
 
     ptx::griddep_wait();          // outputs, residual, unscale and the cross-CTA scratch belong to earlier kernels until now
+    unsigned int xepoch = 0, xset = 0;      // group reduction: this launch's epoch and slot set
+    if (p.xworld > 0) {
+        xepoch = *reinterpret_cast<volatile unsigned int*>(p.xpeer[p.xrank] + xchg::kEpochOff) + 1u;
+        xset = xepoch & 1u;
+    }
 
     int stage = 0;
     uint32_t ph = 0;
@@ -304,11 +317,60 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
                     if (m >= p.M || n >= p.N) continue;
                     float x = (v[j][i] * kBlockScaleUnfold) * p.inv_gs;
                     const size_t o = (size_t)m * p.N + n;
+                    if (p.xworld > 0) {   // the unrounded sum goes to slot [set][this rank] of every rank's buffer
+                        const size_t pair = ((size_t)xset * p.xworld + p.xrank) * p.xslot_pairs + o;
+                        for (int q = 0; q < p.xworld; ++q)
+                            ptx::st_volatile_v2(p.xpeer[q] + xchg::kSlotsOff + pair * 8, __float_as_uint(x), xepoch);
+                        continue;
+                    }
                     if (p.residual) x += __bfloat162float(p.residual[o]);
                     p.C[o] = __float2bfloat16_rn(x);
                 }
         }
         if (kc >= p.kchunks) { kc = 0; ++pair; }
+    }
+
+    // ---------------------------------------------------------------- reduction over the group
+    // Every CTA takes 1/gridDim of the M x N outputs: it polls its own rank's buffer until the pairs of
+    // all ranks carry this launch's epoch (bounded), adds them in rank order, adds the residual and
+    // rounds once.  All CTAs of the grid are resident (one per SM) and an owner's push waits for nothing
+    // that happens after it, so these waits cannot form a cycle.
+    if (p.xworld > 0) {
+        constexpr int kConsumers = kConsumerWarps * 32;
+        unsigned char* mine = p.xpeer[p.xrank];
+        const int E = p.M * p.N;
+        const int e0 = (int)((long long)cta * E / G), e1 = (int)((long long)(cta + 1) * E / G);
+        const long long t0 = clock64();
+        bool failed = false;
+        for (int e = e0 + tid; e < e1 && !failed; e += kConsumers) {
+            float sum = 0.0f;
+            for (int q = 0; q < p.xworld && !failed; ++q) {
+                const unsigned char* src = mine + xchg::kSlotsOff + (((size_t)xset * p.xworld + q) * p.xslot_pairs + e) * 8;
+                uint2 x = ptx::ld_volatile_v2(src);
+                while (x.y != xepoch) {
+                    if (clock64() - t0 > xchg::kWaitClocks) {
+                        atomicCAS(reinterpret_cast<unsigned int*>(mine + xchg::kStatusOff), 0u, 0x710u + (unsigned)q);
+                        failed = true;
+                        break;
+                    }
+                    x = ptx::ld_volatile_v2(src);
+                }
+                sum += __uint_as_float(x.x);
+            }
+            if (failed) break;
+            if (p.residual) sum += __bfloat162float(p.residual[e]);
+            p.C[e] = __float2bfloat16_rn(sum);
+        }
+        // the last CTA to get here advances the launch counter for the next launch
+        ptx::named_barrier_sync(1, kConsumers);
+        if (tid == 0) {
+            __threadfence();
+            unsigned int* done = reinterpret_cast<unsigned int*>(mine + xchg::kDoneOff);
+            if (atomicAdd(done, 1u) == (unsigned)G - 1u) {
+                *done = 0u;
+                *reinterpret_cast<volatile unsigned int*>(mine + xchg::kEpochOff) = xepoch;
+            }
+        }
     }
 }
 
@@ -318,7 +380,8 @@ bool decode_wide_supported(const LinearArgs& a) {
     if (a.M < 9 || a.M > kTokens || (a.K % kKC) != 0) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
     if (a.swiglu_out && a.residual) return false;
-    return !a.out_f32 && !a.px && !a.swiglu_up && !a.a_stride && !a.k_valid && !a.norm_w;
+    if (a.px && a.swiglu_out) return false;
+    return !a.out_f32 && !a.swiglu_up && !a.a_stride && !a.k_valid && !a.norm_w;
 }
 
 size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kUnitRows * 8; }
@@ -348,6 +411,12 @@ cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void
     p.inv_gs = a.inv_gs;
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.swiglu_out = a.swiglu_out ? 1 : 0;
+    if (a.px) {
+        for (int q = 0; q < a.px->world; ++q) p.xpeer[q] = static_cast<unsigned char*>(a.px->peer[q]);
+        p.xrank = a.px->rank;
+        p.xworld = a.px->world;
+        p.xslot_pairs = a.px->slot_pairs;
+    }
     p.kchunks = a.K / kKC;
     p.units = (int)(((long long)a.N + kUnitRows - 1) / kUnitRows * p.kchunks);
     int grid = dev.sm_count < kWideMaxGrid ? dev.sm_count : kWideMaxGrid;
