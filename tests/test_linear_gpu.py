@@ -686,6 +686,47 @@ def test_linear_ex_swiglu_epilogue(handle, M, I, K, norm):
         handle.linear_ex(dX, M, util.to_dev(ip), util.to_dev(isc), 1.7, 2 * I, K, fused, residual=fused, swiglu_epilogue=True)
 
 
+def test_swiglu_interleaved_matches_merged(handle):
+    """The slab-interleaved input layout (8 gate values, their 8 up values, ...) gives the bits of the
+    merged layout on the same numbers."""
+    import torch
+    import nvfp4_tp
+    M, I = 5, 272
+    merged = util.make_bf16((M, 2 * I), seed=91, std=2.0)
+    inter = np.ascontiguousarray(merged[:, nvfp4_tp.interleave_rows(I)])
+    a = torch.zeros((M, I), dtype=torch.int16, device="cuda")
+    b = torch.zeros((M, 512), dtype=torch.int16, device="cuda")          # a padded output row
+    handle.swiglu(util.to_dev(merged), None, M, I, a)
+    handle.swiglu_interleaved(util.to_dev(inter), M, I, 2 * I, b, 512)
+    torch.cuda.synchronize()
+    assert np.array_equal(util.to_host_u16(a), util.to_host_u16(b)[:, :I])
+    assert np.array_equal(util.to_host_u16(a), ob.swiglu_merged(merged))
+    assert not util.to_host_u16(b)[:, I:].any()
+
+
+@pytest.mark.parametrize("M", [24, 200])
+def test_tp_mlp_single_rank_beyond_gemv(handle, M):
+    """More than 16 tokens through the MLP block of one rank: the tcgen05 kernels on the block's
+    row-interleaved gate/up shard, the interleaved SwiGLU kernel, the plain down projection."""
+    import torch
+    import nvfp4_tp
+    H, I = 512, 768
+    gu_p, gu_s = util.make_weight(2 * I, H, seed=41)
+    dn_p, dn_s = util.make_weight(H, I, seed=42)
+    X, R = util.make_bf16((M, H), seed=45), util.make_bf16((M, H), seed=46)
+    comm = nvfp4_tp.Comm(None, 0, 1)
+    mlp = nvfp4_tp.TpMlp(handle, comm, H, I, util.to_dev(gu_p), util.to_dev(gu_s), 1.0, util.to_dev(dn_p), util.to_dev(dn_s), 1.0, M)
+    try:
+        out = util.to_dev(R)
+        mlp.forward(util.to_dev(X), M, out, residual=out)
+        torch.cuda.synchronize()
+        want = ob.mlp(X, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R)
+        assert ob.rel_frobenius(util.to_host_u16(out), want) <= 3e-3
+    finally:
+        mlp.close()
+        comm.close()
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 13])
 def test_linear_ex_swiglu_prologue(handle, M):
     """SwiGLU formed while the GEMV stages its activations (merged gate/up rows, K padded beyond
