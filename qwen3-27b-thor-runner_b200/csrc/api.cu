@@ -65,6 +65,15 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
                          decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset;
     // options only the GEMV kernels implement (the SwiGLU epilogue and the group reduction exist in the wide one too)
     const bool other_options = a.out_f32 || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
+    if (a.swiglu_out && !other_options && !a.px && a.M > 16) {
+        // beyond the GEMV kernels only the 128-token-tile tcgen05 kernel has the SwiGLU epilogue
+        if (h->prefill_impl == 1 || !prefill_umma_supported(a)) return NVFP4_E_LIMIT;
+        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+        int nl = 0;
+        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     if (other_options || ((a.swiglu_out || a.px) && !wide_ok)) {
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;

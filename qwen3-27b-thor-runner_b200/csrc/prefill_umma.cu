@@ -74,6 +74,7 @@ struct PrefillParams {
     float4* partials;          // [grid][2][64 column chunks][128 token rows] FP32 x 4
     unsigned int* flags;       // [grid][2], launch epoch once that partial tile is stored
     unsigned int epoch;
+    int swiglu_out;            // weight rows interleaved in slabs of 16 (8 gate, 8 up): C is [M, N/2] = bf16(silu(gate) * up)
     int dense;                 // 1 = BF16 weights and activations as they are: no token scale, no 2^8, no global scale
 };
 
@@ -106,7 +107,8 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int ti
     const int m = mt * BM + (t & (BM - 1));
     const float mul = p.dense ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
     const float4* head = p.partials + ((size_t)first * 2 + 1) * kPartialVec;
-    for (int j = j0 + t; j < j1; j += nthreads) {
+    // sum of the participants' partials of one chunk (4 columns x this token row), in CTA order
+    auto chunk_sum = [&](int j) {
         float4 s = __ldcg(head + j);
         for (int c = first + 1; c <= last; c += 8) {
             float4 x[8];
@@ -117,7 +119,27 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int ti
 #pragma unroll
             for (int i = 0; i < 8; ++i) { s.x += x[i].x; s.y += x[i].y; s.z += x[i].z; s.w += x[i].w; }
         }
+        return s;
+    };
+    for (int j = j0 + t; j < j1; j += nthreads) {
         const int n = nt * BN + (j / BM) * 4;          // first of the 4 columns of this chunk
+        if (p.swiglu_out) {
+            // columns 16s..16s+7 are gate values, 16s+8..16s+15 their up values: a gate chunk takes the up
+            // chunk two chunks further (wherever it lies in the tile) and writes 4 outputs; up chunks are skipped
+            if ((n & 15) >= 8 || m >= p.M || n >= p.N) continue;
+            const float4 g = chunk_sum(j), u = chunk_sum(j + 2 * BM);
+            const float gf[4] = {g.x, g.y, g.z, g.w}, uf[4] = {u.x, u.y, u.z, u.w};
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                f[i] = silu(__bfloat162float(__float2bfloat16_rn(gf[i] * mul))) * __bfloat162float(__float2bfloat16_rn(uf[i] * mul));
+            const __nv_bfloat162 b0 = __floats2bfloat162_rn(f[0], f[1]);
+            const __nv_bfloat162 b1 = __floats2bfloat162_rn(f[2], f[3]);
+            *reinterpret_cast<uint2*>(p.C + (size_t)m * (p.N / 2) + 8 * (n >> 4) + (n & 15)) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
+            continue;
+        }
+        const float4 s = chunk_sum(j);
         if (m < p.M && n < p.N) {                      // N % 8 == 0: a chunk of 4 is inside or outside
             const size_t o = (size_t)m * p.N + n;
             float f[4] = {s.x * mul, s.y * mul, s.z * mul, s.w * mul};
@@ -352,6 +374,28 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                     uint32_t r[32];
                     tmem_ld32(t_addr + c0, r);
                     const int n0 = nt * BN + c0;
+                    if (p.swiglu_out) {
+                        // 32 columns = two slabs of 8 gate values and their 8 up values (N % 32 == 0 here)
+                        if (m < p.M && n0 < p.N) {
+#pragma unroll
+                            for (int sv = 0; sv < 2; ++sv) {
+                                uint32_t ov[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    float f[2];
+#pragma unroll
+                                    for (int e = 0; e < 2; ++e) {
+                                        const float gate = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[sv * 16 + 2 * i + e]) * mul));
+                                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[sv * 16 + 8 + 2 * i + e]) * mul));
+                                        f[e] = silu(gate) * up;
+                                    }
+                                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(f[0], f[1]);
+                                    ov[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                                }
+                                *reinterpret_cast<uint4*>(p.C + (size_t)m * (p.N / 2) + (n0 >> 1) + 8 * sv) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+                            }
+                        }
+                    } else
                     if (m < p.M && n0 < p.N) {
                         const size_t o = (size_t)m * p.N + n0;
                         if (n0 + 32 <= p.N) {
@@ -428,6 +472,7 @@ size_t act_bytes(int M, int K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }
 
 bool prefill_umma_supported(const LinearArgs& a) {
     if (a.M < 1 || (a.K % WK) != 0 || (a.N % 8) != 0) return false;
+    if (a.swiglu_out && ((a.N % 32) != 0 || a.residual)) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
     return true;
 }
@@ -506,6 +551,7 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.unscale = unscale;
     p.status = static_cast<unsigned int*>(scratch);
     p.inv_gs = a.inv_gs;
+    p.swiglu_out = a.swiglu_out ? 1 : 0;
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.m_tiles = (a.M + BM - 1) / BM;
     p.n_tiles = (a.N + BN - 1) / BN;

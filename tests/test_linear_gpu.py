@@ -644,6 +644,9 @@ def test_linear_ex_rmsnorm_prologue(handle, M, N, K, res, stride):
     (13, 520, 2048, True),         # two launches (the norm keeps it on the 8-token kernel); I not a multiple of the 64 pairs of a tile
     (11, 520, 2048, False),        # 9..16 tokens without other options: the wide GEMV's epilogue
     (16, 2176, 5120, False),
+    (40, 2176, 1024, False),       # beyond the GEMV kernels: the tcgen05 GEMM's epilogue, every tile split along k
+    (300, 1024, 2560, False),      # three token tiles (a pair and a single), whole tiles and split ones
+    (130, 20000, 256, False),      # more tiles than CTAs
 ])
 def test_linear_ex_swiglu_epilogue(handle, M, I, K, norm):
     """gate/up rows interleaved in slabs of 16: the GEMV's epilogue forms bf16(silu(gate) * up) itself;
