@@ -168,7 +168,8 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A_bf16, int M, const 
  *                 nvfp4_interleave_gate_up in nvfp4_checkpoint.h does it at load time); C is then
  *                 [M, N/2] = bf16(silu(gate) * up) with gate and up rounded to BF16 first, i.e. the bits
  *                 of nvfp4_linear followed by nvfp4_swiglu, without the [M, N] round trip and the second
- *                 kernel.  N % 16 == 0, no residual, no px.
+ *                 kernel.  N % 16 == 0, no residual, no px.  More than 16 tokens: N % 32 == 0, no other
+ *                 option (the tcgen05 GEMM's epilogue; NVFP4_E_LIMIT otherwise).
  * Zero / NULL fields mean "not used".  No reference counterpart for the fused forms. */
 typedef struct nvfp4_linear_desc {
     const void* A;
