@@ -111,12 +111,21 @@ int nvfp4_linear(nvfp4_handle* h, const void* A_bf16, int M,
  * grid is capped at 160 CTAs, the size the array was laid out for.
  * The first call on each device looks up the array's device address and sets the kernel's
  * shared-memory attribute; make that first call before capturing a stream.  All calls share the
- * one array: it keeps the previous call's flags and partial sums, which is harmless because every
- * flag carries its call's sequence number and every partial is rewritten before it is read, but
- * two calls that overlap on the GPU (different streams) race on it -- issue them on one stream. */
+ * one array: it keeps the previous call's partial sums, which is harmless because every partial
+ * carries the sequence number of its launch, taken from a counter in the array itself (so a captured
+ * call can be replayed), and is rewritten before it is read; but two calls that overlap on the GPU
+ * (different streams) race on it -- issue them on one stream.  The device of `stream` must be the
+ * current device.  nvfp4_noalloc_status reads back whether a device-side wait ever ran out. */
 int nvfp4_linear_decode_noalloc(const void* A_bf16, int M, const uint8_t* packed, const uint8_t* scale_ue4m3,
                                 float global_scale, int N, int K, const void* residual_bf16_or_null,
                                 void* C_bf16, nvfp4_stream_t stream);
+
+/* The device-side status word of the allocation-free GEMV on the current device (no counterpart in
+ * the reference).  A bounded wait of nvfp4_linear_decode_noalloc that ran out leaves its code in the
+ * fixed array (the first failure wins, codes as for nvfp4_device_status) and part of C unwritten;
+ * the entry point itself cannot see that, it only enqueues.  This call synchronises the device,
+ * copies the four bytes back and, with reset != 0, clears them.  It allocates nothing. */
+int nvfp4_noalloc_status(unsigned int* status, int reset);
 
 /* C_f32[M,N] = A * W^T as unrounded FP32 (no residual, no BF16 rounding): a partial result for
  * callers that sum several of them before rounding once, e.g. the K-split down projection of
@@ -262,6 +271,9 @@ void nvfp4_cleanup_fp4_cublaslt(void); /* cleanup_fp4_cublaslt (:436-441): destr
 int nvfp4_last_status(void);
 /* Workspace of the default handle; call before its first use (default 64 MiB). */
 int nvfp4_default_handle_workspace(size_t bytes);
+
+/* A handle serves one host thread and one stream at a time: its workspace holds the kernels'
+ * cross-CTA scratch, and calls that overlap on the GPU would race on it. */
 
 /* ---- host-memory convenience (the end-to-end path of the benchmark) ------
  * Same as nvfp4_linear but A, residual and C are HOST pointers (pinned for

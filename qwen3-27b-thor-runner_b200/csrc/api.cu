@@ -57,20 +57,22 @@ int validate_linear(const nvfp4_handle* h, const void* A, int M, const uint8_t* 
 int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 
 // One linear call on device buffers.
-int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
+// `ws_bytes`: how much of the workspace the kernels may use (the host-buffer path keeps its staging behind it).
+int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_bytes = 0) {
     if (a.M == 0) return NVFP4_OK;
+    if (ws_bytes == 0) ws_bytes = h->workspace_bytes;
     const bool fast_path_wanted = a.M <= h->decode_max_m ? h->decode_impl != 1 : h->prefill_impl != 1;
     const bool wide_ok = fast_path_wanted && h->wide_gemv && decode_wide_supported(a) &&
-                         kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= h->workspace_bytes &&
+                         kDecodeScratchBytes + prefill_umma_scratch_bytes(17, a.N, a.K) <= ws_bytes &&
                          decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset;
     // options only the GEMV kernels implement (the SwiGLU epilogue and the group reduction exist in the wide one too)
     const bool other_options = a.out_f32 || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
     if (a.swiglu_out && !other_options && !a.px && a.M > 16) {
         // beyond the GEMV kernels only the 128-token-tile tcgen05 kernel has the SwiGLU epilogue
         if (h->prefill_impl == 1 || !prefill_umma_supported(a)) return NVFP4_E_LIMIT;
-        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > ws_bytes) return NVFP4_E_WORKSPACE;
         int nl = 0;
-        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, s);
+        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, ws_bytes, kDecodeScratchBytes, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
@@ -91,9 +93,9 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
         return cuda_status(e);
     }
     if (fast_path_wanted && a.M >= h->skinny_min_m && a.M <= h->skinny_max_m && skinny_umma_supported(a) &&
-        kDecodeScratchBytes + prefill_umma_reserved_bytes() <= h->workspace_bytes) {
+        kDecodeScratchBytes + prefill_umma_reserved_bytes() <= ws_bytes) {
         int nl = 0;
-        cudaError_t e = launch_skinny_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, s);
+        cudaError_t e = launch_skinny_umma(a, h->dev, h->workspace, ws_bytes, kDecodeScratchBytes, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
@@ -104,7 +106,7 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
         if (impl == 2) {
             if (!fast_ok) return NVFP4_E_SHAPE;
             size_t need = decode_mma_scratch_bytes(a, h->dev);
-            if (need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+            if (need > ws_bytes) return NVFP4_E_WORKSPACE;
             int nl = 0;
             cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
             h->launches += (unsigned long long)nl;
@@ -127,9 +129,9 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     if (impl == 0) impl = prefill_umma_supported(a) ? 2 : 1;
     if (impl == 2) {
         if (!prefill_umma_supported(a)) return NVFP4_E_SHAPE;
-        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > ws_bytes) return NVFP4_E_WORKSPACE;
         int nl = 0;
-        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, h->workspace_bytes, kDecodeScratchBytes, &nl, s);
+        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, ws_bytes, kDecodeScratchBytes, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
@@ -137,7 +139,7 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s) {
     // The matrix goes behind the status word, flags and partial tiles of the fast kernels.
     const size_t skip = kDecodeScratchBytes + prefill_umma_reserved_bytes();
     const size_t need = (size_t)a.N * a.K * 2;
-    if (skip + need > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+    if (skip + need > ws_bytes) return NVFP4_E_WORKSPACE;
     cudaError_t e = launch_dequant_bf16(a.packed, a.scale, a.inv_gs, a.N, a.K, h->workspace + skip, s);
     h->launches += 1;
     if (e != cudaSuccess) return (int)e;
@@ -202,6 +204,7 @@ int nvfp4_create(int device, size_t workspace_bytes, nvfp4_handle** out) {
     h->dev.cc_minor = prop.minor;
     h->dev.smem_optin = prop.sharedMemPerBlockOptin;
     if (workspace_bytes < kDecodeScratchBytes) workspace_bytes = kDecodeScratchBytes;
+    workspace_bytes &= ~(size_t)255;     // everything carved out of the workspace, from either end, stays 256-byte aligned
     e = cudaMalloc(&h->workspace, workspace_bytes);
     if (e == cudaSuccess) e = cudaMemset(h->workspace, 0, workspace_bytes);
     if (e == cudaSuccess) e = configure_kernels(h->dev);
@@ -336,6 +339,19 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
     const int k_valid = d->k_valid ? d->k_valid : d->K;
     if (stride < k_valid || (stride & 7) || k_valid < 1 || k_valid > d->K || (k_valid & 7)) return NVFP4_E_SHAPE;
     if (d->swiglu_up && !aligned16(d->swiglu_up)) return NVFP4_E_ALIGN;
+    if (d->M > 0) {
+        // What the kernel reads of A (and of the up half) spans (M-1) strides plus the valid columns; every CTA
+        // re-reads it while others already store C, so neither may overlap the output, nor may the norm weight.
+        const char* c0 = static_cast<const char*>(d->C);
+        const char* c1 = c0 + (size_t)d->M * (d->swiglu_epilogue ? d->N / 2 : d->N) * 2;
+        const size_t span = ((size_t)(d->M - 1) * (size_t)stride + (size_t)k_valid) * 2;
+        auto overlaps = [&](const void* p, size_t bytes) {
+            const char* p0 = static_cast<const char*>(p);
+            return p && p0 < c1 && c0 < p0 + bytes;
+        };
+        if (overlaps(d->A, span) || overlaps(d->swiglu_up, span) || overlaps(d->norm_weight, (size_t)d->K * 2))
+            return NVFP4_E_ALIAS;
+    }
     if (d->norm_weight) {
         if (!aligned16(d->norm_weight)) return NVFP4_E_ALIGN;
         if (d->swiglu_up || k_valid != d->K || !(d->norm_eps >= 0.0f)) return NVFP4_E_SHAPE;   // the norm runs over all K columns of A itself
@@ -489,12 +505,10 @@ int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M, const uint8_t*
         if (e != cudaSuccess) return (int)e;
         dR = dC;
     }
-    // Shrink the workspace seen by the kernels so that their scratch never reaches the staging area.
-    const size_t full_bytes = h->workspace_bytes;
-    h->workspace_bytes = full_bytes - tail;
+    if (!aligned16(dA) || !aligned16(dC)) return NVFP4_E_ALIGN;
+    // The kernels see the workspace without the staging area, so their scratch never reaches it.
     LinearArgs a{dA, packed, scale, 1.0f / global_scale, dR, dC, M, N, K};
-    int st = run_linear(h, a, stream);
-    h->workspace_bytes = full_bytes;
+    int st = run_linear(h, a, stream, h->workspace_bytes - tail);
     if (st) return st;
     e = cudaMemcpyAsync(C_host, dC, (size_t)M * N * 2, cudaMemcpyDeviceToHost, stream);
     if (e != cudaSuccess) return (int)e;

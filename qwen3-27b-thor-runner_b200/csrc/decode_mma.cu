@@ -80,7 +80,6 @@ struct DecodeParams {
     int act_all;         // 1 = slot index is the k-chunk, 0 = position in the CTA's span
     int swiglu_out;      // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
     int out_f32;         // C is FP32 [M,N]: store the scaled sum unrounded (partial results for a later reduction)
-    unsigned int epoch;
     // Tensor-parallel K split: world > 0 = push the sums to the ranks' exchange buffers and reduce
     // over the group at the end of this kernel (C then receives the full sum + residual).
     unsigned char* xpeer[xchg::kMaxWorld];
@@ -109,6 +108,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_amax + 16);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
+    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_abort) + 1;
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     unsigned char* pairs = p.pairs;
@@ -196,6 +196,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // and never overflows.  Pass B converts and stores in natural k order.  The scale is undone in
     // FP32 in the epilogue.
     ptx::griddep_wait();
+    // This launch's tag for the split-tile pairs, from the counter in the scratch (one atomic per CTA;
+    // its round trip hides behind the staging loads, the value reaches shared memory before the
+    // barrier that ends pass A).
+    unsigned int epoch_taken = 0;
+    if (tid == 0) epoch_taken = ptx::take_launch_epoch(p.scratch);
     // Group reduction: this launch's epoch and slot set (the counter was advanced by the previous
     // launch that used the buffer, which has completed by now).
     unsigned int xepoch = 0, xset = 0;
@@ -333,6 +338,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 *reinterpret_cast<uint4*>(s_act + dst[u]) = x[u];
             }
         }
+        if (tid == 0) *s_epoch = epoch_taken;
         ptx::named_barrier_sync(1, kConsumerThreads);
         if (tid < p.M) {
             const int e8 = (int)(s_amax[tid] >> 7);           // biased BF16 exponent of the largest element
@@ -376,6 +382,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         ptx::named_barrier_sync(1, kConsumerThreads);
     }
 
+    const unsigned int epoch = *s_epoch;
     int stage = 0;
     uint32_t ph = 0;
     int hu = u_begin;
@@ -415,7 +422,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            v[j][i] = make_uint2(0u, p.epoch);
+                            v[j][i] = make_uint2(0u, epoch);
                             if (mm[i] < p.M && (j == 0 || two))
                                 v[j][i] = ptx::ld_volatile_v2(src + ((size_t)j * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]) * 8);
                         }
@@ -423,7 +430,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == p.epoch);
+                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == epoch);
                     if (ready) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
@@ -535,7 +542,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 unsigned char* slot = pairs + (size_t)cta * (kMaxTokens * kRT) * 8;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), p.epoch);
+                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), epoch);
             } else {
                 if (!prefetched) {
                     gather_pairs(pre, true);
@@ -762,7 +769,6 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DecodePlan pl;
         if (!plan_decode(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
-        pl.p.epoch = next_epoch(dev);
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(pl.grid);
         cfg.blockDim = dim3((2 * kGroupWarps + 1) * 32);
@@ -838,7 +844,6 @@ int noalloc_setup(int device, NoAllocState** out) {
         st.dev.device = device;
         st.dev.sm_count = sms < kNoAllocMaxGrid ? sms : kNoAllocMaxGrid;   // the grid never exceeds the scratch
         st.dev.cc_major = major;
-        st.dev.decode_epoch = 0;
         st.dev.gemv_pairs_offset = kPartialOffset;     // no other kernel shares this scratch
         st.ready = true;
     }
@@ -870,5 +875,21 @@ extern "C" int nvfp4_linear_decode_noalloc(const void* A, int M, const uint8_t* 
     if (M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, st->dev)) return NVFP4_E_LIMIT;
     int launches = 0;
     cudaError_t e = launch_decode_mma(a, st->dev, st->scratch, &launches, stream);
+    return e == cudaSuccess ? NVFP4_OK : (int)e;
+}
+
+// The status word of the fixed scratch on the current device: a bounded wait of the allocation-free
+// GEMV that ran out leaves its code there (first failure wins) and part of C unwritten.  Reads
+// four bytes with a blocking copy after synchronising the device; allocates nothing.
+extern "C" int nvfp4_noalloc_status(unsigned int* status, int reset) {
+    using namespace nvfp4;
+    if (!status) return NVFP4_E_NULL;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return NVFP4_E_DEVICE;
+    NoAllocState* st = nullptr;
+    if (int e = noalloc_setup(device, &st)) return e;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(status, st->scratch, sizeof(unsigned int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && reset && *status != 0u) e = cudaMemset(st->scratch, 0, sizeof(unsigned int));
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }

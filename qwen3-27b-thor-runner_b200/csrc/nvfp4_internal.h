@@ -33,18 +33,10 @@ struct nvfp4_device_info {
     int sm_count;
     int cc_major, cc_minor;
     size_t smem_optin;
-    unsigned int decode_epoch;   // bumped per launch; tags the cross-CTA flags in the scratch
     int prefill_stream_k = 1;    // split the tiles left after whole waves by k over all CTAs
     int skinny_split_cost = 12;  // stage-times charged to splitting row tiles by k in the few-token kernel
     size_t gemv_pairs_offset = 6u << 20;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
 };
-
-// The tag of one launch in the cross-CTA scratch (flags, {value, epoch} pairs).  Zero is what freshly
-// cleared scratch holds, so it is never handed out, also not when the counter wraps.
-inline unsigned int next_epoch(nvfp4_device_info& dev) {
-    if (++dev.decode_epoch == 0u) ++dev.decode_epoch;
-    return dev.decode_epoch;
-}
 
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
 cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);

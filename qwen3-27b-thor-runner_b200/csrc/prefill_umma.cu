@@ -72,8 +72,7 @@ struct PrefillParams {
     int sk_tiles;
     int sk_pairs;              // the same region counted in pairs of token tiles (see Schedule)
     float4* partials;          // [grid][2][64 column chunks][128 token rows] FP32 x 4
-    unsigned int* flags;       // [grid][2], launch epoch once that partial tile is stored
-    unsigned int epoch;
+    unsigned int* flags;       // [grid][2], the launch's tag once that partial tile is stored
     int swiglu_out;            // weight rows interleaved in slabs of 16 (8 gate, 8 up): C is [M, N/2] = bf16(silu(gate) * up)
     int dense;                 // 1 = BF16 weights and activations as they are: no token scale, no 2^8, no global scale
 };
@@ -95,11 +94,11 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
 // in CTA order over its own 1/P of the tile and writes that part of the output.  All
 // participants add in the same order, so the result does not depend on timing.
 // t = 0..nthreads-1, nthreads a multiple of 128.
-__device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, int tile, int kstages, int t, int nthreads,
-                                                  volatile int* s_abort) {
+__device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, unsigned int epoch, int tile, int kstages, int t,
+                                                  int nthreads, volatile int* s_abort) {
     int first, last;
     split_tile_participants(p.sk_tiles, kstages, tile, first, last);
-    if (!wait_split_tile_flags(p.flags, p.epoch, first, last, t, s_abort, p.status)) return;
+    if (!wait_split_tile_flags(p.flags, epoch, first, last, t, s_abort, p.status)) return;
     const int P = last - first + 1, me = blockIdx.x - first;
     const int j0 = (int)((long long)me * kPartialVec / P) & ~(BM - 1);
     const int j1 = me + 1 == P ? kPartialVec : ((int)((long long)(me + 1) * kPartialVec / P) & ~(BM - 1));
@@ -186,6 +185,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     uint64_t* tempty = tfull + kAccs;        // [kAccs]
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + kAccs);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_tmem + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kstages = p.K / WK;
@@ -197,6 +197,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         for (int i = 0; i < NB; ++i) { ptx::mbar_init(&bfull[i], DENSE ? 1 : kDequantWarps); ptx::mbar_init(&bempty[i], 1); }
         for (int i = 0; i < kAccs; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], kEpiWarps); }
         *s_abort = 0;
+        // The tag of this launch's stream-K flags, from the counter in the scratch.  (This kernel is
+        // launched without programmatic serialisation: the previous launch has completed.)
+        *s_epoch = ptx::take_launch_epoch(p.status);
         ptx::fence_mbar_init();
     }
     if (warp == 1) {   // one warp owns the TMEM allocation: 512 columns = two 128 x 256 FP32 accumulators
@@ -206,6 +209,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    const unsigned int epoch = *s_epoch;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -366,7 +370,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 }
                 __threadfence();
                 ptx::named_barrier_sync(1, kEpiWarps * 32);   // all 128 rows stored before the flag goes up
-                if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], p.epoch);
+                if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], epoch);
                 pend[which] = tile;
             } else {
                 const float mul = DENSE ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
@@ -444,7 +448,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             if (!all_reduce && (pend[0] >= 0 || pend[1] >= 0) && (!more || sg.tile >= p.sk_tiles)) {
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
-                    if (pend[w] >= 0) reduce_split_tile(p, pend[w], kstages, te, kEpiWarps * 32, s_abort);
+                    if (pend[w] >= 0) reduce_split_tile(p, epoch, pend[w], kstages, te, kEpiWarps * 32, s_abort);
                     pend[w] = -1;
                 }
             }
@@ -462,7 +466,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         split_tiles_of_cta(p.sk_tiles, kstages, split);
 #pragma unroll
         for (int w = 0; w < 2; ++w)
-            if (split[w] >= 0) reduce_split_tile(p, split[w], kstages, tid, kThreads, s_abort);
+            if (split[w] >= 0) reduce_split_tile(p, epoch, split[w], kstages, tid, kThreads, s_abort);
     }
 }
 
@@ -483,7 +487,7 @@ constexpr size_t kStreamKBytes = 4096 + 2 * kMaxPrefillGrid * kPartialTileBytes;
 
 size_t prefill_umma_reserved_bytes() { return kStreamKBytes; }
 
-// Stream-K flags and partial tiles (fixed place, so a flag word only ever holds launch epochs),
+// Stream-K flags and partial tiles (fixed place, so a flag word only ever holds launch tags),
 // then the FP16 copy of the activations and one FP32 per token.
 size_t prefill_umma_scratch_bytes(int max_M, int /*max_N*/, int max_K) {
     if (max_M <= 16) return 0;
@@ -557,7 +561,6 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.n_tiles = (a.N + BN - 1) / BN;
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
-    p.epoch = next_epoch(dev);
     const int grid = plan_tiles(p, dev);
     prefill_umma_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
     if (launches) *launches = 2;
@@ -595,7 +598,6 @@ cudaError_t launch_dense_umma(const DenseArgs& a, nvfp4_device_info& dev, void* 
     p.n_tiles = (a.N + BN - 1) / BN;
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
-    p.epoch = next_epoch(dev);
     const int grid = plan_tiles(p, dev);
     prefill_umma_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(tma, tmw, tmw, p);
     if (launches) *launches = 1;

@@ -5,6 +5,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 namespace nvfp4 {
@@ -189,6 +190,31 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
 }
 __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+
+// ---------------------------------------------------------------- launch tag for cross-CTA hand-offs
+// Split-tile partials and flags in the scratch are tagged with a number that must differ from one
+// launch to the next.  It comes from a 64-bit counter in the scratch itself, not from the host: a
+// captured CUDA graph replays its kernel parameters unchanged, so a host-side tag would repeat
+// on every replay and a reader could accept what the previous replay left behind.  Every CTA
+// adds to the counter once, after griddepcontrol.wait (the previous launch on this scratch has
+// completed and its memory is visible), and the additions of one launch always sum to
+// kEpochLaunchSum (CTA 0 adds what the others leave), so the value a CTA gets back lies in this
+// launch's own window of the counter whatever the order of arrival: no CTA waits for another
+// and nothing has to happen at the end of the kernel.  Needs gridDim.x <= kEpochLaunchSum.
+// Tags run over 1 .. 2^32 - 1 (0 is what cleared scratch holds) and consecutive launches never
+// share one.
+constexpr unsigned int kEpochLaunchShift = 10;
+constexpr unsigned long long kEpochLaunchSum = 1ull << kEpochLaunchShift;
+constexpr size_t kEpochCounterOffset = 64;      // byte offset of the counter in a scratch (the status word sits at 0)
+
+__device__ __forceinline__ unsigned int take_launch_epoch(void* scratch_base) {
+    unsigned long long* counter =
+        reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(scratch_base) + kEpochCounterOffset);
+    const unsigned long long add = blockIdx.x == 0 ? kEpochLaunchSum - (unsigned long long)(gridDim.x - 1) : 1ull;
+    const unsigned long long old = atomicAdd(counter, add);
+    return (unsigned int)((old >> kEpochLaunchShift) % 0xFFFFFFFFull) + 1u;
 }
 
 }  // namespace ptx

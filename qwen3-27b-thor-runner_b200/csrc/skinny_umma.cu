@@ -83,8 +83,7 @@ struct SkinnyParams {
     int a_units, a_col0;       // ring of A units (64 columns each) behind the accumulators
     uint32_t idesc;
     float* partials;           // [grid][2][kMaxTokens][128] FP32
-    unsigned int* flags;       // [grid][2], launch epoch once that partial tile is stored
-    unsigned int epoch;
+    unsigned int* flags;       // [grid][2], the launch's tag once that partial tile is stored
 };
 
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
@@ -126,11 +125,11 @@ __device__ __forceinline__ void store_output(const SkinnyParams& p, int m, int n
 // Reduction of one split row tile (see reduce_split_tile of the prefill kernel: same protocol).
 // The P participants each take 1/P of the tokens; with fewer tokens than participants the
 // rows are split instead.  t = 0..nthreads-1, nthreads a multiple of 128.
-__device__ __forceinline__ void reduce_split_rows(const SkinnyParams& p, int tile, int kstages, int t, int nthreads,
-                                                  volatile int* s_abort) {
+__device__ __forceinline__ void reduce_split_rows(const SkinnyParams& p, unsigned int epoch, int tile, int kstages, int t,
+                                                  int nthreads, volatile int* s_abort) {
     int first, last;
     split_tile_participants(p.sk_tiles, kstages, tile, first, last);
-    if (!wait_split_tile_flags(p.flags, p.epoch, first, last, t, s_abort, p.status)) return;
+    if (!wait_split_tile_flags(p.flags, epoch, first, last, t, s_abort, p.status)) return;
     const int P = last - first + 1, me = blockIdx.x - first;
     const int total = p.M * TR;                      // elements [token][row] of the tile that matter
     const int e0 = (int)((long long)me * total / P), e1 = (int)((long long)(me + 1) * total / P);
@@ -173,6 +172,7 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
     uint64_t* tempty = tfull + kAccs;              // [kAccs]
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + kAccs);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_tmem + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kstages = p.K / WK;
@@ -329,6 +329,10 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
         uint32_t pt = 0;
         int pend[2] = {-1, -1};
         ptx::griddep_wait();                              // C, the residual and the scratch belong to earlier kernels until now
+        // the tag of this launch's split-tile flags, from the counter in the scratch; the four epilogue warps share it
+        if (te == 0) *s_epoch = ptx::take_launch_epoch(p.status);
+        ptx::named_barrier_sync(1, kEpiWarps * 32);
+        const unsigned int epoch = *s_epoch;
         Schedule sched(p.sk_tiles, p.row_tiles, kstages);
         Segment sg;
         bool more = sched.next(sg);
@@ -358,7 +362,7 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
             if (!complete) {
                 __threadfence();
                 ptx::named_barrier_sync(1, kEpiWarps * 32);   // all 128 rows stored before the flag goes up
-                if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], p.epoch);
+                if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], epoch);
                 pend[which] = sg.tile;
             }
             tc_fence_before();
@@ -371,7 +375,7 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
             if (!all_reduce && (pend[0] >= 0 || pend[1] >= 0) && (!more || sg.tile >= p.sk_tiles)) {
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
-                    if (pend[w] >= 0) reduce_split_rows(p, pend[w], kstages, te, kEpiWarps * 32, s_abort);
+                    if (pend[w] >= 0) reduce_split_rows(p, epoch, pend[w], kstages, te, kEpiWarps * 32, s_abort);
                     pend[w] = -1;
                 }
             }
@@ -386,11 +390,12 @@ skinny_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_cons
     if (all_reduce) {
         // Every tile was split and nothing else is left to do: all 16 warps reduce.
         ptx::griddep_wait();
+        const unsigned int epoch = *s_epoch;           // written by the epilogue warps before the barrier above
         int split[2];
         split_tiles_of_cta(p.sk_tiles, kstages, split);
 #pragma unroll
         for (int w = 0; w < 2; ++w)
-            if (split[w] >= 0) reduce_split_rows(p, split[w], kstages, tid, kThreads, s_abort);
+            if (split[w] >= 0) reduce_split_rows(p, epoch, split[w], kstages, tid, kThreads, s_abort);
     }
 }
 
@@ -480,7 +485,6 @@ cudaError_t launch_skinny_umma(const LinearArgs& a, nvfp4_device_info& dev, void
     pl.p.inv_gs = a.inv_gs;
     pl.p.flags = reinterpret_cast<unsigned int*>(sk);
     pl.p.partials = reinterpret_cast<float*>(sk + 4096);
-    pl.p.epoch = next_epoch(dev);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.grid);
     cfg.blockDim = dim3(kThreads);

@@ -45,6 +45,7 @@ SIGNATURES = {
                              c_void_p, c_void_p, c_void_p]),
     "nvfp4_linear_decode_noalloc": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p,
                                             c_void_p, c_void_p]),
+    "nvfp4_noalloc_status": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
     "nvfp4_linear_f32": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_linear_reduce_peers": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p,
                                           c_void_p, c_void_p]),

@@ -30,3 +30,17 @@ def handle():
     h = nvfp4.Handle(0, 512 << 20)
     yield h
     h.close()
+
+
+@pytest.fixture(scope="module")
+def big_handle():
+    """A handle whose workspace holds the activation copy of 8192 tokens x 17408 columns."""
+    import ctypes
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import nvfp4
+    need = ctypes.c_size_t()
+    assert nvfp4.load().nvfp4_workspace_bytes(8192, 34816, 17408, ctypes.byref(need)) == 0
+    h = nvfp4.Handle(0, need.value)
+    yield h
+    h.close()

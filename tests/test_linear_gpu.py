@@ -91,10 +91,14 @@ def test_config0_gemv(handle, impl):
 
 @pytest.mark.parametrize("impl", [1, 2])
 def test_decode_small_shapes_exhaustive(handle, impl):
-    def body():
-        worst = 0.0
-        for K in (16, 32, 48, 64, 128, 256, 512):
-            for N in (1, 2, 3, 7, 8, 9, 15, 16, 17, 33):
+    """Every small (K, N, M) combination.  The scalar kernel takes any K % 16 == 0; the TMA + MMA
+    kernels need K % 256 == 0, so their variant walks multiples of 256 and nothing is skipped."""
+    ks = (16, 32, 48, 64, 128, 256, 512) if impl == 1 else (256, 512, 768, 1024)
+    handle.set_option("decode_impl", impl)
+    try:
+        worst, cases = 0.0, 0
+        for K in ks:
+            for N in (1, 2, 3, 7, 8, 9, 15, 16, 17, 33, 127, 128, 129, 257):
                 packed, scale = util.make_weight(N, K, seed=K * 100 + N, sigma=0.14)
                 for M in (1, 2, 3, 4, 5, 7, 8, 9, 15, 16):
                     A = util.make_bf16((M, K), seed=M)
@@ -102,8 +106,11 @@ def test_decode_small_shapes_exhaustive(handle, impl):
                     got = run_linear(handle, A, packed, scale, 1.0, residual=R)
                     want = ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMV)
                     worst = max(worst, ob.rel_frobenius(got, want))
-        return worst
-    assert with_impl(handle, "decode", impl, body) <= TOL
+                    cases += 1
+    finally:
+        handle.set_option("decode_impl", 0)
+    assert cases >= 500 and worst <= TOL
+    assert handle.device_status() == 0
 
 
 @pytest.mark.parametrize("impl", [1, 2])
@@ -118,26 +125,67 @@ def test_decode_mlp_like_shapes(handle, impl, N, K, M):
     assert ob.rel_frobenius(got, want) <= TOL
 
 
+FUZZ_GS = (1.0, 0.37, 7.25, 2688.0)
+FUZZ_STD = (0.01, 1.0, 30.0)
+
+
 @pytest.mark.parametrize("impl", [1, 2])
 def test_decode_fuzz(handle, impl):
-    rng = np.random.default_rng(1234)
-
-    def body():
+    """Random (N, K, M <= 16, global scale, weight and activation magnitude, residual in and out of
+    place).  impl 2 = the TMA + MMA kernels (up to 8 tokens, and the wide one for 9..16): K is drawn
+    from the multiples of 256 they take, so no case is skipped."""
+    rng = np.random.default_rng(1234 + impl)
+    handle.set_option("decode_impl", impl)
+    try:
         worst = 0.0
-        for it in range(40):
-            K = int(rng.integers(1, 80)) * 32
-            N = int(rng.integers(1, 700))
+        for it in range(220):
+            K = int(rng.integers(1, 80)) * 32 if impl == 1 else int(rng.integers(1, 28)) * 256
+            N = int(rng.integers(1, 700)) if it % 8 else int(rng.integers(700, 6000))
             M = int(rng.integers(1, 17))
-            gs = float(rng.choice([1.0, 1.0, 0.37, 7.25, 2048.0]))
+            gs = float(rng.choice(FUZZ_GS))
             sigma = float(rng.choice([0.02, 0.14, 1.0]))
             packed, scale = util.make_weight(N, K, seed=it, sigma=sigma)
-            A = util.make_bf16((M, K), seed=1000 + it, std=float(rng.choice([1.0, 30.0, 0.01])))
+            A = util.make_bf16((M, K), seed=1000 + it, std=float(rng.choice(FUZZ_STD)))
             R = util.make_bf16((M, N), seed=2000 + it) if it % 3 else None
             got = run_linear(handle, A, packed, scale, gs, residual=R, inplace=bool(it % 2))
-            want = ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMV)
-            worst = max(worst, ob.rel_frobenius(got, want))
-        return worst
-    assert with_impl(handle, "decode", impl, body) <= TOL
+            want = ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMV, threads=4)
+            err = ob.rel_frobenius(got, want)
+            assert err <= TOL, (it, M, N, K, gs, sigma, err)
+            worst = max(worst, err)
+    finally:
+        handle.set_option("decode_impl", 0)
+    assert handle.device_status() == 0
+
+
+def test_few_token_and_prefill_fuzz(handle):
+    """17..300 tokens on random shapes the tcgen05 kernels take (K % 256 == 0; N % 8 == 0 above 64
+    tokens), every global scale of the decode fuzz.  The kernels keep exact block-scaled weights and
+    apply 1/global_scale once in FP32 (the reference's M <= 8 arithmetic), so the bar is 1e-3 against
+    that form of the oracle; the reference's own M > 8 path rounds the scaled weights to BF16 first
+    (src/engine/dense_gemm_fp4_sm110.cu:558-583), which moves ITS result by up to ~2e-3 when the
+    global scale is not a power of two -- that distance is bounded at 3e-3 here and printed."""
+    rng = np.random.default_rng(4321)
+    launches0 = handle.launch_count()
+    worst, worst_gemm = 0.0, {}
+    for it in range(60):
+        M = int(rng.integers(17, 65)) if it % 2 else int(rng.integers(65, 301))
+        K = int(rng.integers(1, 24)) * 256
+        N = int(rng.integers(1, 900)) if M <= 64 else int(rng.integers(1, 300)) * 8
+        gs = float(FUZZ_GS[it % 4])
+        packed, scale = util.make_weight(N, K, seed=500 + it, sigma=float(rng.choice([0.02, 0.14])))
+        A = util.make_bf16((M, K), seed=600 + it, std=float(rng.choice(FUZZ_STD)))
+        R = util.make_bf16((M, N), seed=700 + it) if it % 3 else None
+        got = run_linear(handle, A, packed, scale, gs, residual=R, inplace=bool(it % 2))
+        exact = ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMV, threads=8)
+        err = ob.rel_frobenius(got, exact)
+        assert err <= TOL, (it, M, N, K, gs, err)
+        worst = max(worst, err)
+        dist = ob.rel_frobenius(got, ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMM, threads=8))
+        assert dist <= (TOL if gs == 1.0 else 3e-3), (it, M, N, K, gs, dist)
+        worst_gemm[gs] = max(worst_gemm.get(gs, 0.0), dist)
+    print("distance from the BF16-rounded-weight form per global scale:", {k: f"{v:.2e}" for k, v in worst_gemm.items()})
+    assert handle.launch_count() - launches0 >= 120      # activation pre-pass + GEMM per call: the fast kernels ran
+    assert handle.device_status() == 0
 
 
 @pytest.mark.parametrize("impl", [1, 2])
@@ -290,8 +338,8 @@ def test_swiglu(handle, T, I):
 # ---------------------------------------------------------------- prefill (M > 16)
 
 @pytest.mark.parametrize("impl", [1, 2])
-@pytest.mark.parametrize("M,N,K", [(17, 64, 256), (64, 256, 512), (100, 300, 1024), (128, 256, 5120),
-                                   (256, 512, 2048), (300, 1000, 640)])
+@pytest.mark.parametrize("M,N,K", [(17, 64, 256), (64, 256, 512), (100, 296, 1024), (128, 256, 5120),
+                                   (256, 512, 2048), (300, 1000, 768)])
 def test_prefill_small(handle, impl, M, N, K):
     packed, scale = util.make_weight(N, K, seed=M + N, sigma=0.14)
     A = util.make_bf16((M, K), seed=M)
@@ -299,6 +347,17 @@ def test_prefill_small(handle, impl, M, N, K):
     got = with_impl(handle, "prefill", impl, lambda: run_linear(handle, A, packed, scale, 1.0, residual=R))
     want = ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMM, threads=8)
     assert ob.rel_frobenius(got, want) <= TOL
+
+
+@pytest.mark.parametrize("M,N,K", [(100, 300, 1024), (300, 1000, 640), (70, 77, 48)])
+def test_prefill_shapes_the_tensor_core_kernel_does_not_take(handle, M, N, K):
+    """N % 8 != 0 or K % 256 != 0 above 64 tokens: the automatic choice falls back to the plain GEMM on
+    the dequantised matrix (correct, not fast) instead of refusing the call."""
+    packed, scale = util.make_weight(N, K, seed=M + N, sigma=0.14)
+    A = util.make_bf16((M, K), seed=M)
+    R = util.make_bf16((M, N), seed=N)
+    got = run_linear(handle, A, packed, scale, 1.0, residual=R)
+    assert ob.rel_frobenius(got, ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMM, threads=8)) <= TOL
 
 
 @pytest.mark.parametrize("M,N,K,res", [(300, 15360, 3840, True),    # 180 tiles: one whole wave + 32 tiles split by k
@@ -354,6 +413,44 @@ def test_linear_host(handle):
     hC = torch.zeros(M, N, dtype=torch.int16).pin_memory()
     handle.linear_host(hA, M, util.to_dev(packed), util.to_dev(scale), 1.0, N, K, hC, residual_host=hR)
     assert ob.rel_frobenius(hC.numpy().view(np.uint16), ob.linear(A, packed, scale, 1.0, residual=R)) <= TOL
+
+
+def test_linear_host_odd_workspace_size():
+    """A workspace size that is not a multiple of 16: the staging buffers at its end stay aligned."""
+    import torch
+    N, K, M = 128, 512, 3
+    packed, scale = util.make_weight(N, K, seed=6)
+    A = util.make_bf16((M, K), seed=7)
+    hA = torch.from_numpy(A.view(np.int16)).pin_memory()
+    hC = torch.zeros(M, N, dtype=torch.int16).pin_memory()
+    h = nvfp4.Handle(0, (16 << 20) + 13)
+    try:
+        h.linear_host(hA, M, util.to_dev(packed), util.to_dev(scale), 1.0, N, K, hC)
+        assert ob.rel_frobenius(hC.numpy().view(np.uint16), ob.linear(A, packed, scale, 1.0)) <= TOL
+        assert h.device_status() == 0
+    finally:
+        h.close()
+
+
+def test_linear_ex_rejects_output_inside_the_strided_activations(handle):
+    """C inside the rows the kernel reads of A (beyond M*K elements when the row stride is larger) or
+    inside the up half: refused, not launched."""
+    import torch
+    N, K, M, stride = 128, 256, 4, 1024
+    p, s = util.make_weight(N, K, seed=1)
+    dp, ds = util.to_dev(p), util.to_dev(s)
+    buf = torch.zeros(1 << 20, dtype=torch.int16, device="cuda")
+    base = buf.data_ptr()
+    inside_tail = base + ((M - 1) * stride + 16) * 2          # past M*K elements, still inside the last row read
+    with pytest.raises(nvfp4.Nvfp4Error) as e:
+        handle.linear_ex(base, M, dp, ds, 1.0, N, K, inside_tail, a_row_stride=stride)
+    assert e.value.status == -5
+    up = base + 512 * 2
+    with pytest.raises(nvfp4.Nvfp4Error) as e:
+        handle.linear_ex(base, M, dp, ds, 1.0, N, K, up + 64, swiglu_up=up, a_row_stride=stride)
+    assert e.value.status == -5
+    handle.linear_ex(base, M, dp, ds, 1.0, N, K, base + (M * stride + 64) * 2, a_row_stride=stride)   # behind everything: fine
+    torch.cuda.synchronize()
 
 
 # ---------------------------------------------------------------- against the reference itself

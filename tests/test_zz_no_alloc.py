@@ -3,6 +3,8 @@ device memory (their memory is fully planned at start-up, e.g. an engine that ha
 to its KV-cache pool).  It is called through the C ABI, twice in a row, and each result is checked
 against the handle-based nvfp4_linear on the same inputs.  The file sorts last on purpose: a run
 that stops at the first failure has then already been through every other test."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -30,16 +32,27 @@ def test_noalloc_matches_handle_entry_point_twice_in_a_row():
     try:
         # first call: tiles split over CTAs (partials + flags in the fixed array); second call: other shape,
         # residual in place, more than 8 tokens (two launches sharing the array back to back)
-        for (N, K, M, seed, res) in [(5120, 17408, 4, 7, False), (2048, 5120, 12, 9, True)]:
+        # third and fourth: a last row tile that is only partly inside N, and 16 tokens (two full launches) with the
+        # residual aliasing the output
+        first = True
+        for (N, K, M, seed, res) in [(5120, 17408, 4, 7, False), (2048, 5120, 12, 9, True), (1000, 2048, 3, 11, False),
+                                     (4200, 5120, 16, 13, True)]:
             packed, scale, A, R = _case(N, K, M, seed, res)
             dA, dp, ds = util.to_dev(A), util.to_dev(packed), util.to_dev(scale)
             want = util.to_dev(R) if res else torch.zeros(M, N, dtype=torch.int16, device="cuda")
             got = util.to_dev(R) if res else torch.zeros(M, N, dtype=torch.int16, device="cuda")
             h.linear(dA, M, dp, ds, 1.0, N, K, want, residual=want if res else None)
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
             st = lib.nvfp4_linear_decode_noalloc(dA.data_ptr(), M, dp.data_ptr(), ds.data_ptr(), 1.0, N, K,
                                                  got.data_ptr() if res else None, got.data_ptr(), stream)
             assert st == 0, lib.nvfp4_status_string(st).decode()
             torch.cuda.synchronize()
+            # what the entry point is for: free device memory is the same before and after the call (the very
+            # first call may still load the kernel's code, so it is left out)
+            if not first:
+                assert torch.cuda.mem_get_info()[0] == free_before
+            first = False
             g, w = util.to_host_u16(got), util.to_host_u16(want)
             assert ob.rel_frobenius(g, w) <= TOL
             assert ob.rel_frobenius(g, ob.linear(A, packed, scale, 1.0, residual=R, mode=ob.GEMV, threads=8)) <= TOL
@@ -50,5 +63,9 @@ def test_noalloc_matches_handle_entry_point_twice_in_a_row():
         assert lib.nvfp4_linear_decode_noalloc(p, 1, p, p, 1.0, 64, 48, None, p + 65536, stream) == -10
         assert b"allocation-free" in lib.nvfp4_status_string(-10)
         torch.cuda.synchronize()
+        # no device-side wait ran out in any of the calls above; the accessor refuses a null pointer
+        word = ctypes.c_uint(1)
+        assert lib.nvfp4_noalloc_status(ctypes.byref(word), 0) == 0 and word.value == 0
+        assert lib.nvfp4_noalloc_status(None, 0) == -1
     finally:
         h.close()
