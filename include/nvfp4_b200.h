@@ -130,8 +130,8 @@ int nvfp4_noalloc_status(unsigned int* status, int reset);
 /* C_f32[M,N] = A * W^T as unrounded FP32 (no residual, no BF16 rounding): a partial result for
  * callers that sum several of them before rounding once, e.g. the K-split down projection of
  * the tensor-parallel MLP.  No reference counterpart (the reference is single-GPU and always
- * rounds, src/engine/dense_gemm_fp4_sm110.cu:137-140).  M <= 16 and K % 256 == 0, otherwise
- * NVFP4_E_LIMIT. */
+ * rounds, src/engine/dense_gemm_fp4_sm110.cu:137-140).  K % 256 == 0; more than 16 tokens also need
+ * N % 8 == 0 (the tcgen05 GEMM's FP32 epilogue); otherwise NVFP4_E_LIMIT. */
 int nvfp4_linear_f32(nvfp4_handle* h, const void* A_bf16, int M, const uint8_t* packed, const uint8_t* scale_ue4m3,
                      float global_scale, int N, int K, void* C_f32, nvfp4_stream_t stream);
 

@@ -70,6 +70,11 @@ int nvfp4_ckpt_linear(const nvfp4_ckpt* c, const char* prefix, nvfp4_host_weight
  * first part's; a mismatch would dequantise the other parts wrongly, so it is an error here). */
 int nvfp4_merge_rows(const nvfp4_host_weight* parts, int n, uint8_t* packed_out, uint8_t* scale_out,
                      nvfp4_host_weight* merged);
+/* The same with the reference's rule as an option: take_first_scale != 0 accepts parts with different
+ * global scales and gives the merged tensor the first part's (src/engine/model.cpp:329 for QKV, :492
+ * for gate+up), so a checkpoint the reference loads is loaded the same way, wrong rows included. */
+int nvfp4_merge_rows_ex(const nvfp4_host_weight* parts, int n, uint8_t* packed_out, uint8_t* scale_out,
+                        nvfp4_host_weight* merged, int take_first_scale);
 
 /* Merged gate/up [2I, H] (gate rows, then up rows) -> rows interleaved in slabs of 16: rows 16s..16s+7 =
  * gate rows 8s..8s+7, rows 16s+8..16s+15 = up rows 8s..8s+7.  That is the layout the swiglu_epilogue form

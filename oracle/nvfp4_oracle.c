@@ -226,6 +226,45 @@ void nvfp4_oracle_dense_linear(const uint16_t* A, int M, const uint16_t* W, int 
     free(a);
 }
 
+/* The reference's BF16 GEMV for one token, in ITS summation order (src/engine/dense_gemm_sm110.cu:
+ * gemv_kernel :544-604, gemv_kernel_scattered :682-735, the K-tiled variants :612-668 and their
+ * "+ residual" twins :811-1033, dispatched by invoke_dense_gemv / _add :1140-1216).  One warp per
+ * output row; lane l walks the 8-element chunks l, l+32, ... and adds, per pair of elements,
+ * rn(a0*w0 + a1*w1) to its FP32 sum (products of two BF16 are exact in FP32, so fused or not the pair
+ * sum is the same); elements beyond the last whole chunk go one by one to lane (k mod 32); the 32 sums
+ * meet in an xor-shuffle tree (16, 8, 4, 2, 1); the residual is added in FP32 before the one rounding.
+ * Every variant of the family keeps this order (the tile length is a multiple of 256). */
+void nvfp4_oracle_dense_gemv_ref(const uint16_t* A, const uint16_t* W, int N, int K, const uint16_t* residual,
+                                 uint16_t* C) {
+    float* a = (float*)malloc((size_t)K * sizeof(float));
+    for (int k = 0; k < K; ++k) a[k] = nvfp4_oracle_bf2f(A[k]);
+    const int k8 = K / 8;
+    for (int n = 0; n < N; ++n) {
+        const uint16_t* w = W + (size_t)n * K;
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float sum = 0.0f;
+            for (int i = l; i < k8; i += 32)
+                for (int j = 0; j < 4; ++j) {
+                    const int k = 8 * i + 2 * j;
+                    const float pair = a[k] * nvfp4_oracle_bf2f(w[k]) + a[k + 1] * nvfp4_oracle_bf2f(w[k + 1]);
+                    sum += pair;
+                }
+            for (int k = 8 * k8 + l; k < K; k += 32) sum += a[k] * nvfp4_oracle_bf2f(w[k]);
+            lane[l] = sum;
+        }
+        for (int mask = 16; mask > 0; mask >>= 1) {
+            float next[32];
+            for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ mask];
+            memcpy(lane, next, sizeof(lane));
+        }
+        float out = lane[0];
+        if (residual) out = out + nvfp4_oracle_bf2f(residual[n]);
+        C[n] = nvfp4_oracle_f2bf(out);
+    }
+    free(a);
+}
+
 /* src/engine/light_ops.cu:30-57 (blockReduceSum with 256 threads) over per-thread partial sums */
 static float block_reduce_256(float* v) {
     float w[8];

@@ -83,6 +83,12 @@ void nvfp4_oracle_swiglu_merged(const uint16_t* merged, int T, int I, uint16_t* 
  * the FP32 summation order. */
 void nvfp4_oracle_dense_linear(const uint16_t* A, int M, const uint16_t* W, int N, int K,
                                const uint16_t* residual, uint16_t* C);
+/* One token through the reference's BF16 GEMV kernels in their own summation order (lane-strided
+ * 8-element chunks, pairwise products, xor-shuffle tree; src/engine/dense_gemm_sm110.cu:544-604,
+ * 682-735, 811-1033, 1140-1216).  Pinned bit for bit against those kernels' outputs. */
+void nvfp4_oracle_dense_gemv_ref(const uint16_t* A, const uint16_t* W, int N, int K, const uint16_t* residual,
+                                 uint16_t* C);
+
 
 /* RMSNorm with the centred weight, one row per token:
  *   out = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + w) ), FP32 throughout.

@@ -11,6 +11,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_LIB = os.path.join(_HERE, "libnvfp4_oracle.so")
 REF_LIB = os.path.join(_HERE, "_ref", "libref_fp4.so")
+REF_DENSE_LIB = os.path.join(_HERE, "_ref", "libref_dense.so")
 
 AUTO, GEMV, GEMM = 0, 1, 2
 
@@ -55,6 +56,8 @@ def load():
         lib.nvfp4_oracle_swiglu_merged.argtypes = [_u16p, c_int, c_int, _u16p]
         lib.nvfp4_oracle_dense_linear.restype = None
         lib.nvfp4_oracle_dense_linear.argtypes = [_u16p, c_int, _u16p, c_int, c_int, c_void_p, _u16p]
+        lib.nvfp4_oracle_dense_gemv_ref.restype = None
+        lib.nvfp4_oracle_dense_gemv_ref.argtypes = [_u16p, _u16p, c_int, c_int, c_void_p, _u16p]
         lib.nvfp4_oracle_rmsnorm.restype = None
         lib.nvfp4_oracle_rmsnorm.argtypes = [_u16p, c_void_p, _u16p, c_float, c_int, c_int, _u16p, c_void_p]
         lib.nvfp4_oracle_mlp.restype = None
@@ -122,6 +125,17 @@ def dense_linear(A, W, residual=None):
     assert W.shape[1] == K
     C = np.empty((M, N), np.uint16)
     load().nvfp4_oracle_dense_linear(np.ascontiguousarray(A), M, np.ascontiguousarray(W), N, K, _res_ptr(residual), C)
+    return C
+
+
+def dense_gemv_ref(A, W, residual=None):
+    """One token (A [1,K] or [K]) through the reference's BF16 GEMV summation order; returns uint16 [1,N]."""
+    A = np.ascontiguousarray(A).reshape(-1)
+    N, K = W.shape
+    assert A.shape[0] == K
+    C = np.empty((1, N), np.uint16)
+    res = None if residual is None else np.ascontiguousarray(residual).reshape(-1)
+    load().nvfp4_oracle_dense_gemv_ref(A, np.ascontiguousarray(W), N, K, _res_ptr(res), C.reshape(-1))
     return C
 
 
@@ -203,6 +217,10 @@ def ref_available():
     return os.path.exists(REF_LIB)
 
 
+def ref_dense_available():
+    return os.path.exists(REF_LIB) and os.path.exists(REF_DENSE_LIB)
+
+
 _ref = None
 
 
@@ -222,6 +240,12 @@ def load_ref():
         for n in ("ref_fp4_gemv", "ref_fp4_gemv_add", "ref_fp4_dual_gemv", "ref_fp4_gemm", "ref_fp4_gemm_add",
                   "ref_swiglu", "ref_swiglu_merged"):
             getattr(lib, n).restype = None
+        if os.path.exists(REF_DENSE_LIB):
+            dl = ctypes.CDLL(REF_DENSE_LIB)
+            dl.ref_dense_gemv.argtypes = [vp, vp, vp, c_int, c_int, vp]
+            dl.ref_dense_gemv_add.argtypes = [vp, vp, vp, vp, c_int, c_int, vp]
+            dl.ref_dense_gemv.restype = dl.ref_dense_gemv_add.restype = None
+            lib.dense = dl
         if hasattr(lib, "ref_rmsnorm"):
             lib.ref_rmsnorm.argtypes = [vp, vp, vp, c_float, c_int, c_int, vp]
             lib.ref_fused_add_rmsnorm.argtypes = [vp, vp, vp, vp, c_float, c_int, c_int, vp]

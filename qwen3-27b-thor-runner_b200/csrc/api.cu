@@ -25,6 +25,17 @@ struct nvfp4_handle {
     unsigned long long launches = 0;
 };
 
+#include <atomic>
+
+namespace nvfp4 {
+unsigned int next_launch_tag() {
+    static std::atomic<unsigned int> counter{0u};
+    unsigned int t = counter.fetch_add(1u, std::memory_order_relaxed) + 1u;
+    if (t == 0u) t = counter.fetch_add(1u, std::memory_order_relaxed) + 1u;
+    return t;
+}
+}  // namespace nvfp4
+
 namespace {
 
 constexpr size_t kDecodeScratchBytes = 8u << 20;   // status word + the split-tile partial pairs of the two GEMV kernels
@@ -67,6 +78,16 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
                          decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset;
     // options only the GEMV kernels implement (the SwiGLU epilogue and the group reduction exist in the wide one too)
     const bool other_options = a.out_f32 || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
+    if (a.out_f32 && a.M > 16) {
+        // unrounded FP32 sums beyond the GEMV kernels: the 128-token-tile tcgen05 kernel's FP32 epilogue
+        if (a.swiglu_up || a.a_stride || a.k_valid || a.norm_w || a.px || a.swiglu_out) return NVFP4_E_LIMIT;
+        if (h->prefill_impl == 1 || !prefill_umma_supported(a)) return NVFP4_E_LIMIT;
+        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > ws_bytes) return NVFP4_E_WORKSPACE;
+        int nl = 0;
+        cudaError_t e = launch_prefill_umma(a, h->dev, h->workspace, ws_bytes, kDecodeScratchBytes, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     if (a.swiglu_out && !other_options && !a.px && a.M > 16) {
         // beyond the GEMV kernels only the 128-token-tile tcgen05 kernel has the SwiGLU epilogue
         if (h->prefill_impl == 1 || !prefill_umma_supported(a)) return NVFP4_E_LIMIT;

@@ -253,13 +253,18 @@ int nvfp4_ckpt_linear(const nvfp4_ckpt* c, const char* prefix, nvfp4_host_weight
 
 int nvfp4_merge_rows(const nvfp4_host_weight* parts, int n, uint8_t* packed_out, uint8_t* scale_out,
                      nvfp4_host_weight* merged) {
+    return nvfp4_merge_rows_ex(parts, n, packed_out, scale_out, merged, 0);
+}
+
+int nvfp4_merge_rows_ex(const nvfp4_host_weight* parts, int n, uint8_t* packed_out, uint8_t* scale_out,
+                        nvfp4_host_weight* merged, int take_first_scale) {
     if (!parts || !packed_out || !scale_out || !merged || n < 1) return NVFP4_CKPT_E_NULL;
     const int K = parts[0].K;
     long long rows = 0;
     for (int i = 0; i < n; ++i) {
         if (!parts[i].packed || !parts[i].scale) return NVFP4_CKPT_E_NULL;
         if (parts[i].K != K || parts[i].N <= 0) return NVFP4_CKPT_E_SHAPE;
-        if (parts[i].global_scale != parts[0].global_scale) return NVFP4_CKPT_E_SCALE;
+        if (!take_first_scale && parts[i].global_scale != parts[0].global_scale) return NVFP4_CKPT_E_SCALE;
         rows += parts[i].N;
     }
     if (rows > 0x7fffffff) return NVFP4_CKPT_E_SHAPE;

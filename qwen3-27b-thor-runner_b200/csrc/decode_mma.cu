@@ -28,8 +28,9 @@
 //     first half-unit: the others store their FP32 partials to the handle's scratch as 8-byte
 //     {value, launch epoch} pairs (one transaction each, so a pair is its own arrival flag: no
 //     fence, no flag write, one L2 round trip for the reader); the owner adds them in a fixed
-//     order (deterministic), applies 2^8/global_scale and the residual in FP32 and rounds once
-//     to BF16.  Its wait on the pairs is bounded.
+//     order (deterministic), clears the slots it has read (so a replayed launch, which carries
+//     the same tag, never meets the previous replay's pairs), applies 2^8/global_scale and the
+//     residual in FP32 and rounds once to BF16.  Its wait on the pairs is bounded.
 //
 // Arithmetic: group products are summed in FP32 by the MMA, block scales are applied exactly
 // before the sum (they are exact), 1/global_scale once at the end.  This is the reference's
@@ -80,6 +81,7 @@ struct DecodeParams {
     int act_all;         // 1 = slot index is the k-chunk, 0 = position in the CTA's span
     int swiglu_out;      // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
     int out_f32;         // C is FP32 [M,N]: store the scaled sum unrounded (partial results for a later reduction)
+    unsigned int epoch;
     // Tensor-parallel K split: world > 0 = push the sums to the ranks' exchange buffers and reduce
     // over the group at the end of this kernel (C then receives the full sum + residual).
     unsigned char* xpeer[xchg::kMaxWorld];
@@ -108,7 +110,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_amax + 16);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
-    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_abort) + 1;
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     unsigned char* pairs = p.pairs;
@@ -196,11 +197,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // and never overflows.  Pass B converts and stores in natural k order.  The scale is undone in
     // FP32 in the epilogue.
     ptx::griddep_wait();
-    // This launch's tag for the split-tile pairs, from the counter in the scratch (one atomic per CTA;
-    // its round trip hides behind the staging loads, the value reaches shared memory before the
-    // barrier that ends pass A).
-    unsigned int epoch_taken = 0;
-    if (tid == 0) epoch_taken = ptx::take_launch_epoch(p.scratch);
     // Group reduction: this launch's epoch and slot set (the counter was advanced by the previous
     // launch that used the buffer, which has completed by now).
     unsigned int xepoch = 0, xset = 0;
@@ -338,7 +334,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 *reinterpret_cast<uint4*>(s_act + dst[u]) = x[u];
             }
         }
-        if (tid == 0) *s_epoch = epoch_taken;
         ptx::named_barrier_sync(1, kConsumerThreads);
         if (tid < p.M) {
             const int e8 = (int)(s_amax[tid] >> 7);           // biased BF16 exponent of the largest element
@@ -382,7 +377,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         ptx::named_barrier_sync(1, kConsumerThreads);
     }
 
-    const unsigned int epoch = *s_epoch;
     int stage = 0;
     uint32_t ph = 0;
     int hu = u_begin;
@@ -422,7 +416,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            v[j][i] = make_uint2(0u, epoch);
+                            v[j][i] = make_uint2(0u, p.epoch);
                             if (mm[i] < p.M && (j == 0 || two))
                                 v[j][i] = ptx::ld_volatile_v2(src + ((size_t)j * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]) * 8);
                         }
@@ -430,7 +424,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == epoch);
+                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == p.epoch);
                     if (ready) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
@@ -447,6 +441,19 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 }
             }
             return true;
+        };
+        // Once a gather has been ACCEPTED (by the whole warp, for the early look): hand the slots back
+        // cleared.  The tag comes from the host and a captured CUDA graph replays it unchanged, so a pair
+        // left behind would look current to the next replay; a cleared slot cannot.  (Each pair has exactly
+        // one reader, this thread; the next launch's contributors write only after griddepcontrol.wait,
+        // when these stores have landed.)
+        auto clear_pairs = [&]() {
+            for (int c = cta + 1; c <= last; ++c) {
+                unsigned char* src = pairs + ((size_t)c * (kMaxTokens * kRT)) * 8;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (mm[i] < p.M) ptx::st_volatile_v2(src + ((size_t)mm[i] * kRT + rr[i]) * 8, 0u, 0u);
+            }
         };
 
         while (hu < seg_end) {
@@ -468,6 +475,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 4; ++i) pre[i] = got[i];
                     prefetched = true;
+                    clear_pairs();
                 }
             }
             if (grp < cnt) {
@@ -542,10 +550,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 unsigned char* slot = pairs + (size_t)cta * (kMaxTokens * kRT) * 8;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), epoch);
+                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), p.epoch);
             } else {
                 if (!prefetched) {
-                    gather_pairs(pre, true);
+                    if (gather_pairs(pre, true)) clear_pairs();
                     __syncwarp();
                 }
                 const int row_base = tile * kRT;
@@ -769,6 +777,7 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DecodePlan pl;
         if (!plan_decode(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
+        pl.p.epoch = next_launch_tag();
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(pl.grid);
         cfg.blockDim = dim3((2 * kGroupWarps + 1) * 32);

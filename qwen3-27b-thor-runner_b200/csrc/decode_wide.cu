@@ -75,6 +75,7 @@ struct WideParams {
     unsigned char* xpeer[xchg::kMaxWorld];
     int xrank, xworld, xslot_pairs;
     int swiglu_out;            // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
+    unsigned int epoch;
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -89,7 +90,6 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_scale + stages * kUnitScaleBytes);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
-    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_abort) + 1;   // 0 until consumer thread 0 has taken the tag
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     unsigned char* pairs = p.scratch + kPartialOffset;     // [CTA][16 tokens][256 rows] x {FP32 value, epoch}
@@ -106,7 +106,6 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
             ptx::mbar_init(&empty_bar[s], kConsumerWarps);    // every consumer warp releases every stage
         }
         *s_abort = 0;
-        *s_epoch = 0u;
         ptx::fence_mbar_init();
     }
     __syncthreads();
@@ -160,10 +159,6 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
     const int off_a = g * kActRowBytes + t * kActBlockBytes;   // token g (second tile: g + 8), 64-k block t; chunks at immediate offsets
 
     ptx::griddep_wait();          // outputs, residual, unscale and the cross-CTA scratch belong to earlier kernels until now
-    // This launch's tag for the split-tile pairs: thread 0 takes it from the counter in the scratch and
-    // leaves it in shared memory; the warps pick it up at their first segment epilogue, long after.
-    if (tid == 0) *s_epoch = ptx::take_launch_epoch(p.scratch);
-    unsigned int epoch = 0;
     unsigned int xepoch = 0, xset = 0;      // group reduction: this launch's epoch and slot set
     if (p.xworld > 0) {
         xepoch = *reinterpret_cast<volatile unsigned int*>(p.xpeer[p.xrank] + xchg::kEpochOff) + 1u;
@@ -242,16 +237,6 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
             while (last + 1 < G && (long long)(last + 1) * p.units / G < pair_end) ++last;
         const int row_base = pair * kUnitRows;
         const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
-        if (epoch == 0u && !(owner && complete)) {
-            const long long te0 = clock64();
-            while ((epoch = *s_epoch) == 0u) {
-                if (*s_abort || clock64() - te0 > ptx::kWaitBudgetClocks) {
-                    *s_abort = 1;
-                    atomicCAS(status, 0u, 0x640u);
-                    break;
-                }
-            }
-        }
         float v[kTT][4];
 #pragma unroll
         for (int j = 0; j < kTT; ++j)
@@ -268,7 +253,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int m = 8 * j + 2 * t + (i & 1);
-                    if (m < p.M) ptx::st_volatile_v2(slot + (m * kUnitRows + rr[i]) * 8, __float_as_uint(v[j][i]), epoch);
+                    if (m < p.M) ptx::st_volatile_v2(slot + (m * kUnitRows + rr[i]) * 8, __float_as_uint(v[j][i]), p.epoch);
                 }
         } else {
             // contributors in CTA order (a fixed summation order); the eight loads of one contributor
@@ -284,14 +269,14 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int m = 8 * j + 2 * t + (i & 1);
-                            x[j][i] = make_uint2(0u, epoch);
+                            x[j][i] = make_uint2(0u, p.epoch);
                             if (m < p.M) x[j][i] = ptx::ld_volatile_v2(src + (m * kUnitRows + rr[i]) * 8);
                         }
                     bool ready = true;
 #pragma unroll
                     for (int j = 0; j < kTT; ++j)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == epoch);
+                        for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == p.epoch);
                     if (ready) {
 #pragma unroll
                         for (int j = 0; j < kTT; ++j)
@@ -307,6 +292,18 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
                     }
                 }
             }
+            // hand the slots back cleared: a replayed launch carries the same tag (decode_mma.cu explains)
+            if (!failed)
+                for (int c = cta + 1; c <= last; ++c) {
+                    unsigned char* src = pairs + (size_t)c * (kTokens * kUnitRows) * 8;
+#pragma unroll
+                    for (int j = 0; j < kTT; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int m = 8 * j + 2 * t + (i & 1);
+                            if (m < p.M) ptx::st_volatile_v2(src + (m * kUnitRows + rr[i]) * 8, 0u, 0u);
+                        }
+                }
             __syncwarp();
             if (p.swiglu_out) {
                 // the warp's slab is one gate/up slab: row r0 is a gate row (i = 0, 1), row r0 + 8 its up row
@@ -440,6 +437,7 @@ cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void
     int stages = (kSmemBudget - fixed) / kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
+    p.epoch = next_launch_tag();
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);

@@ -53,6 +53,7 @@ struct DenseParams {
     int units, kchunks;       // units in all, units per row tile
     int stages;
     int act_slots, act_all;   // resident activation slots (units of 128 k); 1 = slot index is the k-chunk
+    unsigned int epoch;
 };
 
 __global__ void __launch_bounds__(kDenseThreads, 1)
@@ -66,7 +67,6 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_out + 2 * kDenseMaxTokens * kOutLd);
     uint64_t* empty_bar = full_bar + kDenseStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kDenseStages);
-    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_abort) + 1;
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     unsigned char* pairs = p.pairs;
@@ -119,9 +119,6 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
     ptx::griddep_launch_dependents();
     ptx::named_barrier_sync(2, kDenseThreads);                   // mbarriers initialised
     ptx::griddep_wait();                                         // activations, residual, outputs and scratch belong to earlier kernels until now
-    // this launch's tag for the split-tile pairs (one atomic per CTA, its round trip behind the staging loads)
-    unsigned int epoch_taken = 0;
-    if (tid == 0) epoch_taken = ptx::take_launch_epoch(p.scratch);
 
     {   // resident activations: chunk id = (slot * M + token) * 16 + c, 16 bytes = 8 consecutive k
         const int per_slot = p.M * 16;
@@ -148,10 +145,8 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
             for (int u = 0; u < 4; ++u)
                 if (dst[u] >= 0) *reinterpret_cast<uint4*>(s_act + dst[u]) = x[u];
         }
-        if (tid == 0) *s_epoch = epoch_taken;
         ptx::named_barrier_sync(1, kDenseConsumers);
     }
-    const unsigned int epoch = *s_epoch;
 
     int stage = 0;
     uint32_t ph = 0;
@@ -215,7 +210,7 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
                 unsigned char* slot = pairs + (size_t)cta * (kDenseMaxTokens * kRT) * 8;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), epoch);
+                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), p.epoch);
             } else {
                 // contributors in CTA order (a fixed summation order), two at a time: their eight
                 // loads are issued before any is looked at; the wait for an old epoch is bounded
@@ -230,7 +225,7 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
                         for (int j = 0; j < 2; ++j)
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                x[j][i] = make_uint2(0u, epoch);
+                                x[j][i] = make_uint2(0u, p.epoch);
                                 if (mm[i] < p.M && (j == 0 || two))
                                     x[j][i] = ptx::ld_volatile_v2(src + ((size_t)j * (kDenseMaxTokens * kRT) + mm[i] * kRT + rr[i]) * 8);
                             }
@@ -238,7 +233,7 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == epoch);
+                            for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == p.epoch);
                         if (ready) {
 #pragma unroll
                             for (int j = 0; j < 2; ++j)
@@ -254,6 +249,14 @@ dense_gemv_kernel(const __grid_constant__ CUtensorMap tm_w, const DenseParams p)
                         }
                     }
                 }
+                // hand the slots back cleared: a replayed launch carries the same tag (decode_mma.cu explains)
+                if (!failed)
+                    for (int c = cta + 1; c <= last; ++c) {
+                        unsigned char* src = pairs + (size_t)c * (kDenseMaxTokens * kRT) * 8;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (mm[i] < p.M) ptx::st_volatile_v2(src + ((size_t)mm[i] * kRT + rr[i]) * 8, 0u, 0u);
+                    }
                 __syncwarp();
                 const int row_base = tile * kRT;
 #pragma unroll
@@ -325,8 +328,7 @@ cudaError_t configure_dense_gemv() {
 }
 
 // scratch: the handle workspace (status word at 0, pairs at dev.gemv_pairs_offset, shared with the
-// NVFP4 GEMV: launches on one stream follow each other, and every launch takes its own tag from
-// the counter in the scratch).
+// NVFP4 GEMV: launches on one stream follow each other, and every launch has its own epoch).
 cudaError_t launch_dense_gemv(const DenseArgs& a, nvfp4_device_info& dev, void* scratch, int* launches, cudaStream_t s) {
     CUtensorMap tm;
     if (!umma::make_map(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.W, (uint64_t)a.K, (uint64_t)a.N, 64, kRT,
@@ -343,6 +345,7 @@ cudaError_t launch_dense_gemv(const DenseArgs& a, nvfp4_device_info& dev, void* 
         if (a.residual) b.residual = static_cast<const char*>(a.residual) + (size_t)m0 * a.N * 2;
         DensePlan pl;
         if (!plan_dense(b, m, dev, scratch, &pl)) return cudaErrorInvalidValue;
+        pl.p.epoch = next_launch_tag();
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(pl.grid);
         cfg.blockDim = dim3(kDenseThreads);

@@ -38,6 +38,13 @@ struct nvfp4_device_info {
     size_t gemv_pairs_offset = 6u << 20;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
 };
 
+// The tag of one GEMV launch on the split-tile pairs in its scratch: a process-wide counter, never 0
+// (what a cleared slot holds), safe to call from any host thread.  It is only the second line of
+// defence -- the owner of a row tile clears every pair it has read, so a captured launch that is
+// replayed with the same tag still never meets an old pair; a changing tag additionally keeps a
+// pair that a timed-out launch left behind from being accepted by a later eager launch.
+unsigned int next_launch_tag();
+
 // --- decode_simple.cu: scalar CUDA-core GEMV, any K % 16 == 0, M <= 16 per launch.
 cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);
 

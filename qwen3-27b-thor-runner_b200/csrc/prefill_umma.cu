@@ -75,6 +75,7 @@ struct PrefillParams {
     unsigned int* flags;       // [grid][2], the launch's tag once that partial tile is stored
     int swiglu_out;            // weight rows interleaved in slabs of 16 (8 gate, 8 up): C is [M, N/2] = bf16(silu(gate) * up)
     int dense;                 // 1 = BF16 weights and activations as they are: no token scale, no 2^8, no global scale
+    int out_f32;               // C is FP32 [M,N]: the scaled sums unrounded, no residual (partials a caller reduces itself)
 };
 
 // ---------------------------------------------------------------- tcgen05 helpers
@@ -142,6 +143,10 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, unsign
         if (m < p.M && n < p.N) {                      // N % 8 == 0: a chunk of 4 is inside or outside
             const size_t o = (size_t)m * p.N + n;
             float f[4] = {s.x * mul, s.y * mul, s.z * mul, s.w * mul};
+            if (p.out_f32) {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + o) = make_float4(f[0], f[1], f[2], f[3]);
+                continue;
+            }
             if (p.residual) {
                 const uint2 rr = *reinterpret_cast<const uint2*>(p.residual + o);
                 f[0] += bf16_bits_to_float(rr.x & 0xFFFFu);
@@ -402,6 +407,14 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                     } else
                     if (m < p.M && n0 < p.N) {
                         const size_t o = (size_t)m * p.N + n0;
+                        if (p.out_f32) {
+                            float* dst = reinterpret_cast<float*>(p.C) + o;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)      // N % 8 == 0: whole groups of 4
+                                if (n0 + i < p.N) *reinterpret_cast<float4*>(dst + i) =
+                                    make_float4(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul,
+                                                __uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+                        } else
                         if (n0 + 32 <= p.N) {
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
@@ -426,7 +439,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                                 *reinterpret_cast<uint4*>(p.C + o + v * 8) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
                             }
                         } else {
-                            for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {       // unrolled: r[] stays in registers
+                                if (n0 + i >= p.N) continue;
                                 float f = __uint_as_float(r[i]) * mul;
                                 if (p.residual) f += __bfloat162float(p.residual[o + i]);
                                 p.C[o + i] = __float2bfloat16_rn(f);
@@ -477,6 +492,7 @@ size_t act_bytes(int M, int K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }
 bool prefill_umma_supported(const LinearArgs& a) {
     if (a.M < 1 || (a.K % WK) != 0 || (a.N % 8) != 0) return false;
     if (a.swiglu_out && ((a.N % 32) != 0 || a.residual)) return false;
+    if (a.out_f32 && (a.swiglu_out || a.residual)) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
     return true;
 }
@@ -556,6 +572,7 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.status = static_cast<unsigned int*>(scratch);
     p.inv_gs = a.inv_gs;
     p.swiglu_out = a.swiglu_out ? 1 : 0;
+    p.out_f32 = a.out_f32 ? 1 : 0;
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.m_tiles = (a.M + BM - 1) / BM;
     p.n_tiles = (a.N + BN - 1) / BN;

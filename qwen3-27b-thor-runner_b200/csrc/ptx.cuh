@@ -194,8 +194,9 @@ __device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) 
 
 
 // ---------------------------------------------------------------- launch tag for cross-CTA hand-offs
-// Split-tile partials and flags in the scratch are tagged with a number that must differ from one
-// launch to the next.  It comes from a 64-bit counter in the scratch itself, not from the host: a
+// The stream-K flags of the tcgen05 kernels (several CTAs read one flag, so no reader can clear it)
+// are tagged with a number that must differ from one launch to the next.  It comes from a 64-bit
+// counter in the scratch itself, not from the host: a
 // captured CUDA graph replays its kernel parameters unchanged, so a host-side tag would repeat
 // on every replay and a reader could accept what the previous replay left behind.  Every CTA
 // adds to the counter once, after griddepcontrol.wait (the previous launch on this scratch has

@@ -30,6 +30,7 @@ CKPT_SIGNATURES = {
     "nvfp4_ckpt_get": (c_int, [c_void_p, c_char_p, ctypes.POINTER(CkptTensor)]),
     "nvfp4_ckpt_linear": (c_int, [c_void_p, c_char_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_merge_rows": (c_int, [ctypes.POINTER(HostWeight), c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
+    "nvfp4_merge_rows_ex": (c_int, [ctypes.POINTER(HostWeight), c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight), c_int]),
     "nvfp4_tp_shard_gate_up": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_down": (c_int, [ctypes.POINTER(HostWeight), c_int, c_int, c_void_p, c_void_p, ctypes.POINTER(HostWeight)]),
     "nvfp4_tp_shard_down_k": (c_int, [c_int, c_int]),
@@ -114,8 +115,9 @@ def _host_weight(packed, scale, gs):
     return w
 
 
-def merge_rows(parts):
-    """parts: [(packed, scale, global_scale), ...] with equal K and equal global scale -> merged triple."""
+def merge_rows(parts, take_first_scale=False):
+    """parts: [(packed, scale, global_scale), ...] with equal K -> merged triple.  Different global scales
+    are an error unless take_first_scale (the reference's rule: the first part's scale for all rows)."""
     lib = load()
     arr = (HostWeight * len(parts))(*[_host_weight(np.ascontiguousarray(p), np.ascontiguousarray(s), g) for p, s, g in parts])
     keep = [(np.ascontiguousarray(p), np.ascontiguousarray(s)) for p, s, _ in parts]
@@ -125,7 +127,7 @@ def merge_rows(parts):
     K = keep[0][0].shape[1] * 2
     po, so = np.empty((rows, K // 2), np.uint8), np.empty((rows, K // 16), np.uint8)
     m = HostWeight()
-    _check(lib.nvfp4_merge_rows(arr, len(parts), po.ctypes.data, so.ctypes.data, ctypes.byref(m)))
+    _check(lib.nvfp4_merge_rows_ex(arr, len(parts), po.ctypes.data, so.ctypes.data, ctypes.byref(m), int(take_first_scale)))
     return po, so, float(m.global_scale)
 
 

@@ -103,13 +103,26 @@ def test_reference_namespace_shim_compiles_and_links(tmp_path):
     if not shutil.which("nvcc"):
         pytest.skip("nvcc not on PATH")
     src = tmp_path / "shim_check.cu"
+    ref_engine = os.path.join(os.environ.get("REF_ROOT", os.path.join(os.path.dirname(ROOT), "reference")), "src", "engine")
+    have_ref = os.path.exists(os.path.join(ref_engine, "layer.h"))
     src.write_text('''
 #include <cstdint>
-namespace qwen_thor { namespace core {   // as src/engine/layer.h:197-204 of the reference defines it
+#ifdef NVFP4_TEST_REF_LAYER_H
+#include "layer.h"                       // the reference's own definition (src/engine/layer.h:197-204)
+#else
+namespace qwen_thor { namespace core {   // stand-in with the same members, for hosts without the reference tree
 struct QuantizedWeight { uint8_t* packed = nullptr; uint8_t* scale = nullptr; float global_scale = 1.0f;
                          float input_scale = 1.0f; int N = 0, K = 0; bool valid() const { return packed != nullptr; } };
 }}
+#endif
+#include <cstddef>
 #include "nvfp4_qwen_thor_shim.hpp"
+static_assert(offsetof(qwen_thor::core::QuantizedWeight, packed) == offsetof(nvfp4_quantized_weight, packed), "layout");
+static_assert(offsetof(qwen_thor::core::QuantizedWeight, scale) == offsetof(nvfp4_quantized_weight, scale), "layout");
+static_assert(offsetof(qwen_thor::core::QuantizedWeight, global_scale) == offsetof(nvfp4_quantized_weight, global_scale), "layout");
+static_assert(offsetof(qwen_thor::core::QuantizedWeight, input_scale) == offsetof(nvfp4_quantized_weight, input_scale), "layout");
+static_assert(offsetof(qwen_thor::core::QuantizedWeight, N) == offsetof(nvfp4_quantized_weight, N), "layout");
+static_assert(offsetof(qwen_thor::core::QuantizedWeight, K) == offsetof(nvfp4_quantized_weight, K), "layout");
 static_assert(sizeof(qwen_thor::core::QuantizedWeight) == sizeof(nvfp4_quantized_weight), "layout");
 int main() {
     qwen_thor::core::QuantizedWeight w;
@@ -120,8 +133,21 @@ int main() {
 ''')
     lib_dir = os.path.dirname(nvfp4.LIB_PATH)
     exe = tmp_path / "shim_check"
-    subprocess.run(["nvcc", "-std=c++17", "-Wno-deprecated-gpu-targets", "-I", os.path.join(ROOT, "qwen3-27b-thor-runner_b200", "include"),
-                    "-o", str(exe), str(src), "-L", lib_dir, "-lnvfp4_b200", "-Xlinker", "-rpath", "-Xlinker", lib_dir],
+    extra = ["-DNVFP4_TEST_REF_LAYER_H", "-I", ref_engine] if have_ref else []
+    subprocess.run(["nvcc", "-std=c++17", "-Wno-deprecated-gpu-targets", "-I", os.path.join(ROOT, "qwen3-27b-thor-runner_b200", "include")]
+                   + extra + ["-o", str(exe), str(src), "-L", lib_dir, "-lnvfp4_b200", "-Xlinker", "-rpath", "-Xlinker", lib_dir],
                    check=True, capture_output=True)
     rc = subprocess.run([str(exe)]).returncode
     assert rc == 3    # null pointers / no device: the call is refused and the status says so
+
+
+def test_reference_struct_size_as_the_reference_compiler_sees_it():
+    """sizeof(QuantizedWeight) as compiled from the reference's own layer.h (through the bridge that
+    includes it) equals the C struct of the ABI."""
+    import oracle_binding as ob
+    if not ob.ref_available():
+        pytest.skip("oracle/_ref not built")
+    import ctypes
+    ref = ctypes.CDLL(ob.REF_LIB)
+    ref.ref_sizeof_quantized_weight.restype = ctypes.c_int
+    assert ref.ref_sizeof_quantized_weight() == ctypes.sizeof(nvfp4.QuantizedWeight) == 32

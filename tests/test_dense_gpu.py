@@ -2,6 +2,9 @@
 kernel for up to 16 tokens against the CPU oracle, through the C ABI.  FP32 accumulation of exact
 BF16 products: the only difference allowed is the summation order (relative Frobenius <= 1e-3,
 the tolerance of the quantised path)."""
+import os
+import sys
+
 import numpy as np
 import pytest
 
@@ -101,3 +104,39 @@ def test_dense_argument_errors(handle):
         handle.linear_bf16(A, 1, W, 128, 124, C)            # K % 8
     with pytest.raises(nvfp4.Nvfp4Error):
         handle.linear_bf16(A, 1, W, 128, 128, A)            # output over the input
+
+
+DENSE_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_b200_dense.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(DENSE_GOLDEN), reason="golden file not generated")
+def test_dense_gemv_against_committed_reference_outputs(handle):
+    """The BF16 GEMV against what the reference's own invoke_dense_gemv / _add kernels stored on a B200
+    (src/engine/dense_gemm_sm110.cu:1140-1216)."""
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_reference_dense_golden as g
+    gold = np.load(DENSE_GOLDEN)
+    for name, c in g.cases().items():
+        got = run(handle, c["A"], c["W"], residual=c["residual"])
+        assert ob.rel_frobenius(got, gold[name]) <= TOL, name
+
+
+@pytest.mark.skipif(not ob.ref_dense_available(), reason="oracle/_ref/libref_dense.so not built")
+def test_dense_gemv_side_by_side_with_reference_kernels(handle):
+    """The reference's BF16 GEMV and ours on the same device buffers, model-sized K."""
+    import torch
+    dense = ob.load_ref().dense
+    st = torch.cuda.current_stream().cuda_stream
+    for (N, K, res) in [(5120, 5120, False), (2048, 6144, True), (1024, 17408, True)]:
+        W, A = util.make_bf16((N, K), seed=N + 3, std=0.05), util.make_bf16((1, K), seed=K + 4)
+        R = util.make_bf16((1, N), seed=N + 5) if res else None
+        dA, dW = util.to_dev(A), util.to_dev(W)
+        o_ref = torch.zeros(1, N, dtype=torch.int16, device="cuda")
+        if res:
+            dense.ref_dense_gemv_add(dA.data_ptr(), dW.data_ptr(), o_ref.data_ptr(), util.to_dev(R).data_ptr(), N, K, st)
+        else:
+            dense.ref_dense_gemv(dA.data_ptr(), dW.data_ptr(), o_ref.data_ptr(), N, K, st)
+        torch.cuda.synchronize()
+        ref_bits = util.to_host_u16(o_ref)
+        assert np.array_equal(ref_bits, ob.dense_gemv_ref(A, W, residual=R)), (N, K)      # the restatement, once more
+        assert ob.rel_frobenius(run(handle, A, W, residual=R), ref_bits) <= TOL, (N, K)

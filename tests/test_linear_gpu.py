@@ -551,9 +551,20 @@ def test_linear_f32_matches_bf16_path(handle):
     got32 = dC.cpu().numpy()
     got16 = run_linear(handle, A, packed, scale, 2.0)
     assert np.array_equal(ob.f32_to_bf16(got32), got16)
-    with pytest.raises(nvfp4.Nvfp4Error):     # beyond the GEMV regime
-        handle.linear_f32(util.to_dev(util.make_bf16((17, K), seed=1)), 17, util.to_dev(packed), util.to_dev(scale), 1.0, N, K,
-                          torch.zeros((17, N), dtype=torch.float32, device="cuda"))
+    # beyond the GEMV kernels: the tcgen05 GEMM's FP32 epilogue (whole tiles and tiles split along k)
+    handle.set_option("skinny_min_m", 129)           # the BF16 comparison through the same kernel
+    try:
+        for M2 in (17, 200):
+            A2 = util.make_bf16((M2, K), seed=33 + M2)
+            d32 = torch.full((M2, N), float("nan"), dtype=torch.float32, device="cuda")
+            handle.linear_f32(util.to_dev(A2), M2, util.to_dev(packed), util.to_dev(scale), 2.0, N, K, d32)
+            torch.cuda.synchronize()
+            assert np.array_equal(ob.f32_to_bf16(d32.cpu().numpy()), run_linear(handle, A2, packed, scale, 2.0))
+    finally:
+        handle.set_option("skinny_min_m", 9)
+    with pytest.raises(nvfp4.Nvfp4Error):     # N % 8 != 0 above 16 tokens
+        handle.linear_f32(util.to_dev(util.make_bf16((17, K), seed=1)), 17, util.to_dev(packed[:636]), util.to_dev(scale[:636]), 1.0, 636, K,
+                          torch.zeros((17, 636), dtype=torch.float32, device="cuda"))
 
 
 @pytest.mark.parametrize("M", [1, 4, 16])

@@ -235,3 +235,19 @@ def test_dense_linear_oracle_against_float64():
     want = ob.bf16_to_f32(A).astype(np.float64) @ ob.bf16_to_f32(W).astype(np.float64).T + ob.bf16_to_f32(R)
     got = ob.dense_linear(A, W, residual=R)
     assert util.bf16_ulp_diff(got, ob.f32_to_bf16(want.astype(np.float32))) <= 1
+
+
+DENSE_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_b200_dense.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(DENSE_GOLDEN), reason="golden file not generated")
+def test_dense_gemv_restatement_reproduces_the_reference_kernels_bit_for_bit():
+    """The oracle's statement of the reference's BF16 GEMV order against what the reference's own
+    kernels (plain, scattered and K-tiled, with and without the residual) stored on a B200."""
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_reference_dense_golden as g
+    gold = np.load(DENSE_GOLDEN)
+    for name, c in g.cases().items():
+        assert np.array_equal(g.oracle_output(c), gold[name]), name
+        # the generic FP32 dot in k order is the same sum in another order: last-bit differences only
+        assert ob.rel_frobenius(ob.dense_linear(c["A"], c["W"], residual=c["residual"]), gold[name]) <= 3e-4, name
