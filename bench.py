@@ -29,6 +29,7 @@ for _p in (os.path.join(ROOT, "qwen3-27b-thor-runner_b200"), os.path.join(ROOT, 
     if _p not in sys.path:
         sys.path.insert(0, _p)
 
+WORKLOAD = "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + down 5120x17408"
 H, I = 5120, 17408
 SHAPES = {"gate_up": (2 * I, H), "down": (H, I), "qkv": (7168, 5120), "o": (5120, 6144)}   # name -> (N, K)
 DECODE_MS = (1, 2, 4, 8, 16)
@@ -179,14 +180,73 @@ def run_reference_arm(args):
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * tt / steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc",
             "data": "synthetic",
-            "config": {"workload": "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + down 5120x17408 "
-                                   "(bounded row slice per step, CPU oracle port, all host threads)"},
+            "config": {"workload": WORKLOAD,
+                       "arm": "CPU oracle port of the reference algorithm, all rows of both shapes, all host threads"},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 # ----------------------------------------------------------------------------- our arm
+
+def sweep_parity(h, shapes, rot, acts, outs, torch, n_rows=64):
+    """Relative Frobenius error of every timed (shape, M) of the sweep against the CPU oracle on a seeded
+    sample of weight rows: the timed kernels on the timed buffers, launched once more and read back."""
+    import numpy as np
+    import oracle_binding as ob
+    import util
+    out, worst = [], 0.0
+    for name in rot:
+        N, K = shapes[name]
+        p, s = rot[name].w[0]
+        rows = np.sort(np.random.default_rng(N).choice(N, min(N, n_rows), replace=False))
+        r_idx = torch.from_numpy(rows).to(p.device)
+        hp, hs = p[r_idx].cpu().numpy(), s[r_idx].cpu().numpy()
+        for M in DECODE_MS:
+            A, C = acts[(name, M)], outs[(name, M)]
+            C.zero_()
+            h.linear(A, M, p, s, 1.0, N, K, C)
+            torch.cuda.synchronize()
+            got = util.to_host_u16(C[:, r_idx].contiguous().view(torch.int16))
+            want = ob.linear(util.to_host_u16(A.view(torch.int16)), np.ascontiguousarray(hp), np.ascontiguousarray(hs), 1.0,
+                             mode=ob.GEMV, threads=8)
+            err = float(ob.rel_frobenius(got, want))
+            worst = max(worst, err)
+            out.append({"shape": name, "M": M, "rel_frobenius": round(err, 7)})
+    return {"checked": f"{n_rows} sampled weight rows per shape, all tokens, vs the CPU oracle (FP32 accumulate, one rounding)",
+            "tolerance": 1e-3, "worst": round(worst, 7), "ok": worst <= 1e-3, "rows": out, "device_status": h.device_status()}
+
+
+def config0(h, peaks, torch, dev, use_graph, steps):
+    """configs[0]: one GEMV, M = 1, K = N = 5120 (14.7 MB of weights): time over rotating copies and the
+    whole output against the CPU oracle."""
+    import numpy as np
+    import oracle_binding as ob
+    import util
+    N = K = 5120
+    rot = Rotating(N, K, dev, seed=50)
+    A = device_acts(1, K, seed=0, dev=dev)
+    C = torch.empty((1, N), dtype=torch.bfloat16, device=dev)
+
+    def go():
+        p, s = rot.next()
+        h.linear(A, 1, p, s, 1.0, N, K, C, stream=torch.cuda.current_stream())
+
+    for _ in range(3):
+        go()
+    st = {}
+    time_region(go, max(steps, 20), torch, graph=use_graph, stats=st)
+    p, s = rot.w[0]
+    h.linear(A, 1, p, s, 1.0, N, K, C)
+    torch.cuda.synchronize()
+    want = ob.linear(util.to_host_u16(A.view(torch.int16)), p.cpu().numpy(), s.cpu().numpy(), 1.0, mode=ob.GEMV, threads=8)
+    err = float(ob.rel_frobenius(util.to_host_u16(C.view(torch.int16)), want))
+    gbs = alg_bytes(N, K, 1) / (st["median_ms"] * 1e-3) / 1e9
+    return {"workload": "configs[0]: M=1, K=5120, N=5120", "us": round(st["median_ms"] * 1e3, 2), "us_min": round(st["min_ms"] * 1e3, 2),
+            "replays": st["replays"], "cv": round(st["cv"], 4), "GBps": round(gbs, 1),
+            "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "rel_frobenius_vs_oracle": round(err, 7),
+            "copies": rot.n}
+
 
 class Rotating:
     """Distinct device copies of one weight, used round-robin so that no launch finds its
@@ -203,12 +263,14 @@ class Rotating:
         return self.w[self.i]
 
 
-def time_region(fn, steps, torch, graph=True):
-    """Device time per call of fn over `steps` calls.  graph=True: the `steps` calls are captured
-    into one CUDA graph (the library's launches are capturable: no allocation, no synchronisation)
-    and one replay is timed, so the figure is free of host launch overhead; the replay executes
-    exactly the kernels the calls would."""
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+def time_region(fn, steps, torch, graph=True, replays=50, stats=None, budget_s=0.4):
+    """Device time per call of fn (ms).  graph=True: `steps` calls are captured into one CUDA graph (the
+    library's launches are capturable: no allocation, no synchronisation) and the graph is replayed
+    `replays` times (fewer when one replay is long: the timed replays together stay near budget_s, at
+    least 5), each replay between its own pair of events; the MEDIAN replay is reported, so the figure is
+    free of host launch overhead and of a single outlier.  `stats`, when given, receives the number of
+    timed replays, their median, minimum and coefficient of variation (per call, ms).  graph=False: the
+    calls are issued on the stream between one pair of events."""
     if graph:
         g = torch.cuda.CUDAGraph()
         s = torch.cuda.Stream()
@@ -219,18 +281,37 @@ def time_region(fn, steps, torch, graph=True):
                     fn()
             g.replay()
             torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             g.replay()
             e1.record()
+            torch.cuda.synchronize()
+            first = e0.elapsed_time(e1)
+            n = int(max(5, min(replays, budget_s * 1e3 / max(first, 1e-3))))
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+            for a, b in ev:
+                a.record()
+                g.replay()
+                b.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / steps
+        t = sorted(a.elapsed_time(b) / steps for a, b in ev)
+        med = t[len(t) // 2]
+        if stats is not None:
+            mean = sum(t) / len(t)
+            var = sum((x - mean) ** 2 for x in t) / len(t)
+            stats.update({"replays": len(t), "median_ms": med, "min_ms": t[0], "cv": (var ** 0.5) / mean if mean else 0.0})
+        return med
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps   # ms per step
+    ms = e0.elapsed_time(e1) / steps
+    if stats is not None:
+        stats.update({"replays": 1, "median_ms": ms, "min_ms": ms, "cv": 0.0})
+    return ms   # ms per step
 
 
 def main():
@@ -239,7 +320,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--sections", default="decode,prefill,stream,mlp,dense,e2e,cpu,refkernel,tp",
+    ap.add_argument("--sections", default="decode,parity,config0,prefill,stream,mlp,dense,e2e,cpu,refkernel,tp",
                     help="extra measurements to add to the JSON line")
     ap.add_argument("--small", action="store_true", help="shrunk shapes (profiler captures, smoke runs)")
     ap.add_argument("--prefill-ms", default="64,256,2048,8192", help="token counts of the prefill section")
@@ -302,8 +383,9 @@ def main():
     sampler.start()
     use_graph = not args.no_graph
     l0 = h.launch_count()
-    ms = time_region(step, args.steps, torch, graph=use_graph)
-    launches = h.launch_count() - l0   # kernels launched by the K steps (= kernels in the timed replay)
+    value_stats = {}
+    ms = time_region(step, args.steps, torch, graph=use_graph, stats=value_stats)
+    launches = (h.launch_count() - l0)   # kernels launched by the K steps (= kernels in ONE timed replay)
     # Second pass, same launches regrouped: for every (shape, M) the `steps` launches of the timed
     # region run back to back between one event pair (weights still rotate), which gives the
     # kernel's average launch duration without an event gap between launches.
@@ -311,16 +393,18 @@ def main():
     for M in DECODE_MS:
         for name in ("gate_up", "down"):
             launch(name, M)
-            per[(name, M)] = [time_region(lambda: launch(name, M), args.steps, torch, graph=use_graph) * 1e-3]
+            st = {}
+            time_region(lambda: launch(name, M), args.steps, torch, graph=use_graph, stats=st)
+            per[(name, M)] = st
     clocks = sampler.stop()
     value = step_bytes / (ms * 1e-3) / 1e9
 
     sweep = []
-    for (name, M), ts in sorted(per.items()):
-        ts.sort()
-        t = sum(ts) / len(ts)
+    for (name, M), st in sorted(per.items()):
+        t = st["median_ms"] * 1e-3
         gbs = alg_bytes(*shapes[name], M) / t / 1e9
-        sweep.append({"shape": name, "M": M, "us": round(t * 1e6, 2), "us_min": round(ts[0] * 1e6, 2),
+        sweep.append({"shape": name, "M": M, "us": round(t * 1e6, 2), "us_min": round(st["min_ms"] * 1e3, 2),
+                      "replays": st["replays"], "cv": round(st["cv"], 4),
                       "GBps": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
                       "frac_of_8TBps": round(gbs / 8000.0, 4)})
     # Dominant kernel: the GEMV kernel on gate_up.  Token counts above 8 go through another kernel
@@ -337,15 +421,22 @@ def main():
     line = {"metric": "decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc", "data": "synthetic",
-            "config": {"workload": "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + down 5120x17408"
+            "config": {"workload": WORKLOAD
                                    + (" (SMALL shapes)" if args.small else "")
                                    + (f" (M restricted to {list(DECODE_MS)})" if args.decode_ms else ""),
                        "l2": f"weights rotate over {rot['gate_up'].n}/{rot['down'].n} distinct copies (> 2 x L2)",
                        "global_scale": 1.0, "scale_sigma": 0.02, "seed": 0,
-                       "timing": "one CUDA-graph replay of the K steps" if use_graph else "K steps of stream launches",
+                       "timing": (f"median of {value_stats.get('replays')} CUDA-graph replays of the K steps" if use_graph
+                                  else "K steps of stream launches"),
                        "decode_impl": h.get_option("decode_impl"), "prefill_impl": h.get_option("prefill_impl"),
                        "options": args.option},
-            "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "decode_sweep": sweep}
+            "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "decode_sweep": sweep,
+            "consistency": {"timed_replays": value_stats.get("replays"), "ms_per_step_min": round(value_stats.get("min_ms", ms), 5),
+                            "cv": round(value_stats.get("cv", 0.0), 4)}}
+    if "parity" in sections:
+        line["parity"] = sweep_parity(h, shapes, rot, acts, outs, torch)
+    if "config0" in sections and not args.small:
+        line["config0"] = config0(h, peaks, torch, dev, use_graph, args.steps)
 
     if "e2e" in sections:
         import bench_sections

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 TP_MS = (1, 8, 256, 4096)
 
 
-def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
+def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps, comm=None):
     """tokens/s of the MLP block at M in TP_MS (max over ranks of the device time)."""
     out = []
     for M in TP_MS:
@@ -56,7 +56,12 @@ def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
 
         ms, mode = timed()
         row = {"M": M, "ms": round(ms, 4), "tokens_per_s": round(M / (ms * 1e-3), 1), "timing": mode,
-               "reduction": "in the down-projection kernel, over peer memory" if (M <= 16 and world > 1) else ("nccl all-reduce" if world > 1 else "none")}
+               "reduction": "in the down-projection kernel, over peer memory" if (M <= 16 and world > 1) else
+                            ("nccl reduce-scatter of FP32 partials, residual + rounding on the slice, all-gather of BF16" if world > 1 else "none")}
+        if M > 16 and world > 1:       # the same step with BF16-rounded partials in one all-reduce, for comparison
+            comm.set_bf16_partials(True)
+            row["ms_nccl_allreduce_bf16_partials"] = round(timed()[0], 4)
+            comm.set_bf16_partials(False)
         if M <= 16 and world > 1:      # the same step with the other two reduction paths, for comparison
             for m in mlps:
                 m.set_fused(2)
@@ -72,6 +77,63 @@ def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps):
         del mlps
         torch.cuda.empty_cache()
     return out
+
+
+def full_size_parity(torch, dist, h, comm, dev, world, rank, token_counts=(256, 4096), n_tok=16, n_col=256):
+    """The MLP block at the benchmark's own size (H = 5120, I = 17408) above 16 tokens, where the sum over
+    the ranks goes through the library collective: FP32 partials (default) and BF16 partials, each against
+    the UNSPLIT CPU oracle on a seeded sample of n_tok token rows x n_col output columns.  Rank 0 checks."""
+    import numpy as np
+    import bench
+    import nvfp4_tp
+    import oracle_binding as ob
+    import util
+    H, I = bench.H, bench.I
+    gp, gs = bench.device_weight(2 * I, H, seed=300, dev=dev)
+    dp, ds = bench.device_weight(H, I, seed=301, dev=dev)
+    mlp = nvfp4_tp.TpMlp(h, comm, H, I, gp, gs, 1.0, dp, ds, 1.0, max(token_counts))
+    host = None
+    if rank == 0:
+        host = (gp.cpu().numpy(), gs.cpu().numpy(), dp.cpu().numpy(), ds.cpu().numpy())
+    del gp, gs, dp, ds
+    torch.cuda.empty_cache()
+    rows = []
+    for M in token_counts:
+        X = bench.device_acts(M, H, seed=310 + M, dev=dev)
+        R = bench.device_acts(M, H, seed=311 + M, dev=dev)
+        outs = {}
+        for name, bf16 in (("fp32_partials", False), ("bf16_partials", True)):
+            comm.set_bf16_partials(bf16)
+            out = R.clone()
+            mlp.forward(X, M, out, residual=out)
+            torch.cuda.synchronize()
+            outs[name] = out
+        comm.set_bf16_partials(False)
+        gathered = [torch.empty_like(outs["fp32_partials"].view(torch.uint8)) for _ in range(world)]
+        if dist is not None and world > 1:
+            dist.all_gather(gathered, outs["fp32_partials"].view(torch.uint8))
+        else:
+            gathered = [outs["fp32_partials"].view(torch.uint8)]
+        if rank == 0:
+            rng = np.random.default_rng(1000 + M)
+            toks = np.sort(rng.choice(M, min(M, n_tok), replace=False))
+            cols = np.sort(rng.choice(H, n_col, replace=False))
+            t_idx, c_idx = torch.from_numpy(toks).to(dev), torch.from_numpy(cols).to(dev)
+            Xs = util.to_host_u16(X[t_idx].contiguous().view(torch.int16))
+            Rs = util.to_host_u16(R[t_idx][:, c_idx].contiguous().view(torch.int16))
+            gu = ob.linear(Xs, host[0], host[1], 1.0, mode=ob.GEMM, threads=16)
+            act = ob.swiglu_merged(gu)
+            want = ob.linear(act, np.ascontiguousarray(host[2][cols]), np.ascontiguousarray(host[3][cols]), 1.0,
+                             residual=np.ascontiguousarray(Rs), mode=ob.GEMM, threads=16)
+            row = {"M": M, "sample": f"{len(toks)} token rows x {n_col} output columns, seed {1000 + M}",
+                   "identical_on_all_ranks": all(torch.equal(g, gathered[0]) for g in gathered)}
+            for name, out in outs.items():
+                got = util.to_host_u16(out[t_idx][:, c_idx].contiguous().view(torch.int16))
+                row[name + "_vs_unsplit_oracle"] = float(ob.rel_frobenius(got, want))
+            rows.append(row)
+    mlp.close()
+    torch.cuda.empty_cache()
+    return rows
 
 
 QKV = dict(q_rows=6144, kv_rows=512, n_kv_heads=2, o_in=6144)   # merged qkv [7168, 5120], o [5120, 6144]
@@ -301,15 +363,24 @@ def main(args, world, rank, local_rank):
     torch.cuda.synchronize()
     dist.barrier()
     l0 = h.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
+    step()
+    torch.cuda.synchronize()
+    launches = (h.launch_count() - l0) * args.steps
+    dist.barrier()
+    # Timed exactly as the single-GPU line: the K steps captured in one CUDA graph and replayed (a step's
+    # launches are shorter than the host's time to issue them); stream launches if the capture is refused.
+    timing = "one CUDA-graph replay of the K steps"
+    try:
+        if args.no_graph:
+            raise RuntimeError("--no-graph")
+        ms = bench.time_region(step, args.steps, torch, graph=True)
+    except Exception:
+        torch.cuda.synchronize()
+        timing = "K steps of stream launches"
+        ms = bench.time_region(step, args.steps, torch, graph=False)
     torch.cuda.synchronize()
     dist.barrier()
-    launches = h.launch_count() - l0
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    t = torch.tensor([ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
@@ -355,7 +426,11 @@ def main(args, world, rank, local_rank):
         attn_par = {"error": repr(e)}
     stream = run_tp_layer_stream(torch, dist, h, comm, dev, world)
     table = run_tp_mlp_table(torch, dist, lambda M: make_mlp_set(M, copies=(None if M <= 256 else 2)), H, dev, world,
-                             args.steps)
+                             args.steps, comm=comm)
+    try:
+        big_parity = full_size_parity(torch, dist, h, comm, dev, world, rank)
+    except Exception as e:
+        big_parity = {"error": repr(e)}
     if rank == 0:
         agg_peak = peaks["hbm_gbs"] * world
         line = {"metric": "decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
@@ -364,13 +439,13 @@ def main(args, world, rank, local_rank):
                 "config": {"workload": "configs[1] decode sweep M in {1,2,4,8,16} run as the configs[4] tensor-parallel MLP: "
                                        "gate_up 34816x5120 column-split, SwiGLU, down 5120x17408 row-split with the sum "
                                        "over the ranks fused into its kernel (FP32 pairs over peer memory; NCCL only above 16 tokens)",
-                           "parallelism": f"tp{world}", "l2": "MLP instances rotate; their shards exceed 2 x L2",
+                           "parallelism": f"tp{world}", "l2": "MLP instances rotate; their shards exceed 2 x L2", "timing": timing,
                            "global_scale": 1.0, "scale_sigma": 0.02},
                 "roofline": {"bound": "hbm", "kernel": "whole MLP forward (gate_up, SwiGLU, down + group reduction), aggregate over ranks",
                              "achieved": round(value, 1), "peak": agg_peak, "peak_source": peaks["source"], "unit": "GB/s",
                              "frac": round(value / agg_peak, 4), "traffic": None},
                 "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "tp_mlp": table, "parity": parity,
-                "tp_layer_stream": stream, "attn_parity": attn_par}
+                "tp_layer_stream": stream, "attn_parity": attn_par, "parity_full_size_above_16_tokens": big_parity}
         sys.stdout.flush()
         os.dup2(saved_stdout, 1)
         print(json.dumps(line), flush=True)

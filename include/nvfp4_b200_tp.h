@@ -39,6 +39,13 @@ int nvfp4_tp_unique_id(void* out_128_bytes);
 /* Collective over all ranks: ncclCommInitRank on the current device.  world == 1 needs no id. */
 int nvfp4_tp_comm_create(const void* unique_id_128_bytes, int rank, int world, nvfp4_tp_comm** out);
 int nvfp4_tp_comm_destroy(nvfp4_tp_comm* comm);
+/* How the partial sums travel where the library collective adds them (more than 16 tokens, or no
+ * attached exchange).  Default (0): unrounded FP32 partials -- ncclReduceScatter(FP32), the residual
+ * added and the result rounded once on each rank's slice, ncclAllGather(BF16): within 1e-3 of the
+ * unsplit layer at any group size.  1: the partials are rounded to BF16 first and summed by one
+ * ncclAllReduce(BF16), half the bytes on the wire but one rounding per rank in front of the sum
+ * (about 1.1e-3 / 1.4e-3 from the unsplit layer at 4 / 8 ranks).  Same value on every rank. */
+int nvfp4_tp_comm_set_bf16_partials(nvfp4_tp_comm* comm, int on);
 
 /* Builds this rank's shards from the FULL device-resident tensors (gate_up [2I, H] merged gate
  * rows then up rows, down [H, I]) and allocates the intermediate buffers for up to max_M

@@ -399,6 +399,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         int last = cta;                              // contributors are CTAs cta+1 .. last
         float pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         bool prefetched = complete;
+        bool need_clear = false;
         if (grp == 0 && owner && !complete)
             while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
         // The contributors' pairs for this thread's (up to four) outputs, added in CTA order (a fixed
@@ -442,11 +443,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             }
             return true;
         };
-        // Once a gather has been ACCEPTED (by the whole warp, for the early look): hand the slots back
-        // cleared.  The tag comes from the host and a captured CUDA graph replays it unchanged, so a pair
-        // left behind would look current to the next replay; a cleared slot cannot.  (Each pair has exactly
-        // one reader, this thread; the next launch's contributors write only after griddepcontrol.wait,
-        // when these stores have landed.)
+        // Once a gather has been ACCEPTED (by the whole warp, for the early look) the slots are handed back
+        // cleared, at the end of the segment.  The tag comes from the host and a captured CUDA graph replays
+        // it unchanged, so a pair left behind would look current to the next replay; a cleared slot cannot.
+        // (Each pair has exactly one reader, this thread; the next launch's contributors write only after
+        // griddepcontrol.wait, when these stores have landed.  Measured alternatives: a tag from a counter in
+        // the scratch costs one atomic per CTA on one address, +0.5 us per launch like these stores; the
+        // hardware's %gridid repeats from one replay of a graph to the next and cannot serve.)
         auto clear_pairs = [&]() {
             for (int c = cta + 1; c <= last; ++c) {
                 unsigned char* src = pairs + ((size_t)c * (kMaxTokens * kRT)) * 8;
@@ -475,7 +478,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 4; ++i) pre[i] = got[i];
                     prefetched = true;
-                    clear_pairs();
+                    need_clear = true;
                 }
             }
             if (grp < cnt) {
@@ -553,7 +556,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), p.epoch);
             } else {
                 if (!prefetched) {
-                    if (gather_pairs(pre, true)) clear_pairs();
+                    if (gather_pairs(pre, true)) need_clear = true;
                     __syncwarp();
                 }
                 const int row_base = tile * kRT;
@@ -588,6 +591,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 }
             }
         }
+        if (need_clear) clear_pairs();
         if (kc >= p.kchunks) { kc = 0; ++tile; }
     }
 

@@ -25,7 +25,11 @@
 //     CTA-wide step: contributors store their FP32 partials as 8-byte {value, launch epoch} pairs
 //     (one transaction each: the pair is its own arrival flag), the CTA that holds the row pair's
 //     first unit adds them in CTA order, applies 2^8 / global_scale and the residual in FP32 and
-//     rounds once.  Every wait is bounded and reports through the status word.
+//     rounds once.  The tag comes from a counter in the scratch (ptx.cuh: take_launch_epoch), not from
+//     the host, so a captured launch can be replayed.  (Clearing the pairs after use, as the 8-token
+//     kernel does, doubles this kernel's pair traffic: 16 tokens x 256 rows per contributor; measured
+//     +3.9 us on the down projection, against -0.3..-1.0 us for the counter.)  Every wait is bounded
+//     and reports through the status word.
 // Options shared with the 8-token kernel: the SwiGLU epilogue on row-interleaved gate/up weights and
 // the sum over a tensor-parallel group inside the kernel ({value, epoch} pairs pushed to every
 // rank's exchange buffer, reduced in rank order once the CTA has no weight left to stream).
@@ -75,7 +79,6 @@ struct WideParams {
     unsigned char* xpeer[xchg::kMaxWorld];
     int xrank, xworld, xslot_pairs;
     int swiglu_out;            // rows interleaved in slabs of 16 (8 gate rows, their 8 up rows): C is [M, N/2] = bf16(silu(gate) * up)
-    unsigned int epoch;
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -90,6 +93,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_scale + stages * kUnitScaleBytes);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
+    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_abort) + 1;   // 0 until consumer thread 0 has taken the tag
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     unsigned char* pairs = p.scratch + kPartialOffset;     // [CTA][16 tokens][256 rows] x {FP32 value, epoch}
@@ -106,6 +110,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
             ptx::mbar_init(&empty_bar[s], kConsumerWarps);    // every consumer warp releases every stage
         }
         *s_abort = 0;
+        *s_epoch = 0u;
         ptx::fence_mbar_init();
     }
     __syncthreads();
@@ -159,6 +164,11 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
     const int off_a = g * kActRowBytes + t * kActBlockBytes;   // token g (second tile: g + 8), 64-k block t; chunks at immediate offsets
 
     ptx::griddep_wait();          // outputs, residual, unscale and the cross-CTA scratch belong to earlier kernels until now
+    // This launch's tag for the split-tile pairs: thread 0 takes it from the counter in the scratch and
+    // leaves it in shared memory; the warps pick it up at their first segment epilogue, long after.
+    unsigned int epoch_taken = 0;
+    if (tid == 0) epoch_taken = ptx::take_launch_epoch(p.scratch);      // left in flight: parked at thread 0's first epilogue
+    unsigned int epoch = 0;
     unsigned int xepoch = 0, xset = 0;      // group reduction: this launch's epoch and slot set
     if (p.xworld > 0) {
         xepoch = *reinterpret_cast<volatile unsigned int*>(p.xpeer[p.xrank] + xchg::kEpochOff) + 1u;
@@ -237,6 +247,20 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
             while (last + 1 < G && (long long)(last + 1) * p.units / G < pair_end) ++last;
         const int row_base = pair * kUnitRows;
         const int rr[4] = {r0, r0, r0 + 8, r0 + 8};
+        if (tid == 0 && epoch_taken != 0u) {
+            *s_epoch = epoch_taken;
+            epoch_taken = 0u;
+        }
+        if (epoch == 0u && !(owner && complete)) {
+            const long long te0 = clock64();
+            while ((epoch = *s_epoch) == 0u) {
+                if (*s_abort || clock64() - te0 > ptx::kWaitBudgetClocks) {
+                    *s_abort = 1;
+                    atomicCAS(status, 0u, 0x640u);
+                    break;
+                }
+            }
+        }
         float v[kTT][4];
 #pragma unroll
         for (int j = 0; j < kTT; ++j)
@@ -253,7 +277,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int m = 8 * j + 2 * t + (i & 1);
-                    if (m < p.M) ptx::st_volatile_v2(slot + (m * kUnitRows + rr[i]) * 8, __float_as_uint(v[j][i]), p.epoch);
+                    if (m < p.M) ptx::st_volatile_v2(slot + (m * kUnitRows + rr[i]) * 8, __float_as_uint(v[j][i]), epoch);
                 }
         } else {
             // contributors in CTA order (a fixed summation order); the eight loads of one contributor
@@ -269,14 +293,14 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int m = 8 * j + 2 * t + (i & 1);
-                            x[j][i] = make_uint2(0u, p.epoch);
+                            x[j][i] = make_uint2(0u, epoch);
                             if (m < p.M) x[j][i] = ptx::ld_volatile_v2(src + (m * kUnitRows + rr[i]) * 8);
                         }
                     bool ready = true;
 #pragma unroll
                     for (int j = 0; j < kTT; ++j)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == p.epoch);
+                        for (int i = 0; i < 4; ++i) ready &= (x[j][i].y == epoch);
                     if (ready) {
 #pragma unroll
                         for (int j = 0; j < kTT; ++j)
@@ -292,18 +316,6 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_c
                     }
                 }
             }
-            // hand the slots back cleared: a replayed launch carries the same tag (decode_mma.cu explains)
-            if (!failed)
-                for (int c = cta + 1; c <= last; ++c) {
-                    unsigned char* src = pairs + (size_t)c * (kTokens * kUnitRows) * 8;
-#pragma unroll
-                    for (int j = 0; j < kTT; ++j)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int m = 8 * j + 2 * t + (i & 1);
-                            if (m < p.M) ptx::st_volatile_v2(src + (m * kUnitRows + rr[i]) * 8, 0u, 0u);
-                        }
-                }
             __syncwarp();
             if (p.swiglu_out) {
                 // the warp's slab is one gate/up slab: row r0 is a gate row (i = 0, 1), row r0 + 8 its up row
@@ -437,7 +449,6 @@ cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void
     int stages = (kSmemBudget - fixed) / kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
     p.stages = stages;
-    p.epoch = next_launch_tag();
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);

@@ -87,6 +87,7 @@ int nvfp4_tp_attn_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int q_rows
     if (e == cudaSuccess) e = cudaMemcpy2D(a->o_scale, (size_t)a->Kp / 16, os + (size_t)r * a->o_local / 16, (size_t)o_in / 16, (size_t)a->o_local / 16, H, cudaMemcpyDeviceToDevice);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { nvfp4_tp_attn_destroy(a); return (int)e; }
+    if (int st = nvfp4::tp::reserve_f32_partials(comm, max_M, H)) { nvfp4_tp_attn_destroy(a); return st; }
     *out = a;
     return NVFP4_OK;
 }

@@ -11,6 +11,12 @@
 struct nvfp4_tp_comm {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
+    // NCCL path of the row-split linear: FP32 partial sums [M, H] of the largest block created on this
+    // communicator (reduce-scattered in FP32, finished per slice, all-gathered as BF16); with
+    // bf16_partials the older form, one all-reduce of BF16-rounded partials, is used instead.
+    float* f32_scratch = nullptr;
+    size_t f32_bytes = 0;
+    int bf16_partials = 0;
 };
 
 // One rank's end of the peer exchange.  xbuf: this rank's buffer; peer[q]: rank q's buffer as
@@ -30,9 +36,14 @@ namespace tp {
 
 constexpr int kFusedMaxM = xchg::kMaxTokens;
 
+// Room for [max_M, H] FP32 partial sums on the communicator (grown at block-creation time, never in a forward).
+int reserve_f32_partials(nvfp4_tp_comm* comm, int max_M, int H);
+
 // C[M,H] = sum over ranks of A_r[M,K_r] * W_r[H,K_r]^T (+ residual), identical on every rank.
 // `d` describes this rank's share (A, shard, residual, C; optionally the strided / SwiGLU /
-// k_valid forms of nvfp4_linear_ex).  mode: 0 = NCCL, 1 = reduction inside the GEMV kernel,
+// k_valid forms of nvfp4_linear_ex).  mode: 0 = NCCL (FP32 partials: reduce-scatter, residual and the
+// one rounding on the rank's slice, all-gather; or, with comm->bf16_partials, one all-reduce of
+// BF16-rounded partials), 1 = reduction inside the GEMV kernel,
 // 2 = FP32 GEMV + stand-alone exchange kernel; 1 and 2 need an attached exchange and M <= 16.
 // Returns NVFP4_E_LIMIT when `d` uses nvfp4_linear_ex options and the fused path cannot take
 // it: the caller then materialises plain [M, K] activations and calls again.

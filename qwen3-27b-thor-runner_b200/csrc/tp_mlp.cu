@@ -75,6 +75,7 @@ int nvfp4_tp_mlp_create(nvfp4_handle* h, nvfp4_tp_comm* comm, int H, int I, cons
     if (e == cudaSuccess) e = cudaMemcpy2D(m->dn_scale, (size_t)m->Kp / 16, dns + (size_t)r * m->Ip / 16, (size_t)I / 16, (size_t)m->Ip / 16, H, cudaMemcpyDeviceToDevice);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { nvfp4_tp_mlp_destroy(m); return (int)e; }
+    if (int st = nvfp4::tp::reserve_f32_partials(comm, max_M, H)) { nvfp4_tp_mlp_destroy(m); return st; }
     if (int st = nvfp4_tp_exchange_create(comm, H, &m->own_x)) { nvfp4_tp_mlp_destroy(m); return st; }
     m->x = m->own_x;
     *out = m;

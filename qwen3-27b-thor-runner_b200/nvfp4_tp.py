@@ -20,6 +20,7 @@ TP_SIGNATURES = {
     "nvfp4_tp_unique_id": (c_int, [c_void_p]),
     "nvfp4_tp_comm_create": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p)]),
     "nvfp4_tp_comm_destroy": (c_int, [c_void_p]),
+    "nvfp4_tp_comm_set_bf16_partials": (c_int, [c_void_p, c_int]),
     "nvfp4_tp_mlp_create": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                     c_float, c_int, ctypes.POINTER(c_void_p)]),
     "nvfp4_tp_mlp_destroy": (c_int, [c_void_p]),
@@ -135,6 +136,13 @@ class Comm:
         if st:
             raise nvfp4.Nvfp4Error(st)
         self.c, self.rank, self.world = c, rank, world
+
+    def set_bf16_partials(self, on):
+        """NCCL path of the row-split linears: False (default) = FP32 partials (reduce-scatter, finish on
+        the rank's slice, all-gather), True = one all-reduce of BF16-rounded partials."""
+        st = self.lib.nvfp4_tp_comm_set_bf16_partials(self.c, int(bool(on)))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
 
     def close(self):
         if getattr(self, "c", None):
