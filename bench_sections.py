@@ -119,9 +119,23 @@ def layer_stream(h, SHAPES, peaks, torch, alg_bytes, layers=64):
         ms = bench.time_region(token_step, 3, torch, graph=True)
         nbytes = layers * sum(alg_bytes(*SHAPES[n], M) for n in names)
         gbs = nbytes / (ms * 1e-3) / 1e9
-        res.append({"M": M, "ms_per_token_step": round(ms, 4), "GBps": round(gbs, 1),
-                    "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBps": round(gbs / 8000.0, 4),
-                    "launch_mode": "CUDA-graph replay of 3 token-steps (768 launches)"})
+        row = {"M": M, "ms_per_token_step": round(ms, 4), "GBps": round(gbs, 1),
+               "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4), "frac_of_8TBps": round(gbs / 8000.0, 4),
+               "launch_mode": "CUDA-graph replay of 3 token-steps (768 launches)"}
+        # the same 256 linears as ONE launch: nvfp4_chain (grid-wide barrier between linears, the loader
+        # streaming the next linear's weights across it)
+        import nvfp4
+        chain = nvfp4.Chain(h, [dict(A=acts[n], M=M, packed=ws[l][n][0], scale=ws[l][n][1], N=SHAPES[n][0], K=SHAPES[n][1], C=outs[n])
+                                for l in range(layers) for n in names])
+        chain.run()
+        torch.cuda.synchronize()
+        ms_c = bench.time_region(chain.run, 3, torch, graph=True)
+        chain.close()
+        gbs_c = nbytes / (ms_c * 1e-3) / 1e9
+        row.update({"chain_ms_per_token_step": round(ms_c, 4), "chain_GBps": round(gbs_c, 1),
+                    "chain_frac_of_measured_hbm": round(gbs_c / peaks["hbm_gbs"], 4),
+                    "chain_launch_mode": "one nvfp4_chain launch per token-step (256 linears), CUDA-graph replay of 3"})
+        res.append(row)
     del ws
     torch.cuda.empty_cache()
     return res
@@ -171,11 +185,26 @@ def mlp_block(h, shapes, rot, torch, tokens=(1, 2, 4, 8)):
             h.linear_ex(X, M, p1, s1, 1.0, N1, K1, act, norm_weight=w, norm_eps=1e-6, swiglu_epilogue=True)
             h.linear(act, M, p2, s2, 1.0, N2, K2, Y, residual=X)
 
+        # the same two linears as one launch (nvfp4_chain), one chain per pairing of the rotating weight copies
+        import nvfp4
+        nch = max(rot["gate_up"].n, rot["down"].n)
+        chains = [nvfp4.Chain(h, [dict(A=X, M=M, packed=rot["gate_up"].w[i % rot["gate_up"].n][0], scale=rot["gate_up"].w[i % rot["gate_up"].n][1],
+                                       N=N1, K=K1, C=act, norm_weight=w, norm_eps=1e-6, swiglu_epilogue=True),
+                                  dict(A=act, M=M, packed=rot["down"].w[i % rot["down"].n][0], scale=rot["down"].w[i % rot["down"].n][1],
+                                       N=N2, K=K2, C=Y, residual=X)]) for i in range(nch)]
+        state = {"i": 0}
+
+        def chained():
+            state["i"] = (state["i"] + 1) % nch
+            chains[state["i"]].run()
+
         row = {"M": M}
         for name, fn in (("ms_four_launches", separate), ("ms_fused_prologues", fused),
-                         ("ms_norm_prologue_swiglu_epilogue", fused_epilogue)):
+                         ("ms_norm_prologue_swiglu_epilogue", fused_epilogue), ("ms_chain_one_launch", chained)):
             fn(); fn()
             row[name] = round(bench.time_region(fn, 6, torch, graph=True), 5)
+        for c in chains:
+            c.close()
         out.append(row)
     return out
 

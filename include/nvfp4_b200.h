@@ -199,6 +199,28 @@ typedef struct nvfp4_linear_desc {
 } nvfp4_linear_desc;
 int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* desc, nvfp4_stream_t stream);
 
+/* A chain: a fixed sequence of linears, each with up to 8 tokens and K % 256 == 0 and any of the options of
+ * nvfp4_linear_desc, executed in order by ONE launch of the GEMV kernel.  Linear i+1 may read what linear i
+ * wrote (the activations, the residual stream): between two linears all CTAs meet at a grid-wide barrier
+ * in device memory.  Meanwhile the kernel's loader keeps streaming the next linear's weights into its
+ * shared-memory ring -- weights depend on nothing -- so HBM does not idle across the launch boundaries a
+ * sequence of nvfp4_linear calls would have, and the per-launch cost is paid once.  The reference runs
+ * one kernel per projection (src/engine/layer.cu:62-110, 190-217, 404-409): a decode layer's sequence
+ * o-projection + residual -> RMSNorm -> gate_up -> SwiGLU -> down + residual, or all layers of a token
+ * step, is one chain here.
+ * The descriptors are read at creation: pointers, shapes and options are frozen into the chain (buffers
+ * are fixed, their contents change from run to run, as in a captured decode step).  A run adds one launch;
+ * it may be captured in a CUDA graph and replayed (the barrier and the split-tile tags count in device
+ * memory, nothing comes from the host).  All CTAs of the launch must be resident at the same time: the
+ * grid is one CTA per SM, so nothing else may occupy whole SMs of the device for the duration; a barrier
+ * that is not met within about a second sets the handle's status word (0x9xx) and the launch winds down.
+ * NVFP4_E_LIMIT: a linear the 8-token kernel does not take, or activations that leave no room for the ring.
+ * No reference counterpart. */
+typedef struct nvfp4_chain nvfp4_chain;
+int nvfp4_chain_create(nvfp4_handle* h, const nvfp4_linear_desc* descs, int n, nvfp4_chain** out);
+int nvfp4_chain_run(nvfp4_chain* chain, nvfp4_stream_t stream);
+int nvfp4_chain_destroy(nvfp4_chain* chain);
+
 /* Two linears sharing A: C1 = A*W1^T, C2 = A*W2^T, both [N,K].
  * Replaces invoke_fp4_dual_gemv (:395-416), generalised to any M. */
 int nvfp4_linear_dual(nvfp4_handle* h, const void* A_bf16, int M,

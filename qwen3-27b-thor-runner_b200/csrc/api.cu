@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "nvfp4_internal.h"
 
@@ -236,6 +237,7 @@ int nvfp4_create(int device, size_t workspace_bytes, nvfp4_handle** out) {
         return (int)e;
     }
     h->workspace_bytes = workspace_bytes;
+    h->dev.maps = new TensorMapCache();
     *out = h;
     return NVFP4_OK;
 }
@@ -247,6 +249,7 @@ int nvfp4_destroy(nvfp4_handle* h) {
     cudaSetDevice(h->dev.device);
     cudaError_t e = cudaFree(h->workspace);
     cudaSetDevice(prev);
+    delete h->dev.maps;
     delete h;
     return cuda_status(e);
 }
@@ -351,7 +354,8 @@ int nvfp4_linear_reduce_peers(nvfp4_handle* h, const void* A, int M, const uint8
     return run_linear(h, a, stream);
 }
 
-int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t stream) {
+// Validation of a descriptor and its translation into the kernels' argument record.
+static int desc_to_args(nvfp4_handle* h, const nvfp4_linear_desc* d, LinearArgs* out) {
     if (!d) return NVFP4_E_NULL;
     if (int e = validate_linear(h, d->A, d->M, d->packed, d->scale, d->global_scale, d->N, d->K, d->residual, d->C,
                                 d->swiglu_epilogue ? d->N / 2 : 0))
@@ -386,7 +390,6 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
             if (!d->px->peer[q] || (reinterpret_cast<uintptr_t>(d->px->peer[q]) & 15u)) return NVFP4_E_NULL;
         if ((long long)d->M * d->N > d->px->slot_pairs) return NVFP4_E_LIMIT;
     }
-    if (d->M == 0) return NVFP4_OK;
     LinearArgs a{d->A, d->packed, d->scale, 1.0f / d->global_scale, d->residual, d->C, d->M, d->N, d->K};
     a.px = d->px;
     a.swiglu_up = d->swiglu_up;
@@ -396,7 +399,63 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t 
     a.norm_eps = d->norm_eps;
     a.swiglu_out = d->swiglu_epilogue != 0;
     if (!a.px && !a.swiglu_up && stride == d->K && k_valid == d->K) { a.a_stride = 0; a.k_valid = 0; }   // the plain call
+    *out = a;
+    return NVFP4_OK;
+}
+
+int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* d, nvfp4_stream_t stream) {
+    LinearArgs a{};
+    if (int e = desc_to_args(h, d, &a)) return e;
+    if (d->M == 0) return NVFP4_OK;
     return run_linear(h, a, stream);
+}
+
+struct nvfp4_chain {
+    nvfp4_handle* h = nullptr;
+    nvfp4::DecodeChain* c = nullptr;
+    std::vector<nvfp4_peer_exchange> px;     // copies of the descriptors' exchanges (the kernel parameters keep only the pointers inside)
+    int n = 0;
+};
+
+int nvfp4_chain_create(nvfp4_handle* h, const nvfp4_linear_desc* descs, int n, nvfp4_chain** out) {
+    if (!h || !descs || !out) return NVFP4_E_NULL;
+    *out = nullptr;
+    if (n < 1 || n > 4096) return NVFP4_E_SHAPE;
+    std::vector<LinearArgs> args((size_t)n);
+    for (int l = 0; l < n; ++l) {
+        if (int e = desc_to_args(h, &descs[l], &args[l])) return e;
+        if (descs[l].M < 1 || descs[l].M > 8) return NVFP4_E_LIMIT;
+    }
+    if (decode_mma_scratch_bytes(args[0], h->dev) > h->workspace_bytes) return NVFP4_E_WORKSPACE;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if (cudaSetDevice(h->dev.device) != cudaSuccess) return NVFP4_E_DEVICE;
+    nvfp4_chain* c = new nvfp4_chain();
+    c->h = h;
+    c->n = n;
+    const int st = create_decode_chain(args.data(), n, h->dev, h->workspace, &c->c);
+    cudaSetDevice(prev);
+    if (st != NVFP4_OK) { delete c; return st; }
+    *out = c;
+    return NVFP4_OK;
+}
+
+int nvfp4_chain_run(nvfp4_chain* c, nvfp4_stream_t stream) {
+    if (!c || !c->c) return NVFP4_E_NULL;
+    cudaError_t e = launch_decode_chain(c->c, stream);
+    c->h->launches += 1;
+    return cuda_status(e);
+}
+
+int nvfp4_chain_destroy(nvfp4_chain* c) {
+    if (!c) return NVFP4_E_NULL;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(c->h->dev.device);
+    destroy_decode_chain(c->c);
+    cudaSetDevice(prev);
+    delete c;
+    return NVFP4_OK;
 }
 
 int nvfp4_linear_dual(nvfp4_handle* h, const void* A, int M, const uint8_t* packed1, const uint8_t* scale1,

@@ -40,12 +40,14 @@
 #include <cuda_bf16.h>
 
 #include <mutex>
+#include <vector>
 
 #include "exchange_layout.h"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "gemv_common.cuh"
 #include "ptx.cuh"
+#include "umma.cuh"
 
 namespace nvfp4 {
 namespace {
@@ -87,11 +89,50 @@ struct DecodeParams {
     unsigned char* xpeer[xchg::kMaxWorld];
     int xrank, xworld, xslot_pairs;
 };
+static_assert(sizeof(DecodeParams) % 8 == 0, "DecodeParams is copied in 8-byte pieces");
 
-template <int GROUPS>
+// A chain: several linears run by ONE launch of the kernel, in order (see nvfp4_chain_run).  The
+// per-linear parameters and tensor maps sit in device memory; p0 of the kernel carries what all
+// linears share (ring depth, the size of the activation area).
+struct ChainArgs {
+    const DecodeParams* params;      // [n]
+    const CUtensorMap* maps;         // [2 n]: packed codes, block scales
+    unsigned long long* counter;     // arrivals of all launches of this chain: + gridDim.x per linear
+    int n;
+    int act_bytes;                   // resident-activation area: the largest of the linears
+};
+
+// Inside a chain a linear reads what an earlier linear of the same launch wrote from another SM: those
+// loads go to L2 (this SM's L1 may still hold the buffer's lines from an earlier read); a single linear
+// keeps the read-only path.
+template <bool CHAIN>
+__device__ __forceinline__ uint4 ld_act(const uint4* p) { return CHAIN ? __ldcg(p) : __ldg(p); }
+template <bool CHAIN>
+__device__ __forceinline__ float ld_res(const __nv_bfloat16* p) {
+    if (CHAIN) return __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(p)) << 16);
+    return __bfloat162float(*p);
+}
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// CHAIN = false: one linear, parameters in the kernel's own parameter space (nvfp4_linear and its
+// variants).  CHAIN = true: ch.n linears one after the other in the same launch.  The producer lane
+// walks straight on into the next linear's weights (they depend on nothing), so HBM keeps streaming
+// into the ring while the consumer warps finish a linear, meet the other CTAs at a grid-wide barrier
+// (the next linear reads what this one wrote) and stage the next activations.  The barrier is a
+// 64-bit arrival counter in device memory: every CTA adds one per linear, so a launch adds
+// gridDim.x * n in all and the counter's value modulo that is where the current launch began --
+// nothing comes from the host, a captured launch can be replayed.  The same launch number tags the
+// split-tile pairs, which live in a region of the chain's own.  All CTAs must be resident at once
+// (the grid is one CTA per SM); every wait is bounded.
+template <int GROUPS, bool CHAIN>
 __global__ void __launch_bounds__((kGroupWarps * GROUPS + 1) * 32, 3 - GROUPS)
-decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
-                  const DecodeParams p) {
+decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed0, const __grid_constant__ CUtensorMap tm_scale0,
+                  const __grid_constant__ DecodeParams p0, const __grid_constant__ ChainArgs ch) {
     constexpr int kConsumerWarps = kGroupWarps * GROUPS;
     constexpr int kConsumerThreads = kConsumerWarps * 32;
     constexpr int kThreads = kConsumerThreads + 32;   // + producer warp
@@ -100,25 +141,30 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // address space, so every access below is a shared-memory instruction with a 32-bit address
     // (rounding a generic 64-bit pointer instead turns them into generic loads and stores).
     unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
-    const int stages = p.stages;
+    const int stages = p0.stages;
     unsigned char* s_packed = smem;                                       // stages x GROUPS x 16 KB, 1024-aligned
     unsigned char* s_scale = s_packed + stages * GROUPS * kPackedBytes;   // stages x GROUPS x 2 KB
     unsigned char* s_act = s_scale + stages * GROUPS * kScaleBytes;       // slots x M x 512 B of FP16
-    float* s_out = reinterpret_cast<float*>(s_act + p.act_slots * p.M * kActRowBytes);   // 2 FP32 exchange tiles
+    float* s_out = reinterpret_cast<float*>(s_act + (CHAIN ? ch.act_bytes : p0.act_slots * p0.M * kActRowBytes));   // 2 FP32 exchange tiles
     float* s_tokscale = s_out + 2 * kMaxTokens * kOutLd;                  // [0..7] scale, [8..15] 1/scale per token
     unsigned int* s_amax = reinterpret_cast<unsigned int*>(s_tokscale + 16);   // [0..7] largest |activation| bits per token
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_amax + 16);
     uint64_t* empty_bar = full_bar + kMaxStages;
     volatile int* s_abort = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
+    unsigned long long* s_chain_base = reinterpret_cast<unsigned long long*>(const_cast<int*>(s_abort) + 4);   // [0] counter at launch start
+    DecodeParams* s_params = reinterpret_cast<DecodeParams*>(s_chain_base + 2);   // CHAIN: the current linear's parameters (16-byte aligned)
 
-    unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
-    unsigned char* pairs = p.pairs;
+    unsigned int* status = reinterpret_cast<unsigned int*>(p0.scratch);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cta = blockIdx.x, G = gridDim.x;
-    const int u_begin = (int)((long long)cta * p.units / G);     // half-units [u_begin, u_end) of this CTA
-    const int u_end = (int)((long long)(cta + 1) * p.units / G);
-    const int kc_begin = (int)(u_begin % p.kchunks);
+    const int n_linears = CHAIN ? ch.n : 1;
+    // This CTA's half-units [u_begin, u_end) of the first (or only) linear: worked out before the waits below.
+    // A chain's grid may exceed a linear's half-units: the first Ge CTAs share them, the others idle through it.
+    int Ge = CHAIN && p0.units < G ? p0.units : G;
+    int u_begin = cta < Ge ? (int)((long long)cta * p0.units / Ge) : 0;
+    int u_end = cta < Ge ? (int)((long long)(cta + 1) * p0.units / Ge) : 0;
+    int kc_begin = (int)(u_begin % p0.kchunks);
 
     // The producer lane sets the ring up itself and starts streaming weights at once; the
     // consumers meet it at named barrier 2 (they need the initialised mbarriers, it needs nothing
@@ -138,16 +184,27 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp
         if (lane == 0) {
-            ptx::prefetch_tensormap(&tm_packed);
-            ptx::prefetch_tensormap(&tm_scale);
             const uint64_t pol_stream = ptx::policy_evict_first();
             int stage = 0;
             uint32_t ph = 0;
+          for (int l = 0; l < n_linears; ++l) {
+            const CUtensorMap& tm_packed = CHAIN ? ch.maps[2 * l] : tm_packed0;
+            const CUtensorMap& tm_scale = CHAIN ? ch.maps[2 * l + 1] : tm_scale0;
+            const DecodeParams& p = CHAIN ? ch.params[l] : p0;
+            ptx::prefetch_tensormap(&tm_packed);
+            ptx::prefetch_tensormap(&tm_scale);
+            const int p_units = p.units, p_kchunks = p.kchunks;
+            if (CHAIN && l > 0) {
+                Ge = p_units < G ? p_units : G;
+                u_begin = cta < Ge ? (int)((long long)cta * p_units / Ge) : 0;
+                u_end = cta < Ge ? (int)((long long)(cta + 1) * p_units / Ge) : 0;
+                kc_begin = (int)(u_begin % p_kchunks);
+            }
             int hu = u_begin;
-            int tile = (int)(u_begin / p.kchunks);
+            int tile = (int)(u_begin / p_kchunks);
             int kc = kc_begin;                                // k-chunk of hu inside its row tile
             while (hu < u_end) {
-                const int tile_end = hu - kc + p.kchunks;
+                const int tile_end = hu - kc + p_kchunks;
                 const int seg_end = tile_end < u_end ? tile_end : u_end;
                 const int row0 = tile * kRT;
                 while (hu < seg_end) {
@@ -165,8 +222,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     kc += cnt;
                     if (++stage == stages) { stage = 0; ph ^= 1u; }
                 }
-                if (kc >= p.kchunks) { kc = 0; ++tile; }
+                if (kc >= p_kchunks) { kc = 0; ++tile; }
             }
+          }
         }
         return;
     }
@@ -179,15 +237,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     const int off_w0 = r0 * 128 + (((2 * t) ^ g) << 4);       // row r0, logical 16-byte chunk 2t   (swizzle: chunk ^ (row & 7))
     const int off_w1 = r0 * 128 + (((2 * t + 1) ^ g) << 4);   // row r0, chunk 2t+1
     const int off_s = r0 * 16 + 4 * t;                         // 4 scale bytes: blocks 4t..4t+3 of the row
-    const int tok = g < p.M ? g : 0;                           // token feeding MMA column g (columns >= M are never stored)
 
     // Programmatic dependent launch: the next kernel of the stream may start its own weight
     // streaming while this grid drains; whatever depends on the previous grid (activations,
     // residual, the outputs and the cross-CTA scratch) is only touched after griddep_wait().
     ptx::griddep_launch_dependents();
-    if (tid < 16) s_amax[tid] = 0u;
+    if (!CHAIN && tid < 16) s_amax[tid] = 0u;
     ptx::named_barrier_sync(2, kThreads);            // mbarriers initialised (the producer only arrives)
-    ptx::named_barrier_sync(1, kConsumerThreads);
+    if (!CHAIN) ptx::named_barrier_sync(1, kConsumerThreads);
 
     // Resident activations.  Chunk id = (slot * M + token) * 32 + c names 8 consecutive k of one
     // token; every thread takes ids tid, tid + 512, ... four at a time so that the loads overlap.
@@ -197,8 +254,58 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     // and never overflows.  Pass B converts and stores in natural k order.  The scale is undone in
     // FP32 in the epilogue.
     ptx::griddep_wait();
+    int stage = 0;
+    uint32_t ph = 0;
+    unsigned long long chain_base = 0;       // CHAIN: the arrival counter's value where this launch began
+    if (CHAIN) {
+        // No CTA passes the first barrier before this one has arrived there, so at most gridDim.x - 1
+        // arrivals of this launch are in the value read here: rounding down to a multiple of a launch's
+        // total gives the launch's starting point, the same in every CTA.
+        if (tid == 0) {
+            const unsigned long long v = ld_acquire_gpu_u64(ch.counter);
+            const unsigned long long per_launch = (unsigned long long)G * (unsigned long long)n_linears;
+            s_chain_base[0] = v - v % per_launch;
+        }
+    }
+  for (int l = 0; l < n_linears; ++l) {
+    if (CHAIN) {
+        // this linear's parameters into shared memory; the previous linear is behind a CTA-wide barrier
+        if (tid < (int)(sizeof(DecodeParams) / 8))
+            reinterpret_cast<uint2*>(s_params)[tid] = __ldg(reinterpret_cast<const uint2*>(ch.params + l) + tid);
+        if (tid < 16) s_amax[tid] = 0u;
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        chain_base = s_chain_base[0];
+        if (l > 0) {
+            // Grid-wide barrier: every CTA has stored its share of the previous linear's outputs (it arrives
+            // behind a CTA barrier and a fence), and this linear may read them.  Thread 0 polls, the others
+            // wait for it at the CTA barrier.  Bounded: a CTA that is not resident would otherwise hang us.
+            if (tid == 0) {
+                const unsigned long long target = chain_base + (unsigned long long)G * (unsigned long long)l;
+                const long long t0 = clock64();
+                while (ld_acquire_gpu_u64(ch.counter) < target) {
+                    if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
+                        *s_abort = 1;
+                        atomicCAS(status, 0u, 0x900u + (unsigned)(l & 0xFF));
+                        break;
+                    }
+                }
+            }
+            ptx::named_barrier_sync(1, kConsumerThreads);
+        }
+    }
+    const DecodeParams& p = CHAIN ? *s_params : p0;
+    unsigned char* pairs = p.pairs;
+    // CHAIN: (number of linears all launches of this chain have run before this one) * 2 + 1: odd, never 0, new for every linear of every launch
+    const unsigned int epoch = CHAIN ? (unsigned int)((chain_base / (unsigned long long)G) + (unsigned long long)l) * 2u + 1u : p.epoch;
+    const int tok = g < p.M ? g : 0;                           // token feeding MMA column g (columns >= M are never stored)
+    if (CHAIN && l > 0) {
+        Ge = p.units < G ? p.units : G;
+        u_begin = cta < Ge ? (int)((long long)cta * p.units / Ge) : 0;
+        u_end = cta < Ge ? (int)((long long)(cta + 1) * p.units / Ge) : 0;
+        kc_begin = (int)(u_begin % p.kchunks);
+    }
     // Group reduction: this launch's epoch and slot set (the counter was advanced by the previous
-    // launch that used the buffer, which has completed by now).
+    // launch -- or the previous linear of this chain -- that used the buffer, which has completed by now).
     unsigned int xepoch = 0, xset = 0;
     if (p.xworld > 0) {
         xepoch = *reinterpret_cast<volatile unsigned int*>(p.xpeer[p.xrank] + xchg::kEpochOff) + 1u;
@@ -226,7 +333,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 if (id < total) {
                     tk[u] = id / row_chunks;
                     const int c = id - tk[u] * row_chunks;
-                    x[u] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)tk[u] * p.a_stride) + c);
+                    x[u] = ld_act<CHAIN>(reinterpret_cast<const uint4*>(p.A + (size_t)tk[u] * p.a_stride) + c);
                     w[u] = __ldg(reinterpret_cast<const uint4*>(p.norm_w) + c);
                 }
             }
@@ -295,7 +402,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 if (id < total) {
                     int j, c;
                     const uint4* src = chunk_src(id, j, tk[u], c);
-                    if (src) x[u] = __ldg(src);
+                    if (src) x[u] = ld_act<CHAIN>(src);
                     dst[u] = src ? (j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c) : -2 - ((j * p.M + tk[u]) * kActRowBytes + act_chunk_offset(c));
                 }
             }
@@ -312,7 +419,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                         const int id = base + (h4 + u) * kConsumerThreads;
                         if (id < total && dst[h4 + u] >= 0) {
                             int j, tkk, c;
-                            y[u] = __ldg(chunk_src(id, j, tkk, c) + up_off);
+                            y[u] = ld_act<CHAIN>(chunk_src(id, j, tkk, c) + up_off);
                         }
                     }
 #pragma unroll
@@ -377,8 +484,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         ptx::named_barrier_sync(1, kConsumerThreads);
     }
 
-    int stage = 0;
-    uint32_t ph = 0;
     int hu = u_begin;
     int tile = u_begin / p.kchunks;
     int kc = kc_begin;                                         // k-chunk of hu inside its row tile
@@ -401,7 +506,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         bool prefetched = complete;
         bool need_clear = false;
         if (grp == 0 && owner && !complete)
-            while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
+            while (last + 1 < Ge && (long long)(last + 1) * p.units / Ge < tile_end) ++last;
         // The contributors' pairs for this thread's (up to four) outputs, added in CTA order (a fixed
         // summation order).  Two contributors at a time: their eight loads are issued before any
         // is looked at, so they share one L2 round trip.  blocking: wait (bounded) for pairs that
@@ -417,7 +522,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            v[j][i] = make_uint2(0u, p.epoch);
+                            v[j][i] = make_uint2(0u, epoch);
                             if (mm[i] < p.M && (j == 0 || two))
                                 v[j][i] = ptx::ld_volatile_v2(src + ((size_t)j * (kMaxTokens * kRT) + mm[i] * kRT + rr[i]) * 8);
                         }
@@ -425,7 +530,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == p.epoch);
+                        for (int i = 0; i < 4; ++i) ready &= (v[j][i].y == epoch);
                     if (ready) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
@@ -553,7 +658,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 unsigned char* slot = pairs + (size_t)cta * (kMaxTokens * kRT) * 8;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), p.epoch);
+                    if (mm[i] < p.M) ptx::st_volatile_v2(slot + (mm[i] * kRT + rr[i]) * 8, __float_as_uint(v[i]), epoch);
             } else {
                 if (!prefetched) {
                     if (gather_pairs(pre, true)) need_clear = true;
@@ -586,12 +691,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                             ptx::st_volatile_v2(p.xpeer[q] + xchg::kSlotsOff + pair * 8, __float_as_uint(x), xepoch);
                         continue;
                     }
-                    if (p.residual) x += __bfloat162float(p.residual[o]);
+                    if (p.residual) x += ld_res<CHAIN>(p.residual + o);
                     p.C[o] = __float2bfloat16_rn(x);
                 }
             }
         }
-        if (need_clear) clear_pairs();
+        if (!CHAIN && need_clear) clear_pairs();      // a chain's tags come from the device and never repeat
         if (kc >= p.kchunks) { kc = 0; ++tile; }
     }
 
@@ -623,7 +728,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 sum += __uint_as_float(v.x);
             }
             if (failed) break;
-            if (p.residual) sum += __bfloat162float(p.residual[e]);
+            if (p.residual) sum += ld_res<CHAIN>(p.residual + e);
             p.C[e] = __float2bfloat16_rn(sum);
         }
         // the last CTA to get here advances the launch counter for the next launch
@@ -637,37 +742,25 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             }
         }
     }
+    if (CHAIN) {
+        // This CTA's share of linear l is stored: arrive at the grid-wide barrier (every linear, the last
+        // one too: a launch always adds gridDim.x * n to the counter).  The CTA barrier orders every
+        // thread's stores before thread 0's fence and arrival.
+        ptx::named_barrier_sync(1, kConsumerThreads);
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(ch.counter, 1ull);
+        }
+    }
+  }   // linears
 }
 
 // ------------------------------------------------------------------------------------ host side
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode() {
-    static EncodeFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeFn>(p);
-    }
-    return fn;
-}
-
-bool make_u8_map(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
+// Tensor maps of a weight's packed codes and block scales (uint8, 128 rows per box).
+bool make_u8_map(TensorMapCache* cache, CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint32_t box_cols,
                  uint32_t box_rows, CUtensorMapSwizzle sw) {
-    EncodeFn enc = get_encode();
-    if (!enc) return false;
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {pitch};
-    const cuuint32_t box[2] = {box_cols, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return umma::make_map_cached(cache, m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, cols, rows, box_cols, box_rows, sw);
 }
 
 }  // namespace
@@ -684,7 +777,9 @@ size_t decode_mma_scratch_bytes(const LinearArgs&, const nvfp4_device_info& dev)
 }
 
 cudaError_t configure_decode_mma() {
-    return cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_mma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
 }
 
 namespace {
@@ -696,8 +791,11 @@ struct DecodePlan {
     int grid, smem, groups;
 };
 
+constexpr int kFixedSmem = 1024 + 2 * kMaxTokens * kOutLd * 4 + 128 + 2 * kMaxStages * 8 + 32 + 16 + (int)sizeof(DecodeParams) + 16;
+
+// force_grid: a chain runs every linear on the same grid, also one with fewer half-units than CTAs.
 bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, void* scratch, size_t pairs_offset,
-                        DecodePlan* out) {
+                        DecodePlan* out, bool force_grid = false) {
     DecodeParams p{};
     p.A = static_cast<const __nv_bfloat16*>(a.A);
     p.A_up = static_cast<const __nv_bfloat16*>(a.swiglu_up);
@@ -723,8 +821,8 @@ bool plan_decode_groups(const LinearArgs& a, int m, int groups, int grid_cap, vo
     const long long tiles = (a.N + kRT - 1) / kRT;
     p.units = (int)(tiles * p.kchunks);
     int grid = grid_cap < kMaxGrid ? grid_cap : kMaxGrid;
-    if (grid > p.units) grid = p.units;
-    const int fixed = 1024 + 2 * kMaxTokens * kOutLd * 4 + 128 + 2 * kMaxStages * 8 + 64;
+    if (grid > p.units && !force_grid) grid = p.units;
+    const int fixed = kFixedSmem;
     const int stage_w = groups * (kPackedBytes + kScaleBytes);
     const int budget = groups == 2 ? kSmemBudget : kSmemBudgetHalf;
     const int max_span = (p.units + grid - 1) / grid;
@@ -763,10 +861,8 @@ bool decode_mma_fits(const LinearArgs& a, const nvfp4_device_info& dev) { return
 cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
                               cudaStream_t s) {
     CUtensorMap tmp, tms;
-    if (!make_u8_map(&tmp, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, (uint64_t)a.K / 2, 128, kRT,
-                     CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_u8_map(&tms, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, (uint64_t)a.K / 16, 16, kRT,
-                     CU_TENSOR_MAP_SWIZZLE_NONE))
+    if (!make_u8_map(dev.maps, &tmp, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_u8_map(dev.maps, &tms, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kRT, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     const int per = decode_tokens_per_launch(a, dev);
     if (per <= 0) return cudaErrorInvalidValue;
@@ -792,12 +888,101 @@ cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void*
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<2>, tmp, tms, pl.p);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mma_kernel<2, false>, tmp, tms, pl.p, ChainArgs{});
         ++n;
         if (e != cudaSuccess) { if (launches) *launches = n; return e; }
     }
     if (launches) *launches = n;
     return cudaSuccess;
+}
+
+}  // namespace nvfp4
+
+// ----------------------------------------------------------------------------------------------
+// Chains: a fixed sequence of linears (up to 8 tokens each) run by one launch of the kernel.
+namespace nvfp4 {
+
+struct DecodeChain {
+    unsigned char* dev = nullptr;      // counter | parameters | tensor maps | split-tile pairs
+    DecodeParams p0{};
+    ChainArgs ch{};
+    CUtensorMap map0, map1;            // stand-ins for the kernel's own map parameters (unused by a chain)
+    int grid = 0, smem = 0, n = 0;
+};
+
+void destroy_decode_chain(DecodeChain* c) {
+    if (!c) return;
+    cudaFree(c->dev);
+    delete c;
+}
+
+// status: NVFP4_OK, NVFP4_E_LIMIT (a linear the 8-token kernel does not take, or activations that leave
+// no room for the ring), or a CUDA error code.
+int create_decode_chain(const LinearArgs* linears, int n, const nvfp4_device_info& dev, void* scratch, DecodeChain** out) {
+    *out = nullptr;
+    if (n < 1 || n > 4096) return NVFP4_E_SHAPE;
+    const int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
+    std::vector<DecodeParams> params((size_t)n);
+    std::vector<CUtensorMap> maps((size_t)2 * n);
+    long long act_max = 0;
+    for (int l = 0; l < n; ++l) {
+        const LinearArgs& a = linears[l];
+        if (a.M < 1 || a.M > kMaxTokens || !decode_mma_supported(a)) return NVFP4_E_LIMIT;
+        DecodePlan pl;
+        if (!plan_decode_groups(a, a.M, 2, grid, scratch, 0, &pl, true)) return NVFP4_E_LIMIT;
+        params[l] = pl.p;
+        const long long act = (long long)pl.p.act_slots * a.M * kActRowBytes;
+        act_max = act > act_max ? act : act_max;
+        if (!make_u8_map(nullptr, &maps[2 * l], a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT, CU_TENSOR_MAP_SWIZZLE_128B) ||
+            !make_u8_map(nullptr, &maps[2 * l + 1], a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kRT, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return (int)cudaErrorInvalidValue;
+    }
+    const int stage_w = 2 * (kPackedBytes + kScaleBytes);
+    long long stages = (kSmemBudget - kFixedSmem - act_max) / stage_w;
+    if (stages < 3) return NVFP4_E_LIMIT;
+    if (stages > kMaxStages) stages = kMaxStages;
+    const size_t off_params = 256;
+    const size_t off_maps = (off_params + (size_t)n * sizeof(DecodeParams) + 127) / 128 * 128;
+    const size_t off_pairs = (off_maps + (size_t)2 * n * sizeof(CUtensorMap) + 255) / 256 * 256;
+    const size_t bytes = off_pairs + (size_t)grid * kMaxTokens * kRT * 8;
+    DecodeChain* c = new DecodeChain();
+    cudaError_t e = cudaMalloc((void**)&c->dev, bytes);
+    if (e == cudaSuccess) e = cudaMemset(c->dev, 0, bytes);
+    for (int l = 0; l < n; ++l) {
+        params[l].stages = (int)stages;
+        params[l].pairs = c->dev ? c->dev + off_pairs : nullptr;
+        params[l].epoch = 0u;
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(c->dev + off_params, params.data(), (size_t)n * sizeof(DecodeParams), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(c->dev + off_maps, maps.data(), (size_t)2 * n * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { destroy_decode_chain(c); return (int)e; }
+    c->p0 = params[0];
+    c->ch.params = reinterpret_cast<const DecodeParams*>(c->dev + off_params);
+    c->ch.maps = reinterpret_cast<const CUtensorMap*>(c->dev + off_maps);
+    c->ch.counter = reinterpret_cast<unsigned long long*>(c->dev);
+    c->ch.n = n;
+    c->ch.act_bytes = (int)act_max;
+    c->map0 = maps[0];
+    c->map1 = maps[1];
+    c->grid = grid;
+    c->n = n;
+    c->smem = kFixedSmem + (int)stages * stage_w + (int)act_max;
+    *out = c;
+    return NVFP4_OK;
+}
+
+cudaError_t launch_decode_chain(DecodeChain* c, cudaStream_t s) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(c->grid);
+    cfg.blockDim = dim3((2 * kGroupWarps + 1) * 32);
+    cfg.dynamicSmemBytes = c->smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_mma_kernel<2, true>, c->map0, c->map1, c->p0, c->ch);
 }
 
 }  // namespace nvfp4

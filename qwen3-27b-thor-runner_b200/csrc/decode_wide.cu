@@ -419,9 +419,9 @@ cudaError_t configure_decode_wide() {
 cudaError_t launch_decode_wide(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, void* act_f16, float* unscale,
                                int* launches, cudaStream_t s) {
     CUtensorMap tmp, tms;
-    if (!umma::make_map(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kUnitRows,
+    if (!umma::make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kUnitRows,
                         CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !umma::make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kUnitRows,
+        !umma::make_map_cached(dev.maps, &tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kUnitRows,
                         CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     cudaError_t e = launch_act_to_f16(a.A, a.M, a.K, act_f16, unscale, s);

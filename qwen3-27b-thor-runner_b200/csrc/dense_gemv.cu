@@ -331,7 +331,7 @@ cudaError_t configure_dense_gemv() {
 // NVFP4 GEMV: launches on one stream follow each other, and every launch has its own epoch).
 cudaError_t launch_dense_gemv(const DenseArgs& a, nvfp4_device_info& dev, void* scratch, int* launches, cudaStream_t s) {
     CUtensorMap tm;
-    if (!umma::make_map(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.W, (uint64_t)a.K, (uint64_t)a.N, 64, kRT,
+    if (!umma::make_map_cached(dev.maps, &tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.W, (uint64_t)a.K, (uint64_t)a.N, 64, kRT,
                         CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     const int per = dense_tokens_per_launch(a, dev);

@@ -1,6 +1,7 @@
 // Internal declarations shared by the host-side dispatcher and the kernel files.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -28,6 +29,21 @@ struct LinearArgs {
     float norm_eps = 0.0f;
 };
 
+// Encoded tensor maps of recently used tensors, keyed by everything that goes into the encoding: a decode
+// step calls the same few weights over and over, and cuTensorMapEncodeTiled costs the host more than a
+// microsecond per map.  Direct-mapped, owned by the handle (one host thread at a time).
+struct TensorMapCache {
+    struct Entry {
+        const void* base = nullptr;
+        uint64_t cols = 0, rows = 0;
+        uint32_t box_cols = 0, box_rows = 0;
+        int dtype = 0, esize = 0, swizzle = 0;
+        CUtensorMap map;
+    };
+    static constexpr int kEntries = 128;
+    Entry e[kEntries];
+};
+
 struct nvfp4_device_info {
     int device;
     int sm_count;
@@ -36,6 +52,7 @@ struct nvfp4_device_info {
     int prefill_stream_k = 1;    // split the tiles left after whole waves by k over all CTAs
     int skinny_split_cost = 12;  // stage-times charged to splitting row tiles by k in the few-token kernel
     size_t gemv_pairs_offset = 6u << 20;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
+    TensorMapCache* maps = nullptr;        // null: encode every time
 };
 
 // The tag of one GEMV launch on the split-tile pairs in its scratch: a process-wide counter, never 0
@@ -85,6 +102,12 @@ size_t decode_mma_scratch_bytes(const LinearArgs& a, const nvfp4_device_info& de
 cudaError_t launch_decode_mma(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, int* launches,
                               cudaStream_t s);
 cudaError_t configure_decode_mma();
+// A chain: n linears of up to 8 tokens each, run in order by one persistent launch (the producer streams the
+// next linear's weights while the consumers pass a grid-wide barrier and stage the next activations).
+struct DecodeChain;
+int create_decode_chain(const LinearArgs* linears, int n, const nvfp4_device_info& dev, void* scratch, DecodeChain** out);
+cudaError_t launch_decode_chain(DecodeChain* c, cudaStream_t s);
+void destroy_decode_chain(DecodeChain* c);
 
 // --- act_f16.cu: BF16 activations -> FP16 copy with an exact per-token power-of-two scale; unscale[m] = 1/scale.
 cudaError_t launch_act_to_f16(const void* A, int M, int K, void* out_f16, float* unscale, cudaStream_t s);

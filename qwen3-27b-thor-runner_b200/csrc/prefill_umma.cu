@@ -556,11 +556,11 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     __half* ah = reinterpret_cast<__half*>(base);
     float* unscale = reinterpret_cast<float*>(base + act_bytes(a.M, a.K));
     CUtensorMap tma, tmp, tms;
-    if (!make_map(&tma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ah, (uint64_t)a.K, (uint64_t)a.M, BK, BM,
+    if (!make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ah, (uint64_t)a.K, (uint64_t)a.M, BK, BM,
                   CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, BN,
+        !make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, BN,
                   CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, BN,
+        !make_map_cached(dev.maps, &tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, BN,
                   CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     cudaError_t e = launch_act_to_f16(a.A, a.M, a.K, ah, unscale, s);
@@ -599,9 +599,9 @@ cudaError_t launch_dense_umma(const DenseArgs& a, nvfp4_device_info& dev, void* 
     if (offset + kStreamKBytes > scratch_bytes) return cudaErrorMemoryAllocation;
     char* sk = static_cast<char*>(scratch) + offset;
     CUtensorMap tma, tmw;
-    if (!make_map(&tma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, (uint64_t)a.K, (uint64_t)a.M, BK, BM,
+    if (!make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, (uint64_t)a.K, (uint64_t)a.M, BK, BM,
                   CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tmw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.W, (uint64_t)a.K, (uint64_t)a.N, BK, BN,
+        !make_map_cached(dev.maps, &tmw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.W, (uint64_t)a.K, (uint64_t)a.N, BK, BN,
                   CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     PrefillParams p{};

@@ -469,11 +469,11 @@ cudaError_t launch_skinny_umma(const LinearArgs& a, nvfp4_device_info& dev, void
     char* base = sk + prefill_umma_reserved_bytes();              // FP16 activations, then one FP32 per token
     float* unscale = reinterpret_cast<float*>(base + ((size_t)a.M * a.K * 2 + 255) / 256 * 256);
     CUtensorMap tma, tmp, tms;
-    if (!make_map(&tma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, (uint64_t)a.K, (uint64_t)a.M, BK, pl.p.NT,
+    if (!make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, (uint64_t)a.K, (uint64_t)a.M, BK, pl.p.NT,
                   CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, TR,
+        !make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, TR,
                   CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, TR,
+        !make_map_cached(dev.maps, &tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, TR,
                   CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     cudaError_t e = launch_act_to_f16(a.A, a.M, a.K, base, unscale, s);

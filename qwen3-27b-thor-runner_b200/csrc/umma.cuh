@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "nvfp4_internal.h"
 #include "ptx.cuh"
 
 namespace nvfp4 {
@@ -186,6 +187,25 @@ inline bool make_map(CUtensorMap* m, CUtensorMapDataType dt, int esize, const vo
     const cuuint32_t estr[2] = {1, 1};
     return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The same through a cache (may be null): weights are called again and again with the same geometry.
+inline bool make_map_cached(TensorMapCache* cache, CUtensorMap* m, CUtensorMapDataType dt, int esize, const void* base,
+                            uint64_t cols, uint64_t rows, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+    if (!cache) return make_map(m, dt, esize, base, cols, rows, box_cols, box_rows, sw);
+    const uintptr_t a = reinterpret_cast<uintptr_t>(base);
+    const unsigned slot = (unsigned)(((a >> 8) ^ (a >> 17) ^ (uintptr_t)box_rows ^ ((uintptr_t)box_cols << 3)) % TensorMapCache::kEntries);
+    TensorMapCache::Entry& e = cache->e[slot];
+    if (e.base == base && e.cols == cols && e.rows == rows && e.box_cols == box_cols && e.box_rows == box_rows &&
+        e.dtype == (int)dt && e.esize == esize && e.swizzle == (int)sw) {
+        *m = e.map;
+        return true;
+    }
+    if (!make_map(m, dt, esize, base, cols, rows, box_cols, box_rows, sw)) return false;
+    e.base = base; e.cols = cols; e.rows = rows; e.box_cols = box_cols; e.box_rows = box_rows;
+    e.dtype = (int)dt; e.esize = esize; e.swizzle = (int)sw;
+    e.map = *m;
+    return true;
 }
 
 }  // namespace umma

@@ -50,6 +50,9 @@ SIGNATURES = {
     "nvfp4_linear_reduce_peers": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p,
                                           c_void_p, c_void_p]),
     "nvfp4_linear_ex": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "nvfp4_chain_create": (c_int, [c_void_p, c_void_p, c_int, ctypes.POINTER(c_void_p)]),
+    "nvfp4_chain_run": (c_int, [c_void_p, c_void_p]),
+    "nvfp4_chain_destroy": (c_int, [c_void_p]),
     "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
@@ -218,3 +221,40 @@ class Handle:
     def linear_host(self, A_host, M, packed, scale, global_scale, N, K, C_host, residual_host=None, stream=None):
         self._check(self.lib.nvfp4_linear_host(self.h, _ptr(A_host), M, _ptr(packed), _ptr(scale), global_scale,
                                                N, K, _ptr(residual_host), _ptr(C_host), _stream(stream)))
+
+
+class Chain:
+    """nvfp4_chain: a fixed sequence of linears (up to 8 tokens each) run by one launch.  `linears` is a list
+    of dicts with the fields of nvfp4_linear_desc (A, M, packed, scale, global_scale, N, K, C and the
+    optional residual, swiglu_up, a_row_stride, k_valid, px, norm_weight, norm_eps, swiglu_epilogue);
+    tensors are given as torch tensors or raw addresses and must stay alive while the chain exists."""
+
+    def __init__(self, handle, linears):
+        self.handle = handle
+        self.keep = linears
+        arr = (LinearDesc * len(linears))()
+        for d, l in zip(arr, linears):
+            px = l.get("px")
+            d.A, d.swiglu_up = _ptr(l["A"]), _ptr(l.get("swiglu_up"))
+            d.a_row_stride, d.k_valid, d.M = l.get("a_row_stride", 0), l.get("k_valid", 0), l["M"]
+            d.packed, d.scale, d.global_scale = _ptr(l["packed"]), _ptr(l["scale"]), l.get("global_scale", 1.0)
+            d.N, d.K = l["N"], l["K"]
+            d.residual, d.C = _ptr(l.get("residual")), _ptr(l["C"])
+            d.px = None if px is None else ctypes.addressof(px)
+            d.norm_weight, d.norm_eps = _ptr(l.get("norm_weight")), l.get("norm_eps", 0.0)
+            d.swiglu_epilogue = int(bool(l.get("swiglu_epilogue", False)))
+        c = c_void_p()
+        st = handle.lib.nvfp4_chain_create(handle.h, arr, len(linears), ctypes.byref(c))
+        if st:
+            raise Nvfp4Error(st)
+        self.c = c
+
+    def run(self, stream=None):
+        st = self.handle.lib.nvfp4_chain_run(self.c, _stream(stream))
+        if st:
+            raise Nvfp4Error(st)
+
+    def close(self):
+        if getattr(self, "c", None):
+            self.handle.lib.nvfp4_chain_destroy(self.c)
+            self.c = None

@@ -80,7 +80,7 @@ def test_dequant_random_bitwise(handle, N, K, sigma):
 
 @pytest.mark.parametrize("impl", [0, 1, 2])
 def test_config0_gemv(handle, impl):
-    """BASELINE config 0: M=1, K=N=5120, seed 0, global scale 1.0."""
+    """The single-GEMV configuration of the benchmark: M=1, K=N=5120, seed 0, global scale 1.0."""
     N = K = 5120
     packed, scale = util.make_weight(N, K, seed=0)
     A = util.make_bf16((1, K), seed=0)
@@ -488,7 +488,7 @@ def test_against_committed_reference_outputs(handle):
 
 @pytest.mark.skipif(not ob.ref_available(), reason="oracle/_ref not built")
 def test_side_by_side_with_reference_kernels(handle):
-    """The reference's kernels and ours on the same device buffers, BASELINE-like shapes."""
+    """The reference's kernels and ours on the same device buffers, shapes like the benchmark's."""
     import torch
     ref = ob.load_ref()
     st = torch.cuda.current_stream().cuda_stream
@@ -508,7 +508,7 @@ def test_side_by_side_with_reference_kernels(handle):
 
 @pytest.mark.parametrize("N,K", [(34816, 5120), (5120, 17408)])
 def test_full_size_properties(handle, N, K):
-    """BASELINE's MLP shapes: (a) doubling the activations doubles every output exactly,
+    """The benchmark's MLP shapes: (a) doubling the activations doubles every output exactly,
     (b) zero activations return the residual bit for bit, (c) sampled rows match the oracle."""
     import torch
     M = 4
