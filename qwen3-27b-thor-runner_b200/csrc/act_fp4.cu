@@ -1,0 +1,146 @@
+// Activation pre-pass of the NVFP4 tensor-core GEMV (decode_fp4.cu): BF16 activations -> a short sum of
+// NVFP4 terms.
+//
+// tcgen05.mma kind::mxf4nvf4 multiplies NVFP4 by NVFP4 (E2M1 codes, one unsigned E4M3 scale per 16
+// elements along K) -- exactly the layout the weights already have in HBM, so they need no
+// conversion at all.  The activations are BF16 and must stay at BF16 accuracy, so every token is
+// expanded into T = 5 NVFP4 "term" rows whose sum reproduces it:
+//     x * c = q_0 * s_0 + q_1 * s_1 + ... + q_4 * s_4   (per 16-element block, up to a remainder)
+// c is a per-token power of two that puts the token's largest magnitude into [2^9, 2^10); s_0 is the
+// smallest power of two with |x c| <= 6 s_0 over the block; s_1 = s_0 / 4, then each next scale is 1/8
+// of the one before; q_t is the remainder so far rounded to the nearest E2M1 value (the hardware
+// conversion).  After a term the remainder is at most half the local E2M1 spacing, which gives
+// |remainder| <= s_0 / 4096 after five terms: below 1e-4 of the block's largest element, a
+// twentieth of the BF16 rounding step of that element.  All scales are powers of two, so every
+// product and every remainder is exact in FP32.  The term rows become columns of the MMA's B operand
+// (tokens x 5, padded to a multiple of 16); the GEMV's epilogue adds the five columns of a token.
+//
+// Outputs: codes [NCp, K/2] (row c = token * 5 + term; two codes per byte, low nibble = even k), the
+// block scales in the 512-byte atoms tcgen05.cp copies into tensor memory (32 rows x 16 bytes; see
+// sfb_offset), and 1 / c per token.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "nvfp4_internal.h"
+#include "ptx.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr int kTerms = fp4::kTerms;
+
+// Two FP32 -> one byte of E2M1 codes, `lo` in the low nibble (round to nearest even, saturating at 6).
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+    uint16_t d;
+    asm("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\n\tmov.b16 %0, {b, b};\n\t}" : "=h"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+// One byte of E2M1 codes -> two floats.
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+    uint32_t h2;
+    asm("{\n\t.reg .b8 b, z;\n\tmov.b16 {b, z}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "h"((uint16_t)byte));
+    return __half22float2(*reinterpret_cast<const __half2*>(&h2));
+}
+// 2^p as an unsigned E4M3 byte, p in [-9, 8].
+__device__ __forceinline__ uint32_t ue4m3_pow2(int p) {
+    return p >= -6 ? (uint32_t)(p + 7) << 3 : (p == -7 ? 4u : (p == -8 ? 2u : 1u));
+}
+
+// grid: M token CTAs + 1 CTA that zero-fills the padding columns.
+__global__ void __launch_bounds__(512)
+act_to_fp4_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int M, int K, int NCp,
+                  uint8_t* __restrict__ codes, uint8_t* __restrict__ sfb, float* __restrict__ unscale) {
+    __shared__ unsigned int s_max;
+    const int m = blockIdx.x;
+    const int blocks = K / 16;
+    if (threadIdx.x == 0) s_max = 0u;
+    ptx::griddep_launch_dependents();      // the GEMV behind this kernel may set itself up and start streaming weights
+    ptx::griddep_wait();                   // A is the output of the kernel before this one
+    __syncthreads();
+    if (m == M) {
+        // padding columns M*T .. NCp-1: zero codes, zero scales
+        const int pad0 = M * kTerms;
+        const long long row_bytes = K / 2;
+        for (int c = pad0; c < NCp; ++c)
+            for (long long i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+                reinterpret_cast<uint4*>(codes + (size_t)c * row_bytes)[i] = make_uint4(0u, 0u, 0u, 0u);
+        // every scale byte no token column owns: the rest of the atoms' rows and the bytes of absent column groups
+        for (int b = threadIdx.x; b < blocks; b += blockDim.x)
+            for (int c = pad0; c < 128; ++c) sfb[fp4::sfb_offset(b, c)] = 0;
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(A + (size_t)m * a_stride);
+    unsigned int amax = 0;
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        const uint4 x = __ldg(src + i);
+        const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) amax = max(amax, max(v[q] & 0x7FFFu, (v[q] >> 16) & 0x7FFFu));
+    }
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if ((threadIdx.x & 31) == 0 && amax) atomicMax(&s_max, amax);
+    __syncthreads();
+    // c = 2^(136 - e): the largest element (biased BF16 exponent e) lands in [2^9, 2^10)
+    int se = 263 - (int)(s_max >> 7);
+    se = se < 1 ? 1 : (se > 254 ? 254 : se);
+    const float c = __uint_as_float((uint32_t)se << 23);
+    if (threadIdx.x == 0) unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
+    for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
+        const uint4 x0 = __ldg(src + 2 * b), x1 = __ldg(src + 2 * b + 1);
+        const uint32_t v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        float r[16];
+        float bmax = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            r[2 * q] = __uint_as_float(v[q] << 16) * c;
+            r[2 * q + 1] = __uint_as_float(v[q] & 0xFFFF0000u) * c;
+            bmax = fmaxf(bmax, fmaxf(fabsf(r[2 * q]), fabsf(r[2 * q + 1])));
+        }
+        // p0: smallest p with bmax <= 6 * 2^p, clamped to the unsigned E4M3 range of powers of two
+        int p0 = -9;
+        if (bmax > 0.0f && bmax < 3.0e38f) {
+            const uint32_t u = __float_as_uint(bmax * (1.0f / 6.0f));
+            p0 = (int)(u >> 23) - 127 + ((u & 0x7FFFFFu) ? 1 : 0);
+            if (bmax > 6.0f * __uint_as_float((uint32_t)(p0 + 127) << 23)) ++p0;     // 1/6 is not exact: never let the block exceed 6 s_0
+        }
+        p0 = p0 < -9 ? -9 : (p0 > 8 ? 8 : p0);
+#pragma unroll
+        for (int t = 0; t < kTerms; ++t) {
+            int p = p0 - (t == 0 ? 0 : 2 + 3 * (t - 1));
+            p = p < -9 ? -9 : p;
+            const float s = __uint_as_float((uint32_t)(p + 127) << 23), inv = __uint_as_float((uint32_t)(127 - p) << 23);
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint32_t byte = cvt_e2m1x2(r[2 * q] * inv, r[2 * q + 1] * inv) & 0xFFu;
+                const float2 d = e2m1x2_to_float2(byte);
+                r[2 * q] -= d.x * s;
+                r[2 * q + 1] -= d.y * s;
+                w[q >> 2] |= byte << (8 * (q & 3));
+            }
+            const int col = m * kTerms + t;
+            *reinterpret_cast<uint2*>(codes + (size_t)col * (K / 2) + (size_t)b * 8) = make_uint2(w[0], w[1]);
+            sfb[fp4::sfb_offset(b, col)] = (uint8_t)ue4m3_pow2(p);
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int NCp, void* codes, void* sfb,
+                              float* unscale, cudaStream_t s) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(M + 1);
+    cfg.blockDim = dim3(K / 16 >= 512 ? 512 : (K / 16 + 31) / 32 * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, act_to_fp4_kernel, static_cast<const __nv_bfloat16*>(A), a_stride, M, K, NCp,
+                              static_cast<uint8_t*>(codes), static_cast<uint8_t*>(sfb), unscale);
+}
+
+}  // namespace nvfp4

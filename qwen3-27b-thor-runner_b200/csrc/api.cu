@@ -23,6 +23,7 @@ struct nvfp4_handle {
     int decode_max_m = 16;
     int wide_gemv = 1;                           // 9..16 tokens: one launch of the wide GEMV kernel
     int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
+    int fp4_native = 1;                          // up to 9 tokens: the NVFP4 tensor-core GEMV (weights untouched, activations as NVFP4 terms)
     unsigned long long launches = 0;
 };
 
@@ -39,7 +40,10 @@ unsigned int next_launch_tag() {
 
 namespace {
 
-constexpr size_t kDecodeScratchBytes = 8u << 20;   // status word + the split-tile partial pairs of the two GEMV kernels
+// status word + the split-tile partial pairs of the GEMV kernels: the wide one from 16 KB, the 8-token one from 6 MB,
+// the tensor-core one from 8 MB, and from 10 MB the NVFP4 form of that kernel's activations
+constexpr size_t kDecodeScratchBytes = 12u << 20;
+constexpr size_t kFp4PairsOffset = 8u << 20, kFp4ActOffset = 10u << 20, kFp4ActBytes = 2u << 20;
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -67,6 +71,11 @@ int validate_linear(const nvfp4_handle* h, const void* A, int M, const uint8_t* 
 }
 
 int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
+
+// options only the mma.sync GEMV kernels implement (the tensor-core GEMV takes plain calls, with or without FP32 output)
+bool other_options_but_f32(const LinearArgs& a) {
+    return a.swiglu_up || a.a_stride || a.k_valid || a.norm_w || a.swiglu_out || a.px;
+}
 
 // One linear call on device buffers.
 // `ws_bytes`: how much of the workspace the kernels may use (the host-buffer path keeps its staging behind it).
@@ -102,6 +111,13 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
+    if (fast_path_wanted && h->fp4_native && !other_options_but_f32(a) && decode_fp4_supported(a, h->dev) &&
+        decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
+        int nl = 0;
+        cudaError_t e = launch_decode_fp4(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
@@ -268,6 +284,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "wide_gemv")) {
         if (value < 0 || value > 1) return NVFP4_E_OPTION;
         h->wide_gemv = value;
+    } else if (!std::strcmp(name, "fp4_native")) {
+        if (value < 0 || value > 1) return NVFP4_E_OPTION;
+        h->fp4_native = value;
     } else if (!std::strcmp(name, "skinny_min_m")) {
         if (value < 1 || value > 129) return NVFP4_E_OPTION;
         h->skinny_min_m = value;
@@ -293,6 +312,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "decode_max_m")) *value = h->decode_max_m;
     else if (!std::strcmp(name, "prefill_stream_k")) *value = h->dev.prefill_stream_k;
     else if (!std::strcmp(name, "wide_gemv")) *value = h->wide_gemv;
+    else if (!std::strcmp(name, "fp4_native")) *value = h->fp4_native;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;

@@ -1,0 +1,518 @@
+// Dequant-free GEMV for up to 9 tokens on the NVFP4 tensor-core path: the packed weights go from HBM
+// to the tensor core untouched.
+//
+//   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
+//
+// tcgen05.mma kind::mxf4nvf4 (block_scale, one unsigned E4M3 scale per 16 elements of K) takes both
+// operands as packed E2M1 with block scales -- the weights' own HBM layout.  So, unlike the
+// mma.sync GEMV (decode_mma.cu), whose 16 consumer warps spend their time converting codes and
+// multiplying scales (and top out at the HBM rate with nothing to spare), this kernel has no
+// per-weight instruction at all:
+//   * warp 0 streams half-units (128 weight rows x 256 k: 16 KB of codes + 2 KB of scales) into a
+//     shared-memory ring with plain tiled TMA (128-byte swizzle for the codes: the K-major operand
+//     layout of the tensor core; no multicast); the half-units, row-tile-major, are split evenly
+//     over the CTAs (stream-K);
+//   * warps 4-7 re-order the 2 KB of block scales of each half-unit into the 512-byte atoms
+//     tcgen05.cp copies into tensor memory (row r of the MMA wants its four scales of a 64-k MMA in
+//     lane r % 32, column r / 32); that is the only touch the weights get;
+//   * one thread of warp 1 copies the atoms into tensor memory and issues four
+//     tcgen05.mma (128 rows x NCp columns x 64 k) per half-unit, accumulating FP32 in tensor
+//     memory; tcgen05.commit recycles the ring stage;
+//   * the activations are the B operand: a pre-pass (act_fp4.cu) expands every BF16 token into five
+//     NVFP4 term rows whose sum reproduces it to 1e-4 of each block's largest element; the CTA's k
+//     range of the codes is loaded once by warp 2 and stays resident in shared memory, their block
+//     scales are written straight into tensor memory by warps 8-11 (tcgen05.st) and stay there;
+//   * warps 8-11 read the accumulator (thread = weight row), add the five columns of each token,
+//     undo the token scale, apply 1/global_scale and the residual in FP32 and round once.  A row
+//     tile split over several CTAs is finished by the CTA holding its first half-unit: the others
+//     publish FP32 partials as {value, launch tag} pairs (8-byte single transactions, the tag
+//     from a counter in the scratch), the owner adds them in CTA order (deterministic).
+// Every wait is bounded and reports through the status word; tensor memory is always freed.
+//
+// Arithmetic: the weight side is exact (the tensor core multiplies e2m1 x ue4m3 exactly and
+// accumulates in FP32); the activation side carries the pre-pass's remainder.  Against the
+// reference's GEMV (src/engine/dense_gemm_fp4_sm110.cu:96-141): same products up to that remainder,
+// FP32 accumulation in another order, one rounding.  A scale byte 0x7F / 0xFF is NaN to the tensor
+// core (as in FP8 E4M3, whose finite maximum is 0x7E = 448); the reference's table-free decoder reads
+// it as 480.  No finite FP8 scale, hence no checkpoint, contains it.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "nvfp4_format.cuh"
+#include "nvfp4_internal.h"
+#include "ptx.cuh"
+#include "umma.cuh"
+
+namespace nvfp4 {
+namespace {
+
+using namespace umma;
+
+constexpr int kRT = 128;                           // weight rows per tile (UMMA M, tensor-memory lanes)
+constexpr int kKC = 256;                           // k per half-unit
+constexpr int kPackedBytes = kRT * kKC / 2;        // 16 KB
+constexpr int kScaleBytes = kRT * kKC / 16;        // 2 KB raw scales [row][16], and 2 KB re-ordered into four atoms
+constexpr int kMaxStages = 10;
+constexpr int kThreads = 12 * 32;
+constexpr int kEpiThreads = 4 * 32;
+constexpr int kSmemBudget = 227 * 1024;
+constexpr int kAccStride = 64;                     // tensor-memory columns per accumulator (NCp <= 48)
+constexpr int kSfaCol = 2 * kAccStride;            // two buffers of 16 columns for the weights' scales
+constexpr int kSfbCol = kSfaCol + 32;              // the activations' scales, resident
+constexpr int kMaxGrid = 160;                      // CTAs whose pair slots fit the kernel's 2 MB of scratch
+constexpr int kPairTokens = fp4::kMaxTokens;       // token rows of a CTA's pair slot (9 KB per CTA)
+static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= (2u << 20), "pair slots");
+
+struct Fp4Params {
+    const __nv_bfloat16* residual;
+    __nv_bfloat16* C;
+    const float* unscale;           // per token: 1 / c of the pre-pass
+    const unsigned char* sfb;       // the pre-pass's scale atoms: [K/256][4 MMAs][512]
+    unsigned char* scratch;         // status word at 0, launch counter at 64
+    unsigned char* pairs;           // [CTA][kPairTokens][128 rows] x {FP32 value, tag}
+    float inv_gs;
+    int M, N, K;
+    int NCp;                        // MMA columns (tokens x 5 padded to 16)
+    int units, kchunks;
+    int stages, hps;                // ring depth, half-units per stage (1 or 2)
+    int slots, act_all;             // resident activation chunks; 1 = slot index is the k-chunk
+    int out_f32;
+};
+
+// kind::mxf4nvf4: A = B = E2M1 (format 1), scales unsigned E4M3, both K-major, M = 128, N = NCp, K = 64.
+__device__ __forceinline__ uint32_t fp4_idesc(int ncp) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(ncp >> 3) << 17) | ((uint32_t)(kRT >> 4) << 24);
+}
+__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+// Source of a scale copy: 32 rows x 16 bytes, contiguous (K-major, no swizzle: 8-row groups 128 bytes apart).
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
+                  const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ Fp4Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int stages = p.stages, hps = p.hps;
+    const int b_bytes = p.NCp * 128;                                        // one resident activation chunk (NCp rows x 256 k)
+    unsigned char* s_w = smem;                                              // stages x hps x 16 KB, 1024-aligned
+    unsigned char* s_b = s_w + stages * hps * kPackedBytes;                 // slots x NCp x 128 B, 1024-aligned (NCp % 8 == 0)
+    unsigned char* s_raw = s_b + p.slots * b_bytes;                         // stages x hps x 2 KB: scales as they lie in HBM
+    unsigned char* s_sfa = s_raw + stages * hps * kScaleBytes;              // stages x hps x 2 KB: the same, as atoms
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_sfa + stages * hps * kScaleBytes);
+    uint64_t* empty_bar = full_bar + kMaxStages;
+    uint64_t* sfa_bar = empty_bar + kMaxStages;      // atoms of a stage written
+    uint64_t* b_bar = sfa_bar + kMaxStages;          // [0] resident activation codes loaded, [1] their scales in tensor memory
+    uint64_t* tfull = b_bar + 2;                     // [2] accumulator complete
+    uint64_t* tempty = tfull + 2;                    // [2] accumulator read
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+    volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_tmem + 2);
+
+    unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, G = gridDim.x;
+    const int u_begin = (int)((long long)cta * p.units / G);      // half-units [u_begin, u_end) of this CTA
+    const int u_end = (int)((long long)(cta + 1) * p.units / G);
+    const int kc_begin = u_begin % p.kchunks;
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+            ptx::mbar_init(&sfa_bar[s], 4);
+        }
+        ptx::mbar_init(&b_bar[0], 1);
+        ptx::mbar_init(&b_bar[1], 4);
+        for (int i = 0; i < 2; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], 4); }
+        *s_abort = 0;
+        *s_epoch = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) tmem_alloc_512(s_tmem);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+    ptx::griddep_launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ weight stream
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tm_packed);
+            ptx::prefetch_tensormap(&tm_scale);
+            const uint64_t pol = ptx::policy_evict_first();
+            int stage = 0;
+            uint32_t ph = 0;
+            int hu = u_begin, tile = u_begin / p.kchunks, kc = kc_begin;
+            while (hu < u_end) {
+                const int tile_end = hu - kc + p.kchunks;
+                const int seg_end = tile_end < u_end ? tile_end : u_end;
+                const int row0 = tile * kRT;
+                while (hu < seg_end) {
+                    const int cnt = (seg_end - hu) >= hps ? hps : 1;
+                    ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0xA00u + (unsigned)stage);
+                    ptx::mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(kPackedBytes + kScaleBytes) * cnt);
+                    for (int h = 0; h < cnt; ++h) {
+                        const int k0 = (kc + h) * kKC;
+                        ptx::tma_load_2d(s_w + (stage * hps + h) * kPackedBytes, &tm_packed, &full_bar[stage], k0 >> 1, row0, pol);
+                        ptx::tma_load_2d(s_raw + (stage * hps + h) * kScaleBytes, &tm_scale, &full_bar[stage], k0 >> 4, row0, pol);
+                    }
+                    hu += cnt;
+                    kc += cnt;
+                    if (++stage == stages) { stage = 0; ph ^= 1u; }
+                }
+                if (kc >= p.kchunks) { kc = 0; ++tile; }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ resident activations (the pre-pass's output)
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tm_act);
+            ptx::griddep_wait();
+            const uint64_t pol = ptx::policy_evict_last();
+            ptx::mbar_arrive_expect_tx(&b_bar[0], (uint32_t)(p.slots * b_bytes));
+            const int kc0 = p.act_all ? 0 : kc_begin;
+            for (int j = 0; j < p.slots; ++j) {
+                int kc = kc0 + j;
+                if (kc >= p.kchunks) kc -= p.kchunks;
+                ptx::tma_load_2d(s_b + j * b_bytes, &tm_act, &b_bar[0], kc * (kKC / 2), 0, pol);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = fp4_idesc(p.NCp);
+            ptx::mbar_wait(&b_bar[0], 0u, s_abort, status, 0xA10u);
+            ptx::mbar_wait(&b_bar[1], 0u, s_abort, status, 0xA11u);
+            tc_fence_after();
+            int stage = 0, acc = 0, sfbuf = 0;
+            uint32_t ph = 0, pt = 0;
+            int hu = u_begin, kc = kc_begin;
+            while (hu < u_end) {
+                const int tile_end = hu - kc + p.kchunks;
+                const int seg_end = tile_end < u_end ? tile_end : u_end;
+                ptx::mbar_wait(&tempty[acc], ((pt >> acc) & 1u) ^ 1u, s_abort, status, 0xA20u + (unsigned)acc);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kAccStride);
+                bool first = true;
+                while (hu < seg_end) {
+                    const int cnt = (seg_end - hu) >= hps ? hps : 1;
+                    ptx::mbar_wait(&sfa_bar[stage], ph, s_abort, status, 0xA30u + (unsigned)stage);
+                    tc_fence_after();
+                    for (int h = 0; h < cnt; ++h) {
+                        const int slot = p.act_all ? kc + h : (hu - u_begin) + h;
+                        const uint32_t sfa_t = tmem_base + kSfaCol + 16 * sfbuf;
+                        const uint32_t atoms = ptx::smem_u32(s_sfa + (stage * hps + h) * kScaleBytes);
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) tmem_cp_sf(sfa_t + 4 * s, sf_desc(atoms + 512 * s));
+                        const uint32_t a_addr = ptx::smem_u32(s_w + (stage * hps + h) * kPackedBytes);
+                        const uint32_t b_addr = ptx::smem_u32(s_b + slot * b_bytes);
+                        const uint32_t sfb_t = tmem_base + kSfbCol + (uint32_t)(slot * 16);
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            umma_fp4(d_tmem, umma_desc_sw128(a_addr + 32 * s), umma_desc_sw128(b_addr + 32 * s), idesc,
+                                     sfa_t + 4 * s, sfb_t + 4 * s, first ? 0u : 1u);
+                            first = false;
+                        }
+                        sfbuf ^= 1;
+                    }
+                    umma_commit(&empty_bar[stage]);        // codes, raw scales and atoms of the stage are free once these MMAs have read them
+                    hu += cnt;
+                    kc += cnt;
+                    if (++stage == stages) { stage = 0; ph ^= 1u; }
+                }
+                umma_commit(&tfull[acc]);
+                pt ^= 1u << acc;
+                acc ^= 1;
+                if (kc >= p.kchunks) kc = 0;
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------------------------------------------ scales into atoms: thread = weight row
+        const int r = tid - 4 * 32, r0 = r & 31, r1 = r >> 5;
+        int stage = 0;
+        uint32_t ph = 0;
+        int hu = u_begin, kc = kc_begin;
+        while (hu < u_end) {
+            const int tile_end = hu - kc + p.kchunks;
+            const int seg_end = tile_end < u_end ? tile_end : u_end;
+            while (hu < seg_end) {
+                const int cnt = (seg_end - hu) >= hps ? hps : 1;
+                ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0xA40u + (unsigned)stage);
+                for (int h = 0; h < cnt; ++h) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(s_raw + (stage * hps + h) * kScaleBytes + r * 16);
+                    uint32_t* at = reinterpret_cast<uint32_t*>(s_sfa + (stage * hps + h) * kScaleBytes) + r0 * 4 + r1;
+                    at[0] = raw.x & 0x7F7F7F7Fu;           // bit 7 carries nothing (src/engine/dense_gemm_fp4_sm110.cu:30-41)
+                    at[128] = raw.y & 0x7F7F7F7Fu;
+                    at[256] = raw.z & 0x7F7F7F7Fu;
+                    at[384] = raw.w & 0x7F7F7F7Fu;
+                }
+                ptx::fence_proxy_async_smem();              // generic-proxy stores -> visible to tcgen05.cp
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sfa_bar[stage]);
+                hu += cnt;
+                kc += cnt;
+                if (++stage == stages) { stage = 0; ph ^= 1u; }
+            }
+            if (kc >= p.kchunks) kc = 0;
+        }
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------------ epilogue: thread = weight row
+        const int ew = warp - 8;                              // tensor-memory lanes 32 ew .. +31 (= warp id % 4)
+        const int te = ew * 32 + lane;
+        ptx::griddep_wait();                                  // C, the residual and the scratch belong to earlier kernels until now
+        if (te == 0) *s_epoch = ptx::take_launch_epoch(p.scratch);
+        ptx::named_barrier_sync(1, kEpiThreads);
+        const unsigned int epoch = *s_epoch;
+        unsigned char* pairs = p.pairs;
+        {
+            // The activations' block scales into tensor memory, for the CTA's whole k range, once: per resident
+            // chunk four atoms of 32 rows x 16 bytes (one per 64-k MMA); lane L of every lane quarter gets row L
+            // of each atom as four columns.  The four warps write the same data into their own quarters, which
+            // is the replication the tensor core expects.
+            const int kc0 = p.act_all ? 0 : kc_begin;
+            for (int j = 0; j < p.slots; ++j) {
+                int kcj = kc0 + j;
+                if (kcj >= p.kchunks) kcj -= p.kchunks;
+                const uint4* src = reinterpret_cast<const uint4*>(p.sfb + (size_t)kcj * 2048 + (size_t)lane * 16);
+                uint32_t r[16];
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint4 x = __ldcg(src + s * 32);
+                    r[4 * s] = x.x; r[4 * s + 1] = x.y; r[4 * s + 2] = x.z; r[4 * s + 3] = x.w;
+                }
+                tmem_st16(tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(kSfbCol + 16 * j), r);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&b_bar[1]);
+        }
+        int acc = 0;
+        uint32_t pt = 0;
+        int hu = u_begin, tile = u_begin / p.kchunks, kc = kc_begin;
+        while (hu < u_end) {
+            const int kc_first = kc;
+            const int tile_end = hu - kc + p.kchunks;
+            const int seg_end = tile_end < u_end ? tile_end : u_end;
+            const bool owner = kc_first == 0;
+            const bool complete = owner && seg_end == tile_end;
+            int last = cta;                                   // contributors are CTAs cta+1 .. last
+            if (owner && !complete)
+                while (last + 1 < G && (long long)(last + 1) * p.units / G < tile_end) ++last;
+            ptx::mbar_wait(&tfull[acc], (pt >> acc) & 1u, s_abort, status, 0xA50u + (unsigned)acc);
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * kAccStride);
+            float v[fp4::kMaxTokens];
+#pragma unroll
+            for (int m = 0; m < fp4::kMaxTokens; ++m) v[m] = 0.0f;
+#pragma unroll
+            for (int c0 = 0; c0 < 48; c0 += 16) {
+                if (c0 < p.NCp) {
+                    uint32_t r[16];
+                    tmem_ld16(t_addr + c0, r);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int c = c0 + i;                 // column c = token * 5 + term (compile-time after unrolling)
+                        if (c / fp4::kTerms < fp4::kMaxTokens) v[c / fp4::kTerms] += __uint_as_float(r[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tempty[acc]);
+            pt ^= 1u << acc;
+            acc ^= 1;
+            hu = seg_end;
+            kc = kc_first + (seg_end - (tile_end - p.kchunks + kc_first));
+
+#pragma unroll
+            for (int m = 0; m < fp4::kMaxTokens; ++m)
+                if (m < p.M) v[m] *= p.unscale[m];
+            if (!owner) {
+                unsigned char* slot = pairs + (size_t)cta * (kPairTokens * kRT) * 8;
+#pragma unroll
+                for (int m = 0; m < fp4::kMaxTokens; ++m)
+                    if (m < p.M) ptx::st_volatile_v2(slot + (m * kRT + te) * 8, __float_as_uint(v[m]), epoch);
+            } else {
+                const long long t0 = clock64();
+                bool failed = false;
+                for (int c = cta + 1; c <= last && !failed; ++c) {
+                    const unsigned char* src = pairs + (size_t)c * (kPairTokens * kRT) * 8;
+                    while (true) {
+                        uint2 x[fp4::kMaxTokens];
+#pragma unroll
+                        for (int m = 0; m < fp4::kMaxTokens; ++m) {
+                            x[m] = make_uint2(0u, epoch);
+                            if (m < p.M) x[m] = ptx::ld_volatile_v2(src + (m * kRT + te) * 8);
+                        }
+                        bool ready = true;
+#pragma unroll
+                        for (int m = 0; m < fp4::kMaxTokens; ++m) ready &= (x[m].y == epoch);
+                        if (ready) {
+#pragma unroll
+                            for (int m = 0; m < fp4::kMaxTokens; ++m) v[m] += __uint_as_float(x[m].x);
+                            break;
+                        }
+                        if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
+                            *s_abort = 1;
+                            atomicCAS(status, 0u, 0xA60u);
+                            failed = true;
+                            break;
+                        }
+                    }
+                }
+                const int n = tile * kRT + te;
+                if (n < p.N) {
+#pragma unroll
+                    for (int m = 0; m < fp4::kMaxTokens; ++m) {
+                        if (m >= p.M) continue;
+                        float x = v[m] * p.inv_gs;
+                        const size_t o = (size_t)m * p.N + n;
+                        if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
+                        if (p.residual) x += __bfloat162float(p.residual[o]);
+                        p.C[o] = __float2bfloat16_rn(x);
+                    }
+                }
+            }
+            if (kc >= p.kchunks) { kc = 0; ++tile; }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_512(tmem_base);
+    }
+}
+
+struct Fp4Plan {
+    Fp4Params p;
+    int grid, smem;
+};
+
+constexpr int kFixedSmem = 1024 + (3 * kMaxStages + 6) * 8 + 64;
+
+bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
+    Fp4Params& p = out->p;
+    p = Fp4Params{};
+    p.M = a.M; p.N = a.N; p.K = a.K;
+    p.NCp = (a.M * fp4::kTerms + 15) / 16 * 16;
+    p.kchunks = a.K / kKC;
+    const long long units = (long long)((a.N + kRT - 1) / kRT) * p.kchunks;
+    if (units > 0x7fffffffLL || units < 1) return false;
+    p.units = (int)units;
+    int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
+    if (grid > p.units) grid = p.units;
+    const int max_span = (p.units + grid - 1) / grid;
+    p.act_all = p.kchunks <= max_span ? 1 : 0;
+    p.slots = p.act_all ? p.kchunks : max_span;
+    const long long resident = (long long)p.slots * (p.NCp * 128);
+    if (16 * p.slots > 512 - kSfbCol) return false;                // tensor-memory columns for the activations' scales (16 per chunk)
+    const long long avail = kSmemBudget - kFixedSmem - resident;
+    const int unit = kPackedBytes + 2 * kScaleBytes;                // codes + raw scales + atoms
+    // Two half-units per stage when four such stages fit (one issuing thread keeps HBM busier with larger stages)
+    p.hps = avail / (2 * unit) >= 4 ? 2 : 1;
+    long long stages = avail / ((long long)p.hps * unit);
+    if (stages < 3) return false;
+    if (stages > kMaxStages) stages = kMaxStages;
+    p.stages = (int)stages;
+    out->grid = grid;
+    out->smem = kFixedSmem + (int)stages * p.hps * unit + (int)resident;
+    return true;
+}
+
+size_t round256(size_t x) { return (x + 255) / 256 * 256; }
+
+}  // namespace
+
+bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
+    if (a.M < 1 || a.M > fp4::kMaxTokens || (a.K % kKC) != 0 || a.N < 1) return false;
+    if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
+    if (a.px || a.swiglu_up || a.swiglu_out || a.norm_w || a.k_valid) return false;
+    if (a.a_stride && (a.a_stride & 7)) return false;
+    Fp4Plan pl;
+    return plan_fp4(a, dev, &pl);
+}
+
+// codes [48, K/2] + scale atoms [K/256][4][512] + 16 floats
+size_t decode_fp4_scratch_bytes(int K) {
+    return round256((size_t)48 * (K / 2)) + round256((size_t)(K / kKC) * 2048) + 256;
+}
+
+cudaError_t configure_decode_fp4() {
+    return cudaFuncSetAttribute(decode_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+}
+
+cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t pairs_offset, void* act,
+                              int* launches, cudaStream_t s) {
+    Fp4Plan pl;
+    if (!plan_fp4(a, dev, &pl)) return cudaErrorInvalidValue;
+    Fp4Params& p = pl.p;
+    unsigned char* codes = static_cast<unsigned char*>(act);
+    unsigned char* sfb = codes + round256((size_t)48 * (a.K / 2));
+    float* unscale = reinterpret_cast<float*>(sfb + round256((size_t)p.kchunks * 2048));
+    CUtensorMap tmp, tms, tma;
+    if (!make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT,
+                         CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map_cached(dev.maps, &tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kRT,
+                         CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        !make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, (uint64_t)a.K / 2, (uint64_t)p.NCp, 128,
+                         (uint32_t)p.NCp, CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorInvalidValue;
+    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, p.NCp, codes, sfb, unscale, s);
+    if (e != cudaSuccess) return e;
+    p.residual = static_cast<const __nv_bfloat16*>(a.residual);
+    p.C = static_cast<__nv_bfloat16*>(a.C);
+    p.unscale = unscale;
+    p.sfb = sfb;
+    p.scratch = static_cast<unsigned char*>(scratch);
+    p.pairs = p.scratch + pairs_offset;
+    p.inv_gs = a.inv_gs;
+    p.out_f32 = a.out_f32 ? 1 : 0;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, decode_fp4_kernel, tmp, tms, tma, p);
+    if (launches) *launches = 2;
+    return e;
+}
+
+}  // namespace nvfp4

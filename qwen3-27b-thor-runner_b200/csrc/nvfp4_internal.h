@@ -109,6 +109,29 @@ int create_decode_chain(const LinearArgs* linears, int n, const nvfp4_device_inf
 cudaError_t launch_decode_chain(DecodeChain* c, cudaStream_t s);
 void destroy_decode_chain(DecodeChain* c);
 
+// --- act_fp4.cu / decode_fp4.cu: the GEMV on the NVFP4 tensor-core path (tcgen05.mma kind::mxf4nvf4).
+namespace fp4 {
+constexpr int kTerms = 5;          // NVFP4 term rows per token (act_fp4.cu)
+constexpr int kMaxTokens = 9;      // 9 x 5 = 45 columns <= 48
+// Where the block scale of column c (token * kTerms + term), 16-element block b along K, sits in the
+// scale buffer.  The buffer holds, per 256-k chunk, four 512-byte atoms (one per 64-k MMA), each 32 rows
+// x 16 bytes: an MMA reads, for column c, lane c % 32 of tensor-memory column (base + c / 32), bytes 0..3
+// = its four blocks, and wants the base on a multiple of four columns -- so row c % 32 of the atom, bytes
+// 4 (c / 32) .. + 3.
+__host__ __device__ inline size_t sfb_offset(int b, int c) {
+    const int kc = b >> 4, s = (b >> 2) & 3, kb = b & 3;
+    return (size_t)kc * 2048 + (size_t)s * 512 + (size_t)(c & 31) * 16 + (size_t)(c >> 5) * 4 + kb;
+}
+}  // namespace fp4
+cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int NCp, void* codes, void* sfb,
+                              float* unscale, cudaStream_t s);
+bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev);
+size_t decode_fp4_scratch_bytes(int K);       // codes + scale atoms + per-token factors of the activation pre-pass
+cudaError_t configure_decode_fp4();
+// scratch: the handle workspace (status word at 0, launch counter at 64, pairs at pairs_offset); act: decode_fp4_scratch_bytes.
+cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t pairs_offset, void* act,
+                              int* launches, cudaStream_t s);
+
 // --- act_f16.cu: BF16 activations -> FP16 copy with an exact per-token power-of-two scale; unscale[m] = 1/scale.
 cudaError_t launch_act_to_f16(const void* A, int M, int K, void* out_f16, float* unscale, cudaStream_t s);
 
