@@ -16,8 +16,7 @@
 // (tokens x 5, padded to a multiple of 16); the GEMV's epilogue adds the five columns of a token.
 //
 // Outputs: codes [NCp, K/2] (row c = token * 5 + term; two codes per byte, low nibble = even k), the
-// block scales in the 512-byte atoms tcgen05.cp copies into tensor memory (32 rows x 16 bytes; see
-// sfb_offset), and 1 / c per token.
+// block scales in the order the GEMV moves them into tensor memory (see sfb_offset), and 1 / c per token.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -46,32 +45,27 @@ __device__ __forceinline__ uint32_t ue4m3_pow2(int p) {
     return p >= -6 ? (uint32_t)(p + 7) << 3 : (p == -7 ? 4u : (p == -8 ? 2u : 1u));
 }
 
-// grid: M token CTAs + 1 CTA that zero-fills the padding columns.
-__global__ void __launch_bounds__(512)
-act_to_fp4_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int M, int K, int NCp,
+constexpr int kSliceBlocks = 64;        // 16-element blocks (1024 k) per CTA
+constexpr int kPreThreads = 4 * kSliceBlocks;
+
+// grid: (K slices, tokens).  Every CTA finds the token's largest magnitude over the whole row (cheap, and
+// it saves a grid-wide step), then expands its own slice: four threads per 16-element block, four
+// elements each (the five terms are a dependent chain per element, so more threads, not longer ones).
+// Columns beyond tokens x 5 are never written: whatever an earlier call left there only reaches
+// accumulator columns the GEMV's epilogue does not read (stale codes and scales are finite).
+__global__ void __launch_bounds__(kPreThreads)
+act_to_fp4_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int K, int groups,
                   uint8_t* __restrict__ codes, uint8_t* __restrict__ sfb, float* __restrict__ unscale) {
     __shared__ unsigned int s_max;
-    const int m = blockIdx.x;
+    const int m = blockIdx.y;
     const int blocks = K / 16;
     if (threadIdx.x == 0) s_max = 0u;
     ptx::griddep_launch_dependents();      // the GEMV behind this kernel may set itself up and start streaming weights
     ptx::griddep_wait();                   // A is the output of the kernel before this one
     __syncthreads();
-    if (m == M) {
-        // padding columns M*T .. NCp-1: zero codes, zero scales
-        const int pad0 = M * kTerms;
-        const long long row_bytes = K / 2;
-        for (int c = pad0; c < NCp; ++c)
-            for (long long i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
-                reinterpret_cast<uint4*>(codes + (size_t)c * row_bytes)[i] = make_uint4(0u, 0u, 0u, 0u);
-        // every scale byte no token column owns: the rest of the atoms' rows and the bytes of absent column groups
-        for (int b = threadIdx.x; b < blocks; b += blockDim.x)
-            for (int c = pad0; c < 128; ++c) sfb[fp4::sfb_offset(b, c)] = 0;
-        return;
-    }
     const uint4* src = reinterpret_cast<const uint4*>(A + (size_t)m * a_stride);
     unsigned int amax = 0;
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    for (int i = threadIdx.x; i < K / 8; i += kPreThreads) {
         const uint4 x = __ldg(src + i);
         const uint32_t v[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
@@ -84,54 +78,56 @@ act_to_fp4_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, int M
     int se = 263 - (int)(s_max >> 7);
     se = se < 1 ? 1 : (se > 254 ? 254 : se);
     const float c = __uint_as_float((uint32_t)se << 23);
-    if (threadIdx.x == 0) unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
-    for (int b = threadIdx.x; b < blocks; b += blockDim.x) {
-        const uint4 x0 = __ldg(src + 2 * b), x1 = __ldg(src + 2 * b + 1);
-        const uint32_t v[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-        float r[16];
-        float bmax = 0.0f;
+    if (blockIdx.x == 0 && threadIdx.x == 0) unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
+    const int b = blockIdx.x * kSliceBlocks + (threadIdx.x >> 2), part = threadIdx.x & 3;     // block, quarter of it
+    const bool live = b < blocks;                          // whole quads are live or not: the shuffles below stay converged
+    float r[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
+        const uint2 x = __ldg(reinterpret_cast<const uint2*>(src + 2 * b) + part);
+        r[0] = __uint_as_float(x.x << 16) * c;
+        r[1] = __uint_as_float(x.x & 0xFFFF0000u) * c;
+        r[2] = __uint_as_float(x.y << 16) * c;
+        r[3] = __uint_as_float(x.y & 0xFFFF0000u) * c;
+    }
+    float bmax = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+    bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+    bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+    if (!live) return;
+    // p0: smallest p with bmax <= 6 * 2^p, clamped to the unsigned E4M3 range of powers of two
+    int p0 = -9;
+    if (bmax > 0.0f && bmax < 3.0e38f) {
+        const uint32_t u = __float_as_uint(bmax * (1.0f / 6.0f));
+        p0 = (int)(u >> 23) - 127 + ((u & 0x7FFFFFu) ? 1 : 0);
+        if (bmax > 6.0f * __uint_as_float((uint32_t)(p0 + 127) << 23)) ++p0;     // 1/6 is not exact: never let the block exceed 6 s_0
+    }
+    p0 = p0 < -9 ? -9 : (p0 > 8 ? 8 : p0);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            r[2 * q] = __uint_as_float(v[q] << 16) * c;
-            r[2 * q + 1] = __uint_as_float(v[q] & 0xFFFF0000u) * c;
-            bmax = fmaxf(bmax, fmaxf(fabsf(r[2 * q]), fabsf(r[2 * q + 1])));
-        }
-        // p0: smallest p with bmax <= 6 * 2^p, clamped to the unsigned E4M3 range of powers of two
-        int p0 = -9;
-        if (bmax > 0.0f && bmax < 3.0e38f) {
-            const uint32_t u = __float_as_uint(bmax * (1.0f / 6.0f));
-            p0 = (int)(u >> 23) - 127 + ((u & 0x7FFFFFu) ? 1 : 0);
-            if (bmax > 6.0f * __uint_as_float((uint32_t)(p0 + 127) << 23)) ++p0;     // 1/6 is not exact: never let the block exceed 6 s_0
-        }
-        p0 = p0 < -9 ? -9 : (p0 > 8 ? 8 : p0);
+    for (int t = 0; t < kTerms; ++t) {
+        int p = p0 - (t == 0 ? 0 : 2 + 3 * (t - 1));
+        p = p < -9 ? -9 : p;
+        const float s = __uint_as_float((uint32_t)(p + 127) << 23), inv = __uint_as_float((uint32_t)(127 - p) << 23);
+        uint32_t w = 0u;
 #pragma unroll
-        for (int t = 0; t < kTerms; ++t) {
-            int p = p0 - (t == 0 ? 0 : 2 + 3 * (t - 1));
-            p = p < -9 ? -9 : p;
-            const float s = __uint_as_float((uint32_t)(p + 127) << 23), inv = __uint_as_float((uint32_t)(127 - p) << 23);
-            uint32_t w[2] = {0u, 0u};
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const uint32_t byte = cvt_e2m1x2(r[2 * q] * inv, r[2 * q + 1] * inv) & 0xFFu;
-                const float2 d = e2m1x2_to_float2(byte);
-                r[2 * q] -= d.x * s;
-                r[2 * q + 1] -= d.y * s;
-                w[q >> 2] |= byte << (8 * (q & 3));
-            }
-            const int col = m * kTerms + t;
-            *reinterpret_cast<uint2*>(codes + (size_t)col * (K / 2) + (size_t)b * 8) = make_uint2(w[0], w[1]);
-            sfb[fp4::sfb_offset(b, col)] = (uint8_t)ue4m3_pow2(p);
+        for (int q = 0; q < 2; ++q) {
+            const uint32_t byte = cvt_e2m1x2(r[2 * q] * inv, r[2 * q + 1] * inv) & 0xFFu;
+            const float2 d = e2m1x2_to_float2(byte);
+            r[2 * q] -= d.x * s;
+            r[2 * q + 1] -= d.y * s;
+            w |= byte << (8 * q);
         }
+        const int col = m * kTerms + t;
+        *reinterpret_cast<uint16_t*>(codes + (size_t)col * (K / 2) + (size_t)b * 8 + part * 2) = (uint16_t)w;
+        if (part == 0) sfb[fp4::sfb_offset(b, col, groups)] = (uint8_t)ue4m3_pow2(p);
     }
 }
 
 }  // namespace
 
-cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int NCp, void* codes, void* sfb,
+cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int groups, void* codes, void* sfb,
                               float* unscale, cudaStream_t s) {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(M + 1);
-    cfg.blockDim = dim3(K / 16 >= 512 ? 512 : (K / 16 + 31) / 32 * 32);
+    cfg.gridDim = dim3((K / 16 + kSliceBlocks - 1) / kSliceBlocks, M);
+    cfg.blockDim = dim3(kPreThreads);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -139,7 +135,7 @@ cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, i
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, act_to_fp4_kernel, static_cast<const __nv_bfloat16*>(A), a_stride, M, K, NCp,
+    return cudaLaunchKernelEx(&cfg, act_to_fp4_kernel, static_cast<const __nv_bfloat16*>(A), a_stride, K, groups,
                               static_cast<uint8_t*>(codes), static_cast<uint8_t*>(sfb), unscale);
 }
 

@@ -12,16 +12,17 @@
 //     shared-memory ring with plain tiled TMA (128-byte swizzle for the codes: the K-major operand
 //     layout of the tensor core; no multicast); the half-units, row-tile-major, are split evenly
 //     over the CTAs (stream-K);
-//   * warps 4-7 re-order the 2 KB of block scales of each half-unit into the 512-byte atoms
-//     tcgen05.cp copies into tensor memory (row r of the MMA wants its four scales of a 64-k MMA in
-//     lane r % 32, column r / 32); that is the only touch the weights get;
-//   * one thread of warp 1 copies the atoms into tensor memory and issues four
-//     tcgen05.mma (128 rows x NCp columns x 64 k) per half-unit, accumulating FP32 in tensor
-//     memory; tcgen05.commit recycles the ring stage;
+//   * warps 4-7 move the 2 KB of block scales of each half-unit from shared into tensor memory
+//     (tcgen05.st: row r of the MMA wants the four scales of a 64-k MMA in lane r % 32, column r / 32,
+//     in every lane quarter), together with the activations' scales of the same k range; that is
+//     the only touch the weights get.  (tcgen05.cp from re-ordered atoms does the same, but its four
+//     copies per half-unit queue up in front of the MMAs in the tensor pipe: 5.7 TB/s measured);
+//   * one thread of warp 1 issues four tcgen05.mma (128 rows x NCp columns x 64 k) per half-unit,
+//     accumulating FP32 in tensor memory; tcgen05.commit recycles the ring stage;
 //   * the activations are the B operand: a pre-pass (act_fp4.cu) expands every BF16 token into five
 //     NVFP4 term rows whose sum reproduces it to 1e-4 of each block's largest element; the CTA's k
-//     range of the codes is loaded once by warp 2 and stays resident in shared memory, their block
-//     scales are written straight into tensor memory by warps 8-11 (tcgen05.st) and stay there;
+//     range of the codes is loaded once by warp 2 and stays resident in shared memory, next to their
+//     block scales (copied in by warps 8-11 before their first accumulator arrives);
 //   * warps 8-11 read the accumulator (thread = weight row), add the five columns of each token,
 //     undo the token scale, apply 1/global_scale and the residual in FP32 and round once.  A row
 //     tile split over several CTAs is finished by the CTA holding its first half-unit: the others
@@ -51,14 +52,14 @@ using namespace umma;
 constexpr int kRT = 128;                           // weight rows per tile (UMMA M, tensor-memory lanes)
 constexpr int kKC = 256;                           // k per half-unit
 constexpr int kPackedBytes = kRT * kKC / 2;        // 16 KB
-constexpr int kScaleBytes = kRT * kKC / 16;        // 2 KB raw scales [row][16], and 2 KB re-ordered into four atoms
+constexpr int kScaleBytes = kRT * kKC / 16;        // 2 KB of scales [row][16] per half-unit
 constexpr int kMaxStages = 10;
 constexpr int kThreads = 12 * 32;
 constexpr int kEpiThreads = 4 * 32;
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int kAccStride = 64;                     // tensor-memory columns per accumulator (NCp <= 48)
-constexpr int kSfaCol = 2 * kAccStride;            // two buffers of 16 columns for the weights' scales
-constexpr int kSfbCol = kSfaCol + 32;              // the activations' scales, resident
+constexpr int kSfCol = 2 * kAccStride;             // per half-unit of the ring 32 columns: 16 of the weights' scales, 16 of the activations'
+constexpr int kMaxRingHalfUnits = (512 - kSfCol) / 32;   // 12
 constexpr int kMaxGrid = 160;                      // CTAs whose pair slots fit the kernel's 2 MB of scratch
 constexpr int kPairTokens = fp4::kMaxTokens;       // token rows of a CTA's pair slot (9 KB per CTA)
 static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= (2u << 20), "pair slots");
@@ -67,12 +68,12 @@ struct Fp4Params {
     const __nv_bfloat16* residual;
     __nv_bfloat16* C;
     const float* unscale;           // per token: 1 / c of the pre-pass
-    const unsigned char* sfb;       // the pre-pass's scale atoms: [K/256][4 MMAs][512]
+    const unsigned char* sfb;       // the pre-pass's block scales: [K/256][column groups of 32][32 lanes][16 bytes]
     unsigned char* scratch;         // status word at 0, launch counter at 64
     unsigned char* pairs;           // [CTA][kPairTokens][128 rows] x {FP32 value, tag}
     float inv_gs;
     int M, N, K;
-    int NCp;                        // MMA columns (tokens x 5 padded to 16)
+    int NCp, groups;                // MMA columns (tokens x 5 padded to 16), groups of 32 of them
     int units, kchunks;
     int stages, hps;                // ring depth, half-units per stage (1 or 2)
     int slots, act_all;             // resident activation chunks; 1 = slot index is the k-chunk
@@ -90,13 +91,6 @@ __device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t adesc, uint64
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
-}
-// Source of a scale copy: 32 rows x 16 bytes, contiguous (K-major, no swizzle: 8-row groups 128 bytes apart).
-__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -127,11 +121,11 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     unsigned char* s_w = smem;                                              // stages x hps x 16 KB, 1024-aligned
     unsigned char* s_b = s_w + stages * hps * kPackedBytes;                 // slots x NCp x 128 B, 1024-aligned (NCp % 8 == 0)
     unsigned char* s_raw = s_b + p.slots * b_bytes;                         // stages x hps x 2 KB: scales as they lie in HBM
-    unsigned char* s_sfa = s_raw + stages * hps * kScaleBytes;              // stages x hps x 2 KB: the same, as atoms
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_sfa + stages * hps * kScaleBytes);
+    unsigned char* s_sfb = s_raw + stages * hps * kScaleBytes;              // slots x groups x 512 B: the activations' scales
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_sfb + p.slots * p.groups * 512);
     uint64_t* empty_bar = full_bar + kMaxStages;
-    uint64_t* sfa_bar = empty_bar + kMaxStages;      // atoms of a stage written
-    uint64_t* b_bar = sfa_bar + kMaxStages;          // [0] resident activation codes loaded, [1] their scales in tensor memory
+    uint64_t* sfa_bar = empty_bar + kMaxStages;      // scales of a stage are in tensor memory
+    uint64_t* b_bar = sfa_bar + kMaxStages;          // [0] resident activation codes loaded, [1] their scales in shared memory
     uint64_t* tfull = b_bar + 2;                     // [2] accumulator complete
     uint64_t* tempty = tfull + 2;                    // [2] accumulator read
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + 2);
@@ -213,9 +207,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         if (lane == 0) {
             const uint32_t idesc = fp4_idesc(p.NCp);
             ptx::mbar_wait(&b_bar[0], 0u, s_abort, status, 0xA10u);
-            ptx::mbar_wait(&b_bar[1], 0u, s_abort, status, 0xA11u);
-            tc_fence_after();
-            int stage = 0, acc = 0, sfbuf = 0;
+            int stage = 0, acc = 0;
             uint32_t ph = 0, pt = 0;
             int hu = u_begin, kc = kc_begin;
             while (hu < u_end) {
@@ -231,22 +223,17 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     tc_fence_after();
                     for (int h = 0; h < cnt; ++h) {
                         const int slot = p.act_all ? kc + h : (hu - u_begin) + h;
-                        const uint32_t sfa_t = tmem_base + kSfaCol + 16 * sfbuf;
-                        const uint32_t atoms = ptx::smem_u32(s_sfa + (stage * hps + h) * kScaleBytes);
-#pragma unroll
-                        for (int s = 0; s < 4; ++s) tmem_cp_sf(sfa_t + 4 * s, sf_desc(atoms + 512 * s));
+                        const uint32_t sfa_t = tmem_base + kSfCol + 32 * (uint32_t)(stage * hps + h), sfb_t = sfa_t + 16;
                         const uint32_t a_addr = ptx::smem_u32(s_w + (stage * hps + h) * kPackedBytes);
                         const uint32_t b_addr = ptx::smem_u32(s_b + slot * b_bytes);
-                        const uint32_t sfb_t = tmem_base + kSfbCol + (uint32_t)(slot * 16);
 #pragma unroll
                         for (int s = 0; s < 4; ++s) {
                             umma_fp4(d_tmem, umma_desc_sw128(a_addr + 32 * s), umma_desc_sw128(b_addr + 32 * s), idesc,
                                      sfa_t + 4 * s, sfb_t + 4 * s, first ? 0u : 1u);
                             first = false;
                         }
-                        sfbuf ^= 1;
                     }
-                    umma_commit(&empty_bar[stage]);        // codes, raw scales and atoms of the stage are free once these MMAs have read them
+                    umma_commit(&empty_bar[stage]);        // the stage's codes and its scales in tensor memory are free once these MMAs have read them
                     hu += cnt;
                     kc += cnt;
                     if (++stage == stages) { stage = 0; ph ^= 1u; }
@@ -258,8 +245,13 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             }
         }
     } else if (warp >= 4 && warp < 8) {
-        // ------------------------------------------------------------------ scales into atoms: thread = weight row
-        const int r = tid - 4 * 32, r0 = r & 31, r1 = r >> 5;
+        // ------------------------------------------------------------------ scales into tensor memory
+        // Warp q (= warp id % 4) writes lane quarter q; the four warps write the same data, which is the
+        // replication the tensor core wants.  Lane L holds, for MMA s of the half-unit, the scale words of weight
+        // rows L, L + 32, L + 64, L + 96 in columns 4 s .. 4 s + 3, and the words of activation columns L and
+        // 32 + L in columns 16 + 4 s and 17 + 4 s (an MMA's scale base sits on a multiple of four columns).
+        const int q = warp - 4;
+        ptx::mbar_wait(&b_bar[1], 0u, s_abort, status, 0xA11u);      // the activations' scales are in shared memory
         int stage = 0;
         uint32_t ph = 0;
         int hu = u_begin, kc = kc_begin;
@@ -270,14 +262,30 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 const int cnt = (seg_end - hu) >= hps ? hps : 1;
                 ptx::mbar_wait(&full_bar[stage], ph, s_abort, status, 0xA40u + (unsigned)stage);
                 for (int h = 0; h < cnt; ++h) {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(s_raw + (stage * hps + h) * kScaleBytes + r * 16);
-                    uint32_t* at = reinterpret_cast<uint32_t*>(s_sfa + (stage * hps + h) * kScaleBytes) + r0 * 4 + r1;
-                    at[0] = raw.x & 0x7F7F7F7Fu;           // bit 7 carries nothing (src/engine/dense_gemm_fp4_sm110.cu:30-41)
-                    at[128] = raw.y & 0x7F7F7F7Fu;
-                    at[256] = raw.z & 0x7F7F7F7Fu;
-                    at[384] = raw.w & 0x7F7F7F7Fu;
+                    const int slot = p.act_all ? kc + h : (hu - u_begin) + h;
+                    const unsigned char* raw = s_raw + (stage * hps + h) * kScaleBytes + lane * 16;
+                    uint32_t ra[16], rb[16];
+#pragma unroll
+                    for (int r1 = 0; r1 < 4; ++r1) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(raw + r1 * 512);
+                        ra[r1] = x.x & 0x7F7F7F7Fu;            // bit 7 carries nothing (src/engine/dense_gemm_fp4_sm110.cu:30-41)
+                        ra[4 + r1] = x.y & 0x7F7F7F7Fu;
+                        ra[8 + r1] = x.z & 0x7F7F7F7Fu;
+                        ra[12 + r1] = x.w & 0x7F7F7F7Fu;
+                    }
+                    const uint4 b0 = *reinterpret_cast<const uint4*>(s_sfb + (slot * p.groups) * 512 + lane * 16);
+                    uint4 b1 = make_uint4(0u, 0u, 0u, 0u);
+                    if (p.groups > 1) b1 = *reinterpret_cast<const uint4*>(s_sfb + (slot * p.groups + 1) * 512 + lane * 16);
+                    rb[0] = b0.x; rb[1] = b1.x; rb[2] = 0u; rb[3] = 0u;
+                    rb[4] = b0.y; rb[5] = b1.y; rb[6] = 0u; rb[7] = 0u;
+                    rb[8] = b0.z; rb[9] = b1.z; rb[10] = 0u; rb[11] = 0u;
+                    rb[12] = b0.w; rb[13] = b1.w; rb[14] = 0u; rb[15] = 0u;
+                    const uint32_t t = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kSfCol + 32 * (stage * hps + h));
+                    tmem_st16(t, ra);
+                    tmem_st16(t + 16, rb);
                 }
-                ptx::fence_proxy_async_smem();              // generic-proxy stores -> visible to tcgen05.cp
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&sfa_bar[stage]);
                 hu += cnt;
@@ -291,33 +299,28 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         const int ew = warp - 8;                              // tensor-memory lanes 32 ew .. +31 (= warp id % 4)
         const int te = ew * 32 + lane;
         ptx::griddep_wait();                                  // C, the residual and the scratch belong to earlier kernels until now
-        if (te == 0) *s_epoch = ptx::take_launch_epoch(p.scratch);
-        ptx::named_barrier_sync(1, kEpiThreads);
-        const unsigned int epoch = *s_epoch;
+        // this launch's tag for the split-tile pairs: one atomic per CTA on one address, about a microsecond
+        // under contention, so it is left in flight while the scales are copied
+        unsigned int epoch_taken = 0;
+        if (te == 0) epoch_taken = ptx::take_launch_epoch(p.scratch);
         unsigned char* pairs = p.pairs;
         {
-            // The activations' block scales into tensor memory, for the CTA's whole k range, once: per resident
-            // chunk four atoms of 32 rows x 16 bytes (one per 64-k MMA); lane L of every lane quarter gets row L
-            // of each atom as four columns.  The four warps write the same data into their own quarters, which
-            // is the replication the tensor core expects.
+            // The activations' block scales of the CTA's k range into shared memory (512 bytes per resident chunk
+            // and column group, as the pre-pass left them); the warps of the scale path wait for this.
             const int kc0 = p.act_all ? 0 : kc_begin;
-            for (int j = 0; j < p.slots; ++j) {
+            const int words = p.slots * p.groups * 32;              // 16-byte words
+            for (int i = te; i < words; i += kEpiThreads) {
+                const int j = i / (p.groups * 32), rest = i - j * (p.groups * 32);
                 int kcj = kc0 + j;
                 if (kcj >= p.kchunks) kcj -= p.kchunks;
-                const uint4* src = reinterpret_cast<const uint4*>(p.sfb + (size_t)kcj * 2048 + (size_t)lane * 16);
-                uint32_t r[16];
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const uint4 x = __ldcg(src + s * 32);
-                    r[4 * s] = x.x; r[4 * s + 1] = x.y; r[4 * s + 2] = x.z; r[4 * s + 3] = x.w;
-                }
-                tmem_st16(tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(kSfbCol + 16 * j), r);
+                reinterpret_cast<uint4*>(s_sfb)[i] = __ldcg(reinterpret_cast<const uint4*>(p.sfb + (size_t)kcj * p.groups * 512) + rest);
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&b_bar[1]);
         }
+        if (te == 0) *s_epoch = epoch_taken;
+        ptx::named_barrier_sync(1, kEpiThreads);
+        const unsigned int epoch = *s_epoch;
         int acc = 0;
         uint32_t pt = 0;
         int hu = u_begin, tile = u_begin / p.kchunks, kc = kc_begin;
@@ -428,6 +431,7 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
     p = Fp4Params{};
     p.M = a.M; p.N = a.N; p.K = a.K;
     p.NCp = (a.M * fp4::kTerms + 15) / 16 * 16;
+    p.groups = (p.NCp + 31) / 32;
     p.kchunks = a.K / kKC;
     const long long units = (long long)((a.N + kRT - 1) / kRT) * p.kchunks;
     if (units > 0x7fffffffLL || units < 1) return false;
@@ -437,15 +441,15 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
     const int max_span = (p.units + grid - 1) / grid;
     p.act_all = p.kchunks <= max_span ? 1 : 0;
     p.slots = p.act_all ? p.kchunks : max_span;
-    const long long resident = (long long)p.slots * (p.NCp * 128);
-    if (16 * p.slots > 512 - kSfbCol) return false;                // tensor-memory columns for the activations' scales (16 per chunk)
+    const long long resident = (long long)p.slots * (p.NCp * 128 + p.groups * 512);
     const long long avail = kSmemBudget - kFixedSmem - resident;
-    const int unit = kPackedBytes + 2 * kScaleBytes;                // codes + raw scales + atoms
+    const int unit = kPackedBytes + kScaleBytes;                    // codes + scales
     // Two half-units per stage when four such stages fit (one issuing thread keeps HBM busier with larger stages)
     p.hps = avail / (2 * unit) >= 4 ? 2 : 1;
     long long stages = avail / ((long long)p.hps * unit);
     if (stages < 3) return false;
     if (stages > kMaxStages) stages = kMaxStages;
+    if (stages * p.hps > kMaxRingHalfUnits) stages = kMaxRingHalfUnits / p.hps;     // 32 tensor-memory columns of scales per half-unit of the ring
     p.stages = (int)stages;
     out->grid = grid;
     out->smem = kFixedSmem + (int)stages * p.hps * unit + (int)resident;
@@ -465,9 +469,9 @@ bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
     return plan_fp4(a, dev, &pl);
 }
 
-// codes [48, K/2] + scale atoms [K/256][4][512] + 16 floats
+// codes [48, K/2] + block scales [K/256][2][512] + 16 floats
 size_t decode_fp4_scratch_bytes(int K) {
-    return round256((size_t)48 * (K / 2)) + round256((size_t)(K / kKC) * 2048) + 256;
+    return round256((size_t)48 * (K / 2)) + round256((size_t)(K / kKC) * 1024) + 256;
 }
 
 cudaError_t configure_decode_fp4() {
@@ -481,7 +485,7 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     Fp4Params& p = pl.p;
     unsigned char* codes = static_cast<unsigned char*>(act);
     unsigned char* sfb = codes + round256((size_t)48 * (a.K / 2));
-    float* unscale = reinterpret_cast<float*>(sfb + round256((size_t)p.kchunks * 2048));
+    float* unscale = reinterpret_cast<float*>(sfb + round256((size_t)p.kchunks * 1024));
     CUtensorMap tmp, tms, tma;
     if (!make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT,
                          CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -490,7 +494,7 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
         !make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, (uint64_t)a.K / 2, (uint64_t)p.NCp, 128,
                          (uint32_t)p.NCp, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
-    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, p.NCp, codes, sfb, unscale, s);
+    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, p.groups, codes, sfb, unscale, s);
     if (e != cudaSuccess) return e;
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.C = static_cast<__nv_bfloat16*>(a.C);

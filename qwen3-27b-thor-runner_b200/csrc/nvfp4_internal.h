@@ -114,16 +114,15 @@ namespace fp4 {
 constexpr int kTerms = 5;          // NVFP4 term rows per token (act_fp4.cu)
 constexpr int kMaxTokens = 9;      // 9 x 5 = 45 columns <= 48
 // Where the block scale of column c (token * kTerms + term), 16-element block b along K, sits in the
-// scale buffer.  The buffer holds, per 256-k chunk, four 512-byte atoms (one per 64-k MMA), each 32 rows
-// x 16 bytes: an MMA reads, for column c, lane c % 32 of tensor-memory column (base + c / 32), bytes 0..3
-// = its four blocks, and wants the base on a multiple of four columns -- so row c % 32 of the atom, bytes
-// 4 (c / 32) .. + 3.
-__host__ __device__ inline size_t sfb_offset(int b, int c) {
+// scale buffer: [256-k chunk][column group c / 32][lane c % 32][64-k MMA of the chunk][block of the MMA],
+// i.e. per chunk and column group one 16-byte word per tensor-memory lane, which the GEMV loads with one
+// 128-bit access and spreads over the four tensor-memory columns the four MMAs of the chunk read.
+__host__ __device__ inline size_t sfb_offset(int b, int c, int groups) {
     const int kc = b >> 4, s = (b >> 2) & 3, kb = b & 3;
-    return (size_t)kc * 2048 + (size_t)s * 512 + (size_t)(c & 31) * 16 + (size_t)(c >> 5) * 4 + kb;
+    return ((size_t)kc * groups + (size_t)(c >> 5)) * 512 + (size_t)(c & 31) * 16 + (size_t)s * 4 + kb;
 }
 }  // namespace fp4
-cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int NCp, void* codes, void* sfb,
+cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int groups, void* codes, void* sfb,
                               float* unscale, cudaStream_t s);
 bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev);
 size_t decode_fp4_scratch_bytes(int K);       // codes + scale atoms + per-token factors of the activation pre-pass
