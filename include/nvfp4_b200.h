@@ -68,7 +68,17 @@ int nvfp4_workspace_bytes(int max_M, int max_N, int max_K, size_t* bytes);
 const char* nvfp4_status_string(int status);
 
 /* Kernel-selection knobs for tests and benchmarks.
- *   "decode_impl":  0 = auto, 1 = scalar CUDA-core GEMV, 2 = TMA ring + MMA GEMV
+ *   "decode_impl":  0 = auto, 1 = scalar CUDA-core GEMV, 2 = TMA ring + mma.sync GEMV,
+ *                   3 = the NVFP4 tensor-core GEMV wherever it applies (1..9 tokens, K % 256 == 0,
+ *                   plain [M, K] activations), the auto choice elsewhere
+ *   "fp4_native":   1 (default) = in auto mode "fp4_min_m" (default 1) .. 9 tokens take the NVFP4
+ *                   tensor-core GEMV: tcgen05.mma kind::mxf4nvf4 on the packed weights as they lie
+ *                   in HBM, the BF16 activations expanded into six NVFP4 terms per token (five for
+ *                   3, 6 and 9 tokens); their sum reproduces a token to 1e-5 (8e-5) of each 16-element
+ *                   block's largest value, whose own BF16 rounding step is 4e-3.  A scale byte 0x7F / 0xFF is NaN to the
+ *                   tensor core, as it is in FP8 E4M3; every other kernel, like the reference's
+ *                   table-free decoder (dense_gemm_fp4_sm110.cu:30-41), reads it as 480.  No finite
+ *                   FP8 E4M3 value encodes to it.  0 = off
  *   "prefill_impl": 0 = auto, 1 = dequant-to-workspace + CUDA-core GEMM (debug),
  *                   2 = fused dequant + tcgen05 GEMM
  *   "decode_max_m": largest M routed to the GEMV path (default 16)

@@ -23,7 +23,8 @@ struct nvfp4_handle {
     int decode_max_m = 16;
     int wide_gemv = 1;                           // 9..16 tokens: one launch of the wide GEMV kernel
     int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
-    int fp4_native = 1;                          // up to 9 tokens: the NVFP4 tensor-core GEMV (weights untouched, activations as NVFP4 terms)
+    int fp4_native = 1;                          // the NVFP4 tensor-core GEMV (weights untouched, activations as NVFP4 terms) ...
+    int fp4_min_m = 1;                           // ... from this token count on (up to 9)
     unsigned long long launches = 0;
 };
 
@@ -107,17 +108,21 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
+    // One token on a small matrix is the one case where the mma.sync GEMV, with no pre-pass in front, is still ahead (by 0.3 us).
+    const bool small_single = a.M == 1 && (size_t)a.N * a.K / 2 < (24u << 20);
+    const bool fp4_wanted = a.M <= h->decode_max_m &&
+                            (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m && !small_single));
+    if (fp4_wanted && !other_options_but_f32(a) && decode_fp4_supported(a, h->dev) &&
+        decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
+        int nl = 0;
+        cudaError_t e = launch_decode_fp4(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     if (other_options || ((a.swiglu_out || a.px) && !wide_ok)) {
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;
         int nl = 0;
         cudaError_t e = launch_decode_mma(a, h->dev, h->workspace, &nl, s);
-        h->launches += (unsigned long long)nl;
-        return cuda_status(e);
-    }
-    if (fast_path_wanted && h->fp4_native && !other_options_but_f32(a) && decode_fp4_supported(a, h->dev) &&
-        decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
-        int nl = 0;
-        cudaError_t e = launch_decode_fp4(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s);
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
@@ -140,7 +145,7 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
     if (a.M <= h->decode_max_m) {
         int impl = h->decode_impl;
         const bool fast_ok = decode_mma_supported(a) && decode_mma_fits(a, h->dev);
-        if (impl == 0) impl = fast_ok ? 2 : 1;
+        if (impl == 0 || impl == 3) impl = fast_ok ? 2 : 1;
         if (impl == 2) {
             if (!fast_ok) return NVFP4_E_SHAPE;
             size_t need = decode_mma_scratch_bytes(a, h->dev);
@@ -273,7 +278,7 @@ int nvfp4_destroy(nvfp4_handle* h) {
 int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     if (!h || !name) return NVFP4_E_NULL;
     if (!std::strcmp(name, "decode_impl")) {
-        if (value < 0 || value > 2) return NVFP4_E_OPTION;
+        if (value < 0 || value > 3) return NVFP4_E_OPTION;
         h->decode_impl = value;
     } else if (!std::strcmp(name, "prefill_impl")) {
         if (value < 0 || value > 2) return NVFP4_E_OPTION;
@@ -287,6 +292,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "fp4_native")) {
         if (value < 0 || value > 1) return NVFP4_E_OPTION;
         h->fp4_native = value;
+    } else if (!std::strcmp(name, "fp4_min_m")) {
+        if (value < 1 || value > 16) return NVFP4_E_OPTION;
+        h->fp4_min_m = value;
     } else if (!std::strcmp(name, "skinny_min_m")) {
         if (value < 1 || value > 129) return NVFP4_E_OPTION;
         h->skinny_min_m = value;
@@ -313,6 +321,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "prefill_stream_k")) *value = h->dev.prefill_stream_k;
     else if (!std::strcmp(name, "wide_gemv")) *value = h->wide_gemv;
     else if (!std::strcmp(name, "fp4_native")) *value = h->fp4_native;
+    else if (!std::strcmp(name, "fp4_min_m")) *value = h->fp4_min_m;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;

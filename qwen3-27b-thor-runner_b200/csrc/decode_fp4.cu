@@ -19,11 +19,11 @@
 //     copies per half-unit queue up in front of the MMAs in the tensor pipe: 5.7 TB/s measured);
 //   * one thread of warp 1 issues four tcgen05.mma (128 rows x NCp columns x 64 k) per half-unit,
 //     accumulating FP32 in tensor memory; tcgen05.commit recycles the ring stage;
-//   * the activations are the B operand: a pre-pass (act_fp4.cu) expands every BF16 token into five
-//     NVFP4 term rows whose sum reproduces it to 1e-4 of each block's largest element; the CTA's k
+//   * the activations are the B operand: a pre-pass (act_fp4.cu) expands every BF16 token into six
+//     (five for 3, 6 and 9 tokens) NVFP4 term rows whose sum reproduces it to 1e-5 (8e-5) of each block's largest element; the CTA's k
 //     range of the codes is loaded once by warp 2 and stays resident in shared memory, next to their
 //     block scales (copied in by warps 8-11 before their first accumulator arrives);
-//   * warps 8-11 read the accumulator (thread = weight row), add the five columns of each token,
+//   * warps 8-11 read the accumulator (thread = weight row), add the term columns of each token,
 //     undo the token scale, apply 1/global_scale and the residual in FP32 and round once.  A row
 //     tile split over several CTAs is finished by the CTA holding its first half-unit: the others
 //     publish FP32 partials as {value, launch tag} pairs (8-byte single transactions, the tag
@@ -73,7 +73,7 @@ struct Fp4Params {
     unsigned char* pairs;           // [CTA][kPairTokens][128 rows] x {FP32 value, tag}
     float inv_gs;
     int M, N, K;
-    int NCp, groups;                // MMA columns (tokens x 5 padded to 16), groups of 32 of them
+    int NCp, groups;                // MMA columns (tokens x terms padded to 16), groups of 32 of them
     int units, kchunks;
     int stages, hps;                // ring depth, half-units per stage (1 or 2)
     int slots, act_all;             // resident activation chunks; 1 = slot index is the k-chunk
@@ -111,6 +111,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+template <int TERMS>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ Fp4Params p) {
@@ -346,8 +347,8 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                     tmem_ld16(t_addr + c0, r);
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const int c = c0 + i;                 // column c = token * 5 + term (compile-time after unrolling)
-                        if (c / fp4::kTerms < fp4::kMaxTokens) v[c / fp4::kTerms] += __uint_as_float(r[i]);
+                        const int c = c0 + i;                 // column c = token * TERMS + term (compile-time after unrolling)
+                        if (c / TERMS < fp4::kMaxTokens) v[c / TERMS] += __uint_as_float(r[i]);
                     }
                 }
             }
@@ -430,7 +431,7 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
     Fp4Params& p = out->p;
     p = Fp4Params{};
     p.M = a.M; p.N = a.N; p.K = a.K;
-    p.NCp = (a.M * fp4::kTerms + 15) / 16 * 16;
+    p.NCp = (a.M * fp4::terms_for(a.M) + 15) / 16 * 16;
     p.groups = (p.NCp + 31) / 32;
     p.kchunks = a.K / kKC;
     const long long units = (long long)((a.N + kRT - 1) / kRT) * p.kchunks;
@@ -475,7 +476,9 @@ size_t decode_fp4_scratch_bytes(int K) {
 }
 
 cudaError_t configure_decode_fp4() {
-    return cudaFuncSetAttribute(decode_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = configure_large_smem(decode_fp4_kernel<5>, kSmemBudget);
+    if (e != cudaSuccess) return e;
+    return configure_large_smem(decode_fp4_kernel<6>, kSmemBudget);
 }
 
 cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t pairs_offset, void* act,
@@ -494,7 +497,8 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
         !make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, (uint64_t)a.K / 2, (uint64_t)p.NCp, 128,
                          (uint32_t)p.NCp, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
-    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, p.groups, codes, sfb, unscale, s);
+    const int terms = fp4::terms_for(a.M);
+    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, terms, p.groups, codes, sfb, unscale, s);
     if (e != cudaSuccess) return e;
     p.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.C = static_cast<__nv_bfloat16*>(a.C);
@@ -514,7 +518,8 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, decode_fp4_kernel, tmp, tms, tma, p);
+    e = terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6>, tmp, tms, tma, p)
+                   : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5>, tmp, tms, tma, p);
     if (launches) *launches = 2;
     return e;
 }

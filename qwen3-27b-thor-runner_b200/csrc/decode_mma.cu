@@ -777,9 +777,9 @@ size_t decode_mma_scratch_bytes(const LinearArgs&, const nvfp4_device_info& dev)
 }
 
 cudaError_t configure_decode_mma() {
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    cudaError_t e = configure_large_smem(decode_mma_kernel<2, false>, kSmemBudget);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(decode_mma_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    return configure_large_smem(decode_mma_kernel<2, true>, kSmemBudget);
 }
 
 namespace {

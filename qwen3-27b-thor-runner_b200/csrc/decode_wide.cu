@@ -411,7 +411,7 @@ bool decode_wide_supported(const LinearArgs& a) {
 size_t decode_wide_scratch_bytes(int sm_count) { return kPartialOffset + (size_t)sm_count * kTokens * kUnitRows * 8; }
 
 cudaError_t configure_decode_wide() {
-    return cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    return configure_large_smem(decode_wide_kernel, kSmemBudget);
 }
 
 // scratch: the handle workspace ([0, 16 KB) status word, then the partial pairs);

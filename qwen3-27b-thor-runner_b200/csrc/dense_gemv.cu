@@ -324,7 +324,7 @@ bool dense_gemv_supported(const DenseArgs& a, const nvfp4_device_info& dev) {
 }
 
 cudaError_t configure_dense_gemv() {
-    return cudaFuncSetAttribute(dense_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmem);
+    return configure_large_smem(dense_gemv_kernel, kDenseSmem);
 }
 
 // scratch: the handle workspace (status word at 0, pairs at dev.gemv_pairs_offset, shared with the

@@ -109,11 +109,28 @@ int create_decode_chain(const LinearArgs* linears, int n, const nvfp4_device_inf
 cudaError_t launch_decode_chain(DecodeChain* c, cudaStream_t s);
 void destroy_decode_chain(DecodeChain* c);
 
+// Opt a kernel in to `bytes` of dynamic shared memory and pin its carve-out to the largest one.  Left to
+// itself the driver picks the smallest carve-out that holds one CTA; a launch that lands just under a
+// carve-out step (196 KB, say) then leaves no room for the small kernels launched next to it with
+// programmatic stream serialization (activation pre-passes, norms), and those and the next GEMV's
+// CTAs wait for each other's SMs: 4 us on a 10 us call, measured.
+template <class Kernel>
+inline cudaError_t configure_large_smem(Kernel kernel, int bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
 // --- act_fp4.cu / decode_fp4.cu: the GEMV on the NVFP4 tensor-core path (tcgen05.mma kind::mxf4nvf4).
 namespace fp4 {
-constexpr int kTerms = 5;          // NVFP4 term rows per token (act_fp4.cu)
-constexpr int kMaxTokens = 9;      // 9 x 5 = 45 columns <= 48
-// Where the block scale of column c (token * kTerms + term), 16-element block b along K, sits in the
+constexpr int kMaxTokens = 9;
+constexpr int kMaxTerms = 6;
+// NVFP4 term rows per token (act_fp4.cu): five, and a sixth where it fits the MMA columns five need anyway
+// (tokens x terms padded to a multiple of 16): every token count but 3, 6 and 9.
+__host__ __device__ constexpr int terms_for(int tokens) {
+    return ((tokens * 5 + 15) / 16 * 16) / tokens >= 6 ? 6 : 5;
+}
+// Where the block scale of column c (token * terms + term), 16-element block b along K, sits in the
 // scale buffer: [256-k chunk][column group c / 32][lane c % 32][64-k MMA of the chunk][block of the MMA],
 // i.e. per chunk and column group one 16-byte word per tensor-memory lane, which the GEMV loads with one
 // 128-bit access and spreads over the four tensor-memory columns the four MMAs of the chunk read.
@@ -122,7 +139,7 @@ __host__ __device__ inline size_t sfb_offset(int b, int c, int groups) {
     return ((size_t)kc * groups + (size_t)(c >> 5)) * 512 + (size_t)(c & 31) * 16 + (size_t)s * 4 + kb;
 }
 }  // namespace fp4
-cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int groups, void* codes, void* sfb,
+cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int terms, int groups, void* codes, void* sfb,
                               float* unscale, cudaStream_t s);
 bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev);
 size_t decode_fp4_scratch_bytes(int K);       // codes + scale atoms + per-token factors of the activation pre-pass

@@ -511,9 +511,9 @@ size_t prefill_umma_scratch_bytes(int max_M, int /*max_N*/, int max_K) {
 }
 
 cudaError_t configure_prefill_umma() {
-    cudaError_t e = cudaFuncSetAttribute(prefill_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = configure_large_smem(prefill_umma_kernel<true>, kSmemBytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(prefill_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    return configure_large_smem(prefill_umma_kernel<false>, kSmemBytes);
 }
 
 // Plans the tiles of one launch (fills sk_tiles / sk_pairs) and returns the grid.

@@ -454,7 +454,7 @@ bool skinny_umma_supported(const LinearArgs& a) {
 }
 
 cudaError_t configure_skinny_umma() {
-    return cudaFuncSetAttribute(skinny_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + kSmemBudget + 1536);
+    return configure_large_smem(skinny_umma_kernel, 1024 + kSmemBudget + 1536);
 }
 
 // scratch: [0, 256) status word; from `offset` the same layout as the prefill kernel's scratch

@@ -27,6 +27,7 @@ def test_chain_of_independent_linears_equals_single_calls(handle, M):
     import torch
     shapes = [(5120, 2048), (640, 5120), (128, 256), (1000, 1024), (2304, 17408), (5120, 2048)]
     handle.set_option("skinny_min_m", 129)
+    handle.set_option("decode_impl", 2)          # the single calls through the chain's own kernel, the mma.sync GEMV
     try:
         lin, want = [], []
         for i, (N, K) in enumerate(shapes):
@@ -50,6 +51,7 @@ def test_chain_of_independent_linears_equals_single_calls(handle, M):
             chain.close()
     finally:
         handle.set_option("skinny_min_m", 9)
+        handle.set_option("decode_impl", 0)
     assert handle.device_status() == 0
 
 
@@ -88,9 +90,13 @@ def test_chain_decode_layer_sequence(handle, M):
     attn, hid = util.make_bf16((M, O), seed=60), util.make_bf16((M, H), seed=61)
     bufs["attn"].copy_(util.to_dev(attn))
     bufs["hid"].copy_(util.to_dev(hid))
-    for d in descs:                                            # one by one
-        handle.linear_ex(d["A"], M, d["packed"], d["scale"], 1.0, d["N"], d["K"], d["C"], residual=d.get("residual"),
-                         norm_weight=d.get("norm_weight"), norm_eps=d.get("norm_eps", 0.0), swiglu_epilogue=d.get("swiglu_epilogue", False))
+    handle.set_option("decode_impl", 2)                        # one by one, through the chain's own kernel
+    try:
+        for d in descs:
+            handle.linear_ex(d["A"], M, d["packed"], d["scale"], 1.0, d["N"], d["K"], d["C"], residual=d.get("residual"),
+                             norm_weight=d.get("norm_weight"), norm_eps=d.get("norm_eps", 0.0), swiglu_epilogue=d.get("swiglu_epilogue", False))
+    finally:
+        handle.set_option("decode_impl", 0)
     torch.cuda.synchronize()
     single = bufs["out"].clone()
     for k in ("hid2", "act", "out"):

@@ -23,13 +23,13 @@ def run(h, A, packed, scale, gs, residual=None, native=True):
     if residual is not None:
         dC.copy_(util.to_dev(residual))
         dR = dC
-    h.set_option("fp4_native", int(native))
+    h.set_option("decode_impl", 3 if native else 2)
     try:
         l0 = h.launch_count()
         h.linear(util.to_dev(A), M, util.to_dev(packed), util.to_dev(scale), gs, N, K, dC, residual=dR)
         launches = h.launch_count() - l0
     finally:
-        h.set_option("fp4_native", 1)
+        h.set_option("decode_impl", 0)
     torch.cuda.synchronize()
     return util.to_host_u16(dC), launches
 
