@@ -33,7 +33,9 @@ WORKLOAD = "configs[1]: decode sweep M in {1,2,4,8,16}, gate_up 34816x5120 + dow
 H, I = 5120, 17408
 SHAPES = {"gate_up": (2 * I, H), "down": (H, I), "qkv": (7168, 5120), "o": (5120, 6144)}   # name -> (N, K)
 DECODE_MS = (1, 2, 4, 8, 16)
-NCU_TRAFFIC_GATE_UP_M1 = 106047744   # bytes per launch; see the roofline object below
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up call at M = 1 (algorithmic: 100.35 MB), from one
+# ncu capture per kernel: the NVFP4 tensor-core GEMV with its pre-pass, and the mma.sync GEMV
+NCU_TRAFFIC_GATE_UP_M1 = {"fp4": None, "mma": 106047744}
 L2_BYTES = 126 << 20
 
 
@@ -407,17 +409,18 @@ def main():
                       "replays": st["replays"], "cv": round(st["cv"], 4),
                       "GBps": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 4),
                       "frac_of_8TBps": round(gbs / 8000.0, 4)})
-    # Dominant kernel: the GEMV kernel on gate_up.  Token counts above 8 go through another kernel
+    # Dominant kernel: the GEMV kernel on gate_up.  Token counts above 9 go through another kernel
     # (see decode_sweep), so the roofline object averages the launches of M <= 8.
     gu = [x for x in sweep if x["shape"] == "gate_up" and x["M"] <= 8] or [x for x in sweep if x["shape"] == "gate_up"]
     ach = sum(alg_bytes(*shapes["gate_up"], x["M"]) for x in gu) / sum(x["us"] * 1e-6 for x in gu) / 1e9
-    roofline = {"bound": "hbm", "kernel": "decode GEMV (decode_mma_kernel), gate_up 34816x5120, mean over its launches at M in "
-                                          + str([x["M"] for x in gu]),
+    fp4 = h.get_option("fp4_native") == 1 and h.get_option("decode_impl") in (0, 3)
+    roofline = {"bound": "hbm",
+                "kernel": ("decode GEMV on the NVFP4 tensor-core path (decode_fp4_kernel; its launch time includes the activation "
+                           "pre-pass act_to_fp4_kernel in front of it)" if fp4 else "decode GEMV (decode_mma_kernel)")
+                          + ", gate_up 34816x5120, mean over its calls at M in " + str([x["M"] for x in gu]),
                 "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "peak_source": peaks["source"],
                 "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4),
-                # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch at M = 1, from the ncu
-                # capture summarised in profiles/decode_gemv_gate_up_down_M1.md (algorithmic: 100.35 MB)
-                "traffic": None if args.small else NCU_TRAFFIC_GATE_UP_M1}
+                "traffic": None if args.small else NCU_TRAFFIC_GATE_UP_M1["fp4" if fp4 else "mma"]}
     line = {"metric": "decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc", "data": "synthetic",

@@ -36,9 +36,22 @@ typedef struct nvfp4_tp_exchange nvfp4_tp_exchange;
 /* Rank 0 makes the id (ncclGetUniqueId) and ships the 128 bytes to the other ranks by any
  * means (the benchmark uses a torch.distributed broadcast). */
 int nvfp4_tp_unique_id(void* out_128_bytes);
-/* Collective over all ranks: ncclCommInitRank on the current device.  world == 1 needs no id. */
+/* Collective over all ranks: ncclCommInitRankConfig on the current device with a NON-BLOCKING
+ * communicator.  Every library call on it (the set-up itself, the collectives of the forward
+ * calls, the finalize in destroy) may come back "in progress"; the library then polls
+ * ncclCommGetAsyncError until the call settles or the deadline (default 30 s) has passed.  After
+ * an error or the deadline it aborts the communicator (ncclCommAbort) and returns NVFP4_E_TP, as
+ * does every later call that needs it.  So a rank that never shows up costs the others the
+ * deadline, not a process stuck inside the library.  (The reference's analogue, for its one GPU:
+ * sync_stream_with_timeout, src/engine/engine.cpp:38-61.)  world == 1 needs no id. */
 int nvfp4_tp_comm_create(const void* unique_id_128_bytes, int rank, int world, nvfp4_tp_comm** out);
 int nvfp4_tp_comm_destroy(nvfp4_tp_comm* comm);
+int nvfp4_tp_comm_set_deadline_ms(nvfp4_tp_comm* comm, int milliseconds);
+/* For a caller's watchdog.  state: 0 = idle or healthy, 1 = a call is in progress, -1 = failed or aborted. */
+int nvfp4_tp_comm_state(nvfp4_tp_comm* comm, int* state);
+/* Gives the communicator up without waiting for the peers (ncclCommAbort); the blocks built on it return
+ * NVFP4_E_TP from then on wherever they would need it. */
+int nvfp4_tp_comm_abort(nvfp4_tp_comm* comm);
 /* How the partial sums travel where the library collective adds them (more than 16 tokens, or no
  * attached exchange).  Default (0): unrounded FP32 partials -- ncclReduceScatter(FP32), the residual
  * added and the result rounded once on each rank's slice, ncclAllGather(BF16): within 1e-3 of the

@@ -108,10 +108,8 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
         h->launches += (unsigned long long)nl;
         return cuda_status(e);
     }
-    // One token on a small matrix is the one case where the mma.sync GEMV, with no pre-pass in front, is still ahead (by 0.3 us).
-    const bool small_single = a.M == 1 && (size_t)a.N * a.K / 2 < (24u << 20);
     const bool fp4_wanted = a.M <= h->decode_max_m &&
-                            (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m && !small_single));
+                            (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m));
     if (fp4_wanted && !other_options_but_f32(a) && decode_fp4_supported(a, h->dev) &&
         decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
         int nl = 0;

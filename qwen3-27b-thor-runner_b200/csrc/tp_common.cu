@@ -10,7 +10,9 @@
 //   * otherwise one NCCL all-reduce of the BF16 partials, the residual added in FP32 after it.
 #include <cuda_bf16.h>
 
+#include <chrono>
 #include <cstring>
+#include <thread>
 
 #include "tp_internal.h"
 
@@ -153,6 +155,25 @@ __global__ void __launch_bounds__(256) finish_slice_kernel(const float4* sum, co
 namespace nvfp4 {
 namespace tp {
 
+int settle(nvfp4_tp_comm* comm, ncclResult_t r) {
+    if (!comm || !comm->comm || comm->aborted) return NVFP4_E_TP;
+    if (r == ncclSuccess) return NVFP4_OK;
+    const auto t0 = std::chrono::steady_clock::now();
+    while (r == ncclInProgress) {
+        if (ncclCommGetAsyncError(comm->comm, &r) != ncclSuccess) { r = ncclInternalError; break; }
+        if (r != ncclInProgress) break;
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > comm->deadline_ms) break;
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    if (r == ncclSuccess) return NVFP4_OK;
+    // an error, or a peer that did not show up in time: give the communicator up (frees its resources, never blocks)
+    ncclCommAbort(comm->comm);
+    comm->comm = nullptr;
+    comm->aborted = true;
+    return NVFP4_E_TP;
+}
+
 int reserve_f32_partials(nvfp4_tp_comm* comm, int max_M, int H) {
     if (!comm || comm->world == 1) return NVFP4_OK;
     const size_t need = (size_t)max_M * H * 4;
@@ -216,12 +237,13 @@ int rowsplit_linear(nvfp4_handle* h, nvfp4_tp_comm* comm, nvfp4_tp_exchange* x, 
     // to its slice and rounds ONCE, the BF16 slices are all-gathered.  (BF16-rounded partials put P
     // roundings in front of the sum: 1.1e-3 / 1.4e-3 from the unsplit result at 4 / 8 ranks, measured.)
     // An in-place residual needs no copy: a rank reads only its own slice of it before the gather.
+    if (!comm->comm) return NVFP4_E_TP;          // a group without a live communicator (never created, or aborted)
     const size_t total = (size_t)M * H;
     if (!comm->bf16_partials && comm->f32_scratch && total * 4 <= comm->f32_bytes && (total % ((size_t)P * 8)) == 0) {
         int st = nvfp4_linear_f32(h, d.A, M, d.packed, d.scale, d.global_scale, H, d.K, comm->f32_scratch, s);
         if (st == NVFP4_OK) {
             const size_t cnt = total / P, off = (size_t)comm->rank * cnt;
-            if (ncclReduceScatter(comm->f32_scratch, comm->f32_scratch + off, cnt, ncclFloat, ncclSum, comm->comm, s) != ncclSuccess)
+            if (settle(comm, ncclReduceScatter(comm->f32_scratch, comm->f32_scratch + off, cnt, ncclFloat, ncclSum, comm->comm, s)))
                 return NVFP4_E_TP;
             const long long n8 = (long long)(cnt / 8);
             int blocks = (int)((n8 + 255) / 256);
@@ -231,7 +253,7 @@ int rowsplit_linear(nvfp4_handle* h, nvfp4_tp_comm* comm, nvfp4_tp_exchange* x, 
                 d.residual ? reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(d.residual) + off) : nullptr,
                 reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(d.C) + off), n8);
             if (cudaGetLastError() != cudaSuccess) return NVFP4_E_TP;
-            if (ncclAllGather(static_cast<const __nv_bfloat16*>(d.C) + off, d.C, cnt, ncclBfloat16, comm->comm, s) != ncclSuccess)
+            if (settle(comm, ncclAllGather(static_cast<const __nv_bfloat16*>(d.C) + off, d.C, cnt, ncclBfloat16, comm->comm, s)))
                 return NVFP4_E_TP;
             return NVFP4_OK;
         }
@@ -248,7 +270,7 @@ int rowsplit_linear(nvfp4_handle* h, nvfp4_tp_comm* comm, nvfp4_tp_exchange* x, 
     }
     int st = nvfp4_linear(h, d.A, M, d.packed, d.scale, d.global_scale, H, d.K, nullptr, d.C, s);
     if (st) return st;
-    if (ncclAllReduce(d.C, d.C, (size_t)M * H, ncclBfloat16, ncclSum, comm->comm, s) != ncclSuccess)
+    if (settle(comm, ncclAllReduce(d.C, d.C, (size_t)M * H, ncclBfloat16, ncclSum, comm->comm, s)))
         return NVFP4_E_TP;
     if (res_src) {
         const long long n8 = (long long)M * H / 8;
@@ -285,9 +307,40 @@ int nvfp4_tp_comm_create(const void* uid, int rank, int world, nvfp4_tp_comm** o
         if (!uid) { delete c; return NVFP4_E_NULL; }
         ncclUniqueId id;
         std::memcpy(&id, uid, sizeof id);
-        if (ncclCommInitRank(&c->comm, world, id, rank) != ncclSuccess) { delete c; return NVFP4_E_TP; }
+        // Non-blocking: the call returns at once and the set-up proceeds in the background; a rank that never
+        // calls leaves the others polling until the deadline instead of blocked inside the library for good.
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.blocking = 0;
+        const ncclResult_t r = ncclCommInitRankConfig(&c->comm, world, id, rank, &cfg);
+        if (r != ncclSuccess && r != ncclInProgress) { delete c; return NVFP4_E_TP; }
+        if (nvfp4::tp::settle(c, r) != NVFP4_OK) { delete c; return NVFP4_E_TP; }
     }
     *out = c;
+    return NVFP4_OK;
+}
+
+int nvfp4_tp_comm_set_deadline_ms(nvfp4_tp_comm* c, int ms) {
+    if (!c) return NVFP4_E_NULL;
+    if (ms < 1) return NVFP4_E_OPTION;
+    c->deadline_ms = ms;
+    return NVFP4_OK;
+}
+
+int nvfp4_tp_comm_state(nvfp4_tp_comm* c, int* state) {
+    if (!c || !state) return NVFP4_E_NULL;
+    if (c->aborted) { *state = -1; return NVFP4_OK; }
+    if (!c->comm) { *state = 0; return NVFP4_OK; }            // a group of one has no communicator to ask
+    ncclResult_t r = ncclSuccess;
+    if (ncclCommGetAsyncError(c->comm, &r) != ncclSuccess) { *state = -1; return NVFP4_OK; }
+    *state = r == ncclSuccess ? 0 : (r == ncclInProgress ? 1 : -1);
+    return NVFP4_OK;
+}
+
+int nvfp4_tp_comm_abort(nvfp4_tp_comm* c) {
+    if (!c) return NVFP4_E_NULL;
+    if (c->comm) ncclCommAbort(c->comm);
+    c->comm = nullptr;
+    c->aborted = true;
     return NVFP4_OK;
 }
 
@@ -300,7 +353,10 @@ int nvfp4_tp_comm_set_bf16_partials(nvfp4_tp_comm* c, int on) {
 int nvfp4_tp_comm_destroy(nvfp4_tp_comm* c) {
     if (!c) return NVFP4_E_NULL;
     cudaFree(c->f32_scratch);
-    if (c->comm) ncclCommDestroy(c->comm);
+    if (c->comm) {
+        // a non-blocking communicator is finalized first (that call, too, may come back as "in progress")
+        if (nvfp4::tp::settle(c, ncclCommFinalize(c->comm)) == NVFP4_OK && c->comm) ncclCommDestroy(c->comm);
+    }
     delete c;
     return NVFP4_OK;
 }

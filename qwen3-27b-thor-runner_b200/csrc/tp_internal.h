@@ -17,6 +17,11 @@ struct nvfp4_tp_comm {
     float* f32_scratch = nullptr;
     size_t f32_bytes = 0;
     int bf16_partials = 0;
+    // The communicator is non-blocking: a call may come back as "in progress", and the caller polls the
+    // communicator's asynchronous state until it settles or this many milliseconds have passed; then the
+    // communicator is aborted and every later call on it fails.
+    int deadline_ms = 30000;
+    bool aborted = false;
 };
 
 // One rank's end of the peer exchange.  xbuf: this rank's buffer; peer[q]: rank q's buffer as
@@ -35,6 +40,10 @@ namespace nvfp4 {
 namespace tp {
 
 constexpr int kFusedMaxM = xchg::kMaxTokens;
+
+// Settles the result of an NCCL call on the non-blocking communicator: NVFP4_OK, or NVFP4_E_TP after an
+// error or after the deadline (the communicator is aborted then).
+int settle(nvfp4_tp_comm* comm, ncclResult_t r);
 
 // Room for [max_M, H] FP32 partial sums on the communicator (grown at block-creation time, never in a forward).
 int reserve_f32_partials(nvfp4_tp_comm* comm, int max_M, int H);

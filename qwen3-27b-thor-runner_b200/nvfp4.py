@@ -27,6 +27,11 @@ class LinearDesc(ctypes.Structure):
                 ("norm_eps", ctypes.c_float), ("swiglu_epilogue", ctypes.c_int)]
 
 
+class PeerExchange(ctypes.Structure):
+    """nvfp4_peer_exchange of include/nvfp4_b200.h."""
+    _fields_ = [("peer", c_void_p * 8), ("rank", c_int), ("world", c_int), ("slot_pairs", c_int)]
+
+
 class QuantizedWeight(ctypes.Structure):
     """Layout of qwen_thor::core::QuantizedWeight (reference src/engine/layer.h:197-204)."""
     _fields_ = [("packed", c_void_p), ("scale", c_void_p), ("global_scale", c_float),
@@ -181,6 +186,20 @@ class Handle:
     def linear_f32(self, A, M, packed, scale, global_scale, N, K, C_f32, stream=None):
         self._check(self.lib.nvfp4_linear_f32(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,
                                               _ptr(C_f32), _stream(stream)))
+
+    def linear_reduce_peers(self, A, M, packed, scale, global_scale, N, K, C, peers, rank, slot_pairs, residual=None,
+                            stream=None, check=True):
+        """nvfp4_linear_reduce_peers: `peers` = the world's exchange buffers as mapped into this process
+        (device tensors or raw pointers), `rank` = this rank's place among them."""
+        px = PeerExchange()
+        for q, b in enumerate(peers):
+            px.peer[q] = _ptr(b)
+        px.rank, px.world, px.slot_pairs = rank, len(peers), slot_pairs
+        st = self.lib.nvfp4_linear_reduce_peers(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,
+                                                _ptr(residual), _ptr(C), ctypes.byref(px), _stream(stream))
+        if check:
+            self._check(st)
+        return st
 
     def linear(self, A, M, packed, scale, global_scale, N, K, C, residual=None, stream=None, check=True):
         st = self.lib.nvfp4_linear(self.h, _ptr(A), M, _ptr(packed), _ptr(scale), global_scale, N, K,

@@ -21,6 +21,9 @@ TP_SIGNATURES = {
     "nvfp4_tp_comm_create": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p)]),
     "nvfp4_tp_comm_destroy": (c_int, [c_void_p]),
     "nvfp4_tp_comm_set_bf16_partials": (c_int, [c_void_p, c_int]),
+    "nvfp4_tp_comm_set_deadline_ms": (c_int, [c_void_p, c_int]),
+    "nvfp4_tp_comm_state": (c_int, [c_void_p, ctypes.POINTER(c_int)]),
+    "nvfp4_tp_comm_abort": (c_int, [c_void_p]),
     "nvfp4_tp_mlp_create": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                     c_float, c_int, ctypes.POINTER(c_void_p)]),
     "nvfp4_tp_mlp_destroy": (c_int, [c_void_p]),
@@ -125,6 +128,61 @@ def pad_activation(act, kp):
     return out
 
 
+# ------------------------------------------------------------------ host-side pre-flight of a step
+
+class TpStepError(RuntimeError):
+    """A tensor-parallel step was called off before anything was enqueued."""
+
+
+class StepGuard:
+    """Pre-flight of a tensor-parallel step, on the host, before any kernel or collective is enqueued.
+
+    A collective that one rank never joins, or joins with another token count, leaves the other
+    ranks waiting on the device; so every rank first posts the token count it is about to enqueue
+    (or the failure it hit) in a key-value store all ranks reach -- the torch.distributed store of
+    the process group, or any object with set / get / wait(keys, timeout) -- and reads the others'.
+    A rank that posts another count, posts a failure, or posts nothing within the deadline makes
+    every rank raise TpStepError; the caller then skips the step (and, for a rank that is gone for
+    good, aborts the communicator: Comm.abort).  Failures are found out between steps only, with
+    nothing in flight on the GPUs.
+    (The reference's single-GPU analogue: the bounded polling of sync_stream_with_timeout,
+    src/engine/engine.cpp:38-61, and the request-level error codes of :332-337.)"""
+
+    def __init__(self, store, rank, world, deadline_s=5.0, prefix="nvfp4_tp_step"):
+        self.store, self.rank, self.world = store, rank, world
+        self.deadline_s, self.prefix = float(deadline_s), prefix
+        self.step = 0
+
+    def _key(self, rank):
+        return f"{self.prefix}/{self.step}/{rank}"
+
+    def fail(self, reason):
+        """Call instead of check() when this rank cannot take part in the step: the others learn of it at once."""
+        self.store.set(self._key(self.rank), "fail:" + str(reason))
+        self.step += 1
+
+    def check(self, M):
+        """Every rank calls this with its token count before it enqueues the step."""
+        import datetime
+        self.store.set(self._key(self.rank), str(int(M)))
+        others = [r for r in range(self.world) if r != self.rank]
+        step = self.step
+        self.step += 1
+        try:
+            if others:
+                self.store.wait([f"{self.prefix}/{step}/{r}" for r in others], datetime.timedelta(seconds=self.deadline_s))
+        except Exception as e:      # the store's timeout error type depends on the store
+            raise TpStepError(f"step {step}: a rank did not report within {self.deadline_s} s ({type(e).__name__})") from None
+        for r in others:
+            v = self.store.get(f"{self.prefix}/{step}/{r}")
+            v = v.decode() if isinstance(v, (bytes, bytearray)) else str(v)
+            if v.startswith("fail:"):
+                raise TpStepError(f"step {step}: rank {r} failed before the step: {v[5:]}")
+            if int(v) != int(M):
+                raise TpStepError(f"step {step}: rank {r} is about to enqueue {v} tokens, this rank {int(M)}")
+        return True
+
+
 # ------------------------------------------------------------------ device objects
 
 class Comm:
@@ -141,6 +199,25 @@ class Comm:
         """NCCL path of the row-split linears: False (default) = FP32 partials (reduce-scatter, finish on
         the rank's slice, all-gather), True = one all-reduce of BF16-rounded partials."""
         st = self.lib.nvfp4_tp_comm_set_bf16_partials(self.c, int(bool(on)))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def set_deadline_ms(self, ms):
+        """How long a call on the (non-blocking) communicator may stay "in progress" before it is aborted."""
+        st = self.lib.nvfp4_tp_comm_set_deadline_ms(self.c, int(ms))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+
+    def state(self):
+        """0 = idle or healthy, 1 = a call is in progress, -1 = failed or aborted."""
+        v = c_int()
+        st = self.lib.nvfp4_tp_comm_state(self.c, ctypes.byref(v))
+        if st:
+            raise nvfp4.Nvfp4Error(st)
+        return v.value
+
+    def abort(self):
+        st = self.lib.nvfp4_tp_comm_abort(self.c)
         if st:
             raise nvfp4.Nvfp4Error(st)
 
