@@ -265,14 +265,17 @@ class Rotating:
         return self.w[self.i]
 
 
-def time_region(fn, steps, torch, graph=True, replays=50, stats=None, budget_s=0.4):
+def time_region(fn, steps, torch, graph=True, replays=50, stats=None, budget_s=0.4, exact_replays=None):
     """Device time per call of fn (ms).  graph=True: `steps` calls are captured into one CUDA graph (the
     library's launches are capturable: no allocation, no synchronisation) and the graph is replayed
     `replays` times (fewer when one replay is long: the timed replays together stay near budget_s, at
     least 5), each replay between its own pair of events; the MEDIAN replay is reported, so the figure is
     free of host launch overhead and of a single outlier.  `stats`, when given, receives the number of
     timed replays, their median, minimum and coefficient of variation (per call, ms).  graph=False: the
-    calls are issued on the stream between one pair of events."""
+    calls are issued on the stream between one pair of events.
+    exact_replays: replay exactly that many times, whatever one replay takes.  Ranks whose calls contain
+    a collective or wait for each other's kernels MUST pass it: a count derived from a rank's own clock
+    can differ between the ranks, and the rank that replays once more waits for peers that have stopped."""
     if graph:
         g = torch.cuda.CUDAGraph()
         s = torch.cuda.Stream()
@@ -289,7 +292,7 @@ def time_region(fn, steps, torch, graph=True, replays=50, stats=None, budget_s=0
             e1.record()
             torch.cuda.synchronize()
             first = e0.elapsed_time(e1)
-            n = int(max(5, min(replays, budget_s * 1e3 / max(first, 1e-3))))
+            n = int(max(5, min(replays, budget_s * 1e3 / max(first, 1e-3)))) if exact_replays is None else int(exact_replays)
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
             for a, b in ev:
                 a.record()

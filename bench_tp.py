@@ -43,7 +43,7 @@ def run_tp_mlp_table(torch, dist, make_mlp, H, dev, world, steps, comm=None):
             ms = None
             if M <= 256:
                 try:
-                    ms = bench.time_region(one, reps, torch, graph=True)
+                    ms = bench.time_region(one, reps, torch, graph=True, exact_replays=20 if M <= 16 else 8)
                     mode = "graph"
                 except Exception:
                     torch.cuda.synchronize()
@@ -183,7 +183,7 @@ def run_tp_layer_stream(torch, dist, h, comm, dev, world, layers=64, tokens=(1, 
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
-        ms = bench.time_region(token_step, 3, torch, graph=True)
+        ms = bench.time_region(token_step, 3, torch, graph=True, exact_replays=8)
         t = torch.tensor([ms], device=dev)
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -226,9 +226,10 @@ def attn_parity(torch, dist, h, comm, dev, world, rank):
     rows = nvfp4_tp.qkv_rows(q_rows, kv_rows, n_kv, rank, world)
     full_qkv = ob.linear(X, qkv_p, qkv_s, 1.0)
     mine = util.to_host_u16(qkv)
-    ok_rows = torch.tensor([int(np_equal(mine, full_qkv[:, rows]))], device=dev)
+    # a shard's outputs are the unsplit layer's rows (no sum over ranks): the linear's own bar against the oracle
+    err_rows = torch.tensor([float(ob.rel_frobenius(mine, np_ascontig(full_qkv[:, rows])))], device=dev)
     if dist is not None:
-        dist.all_reduce(ok_rows, op=dist.ReduceOp.MIN)
+        dist.all_reduce(err_rows, op=dist.ReduceOp.MAX)
     gathered = [torch.empty_like(out_f.view(torch.uint8)) for _ in range(world)]
     if dist is not None:
         dist.all_gather(gathered, out_f.view(torch.uint8))
@@ -237,7 +238,7 @@ def attn_parity(torch, dist, h, comm, dev, world, rank):
     res = None
     if rank == 0:
         want = ob.linear(np_ascontig(full_qkv[:, :q_rows]), o_p, o_s, 1.0, residual=R)   # stub attention: the q columns
-        res = {"qkv_shards_equal_unsplit_oracle_rows": bool(ok_rows.item()),
+        res = {"qkv_shards_vs_unsplit_oracle_rows_worst_rank": float(err_rows.item()),
                "o_nccl_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out_n), want)),
                "o_fused_path_vs_unsplit_oracle": float(ob.rel_frobenius(util.to_host_u16(out_f), want)),
                "o_fused_identical_on_all_ranks": all(torch.equal(g, gathered[0]) for g in gathered),
@@ -247,11 +248,6 @@ def attn_parity(torch, dist, h, comm, dev, world, rank):
     blk.close()
     x.close()
     return res
-
-
-def np_equal(a, b):
-    import numpy as np
-    return np.array_equal(a, b)
 
 
 def np_ascontig(a):
@@ -281,8 +277,18 @@ def main(args, world, rank, local_rank):
     else:
         uid = torch.zeros(nvfp4_tp.UNIQUE_ID_BYTES, dtype=torch.uint8, device=dev)
     dist.broadcast(uid, 0)
+    import time
+    t_start = time.monotonic()
+
+    def note(what):
+        """Progress on stderr: a run that stops short shows where."""
+        if rank == 0:
+            print(f"[bench_tp {time.monotonic() - t_start:7.1f}s] {what}", file=sys.stderr, flush=True)
+
+    note("communicator")
     comm = nvfp4_tp.Comm(bytes(uid.cpu().tolist()), rank, world)
     peaks = bench.load_peaks()
+    note("small-block parity")
 
     def make_mlp_set(max_M, copies=None):
         """Distinct MLPs (same seeds on every rank) whose shards together exceed 2 x L2."""
@@ -345,6 +351,7 @@ def main(args, world, rank, local_rank):
         parity = {"error": repr(e)}
 
     # ---- timed region: decode sweep through the MLP block
+    note("decode sweep: set-up")
     mlps = make_mlp_set(16)
     X = {M: bench.device_acts(M, H, seed=M, dev=dev) for M in bench.DECODE_MS}
     Y = {M: torch.empty((M, H), dtype=torch.bfloat16, device=dev) for M in bench.DECODE_MS}
@@ -357,6 +364,7 @@ def main(args, world, rank, local_rank):
 
     for _ in range(args.warmup):
         step()
+    note("decode sweep: timed region")
     sampler = bench.ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -373,7 +381,7 @@ def main(args, world, rank, local_rank):
     try:
         if args.no_graph:
             raise RuntimeError("--no-graph")
-        ms = bench.time_region(step, args.steps, torch, graph=True)
+        ms = bench.time_region(step, args.steps, torch, graph=True, exact_replays=20)
     except Exception:
         torch.cuda.synchronize()
         timing = "K steps of stream launches"
@@ -387,6 +395,7 @@ def main(args, world, rank, local_rank):
     step_bytes = sum(bench.alg_bytes(2 * I, H, M) + bench.alg_bytes(H, I, M) for M in bench.DECODE_MS)
     value = step_bytes / (ms * 1e-3) / 1e9
 
+    note("end to end")
     # ---- end to end: tokens start in pinned host memory, results end there
     hX = {M: torch.randn((M, H)).to(torch.bfloat16).pin_memory() for M in bench.DECODE_MS}
     hY = {M: torch.empty((M, H), dtype=torch.bfloat16).pin_memory() for M in bench.DECODE_MS}
@@ -420,13 +429,17 @@ def main(args, world, rank, local_rank):
     del mlps
     torch.cuda.empty_cache()
 
+    note("attention-projection parity")
     try:
         attn_par = attn_parity(torch, dist, h, comm, dev, world, rank)
     except Exception as e:
         attn_par = {"error": repr(e)}
+    note("layer stream")
     stream = run_tp_layer_stream(torch, dist, h, comm, dev, world)
+    note("MLP table")
     table = run_tp_mlp_table(torch, dist, lambda M: make_mlp_set(M, copies=(None if M <= 256 else 2)), H, dev, world,
                              args.steps, comm=comm)
+    note("full-size parity above 16 tokens")
     try:
         big_parity = full_size_parity(torch, dist, h, comm, dev, world, rank)
     except Exception as e:
@@ -450,5 +463,6 @@ def main(args, world, rank, local_rank):
         os.dup2(saved_stdout, 1)
         print(json.dumps(line), flush=True)
         os.dup2(2, 1)
+    note("done")
     comm.close()
     dist.destroy_process_group()
