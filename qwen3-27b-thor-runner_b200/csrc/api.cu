@@ -24,7 +24,7 @@ struct nvfp4_handle {
     int wide_gemv = 1;                           // 9..16 tokens: one launch of the wide GEMV kernel
     int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
     int fp4_native = 1;                          // the NVFP4 tensor-core GEMV (weights untouched, activations as NVFP4 terms) ...
-    int fp4_min_m = 1;                           // ... from this token count on (up to 9)
+    int fp4_min_m = 1;                           // ... from this token count on (up to 16)
     unsigned long long launches = 0;
 };
 
@@ -41,10 +41,11 @@ unsigned int next_launch_tag() {
 
 namespace {
 
-// status word + the split-tile partial pairs of the GEMV kernels: the wide one from 16 KB, the 8-token one from 6 MB,
-// the tensor-core one from 8 MB, and from 10 MB the NVFP4 form of that kernel's activations
+// status word + the split-tile partial pairs of the GEMV kernels: the wide one from 16 KB, the 8-token one from 6 MB
+// (1.2 MB), the tensor-core one from 7.25 MB (2.5 MB), and from 10 MB the NVFP4 form of that kernel's activations
 constexpr size_t kDecodeScratchBytes = 12u << 20;
-constexpr size_t kFp4PairsOffset = 8u << 20, kFp4ActOffset = 10u << 20, kFp4ActBytes = 2u << 20;
+constexpr size_t kFp4PairsOffset = 29u << 18, kFp4ActOffset = 10u << 20, kFp4ActBytes = 2u << 20;
+static_assert(kFp4PairsOffset + nvfp4::fp4::kPairBytes <= kFp4ActOffset, "scratch layout");
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -110,12 +111,16 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
     }
     const bool fp4_wanted = a.M <= h->decode_max_m &&
                             (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m));
-    if (fp4_wanted && !other_options_but_f32(a) && decode_fp4_supported(a, h->dev) &&
-        decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
-        int nl = 0;
-        cudaError_t e = launch_decode_fp4(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s);
-        h->launches += (unsigned long long)nl;
-        return cuda_status(e);
+    if (fp4_wanted && !other_options_but_f32(a) && decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
+        // up to 9 tokens with the activations resident beside the ring, else streamed through it
+        const bool res = decode_fp4_supported(a, h->dev);
+        if (res || decode_fp4_stream_supported(a, h->dev)) {
+            int nl = 0;
+            cudaError_t e = res ? launch_decode_fp4(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s)
+                                : launch_decode_fp4_stream(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s);
+            h->launches += (unsigned long long)nl;
+            return cuda_status(e);
+        }
     }
     if (other_options || ((a.swiglu_out || a.px) && !wide_ok)) {
         if (a.M > 16 || !decode_mma_supported(a) || !decode_mma_fits(a, h->dev)) return NVFP4_E_LIMIT;

@@ -1,4 +1,4 @@
-// Dequant-free GEMV for up to 9 tokens on the NVFP4 tensor-core path: the packed weights go from HBM
+// Dequant-free GEMV for up to 9 tokens on the NVFP4 tensor-core path (10 to 16 tokens: decode_fp4_stream.cu): the packed weights go from HBM
 // to the tensor core untouched.
 //
 //   C[M,N] = bf16( A[M,K] * W[N,K]^T (+ residual) ),  W = e2m1(code) * ue4m3(scale) / global_scale
@@ -56,13 +56,17 @@ constexpr int kScaleBytes = kRT * kKC / 16;        // 2 KB of scales [row][16] p
 constexpr int kMaxStages = 10;
 constexpr int kThreads = 12 * 32;
 constexpr int kEpiThreads = 4 * 32;
-constexpr int kSmemBudget = 227 * 1024;
+// Not all of an SM's 228 KB: the activation pre-pass of the NEXT call (launched with programmatic stream
+// serialization while this kernel runs) must find room for its CTAs beside this kernel's, or the two
+// calls serialize (5 us on a 10 us call, measured, when 544 bytes were left).
+constexpr int kSmemBudget = 225 * 1024;
 constexpr int kAccStride = 64;                     // tensor-memory columns per accumulator (NCp <= 48)
 constexpr int kSfCol = 2 * kAccStride;             // per half-unit of the ring 32 columns: 16 of the weights' scales, 16 of the activations'
 constexpr int kMaxRingHalfUnits = (512 - kSfCol) / 32;   // 12
-constexpr int kMaxGrid = 160;                      // CTAs whose pair slots fit the kernel's 2 MB of scratch
-constexpr int kPairTokens = fp4::kMaxTokens;       // token rows of a CTA's pair slot (9 KB per CTA)
-static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= (2u << 20), "pair slots");
+constexpr int kTokens = 9;                         // most tokens of this kernel: 9 x 5 = 45 of its 48 MMA columns
+constexpr int kMaxGrid = 160;                      // CTAs whose pair slots fit the kernel's share of the scratch
+constexpr int kPairTokens = kTokens;               // token rows of a CTA's pair slot (9 KB per CTA)
+static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= fp4::kPairBytes, "pair slots");
 
 struct Fp4Params {
     const __nv_bfloat16* residual;
@@ -337,9 +341,9 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             ptx::mbar_wait(&tfull[acc], (pt >> acc) & 1u, s_abort, status, 0xA50u + (unsigned)acc);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * kAccStride);
-            float v[fp4::kMaxTokens];
+            float v[kTokens];
 #pragma unroll
-            for (int m = 0; m < fp4::kMaxTokens; ++m) v[m] = 0.0f;
+            for (int m = 0; m < kTokens; ++m) v[m] = 0.0f;
 #pragma unroll
             for (int c0 = 0; c0 < 48; c0 += 16) {
                 if (c0 < p.NCp) {
@@ -348,7 +352,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int c = c0 + i;                 // column c = token * TERMS + term (compile-time after unrolling)
-                        if (c / TERMS < fp4::kMaxTokens) v[c / TERMS] += __uint_as_float(r[i]);
+                        if (c / TERMS < kTokens) v[c / TERMS] += __uint_as_float(r[i]);
                     }
                 }
             }
@@ -361,12 +365,12 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             kc = kc_first + (seg_end - (tile_end - p.kchunks + kc_first));
 
 #pragma unroll
-            for (int m = 0; m < fp4::kMaxTokens; ++m)
+            for (int m = 0; m < kTokens; ++m)
                 if (m < p.M) v[m] *= p.unscale[m];
             if (!owner) {
                 unsigned char* slot = pairs + (size_t)cta * (kPairTokens * kRT) * 8;
 #pragma unroll
-                for (int m = 0; m < fp4::kMaxTokens; ++m)
+                for (int m = 0; m < kTokens; ++m)
                     if (m < p.M) ptx::st_volatile_v2(slot + (m * kRT + te) * 8, __float_as_uint(v[m]), epoch);
             } else {
                 const long long t0 = clock64();
@@ -374,18 +378,18 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 for (int c = cta + 1; c <= last && !failed; ++c) {
                     const unsigned char* src = pairs + (size_t)c * (kPairTokens * kRT) * 8;
                     while (true) {
-                        uint2 x[fp4::kMaxTokens];
+                        uint2 x[kTokens];
 #pragma unroll
-                        for (int m = 0; m < fp4::kMaxTokens; ++m) {
+                        for (int m = 0; m < kTokens; ++m) {
                             x[m] = make_uint2(0u, epoch);
                             if (m < p.M) x[m] = ptx::ld_volatile_v2(src + (m * kRT + te) * 8);
                         }
                         bool ready = true;
 #pragma unroll
-                        for (int m = 0; m < fp4::kMaxTokens; ++m) ready &= (x[m].y == epoch);
+                        for (int m = 0; m < kTokens; ++m) ready &= (x[m].y == epoch);
                         if (ready) {
 #pragma unroll
-                            for (int m = 0; m < fp4::kMaxTokens; ++m) v[m] += __uint_as_float(x[m].x);
+                            for (int m = 0; m < kTokens; ++m) v[m] += __uint_as_float(x[m].x);
                             break;
                         }
                         if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
@@ -399,7 +403,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 const int n = tile * kRT + te;
                 if (n < p.N) {
 #pragma unroll
-                    for (int m = 0; m < fp4::kMaxTokens; ++m) {
+                    for (int m = 0; m < kTokens; ++m) {
                         if (m >= p.M) continue;
                         float x = v[m] * p.inv_gs;
                         const size_t o = (size_t)m * p.N + n;
@@ -457,12 +461,10 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
     return true;
 }
 
-size_t round256(size_t x) { return (x + 255) / 256 * 256; }
-
 }  // namespace
 
 bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
-    if (a.M < 1 || a.M > fp4::kMaxTokens || (a.K % kKC) != 0 || a.N < 1) return false;
+    if (a.M < 1 || a.M > kTokens || (a.K % kKC) != 0 || a.N < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
     if (a.px || a.swiglu_up || a.swiglu_out || a.norm_w || a.k_valid) return false;
     if (a.a_stride && (a.a_stride & 7)) return false;
@@ -470,10 +472,7 @@ bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
     return plan_fp4(a, dev, &pl);
 }
 
-// codes [48, K/2] + block scales [K/256][2][512] + 16 floats
-size_t decode_fp4_scratch_bytes(int K) {
-    return round256((size_t)48 * (K / 2)) + round256((size_t)(K / kKC) * 1024) + 256;
-}
+size_t decode_fp4_scratch_bytes(int K) { return fp4::act_scratch_bytes(K); }
 
 cudaError_t configure_decode_fp4() {
     cudaError_t e = configure_large_smem(decode_fp4_kernel<5>, kSmemBudget);
@@ -487,8 +486,8 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     if (!plan_fp4(a, dev, &pl)) return cudaErrorInvalidValue;
     Fp4Params& p = pl.p;
     unsigned char* codes = static_cast<unsigned char*>(act);
-    unsigned char* sfb = codes + round256((size_t)48 * (a.K / 2));
-    float* unscale = reinterpret_cast<float*>(sfb + round256((size_t)p.kchunks * 1024));
+    unsigned char* sfb = codes + fp4::act_sfb_offset(a.K);
+    float* unscale = reinterpret_cast<float*>(codes + fp4::act_unscale_offset(a.K));
     CUtensorMap tmp, tms, tma;
     if (!make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT,
                          CU_TENSOR_MAP_SWIZZLE_128B) ||

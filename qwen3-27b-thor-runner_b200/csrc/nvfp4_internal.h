@@ -123,10 +123,11 @@ inline cudaError_t configure_large_smem(Kernel kernel, int bytes) {
 
 // --- act_fp4.cu / decode_fp4.cu: the GEMV on the NVFP4 tensor-core path (tcgen05.mma kind::mxf4nvf4).
 namespace fp4 {
-constexpr int kMaxTokens = 9;
+constexpr int kMaxTokens = 16;
 constexpr int kMaxTerms = 6;
+constexpr size_t kPairBytes = 5u << 19;     // 2.5 MB of split-tile pair slots in the handle's scratch
 // NVFP4 term rows per token (act_fp4.cu): five, and a sixth where it fits the MMA columns five need anyway
-// (tokens x terms padded to a multiple of 16): every token count but 3, 6 and 9.
+// (tokens x terms padded to a multiple of 16): 1, 2, 4, 5, 7, 8, 10 and 13 tokens.
 __host__ __device__ constexpr int terms_for(int tokens) {
     return ((tokens * 5 + 15) / 16 * 16) / tokens >= 6 ? 6 : 5;
 }
@@ -138,6 +139,12 @@ __host__ __device__ inline size_t sfb_offset(int b, int c, int groups) {
     const int kc = b >> 4, s = (b >> 2) & 3, kb = b & 3;
     return ((size_t)kc * groups + (size_t)(c >> 5)) * 512 + (size_t)(c & 31) * 16 + (size_t)s * 4 + kb;
 }
+// The activation scratch the pre-pass fills and the GEMV kernels read: codes [kMaxCols, K/2], block scales
+// [K/256][3 groups][512 bytes] (a kernel with fewer column groups uses a prefix), 16 per-token factors.
+constexpr int kMaxCols = 96;
+inline size_t act_sfb_offset(int K) { return ((size_t)kMaxCols * (K / 2) + 255) / 256 * 256; }
+inline size_t act_unscale_offset(int K) { return act_sfb_offset(K) + ((size_t)(K / 256) * 1536 + 255) / 256 * 256; }
+inline size_t act_scratch_bytes(int K) { return act_unscale_offset(K) + 256; }
 }  // namespace fp4
 cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int terms, int groups, void* codes, void* sfb,
                               float* unscale, cudaStream_t s);
@@ -147,6 +154,12 @@ cudaError_t configure_decode_fp4();
 // scratch: the handle workspace (status word at 0, launch counter at 64, pairs at pairs_offset); act: decode_fp4_scratch_bytes.
 cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t pairs_offset, void* act,
                               int* launches, cudaStream_t s);
+// decode_fp4_stream.cu: the same GEMV for 10 to 16 tokens (and any shape whose activations do not fit beside the
+// ring): the activations travel through the ring with the weights.  Same scratch, same arguments.
+bool decode_fp4_stream_supported(const LinearArgs& a, const nvfp4_device_info& dev);
+cudaError_t configure_decode_fp4_stream();
+cudaError_t launch_decode_fp4_stream(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t pairs_offset, void* act,
+                                     int* launches, cudaStream_t s);
 
 // --- act_f16.cu: BF16 activations -> FP16 copy with an exact per-token power-of-two scale; unscale[m] = 1/scale.
 cudaError_t launch_act_to_f16(const void* A, int M, int K, void* out_f16, float* unscale, cudaStream_t s);

@@ -628,6 +628,7 @@ cudaError_t configure_kernels(const nvfp4_device_info&) {
     if (e == cudaSuccess) e = configure_decode_wide();
     if (e == cudaSuccess) e = configure_dense_gemv();
     if (e == cudaSuccess) e = configure_decode_fp4();
+    if (e == cudaSuccess) e = configure_decode_fp4_stream();
     return e;
 }
 

@@ -1,5 +1,5 @@
-"""The GEMV on the NVFP4 tensor-core path (tcgen05.mma kind::mxf4nvf4; up to 9 tokens): weights go from
-HBM to the tensor core untouched, the BF16 activations are expanded into five NVFP4 term rows per
+"""The GEMV on the NVFP4 tensor-core path (tcgen05.mma kind::mxf4nvf4; up to 16 tokens): weights go from
+HBM to the tensor core untouched, the BF16 activations are expanded into five or six NVFP4 term rows per
 token.  Checked against the CPU oracle (relative Frobenius <= 1e-3, the bar of every linear), against
 the mma.sync GEMV on the same inputs, for exactness where the expansion is exact, and under
 CUDA-graph replay."""
@@ -41,9 +41,14 @@ def run(h, A, packed, scale, gs, residual=None, native=True):
     (3, 2048, 5120, True),
     (4, 1024, 17408, True),        # deep K: row tiles split over many CTAs
     (5, 640, 5120, False),         # few row tiles over all CTAs
-    (8, 4352, 5120, True),         # 40 columns -> 48: the resident activations leave a short ring
-    (9, 1000, 2048, True),         # the largest token count of the kernel
+    (8, 4352, 5120, True),         # 48 MMA columns, two groups of activation scales
+    (9, 1000, 2048, True),
     (7, 20000, 512, False),        # many row tiles, two half-units each
+    (10, 640, 5120, True),         # six terms in 64 columns
+    (12, 1000, 2048, True),        # 64 columns, five terms
+    (13, 2048, 1024, False),       # 80 columns: the 128-column accumulators, three groups of activation scales
+    (16, 4352, 5120, True),        # the largest token count of the kernel
+    (16, 5120, 17408, True),       # ... on the deep shape of the benchmark
 ])
 def test_fp4_gemv_vs_oracle(handle, M, N, K, res):
     packed, scale = util.make_weight(N, K, seed=N + K)
@@ -67,7 +72,7 @@ def test_fp4_gemv_fuzz(handle):
     for it in range(120):
         K = int(rng.integers(1, 28)) * 256
         N = int(rng.integers(1, 700)) if it % 6 else int(rng.integers(700, 6000))
-        M = int(rng.integers(1, 10))
+        M = int(rng.integers(1, 17))
         gs = float(rng.choice([1.0, 0.37, 7.25, 2688.0]))
         packed, scale = util.make_weight(N, K, seed=it, sigma=float(rng.choice([0.02, 0.14, 1.0])))
         A = util.make_bf16((M, K), seed=1000 + it, std=float(rng.choice([0.01, 1.0, 30.0])))

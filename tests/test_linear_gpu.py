@@ -92,7 +92,7 @@ def test_config0_gemv(handle, impl):
 @pytest.mark.parametrize("impl", [1, 2, 3])
 def test_decode_small_shapes_exhaustive(handle, impl):
     """Every small (K, N, M) combination.  The scalar kernel takes any K % 16 == 0; the TMA + MMA
-    kernels (2: mma.sync, 3: the NVFP4 tensor-core GEMV up to 9 tokens) need K % 256 == 0, so their
+    kernels (2: mma.sync, 3: the NVFP4 tensor-core GEMV) need K % 256 == 0, so their
     variants walk multiples of 256 and nothing is skipped."""
     ks = (16, 32, 48, 64, 128, 256, 512) if impl == 1 else (256, 512, 768, 1024)
     handle.set_option("decode_impl", impl)
@@ -143,7 +143,7 @@ FUZZ_STD = (0.01, 1.0, 30.0)
 def test_decode_fuzz(handle, impl):
     """Random (N, K, M <= 16, global scale, weight and activation magnitude, residual in and out of
     place).  impl 2 = the TMA + mma.sync kernels (up to 8 tokens, and the wide one for 9..16), 3 = the
-    NVFP4 tensor-core GEMV up to 9 tokens: K is drawn from the multiples of 256 they take, so no
+    NVFP4 tensor-core GEMV: K is drawn from the multiples of 256 they take, so no
     case is skipped."""
     rng = np.random.default_rng(1234 + impl)
     handle.set_option("decode_impl", impl)
