@@ -75,10 +75,6 @@ int validate_linear(const nvfp4_handle* h, const void* A, int M, const uint8_t* 
 int cuda_status(cudaError_t e) { return e == cudaSuccess ? NVFP4_OK : (int)e; }
 
 // options only the mma.sync GEMV kernels implement (the tensor-core GEMV takes plain calls, with or without FP32 output)
-bool other_options_but_f32(const LinearArgs& a) {
-    return a.swiglu_up || a.a_stride || a.k_valid || a.norm_w || a.swiglu_out || a.px;
-}
-
 // One linear call on device buffers.
 // `ws_bytes`: how much of the workspace the kernels may use (the host-buffer path keeps its staging behind it).
 int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_bytes = 0) {
@@ -111,7 +107,7 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
     }
     const bool fp4_wanted = a.M <= h->decode_max_m &&
                             (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m));
-    if (fp4_wanted && !other_options_but_f32(a) && decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
+    if (fp4_wanted && !a.px && decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
         // up to 9 tokens with the activations resident beside the ring, else streamed through it
         const bool res = decode_fp4_supported(a, h->dev);
         if (res || decode_fp4_stream_supported(a, h->dev)) {

@@ -39,6 +39,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "fp4_store.cuh"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
@@ -69,19 +70,16 @@ constexpr int kPairTokens = kTokens;               // token rows of a CTA's pair
 static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= fp4::kPairBytes, "pair slots");
 
 struct Fp4Params {
-    const __nv_bfloat16* residual;
-    __nv_bfloat16* C;
+    Fp4Out out;                     // residual, C, 1 / global_scale, M, N and the output options
     const float* unscale;           // per token: 1 / c of the pre-pass
     const unsigned char* sfb;       // the pre-pass's block scales: [K/256][column groups of 32][32 lanes][16 bytes]
     unsigned char* scratch;         // status word at 0, launch counter at 64
     unsigned char* pairs;           // [CTA][kPairTokens][128 rows] x {FP32 value, tag}
-    float inv_gs;
     int M, N, K;
     int NCp, groups;                // MMA columns (tokens x terms padded to 16), groups of 32 of them
     int units, kchunks;
     int stages, hps;                // ring depth, half-units per stage (1 or 2)
     int slots, act_all;             // resident activation chunks; 1 = slot index is the k-chunk
-    int out_f32;
 };
 
 // kind::mxf4nvf4: A = B = E2M1 (format 1), scales unsigned E4M3, both K-major, M = 128, N = NCp, K = 64.
@@ -400,18 +398,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                         }
                     }
                 }
-                const int n = tile * kRT + te;
-                if (n < p.N) {
-#pragma unroll
-                    for (int m = 0; m < kTokens; ++m) {
-                        if (m >= p.M) continue;
-                        float x = v[m] * p.inv_gs;
-                        const size_t o = (size_t)m * p.N + n;
-                        if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
-                        if (p.residual) x += __bfloat162float(p.residual[o]);
-                        p.C[o] = __float2bfloat16_rn(x);
-                    }
-                }
+                fp4_store_rows(v, p.out, tile, te);
             }
             if (kc >= p.kchunks) { kc = 0; ++tile; }
         }
@@ -466,8 +453,8 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
 bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
     if (a.M < 1 || a.M > kTokens || (a.K % kKC) != 0 || a.N < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
-    if (a.px || a.swiglu_up || a.swiglu_out || a.norm_w || a.k_valid) return false;
-    if (a.a_stride && (a.a_stride & 7)) return false;
+    if (a.px || !act_to_fp4_supported(a)) return false;
+    if (a.swiglu_out && (a.residual || a.out_f32 || (a.N & 15))) return false;
     Fp4Plan pl;
     return plan_fp4(a, dev, &pl);
 }
@@ -497,16 +484,19 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
                          (uint32_t)p.NCp, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     const int terms = fp4::terms_for(a.M);
-    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, terms, p.groups, codes, sfb, unscale, s);
+    cudaError_t e = launch_act_to_fp4(a, terms, p.groups, codes, sfb, unscale, s);
     if (e != cudaSuccess) return e;
-    p.residual = static_cast<const __nv_bfloat16*>(a.residual);
-    p.C = static_cast<__nv_bfloat16*>(a.C);
+    p.out.residual = static_cast<const __nv_bfloat16*>(a.residual);
+    p.out.C = static_cast<__nv_bfloat16*>(a.C);
+    p.out.M = a.M;
+    p.out.N = a.N;
+    p.out.swiglu_out = a.swiglu_out ? 1 : 0;
     p.unscale = unscale;
     p.sfb = sfb;
     p.scratch = static_cast<unsigned char*>(scratch);
     p.pairs = p.scratch + pairs_offset;
-    p.inv_gs = a.inv_gs;
-    p.out_f32 = a.out_f32 ? 1 : 0;
+    p.out.inv_gs = a.inv_gs;
+    p.out.out_f32 = a.out_f32 ? 1 : 0;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.grid);
     cfg.blockDim = dim3(kThreads);

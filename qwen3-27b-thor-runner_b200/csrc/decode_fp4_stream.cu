@@ -44,6 +44,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "fp4_store.cuh"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
@@ -73,18 +74,15 @@ constexpr int kPairTokens = fp4::kMaxTokens;       // token rows of a CTA's pair
 static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= fp4::kPairBytes, "pair slots");
 
 struct Fp4Params {
-    const __nv_bfloat16* residual;
-    __nv_bfloat16* C;
+    Fp4Out out;                     // residual, C, 1 / global_scale, M, N and the output options
     const float* unscale;           // per token: 1 / c of the pre-pass
     unsigned char* scratch;         // status word at 0, launch counter at 64
     unsigned char* pairs;           // [CTA][kPairTokens][128 rows] x {FP32 value, tag}
-    float inv_gs;
     int M, N, K;
     int NCp, groups;                // MMA columns (tokens x terms padded to 16), groups of 32 of them
     int acc_stride;                 // tensor-memory columns per accumulator
     int units, kchunks;
     int stages, hps;                // ring depth, half-units per stage (1 or 2)
-    int out_f32;
 };
 
 // kind::mxf4nvf4: A = B = E2M1 (format 1), scales unsigned E4M3, both K-major, M = 128, N = NCp, K = 64.
@@ -410,18 +408,7 @@ decode_fp4_stream_kernel(const __grid_constant__ CUtensorMap tm_packed, const __
                         }
                     }
                 }
-                const int n = tile * kRT + te;
-                if (n < p.N) {
-#pragma unroll
-                    for (int m = 0; m < fp4::kMaxTokens; ++m) {
-                        if (m >= p.M) continue;
-                        float x = v[m] * p.inv_gs;
-                        const size_t o = (size_t)m * p.N + n;
-                        if (p.out_f32) { reinterpret_cast<float*>(p.C)[o] = x; continue; }
-                        if (p.residual) x += __bfloat162float(p.residual[o]);
-                        p.C[o] = __float2bfloat16_rn(x);
-                    }
-                }
+                fp4_store_rows(v, p.out, tile, te);
             }
             if (kc >= p.kchunks) { kc = 0; ++tile; }
         }
@@ -477,8 +464,8 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
 bool decode_fp4_stream_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
     if (a.M < 1 || a.M > fp4::kMaxTokens || (a.K % kKC) != 0 || a.N < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
-    if (a.px || a.swiglu_up || a.swiglu_out || a.norm_w || a.k_valid) return false;
-    if (a.a_stride && (a.a_stride & 7)) return false;
+    if (a.px || !act_to_fp4_supported(a)) return false;
+    if (a.swiglu_out && (a.residual || a.out_f32 || (a.N & 15))) return false;
     Fp4Plan pl;
     return plan_fp4(a, dev, &pl);
 }
@@ -509,15 +496,18 @@ cudaError_t launch_decode_fp4_stream(const LinearArgs& a, nvfp4_device_info& dev
                          (uint32_t)p.groups, CU_TENSOR_MAP_SWIZZLE_NONE))
         return cudaErrorInvalidValue;
     const int terms = fp4::terms_for(a.M);
-    cudaError_t e = launch_act_to_fp4(a.A, a.a_stride ? a.a_stride : a.K, a.M, a.K, terms, p.groups, codes, sfb, unscale, s);
+    cudaError_t e = launch_act_to_fp4(a, terms, p.groups, codes, sfb, unscale, s);
     if (e != cudaSuccess) return e;
-    p.residual = static_cast<const __nv_bfloat16*>(a.residual);
-    p.C = static_cast<__nv_bfloat16*>(a.C);
+    p.out.residual = static_cast<const __nv_bfloat16*>(a.residual);
+    p.out.C = static_cast<__nv_bfloat16*>(a.C);
+    p.out.M = a.M;
+    p.out.N = a.N;
+    p.out.swiglu_out = a.swiglu_out ? 1 : 0;
     p.unscale = unscale;
     p.scratch = static_cast<unsigned char*>(scratch);
     p.pairs = p.scratch + pairs_offset;
-    p.inv_gs = a.inv_gs;
-    p.out_f32 = a.out_f32 ? 1 : 0;
+    p.out.inv_gs = a.inv_gs;
+    p.out.out_f32 = a.out_f32 ? 1 : 0;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.grid);
     cfg.blockDim = dim3(kThreads);

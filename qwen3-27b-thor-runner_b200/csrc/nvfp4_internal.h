@@ -146,8 +146,9 @@ inline size_t act_sfb_offset(int K) { return ((size_t)kMaxCols * (K / 2) + 255) 
 inline size_t act_unscale_offset(int K) { return act_sfb_offset(K) + ((size_t)(K / 256) * 1536 + 255) / 256 * 256; }
 inline size_t act_scratch_bytes(int K) { return act_unscale_offset(K) + 256; }
 }  // namespace fp4
-cudaError_t launch_act_to_fp4(const void* A, long long a_stride, int M, int K, int terms, int groups, void* codes, void* sfb,
-                              float* unscale, cudaStream_t s);
+// The pre-pass takes the activation-side options of `a` (swiglu_up, norm_w, a_stride, k_valid).
+bool act_to_fp4_supported(const LinearArgs& a);
+cudaError_t launch_act_to_fp4(const LinearArgs& a, int terms, int groups, void* codes, void* sfb, float* unscale, cudaStream_t s);
 bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev);
 size_t decode_fp4_scratch_bytes(int K);       // codes + scale atoms + per-token factors of the activation pre-pass
 cudaError_t configure_decode_fp4();

@@ -854,10 +854,12 @@ def test_tp_mlp_single_rank_beyond_gemv(handle, M):
         comm.close()
 
 
+@pytest.mark.parametrize("impl", [2, 3])
 @pytest.mark.parametrize("M", [1, 3, 8, 13])
-def test_linear_ex_swiglu_prologue(handle, M):
-    """SwiGLU formed while the GEMV stages its activations (merged gate/up rows, K padded beyond
-    the tensor) gives the very bits of the separate SwiGLU kernel followed by the plain linear."""
+def test_linear_ex_swiglu_prologue(handle, M, impl):
+    """SwiGLU formed on the activations' way into the GEMV (merged gate/up rows, K padded beyond the
+    tensor) gives the very bits of the separate SwiGLU kernel followed by the plain linear: in the
+    mma.sync GEMV's staging code (2) and in the pre-pass of the NVFP4 tensor-core GEMV (3)."""
     import torch
     I, Kp, N = 448, 512, 384                 # down-projection shard: 448 real columns in a K of 512
     packed, scale = util.make_weight(N, Kp, seed=51)
@@ -870,17 +872,17 @@ def test_linear_ex_swiglu_prologue(handle, M):
     handle.swiglu_strided(dGU, dGU[:, I:], M, I, 2 * I, act, Kp)
     want = ob.linear(util.pad_cols(ob.swiglu_merged(GU), Kp), packed, scale, 1.5, residual=R, mode=ob.GEMV, threads=4)
     dC = util.to_dev(R)
-    handle.linear_ex(dGU, M, dp, ds, 1.5, N, Kp, dC, residual=dC, swiglu_up=dGU[:, I:], a_row_stride=2 * I, k_valid=I)
-    torch.cuda.synchronize()
-    got = util.to_host_u16(dC)
-    assert ob.rel_frobenius(got, want) <= TOL
     dC2 = util.to_dev(R)
     handle.set_option("skinny_min_m", 129)           # the plain linear through the same GEMV kernel
-    handle.set_option("decode_impl", 2)
+    handle.set_option("decode_impl", impl)
     try:
+        handle.linear_ex(dGU, M, dp, ds, 1.5, N, Kp, dC, residual=dC, swiglu_up=dGU[:, I:], a_row_stride=2 * I, k_valid=I)
         handle.linear(act, M, dp, ds, 1.5, N, Kp, dC2, residual=dC2)
     finally:
         handle.set_option("skinny_min_m", 9)
         handle.set_option("decode_impl", 0)
+    torch.cuda.synchronize()
+    got = util.to_host_u16(dC)
+    assert ob.rel_frobenius(got, want) <= TOL
     torch.cuda.synchronize()
     assert np.array_equal(got, util.to_host_u16(dC2))
