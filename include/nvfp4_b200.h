@@ -79,6 +79,9 @@ const char* nvfp4_status_string(int status);
  *                   tensor core, as it is in FP8 E4M3; every other kernel, like the reference's
  *                   table-free decoder (dense_gemm_fp4_sm110.cu:30-41), reads it as 480.  No finite
  *                   FP8 E4M3 value encodes to it.  0 = off
+ *   "fp4_own_quant": 1 (default) = for one or two tokens (no SwiGLU or RMSNorm in front) that kernel
+ *                   expands the activations itself and no pre-pass kernel is launched; 0 = always
+ *                   the pre-pass
  *   "prefill_impl": 0 = auto, 1 = dequant-to-workspace + CUDA-core GEMM (debug),
  *                   2 = fused dequant + tcgen05 GEMM
  *   "decode_max_m": largest M routed to the GEMV path (default 16)

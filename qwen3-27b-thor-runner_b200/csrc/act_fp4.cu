@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "fp4_quant.cuh"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
 #include "ptx.cuh"
@@ -31,22 +32,7 @@
 namespace nvfp4 {
 namespace {
 
-// Two FP32 -> one byte of E2M1 codes, `lo` in the low nibble (round to nearest even, saturating at 6).
-__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
-    uint16_t d;
-    asm("{\n\t.reg .b8 b;\n\tcvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\n\tmov.b16 %0, {b, b};\n\t}" : "=h"(d) : "f"(hi), "f"(lo));
-    return d;
-}
-// One byte of E2M1 codes -> two floats.
-__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
-    uint32_t h2;
-    asm("{\n\t.reg .b8 b, z;\n\tmov.b16 {b, z}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "h"((uint16_t)byte));
-    return __half22float2(*reinterpret_cast<const __half2*>(&h2));
-}
-// 2^p as an unsigned E4M3 byte, p in [-9, 8].
-__device__ __forceinline__ uint32_t ue4m3_pow2(int p) {
-    return p >= -6 ? (uint32_t)(p + 7) << 3 : (p == -7 ? 4u : (p == -8 ? 2u : 1u));
-}
+using namespace fp4q;
 
 constexpr int kSliceBlocks = 64;        // 16-element blocks (1024 k) per CTA
 constexpr int kPreThreads = 4 * kSliceBlocks;
@@ -170,9 +156,7 @@ act_to_fp4_kernel(const ActParams p) {
         __syncthreads();
         amax = s_max;
     }
-    // c = 2^(136 - e): the largest element (biased BF16 exponent e) lands in [2^9, 2^10)
-    int se = 263 - (int)(amax >> 7);
-    se = se < 1 ? 1 : (se > 254 ? 254 : se);
+    const int se = token_scale_exponent(amax);
     const float c = __uint_as_float((uint32_t)se << 23);
     if (blockIdx.x == 0 && threadIdx.x == 0) p.unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
     float r[4];
@@ -195,28 +179,11 @@ act_to_fp4_kernel(const ActParams p) {
     bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
     bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
     if (live) {
-        // p0: smallest p with bmax <= 6 * 2^p, clamped to the unsigned E4M3 range of powers of two
-        int p0 = -9;
-        if (bmax > 0.0f && bmax < 3.0e38f) {
-            const uint32_t u = __float_as_uint(bmax * (1.0f / 6.0f));
-            p0 = (int)(u >> 23) - 127 + ((u & 0x7FFFFFu) ? 1 : 0);
-            if (bmax > 6.0f * __uint_as_float((uint32_t)(p0 + 127) << 23)) ++p0;     // 1/6 is not exact: never let the block exceed 6 s_0
-        }
-        p0 = p0 < -9 ? -9 : (p0 > 8 ? 8 : p0);
+        const int p0 = first_term_exponent(bmax);
 #pragma unroll
         for (int t = 0; t < TERMS; ++t) {
-            int pw = p0 - (t == 0 ? 0 : 2 + 3 * (t - 1));
-            pw = pw < -9 ? -9 : pw;
-            const float s = __uint_as_float((uint32_t)(pw + 127) << 23), inv = __uint_as_float((uint32_t)(127 - pw) << 23);
-            uint32_t w = 0u;
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const uint32_t byte = cvt_e2m1x2(r[2 * q] * inv, r[2 * q + 1] * inv) & 0xFFu;
-                const float2 d = e2m1x2_to_float2(byte);
-                r[2 * q] -= d.x * s;
-                r[2 * q + 1] -= d.y * s;
-                w |= byte << (8 * q);
-            }
+            const int pw = term_exponent(p0, t);
+            const uint32_t w = take_term(r, pw);
             const int col = m * TERMS + t;
             *reinterpret_cast<uint16_t*>(p.codes + (size_t)col * (K / 2) + (size_t)b * 8 + part * 2) = (uint16_t)w;
             if (part == 0) p.sfb[fp4::sfb_offset(b, col, p.groups)] = (uint8_t)ue4m3_pow2(pw);

@@ -294,6 +294,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "fp4_min_m")) {
         if (value < 1 || value > 16) return NVFP4_E_OPTION;
         h->fp4_min_m = value;
+    } else if (!std::strcmp(name, "fp4_own_quant")) {
+        if (value < 0 || value > 1) return NVFP4_E_OPTION;
+        h->dev.fp4_own_quant = value;
     } else if (!std::strcmp(name, "skinny_min_m")) {
         if (value < 1 || value > 129) return NVFP4_E_OPTION;
         h->skinny_min_m = value;
@@ -321,6 +324,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "wide_gemv")) *value = h->wide_gemv;
     else if (!std::strcmp(name, "fp4_native")) *value = h->fp4_native;
     else if (!std::strcmp(name, "fp4_min_m")) *value = h->fp4_min_m;
+    else if (!std::strcmp(name, "fp4_own_quant")) *value = h->dev.fp4_own_quant;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;

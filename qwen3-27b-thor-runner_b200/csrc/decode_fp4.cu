@@ -22,7 +22,11 @@
 //   * the activations are the B operand: a pre-pass (act_fp4.cu) expands every BF16 token into six
 //     (five for 3, 6 and 9 tokens) NVFP4 term rows whose sum reproduces it to 1e-5 (8e-5) of each block's largest element; the CTA's k
 //     range of the codes is loaded once by warp 2 and stays resident in shared memory, next to their
-//     block scales (copied in by warps 8-11 before their first accumulator arrives);
+//     block scales (copied in by warps 8-11 before their first accumulator arrives).  For one or two
+//     tokens without SwiGLU or RMSNorm in front, where a CTA's k range is short (up to 8 chunks), there
+//     is no pre-pass at all: warps 4-11 expand the CTA's k range of the activations themselves,
+//     straight into the operand layout in shared memory (CTAs repeat each other's work, but a
+//     kernel boundary is gone);
 //   * warps 8-11 read the accumulator (thread = weight row), add the term columns of each token,
 //     undo the token scale, apply 1/global_scale and the residual in FP32 and round once.  A row
 //     tile split over several CTAs is finished by the CTA holding its first half-unit: the others
@@ -39,6 +43,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "fp4_quant.cuh"
 #include "fp4_store.cuh"
 #include "nvfp4_format.cuh"
 #include "nvfp4_internal.h"
@@ -72,6 +77,9 @@ static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= fp4::kPairBytes, "pair
 struct Fp4Params {
     Fp4Out out;                     // residual, C, 1 / global_scale, M, N and the output options
     const float* unscale;           // per token: 1 / c of the pre-pass
+    const __nv_bfloat16* A;         // the kernel expands the activations itself: [M, K] BF16 rows a_stride apart,
+    long long a_stride;             // ... columns from k_valid on count as zero and are never read
+    int k_valid;
     const unsigned char* sfb;       // the pre-pass's block scales: [K/256][column groups of 32][32 lanes][16 bytes]
     unsigned char* scratch;         // status word at 0, launch counter at 64
     unsigned char* pairs;           // [CTA][kPairTokens][128 rows] x {FP32 value, tag}
@@ -113,7 +121,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
-template <int TERMS>
+constexpr int kOwnTokens = 2;       // most tokens the kernel expands itself
+constexpr int kOwnThreads = 8 * 32; // warps 4-11
+constexpr int kOwnMaxChunks = 8;    // ... and most resident 256-k chunks x tokens it does so for
+
+template <int TERMS, bool OWN>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ Fp4Params p) {
@@ -134,6 +146,8 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
     volatile unsigned int* s_epoch = reinterpret_cast<volatile unsigned int*>(s_tmem + 2);
+    unsigned int* s_amax = s_tmem + 3;                                      // [2] largest magnitude of a token (BF16 bits)
+    float* s_unscale = reinterpret_cast<float*>(s_tmem + 5);                // [2] 1 / c of a token
 
     unsigned int* status = reinterpret_cast<unsigned int*>(p.scratch);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -149,7 +163,8 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             ptx::mbar_init(&sfa_bar[s], 4);
         }
         ptx::mbar_init(&b_bar[0], 1);
-        ptx::mbar_init(&b_bar[1], 4);
+        ptx::mbar_init(&b_bar[1], OWN ? 1 : 4);
+        s_amax[0] = s_amax[1] = 0u;
         for (int i = 0; i < 2; ++i) { ptx::mbar_init(&tfull[i], 1); ptx::mbar_init(&tempty[i], 4); }
         *s_abort = 0;
         *s_epoch = 0u;
@@ -161,6 +176,96 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
     ptx::griddep_launch_dependents();
+
+    if (OWN && warp >= 4) {
+        // ------------------------------------------------------------------ the activations, expanded here (see act_fp4.cu for the scheme)
+        using namespace fp4q;
+        const int tq = tid - 4 * 32;
+        ptx::griddep_wait();                                  // A is the output of the kernel before this one
+        const int chunks = p.k_valid / 8;
+#pragma unroll
+        for (int m = 0; m < kOwnTokens; ++m) {
+            if (m >= p.M) continue;
+            const uint4* src = reinterpret_cast<const uint4*>(p.A + (size_t)m * p.a_stride);
+            unsigned int amax = 0;
+            for (int i0 = tq; i0 < chunks; i0 += kOwnThreads * 4) {
+                uint4 x[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * kOwnThreads;
+                    x[j] = i < chunks ? __ldcg(src + i) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t v[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) amax = max(amax, max(v[q] & 0x7FFFu, (v[q] >> 16) & 0x7FFFu));
+                }
+            }
+            amax = __reduce_max_sync(0xffffffffu, amax);
+            if (lane == 0 && amax) atomicMax(&s_amax[m], amax);
+        }
+        ptx::named_barrier_sync(2, kOwnThreads);
+        float c[kOwnTokens];
+#pragma unroll
+        for (int m = 0; m < kOwnTokens; ++m) {
+            const int se = token_scale_exponent(s_amax[m]);
+            c[m] = __uint_as_float((uint32_t)se << 23);
+            if (tq == m) s_unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
+        }
+        // One task = a quarter (4 elements) of a 16-element block of one token in one resident chunk; a quad of
+        // lanes holds the block.  64 tasks per token and chunk, so whole warps are in or out of range together.
+        const int total = p.M * p.slots * 64;
+        const int kc0 = p.act_all ? 0 : kc_begin;
+        for (int id0 = tq; id0 < total; id0 += kOwnThreads * 4) {
+            uint2 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int id = id0 + u * kOwnThreads;
+                x[u] = make_uint2(0u, 0u);
+                if (id < total) {
+                    const int part = id & 3, bl = (id >> 2) & 15, rest = id >> 6;
+                    const int m = rest / p.slots, j = rest - m * p.slots;
+                    int kcj = kc0 + j;
+                    if (kcj >= p.kchunks) kcj -= p.kchunks;
+                    const int k = kcj * kKC + bl * 16 + part * 4;
+                    if (k < p.k_valid) x[u] = __ldcg(reinterpret_cast<const uint2*>(p.A + (size_t)m * p.a_stride + k));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int id = id0 + u * kOwnThreads;
+                if (id >= total) continue;                        // uniform across the warp
+                const int part = id & 3, bl = (id >> 2) & 15, rest = id >> 6;
+                const int m = rest / p.slots, j = rest - m * p.slots;
+                const float cm = m == 0 ? c[0] : c[1];
+                float r[4] = {__uint_as_float(x[u].x << 16) * cm, __uint_as_float(x[u].x & 0xFFFF0000u) * cm,
+                              __uint_as_float(x[u].y << 16) * cm, __uint_as_float(x[u].y & 0xFFFF0000u) * cm};
+                float bmax = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+                bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+                bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 2));
+                const int p0 = first_term_exponent(bmax);
+                // Operand layout (K-major, 128-byte swizzle, as TMA would have written it): row = MMA column, a row
+                // holds the chunk's 256 codes in eight 16-byte pieces, piece i of row r at position i ^ (r % 8).
+                unsigned char* row0 = s_b + j * b_bytes;
+                unsigned char* sf0 = s_sfb + j * p.groups * 512 + (bl >> 2) * 4 + (bl & 3);
+#pragma unroll
+                for (int t = 0; t < TERMS; ++t) {
+                    const int pw = term_exponent(p0, t);
+                    const uint32_t w = take_term(r, pw);
+                    const int col = m * TERMS + t;
+                    *reinterpret_cast<uint16_t*>(row0 + col * 128 + (((bl >> 1) ^ (col & 7)) << 4) + (bl & 1) * 8 + part * 2) = (uint16_t)w;
+                    if (part == 0) sf0[(col & 31) * 16] = (uint8_t)ue4m3_pow2(pw);
+                }
+            }
+        }
+        ptx::fence_proxy_async_smem();                        // the tensor core reads the codes through the asynchronous proxy
+        ptx::named_barrier_sync(2, kOwnThreads);
+        if (tq == 0) {
+            ptx::mbar_arrive(&b_bar[0]);
+            ptx::mbar_arrive(&b_bar[1]);
+        }
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ weight stream
@@ -193,7 +298,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ resident activations (the pre-pass's output)
-        if (lane == 0) {
+        if (lane == 0 && !OWN) {
             ptx::prefetch_tensormap(&tm_act);
             ptx::griddep_wait();
             const uint64_t pol = ptx::policy_evict_last();
@@ -307,7 +412,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         unsigned int epoch_taken = 0;
         if (te == 0) epoch_taken = ptx::take_launch_epoch(p.scratch);
         unsigned char* pairs = p.pairs;
-        {
+        if (!OWN) {
             // The activations' block scales of the CTA's k range into shared memory (512 bytes per resident chunk
             // and column group, as the pre-pass left them); the warps of the scale path wait for this.
             const int kc0 = p.act_all ? 0 : kc_begin;
@@ -364,7 +469,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
 
 #pragma unroll
             for (int m = 0; m < kTokens; ++m)
-                if (m < p.M) v[m] *= p.unscale[m];
+                if (m < p.M) v[m] *= OWN ? s_unscale[m < kOwnTokens ? m : 0] : p.unscale[m];
             if (!owner) {
                 unsigned char* slot = pairs + (size_t)cta * (kPairTokens * kRT) * 8;
 #pragma unroll
@@ -462,9 +567,10 @@ bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
 size_t decode_fp4_scratch_bytes(int K) { return fp4::act_scratch_bytes(K); }
 
 cudaError_t configure_decode_fp4() {
-    cudaError_t e = configure_large_smem(decode_fp4_kernel<5>, kSmemBudget);
-    if (e != cudaSuccess) return e;
-    return configure_large_smem(decode_fp4_kernel<6>, kSmemBudget);
+    cudaError_t e = configure_large_smem(decode_fp4_kernel<5, false>, kSmemBudget);
+    if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<6, false>, kSmemBudget);
+    if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<6, true>, kSmemBudget);
+    return e;
 }
 
 cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void* scratch, size_t pairs_offset, void* act,
@@ -484,8 +590,15 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
                          (uint32_t)p.NCp, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     const int terms = fp4::terms_for(a.M);
-    cudaError_t e = launch_act_to_fp4(a, terms, p.groups, codes, sfb, unscale, s);
+    // One or two plain tokens on a short k range per CTA: the kernel expands them itself and no pre-pass runs.
+    // (Measured: 0.7 us ahead of the pre-pass at 7 and 8 resident chunks, 1.8 us behind at 19 and 20.)
+    const bool own = dev.fp4_own_quant && a.M <= kOwnTokens && terms == 6 && !a.swiglu_up && !a.norm_w && a.M * p.slots <= kOwnMaxChunks;
+    cudaError_t e = cudaSuccess;
+    if (!own) e = launch_act_to_fp4(a, terms, p.groups, codes, sfb, unscale, s);
     if (e != cudaSuccess) return e;
+    p.A = static_cast<const __nv_bfloat16*>(a.A);
+    p.a_stride = a.a_stride ? a.a_stride : a.K;
+    p.k_valid = a.k_valid ? a.k_valid : a.K;
     p.out.residual = static_cast<const __nv_bfloat16*>(a.residual);
     p.out.C = static_cast<__nv_bfloat16*>(a.C);
     p.out.M = a.M;
@@ -507,9 +620,10 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6>, tmp, tms, tma, p)
-                   : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5>, tmp, tms, tma, p);
-    if (launches) *launches = 2;
+    e = own ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, true>, tmp, tms, tma, p)
+            : (terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, false>, tmp, tms, tma, p)
+                          : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5, false>, tmp, tms, tma, p));
+    if (launches) *launches = own ? 1 : 2;
     return e;
 }
 

@@ -51,6 +51,7 @@ struct nvfp4_device_info {
     size_t smem_optin;
     int prefill_stream_k = 1;    // split the tiles left after whole waves by k over all CTAs
     int skinny_split_cost = 12;  // stage-times charged to splitting row tiles by k in the few-token kernel
+    int fp4_own_quant = 1;       // one or two tokens: the tensor-core GEMV expands its activations itself, no pre-pass launch
     size_t gemv_pairs_offset = 6u << 20;   // where the 8-token GEMV's {value, epoch} partial pairs start in its scratch
     TensorMapCache* maps = nullptr;        // null: encode every time
 };
