@@ -35,7 +35,7 @@ SHAPES = {"gate_up": (2 * I, H), "down": (H, I), "qkv": (7168, 5120), "o": (5120
 DECODE_MS = (1, 2, 4, 8, 16)
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up call at M = 1 (algorithmic: 100.35 MB), from one
 # ncu capture per kernel: the NVFP4 tensor-core GEMV with its pre-pass, and the mma.sync GEMV
-NCU_TRAFFIC_GATE_UP_M1 = {"fp4": None, "mma": 106047744}
+NCU_TRAFFIC_GATE_UP_M1 = {"fp4": 106466560, "mma": 106047744}
 L2_BYTES = 126 << 20
 
 

@@ -216,8 +216,9 @@ int nvfp4_linear_ex(nvfp4_handle* h, const nvfp4_linear_desc* desc, nvfp4_stream
  * nvfp4_linear_desc, executed in order by ONE launch of the GEMV kernel.  Linear i+1 may read what linear i
  * wrote (the activations, the residual stream): between two linears all CTAs meet at a grid-wide barrier
  * in device memory.  Meanwhile the kernel's loader keeps streaming the next linear's weights into its
- * shared-memory ring -- weights depend on nothing -- so HBM does not idle across the launch boundaries a
- * sequence of nvfp4_linear calls would have, and the per-launch cost is paid once.  The reference runs
+ * shared-memory ring -- weights depend on nothing -- and the per-launch cost is paid once.  (Measured on a
+ * B200 this saves launches, not time: separate launches with programmatic dependent launch overlap what the
+ * barrier serialises, and a 64-layer token step takes 3.97 ms as a chain against 3.63 ms.)  The reference runs
  * one kernel per projection (src/engine/layer.cu:62-110, 190-217, 404-409): a decode layer's sequence
  * o-projection + residual -> RMSNorm -> gate_up -> SwiGLU -> down + residual, or all layers of a token
  * step, is one chain here.
