@@ -153,6 +153,63 @@ def test_two_rank_gloo_matches_partition_aware_oracle(world):
     assert ob.rel_frobenius(outs[0], full) < 1e-2
 
 
+def _rank_main_fp32(rank, world, port, q):
+    """The NCCL path of the row-split linear as the library runs it above 16 tokens, with gloo and numpy in
+    place of NCCL and the kernels: unrounded FP32 partial sums, summed over the ranks, each rank finishes ITS
+    slice (residual, one rounding), the BF16 slices are gathered."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, H, I = 24, 256, 512
+        gu_p, gu_s = util.make_weight(2 * I, H, seed=11)
+        dn_p, dn_s = util.make_weight(H, I, seed=12)
+        X = util.make_bf16((M, H), seed=13)
+        R = util.make_bf16((M, H), seed=14)
+        p, s = nvfp4_tp.shard_gate_up(gu_p, gu_s, rank, world)
+        act = ob.swiglu_merged(ob.linear(X, p, s, 1.0))
+        dp, ds = nvfp4_tp.shard_down(dn_p, dn_s, rank, world)
+        a32 = ob.bf16_to_f32(nvfp4_tp.pad_activation(act, dp.shape[1] * 2))
+        w32 = ob.bf16_to_f32(ob.dequant(dp, ds, 1.0))                  # exact: 2 + 4 significant bits
+        part = torch.from_numpy((a32 @ w32.T).astype(np.float32))      # unrounded FP32 partial [M, H]
+        dist.all_reduce(part)                                          # reduce-scatter: the sum, of which a rank keeps its slice
+        cnt = M * H // world
+        mine = part.reshape(-1)[rank * cnt:(rank + 1) * cnt].numpy()
+        res = ob.bf16_to_f32(R).reshape(-1)[rank * cnt:(rank + 1) * cnt]
+        piece = torch.from_numpy(ob.f32_to_bf16(mine + res).astype(np.int32))
+        pieces = [torch.empty_like(piece) for _ in range(world)]
+        dist.all_gather(pieces, piece)                                 # all-gather of the finished BF16 slices
+        got = np.concatenate([t.numpy() for t in pieces]).astype(np.uint16).reshape(M, H)
+        q.put((rank, got))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_fp32_partials_stay_within_the_linear_tolerance():
+    import torch.multiprocessing as mp
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main_fp32, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    M, H, I = 24, 256, 512
+    gu_p, gu_s = util.make_weight(2 * I, H, seed=11)
+    dn_p, dn_s = util.make_weight(H, I, seed=12)
+    X, R = util.make_bf16((M, H), seed=13), util.make_bf16((M, H), seed=14)
+    assert np.array_equal(outs[0], outs[1])
+    full = ob.mlp(X, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R)
+    assert ob.rel_frobenius(outs[0], full) <= 1e-3                     # one rounding, as the unsplit layer
+    bf16_form = ob.tp_mlp(X, world, gu_p, gu_s, 1.0, dn_p, dn_s, 1.0, residual=R, partial_bf16=True)
+    assert ob.rel_frobenius(bf16_form, full) > ob.rel_frobenius(outs[0], full)     # what BF16-rounded partials cost
+
+
 def _attn_rank_main(rank, world, port, q):
     import torch
     import torch.distributed as dist
