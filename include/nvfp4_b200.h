@@ -79,6 +79,14 @@ const char* nvfp4_status_string(int status);
  *                   tensor core, as it is in FP8 E4M3; every other kernel, like the reference's
  *                   table-free decoder (dense_gemm_fp4_sm110.cu:30-41), reads it as 480.  No finite
  *                   FP8 E4M3 value encodes to it.  0 = off
+ *   "gemm_weight_rounding": 0 (default) = every kernel multiplies the exact block-scaled weights and applies
+ *                   1 / global_scale once, in FP32 (the reference's arithmetic up to 8 tokens,
+ *                   dense_gemm_fp4_sm110.cu:96-141).  1 = above 8 tokens the weights are rounded to BF16
+ *                   after the global scale, bf16(e2m1 * (ue4m3 * 1/gs)), operation for operation what the
+ *                   reference's GEMM branch does (:444-467, 558-583); with a global scale that is not a
+ *                   power of two the two forms lie 2.7e-3 apart.  Plain calls with N % 8 == 0 and
+ *                   K % 256 == 0 only (NVFP4_E_LIMIT otherwise); slower (the tcgen05 GEMM with a longer
+ *                   dequantisation)
  *   "fp4_own_quant": 1 (default) = for one or two tokens (no SwiGLU or RMSNorm in front) that kernel
  *                   expands the activations itself and no pre-pass kernel is launched; 0 = always
  *                   the pre-pass

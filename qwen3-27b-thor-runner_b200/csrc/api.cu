@@ -25,6 +25,7 @@ struct nvfp4_handle {
     int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
     int fp4_native = 1;                          // the NVFP4 tensor-core GEMV (weights untouched, activations as NVFP4 terms) ...
     int fp4_min_m = 1;                           // ... from this token count on (up to 16)
+    int gemm_weight_rounding = 0;                // above 8 tokens: the reference's BF16-rounded weights (its GEMM branch)
     unsigned long long launches = 0;
 };
 
@@ -86,6 +87,18 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
                          decode_wide_scratch_bytes(h->dev.sm_count) <= h->dev.gemv_pairs_offset;
     // options only the GEMV kernels implement (the SwiGLU epilogue and the group reduction exist in the wide one too)
     const bool other_options = a.out_f32 || a.swiglu_up || a.a_stride || a.k_valid || a.norm_w;
+    if (h->gemm_weight_rounding && a.M > 8 && !a.out_f32 && !a.px && !a.swiglu_up && !a.a_stride && !a.k_valid && !a.norm_w &&
+        !a.swiglu_out) {
+        // The reference's own arithmetic above 8 tokens, for a caller who wants ITS bits rather than exact weights.
+        if (h->prefill_impl == 1 || !prefill_umma_supported(a)) return NVFP4_E_LIMIT;
+        if (kDecodeScratchBytes + prefill_umma_scratch_bytes(a.M, a.N, a.K) > ws_bytes) return NVFP4_E_WORKSPACE;
+        LinearArgs r = a;
+        r.round_weights = true;
+        int nl = 0;
+        cudaError_t e = launch_prefill_umma(r, h->dev, h->workspace, ws_bytes, kDecodeScratchBytes, &nl, s);
+        h->launches += (unsigned long long)nl;
+        return cuda_status(e);
+    }
     if (a.out_f32 && a.M > 16) {
         // unrounded FP32 sums beyond the GEMV kernels: the 128-token-tile tcgen05 kernel's FP32 epilogue
         if (a.swiglu_up || a.a_stride || a.k_valid || a.norm_w || a.px || a.swiglu_out) return NVFP4_E_LIMIT;
@@ -294,6 +307,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "fp4_min_m")) {
         if (value < 1 || value > 16) return NVFP4_E_OPTION;
         h->fp4_min_m = value;
+    } else if (!std::strcmp(name, "gemm_weight_rounding")) {
+        if (value < 0 || value > 1) return NVFP4_E_OPTION;
+        h->gemm_weight_rounding = value;
     } else if (!std::strcmp(name, "fp4_own_quant")) {
         if (value < 0 || value > 1) return NVFP4_E_OPTION;
         h->dev.fp4_own_quant = value;
@@ -325,6 +341,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "fp4_native")) *value = h->fp4_native;
     else if (!std::strcmp(name, "fp4_min_m")) *value = h->fp4_min_m;
     else if (!std::strcmp(name, "fp4_own_quant")) *value = h->dev.fp4_own_quant;
+    else if (!std::strcmp(name, "gemm_weight_rounding")) *value = h->gemm_weight_rounding;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;
@@ -495,9 +512,22 @@ int nvfp4_linear_dual(nvfp4_handle* h, const void* A, int M, const uint8_t* pack
                       void* C1, void* C2, nvfp4_stream_t stream) {
     if (int e = validate_linear(h, A, M, packed1, scale1, gs1, N, K, nullptr, C1)) return e;
     if (int e = validate_linear(h, A, M, packed2, scale2, gs2, N, K, nullptr, C2)) return e;
-    // Two back-to-back launches on one stream: A (tens of KB) stays in L2 between
-    // them, which is all the reference's single dual launch buys.
     LinearArgs a{A, packed1, scale1, 1.0f / gs1, nullptr, C1, M, N, K};
+    {
+        // One launch of the NVFP4 tensor-core GEMV over both weights (one activation pre-pass), as the reference's
+        // dual kernel is one launch (src/engine/dense_gemm_fp4_sm110.cu:264-351).
+        LinearArgs d = a;
+        d.packed2 = packed2; d.scale2 = scale2; d.inv_gs2 = 1.0f / gs2; d.C2 = C2;
+        const bool fp4_wanted = M <= h->decode_max_m && (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && M >= h->fp4_min_m));
+        if (fp4_wanted && decode_fp4_scratch_bytes(K) <= kFp4ActBytes && kDecodeScratchBytes <= h->workspace_bytes &&
+            decode_fp4_supported(d, h->dev)) {
+            int nl = 0;
+            cudaError_t e = launch_decode_fp4(d, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, stream);
+            h->launches += (unsigned long long)nl;
+            return cuda_status(e);
+        }
+    }
+    // Otherwise two back-to-back launches on one stream: A (tens of KB) stays in L2 between them.
     if (int e = run_linear(h, a, stream)) return e;
     LinearArgs b{A, packed2, scale2, 1.0f / gs2, nullptr, C2, M, N, K};
     return run_linear(h, b, stream);

@@ -76,6 +76,8 @@ static_assert((size_t)kMaxGrid * kPairTokens * kRT * 8 <= fp4::kPairBytes, "pair
 
 struct Fp4Params {
     Fp4Out out;                     // residual, C, 1 / global_scale, M, N and the output options
+    Fp4Out out2;                    // ... of the second weight of a dual call (row tiles from tiles0 on)
+    int tiles0;                     // row tiles of the first weight (all of them unless the call is dual)
     const float* unscale;           // per token: 1 / c of the pre-pass
     const __nv_bfloat16* A;         // the kernel expands the activations itself: [M, K] BF16 rows a_stride apart,
     long long a_stride;             // ... columns from k_valid on count as zero and are never read
@@ -128,6 +130,7 @@ constexpr int kOwnMaxChunks = 8;    // ... and most resident 256-k chunks x toke
 template <int TERMS, bool OWN>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
+                  const __grid_constant__ CUtensorMap tm_packed2, const __grid_constant__ CUtensorMap tm_scale2,
                   const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ Fp4Params p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -272,6 +275,10 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         if (lane == 0) {
             ptx::prefetch_tensormap(&tm_packed);
             ptx::prefetch_tensormap(&tm_scale);
+            if (p.tiles0 * p.kchunks < p.units) {
+                ptx::prefetch_tensormap(&tm_packed2);
+                ptx::prefetch_tensormap(&tm_scale2);
+            }
             const uint64_t pol = ptx::policy_evict_first();
             int stage = 0;
             uint32_t ph = 0;
@@ -279,15 +286,18 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             while (hu < u_end) {
                 const int tile_end = hu - kc + p.kchunks;
                 const int seg_end = tile_end < u_end ? tile_end : u_end;
-                const int row0 = tile * kRT;
+                const bool second = tile >= p.tiles0;             // a dual call: the second weight's row tiles follow the first's
+                const int row0 = (second ? tile - p.tiles0 : tile) * kRT;
+                const CUtensorMap* mp = second ? &tm_packed2 : &tm_packed;
+                const CUtensorMap* ms = second ? &tm_scale2 : &tm_scale;
                 while (hu < seg_end) {
                     const int cnt = (seg_end - hu) >= hps ? hps : 1;
                     ptx::mbar_wait(&empty_bar[stage], ph ^ 1u, s_abort, status, 0xA00u + (unsigned)stage);
                     ptx::mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(kPackedBytes + kScaleBytes) * cnt);
                     for (int h = 0; h < cnt; ++h) {
                         const int k0 = (kc + h) * kKC;
-                        ptx::tma_load_2d(s_w + (stage * hps + h) * kPackedBytes, &tm_packed, &full_bar[stage], k0 >> 1, row0, pol);
-                        ptx::tma_load_2d(s_raw + (stage * hps + h) * kScaleBytes, &tm_scale, &full_bar[stage], k0 >> 4, row0, pol);
+                        ptx::tma_load_2d(s_w + (stage * hps + h) * kPackedBytes, mp, &full_bar[stage], k0 >> 1, row0, pol);
+                        ptx::tma_load_2d(s_raw + (stage * hps + h) * kScaleBytes, ms, &full_bar[stage], k0 >> 4, row0, pol);
                     }
                     hu += cnt;
                     kc += cnt;
@@ -503,7 +513,8 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                         }
                     }
                 }
-                fp4_store_rows(v, p.out, tile, te);
+                if (tile < p.tiles0) fp4_store_rows(v, p.out, tile, te);
+                else fp4_store_rows(v, p.out2, tile - p.tiles0, te);
             }
             if (kc >= p.kchunks) { kc = 0; ++tile; }
         }
@@ -530,7 +541,8 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
     p.NCp = (a.M * fp4::terms_for(a.M) + 15) / 16 * 16;
     p.groups = (p.NCp + 31) / 32;
     p.kchunks = a.K / kKC;
-    const long long units = (long long)((a.N + kRT - 1) / kRT) * p.kchunks;
+    p.tiles0 = (a.N + kRT - 1) / kRT;
+    const long long units = (long long)p.tiles0 * (a.packed2 ? 2 : 1) * p.kchunks;
     if (units > 0x7fffffffLL || units < 1) return false;
     p.units = (int)units;
     int grid = dev.sm_count < kMaxGrid ? dev.sm_count : kMaxGrid;
@@ -559,6 +571,9 @@ bool decode_fp4_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
     if (a.M < 1 || a.M > kTokens || (a.K % kKC) != 0 || a.N < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
     if (a.px || !act_to_fp4_supported(a)) return false;
+    if (a.packed2 && (!a.scale2 || !a.C2 || a.residual || a.swiglu_out || (reinterpret_cast<uintptr_t>(a.packed2) & 15u) ||
+                      (reinterpret_cast<uintptr_t>(a.scale2) & 15u)))
+        return false;
     if (a.swiglu_out && (a.residual || a.out_f32 || (a.N & 15))) return false;
     Fp4Plan pl;
     return plan_fp4(a, dev, &pl);
@@ -581,13 +596,21 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     unsigned char* codes = static_cast<unsigned char*>(act);
     unsigned char* sfb = codes + fp4::act_sfb_offset(a.K);
     float* unscale = reinterpret_cast<float*>(codes + fp4::act_unscale_offset(a.K));
-    CUtensorMap tmp, tms, tma;
+    CUtensorMap tmp, tms, tma, tmp2, tms2;
     if (!make_map_cached(dev.maps, &tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT,
                          CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map_cached(dev.maps, &tms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kRT,
                          CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !make_map_cached(dev.maps, &tma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, (uint64_t)a.K / 2, (uint64_t)p.NCp, 128,
                          (uint32_t)p.NCp, CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorInvalidValue;
+    tmp2 = tmp;
+    tms2 = tms;
+    if (a.packed2 &&
+        (!make_map_cached(dev.maps, &tmp2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.packed2, (uint64_t)a.K / 2, (uint64_t)a.N, 128, kRT,
+                          CU_TENSOR_MAP_SWIZZLE_128B) ||
+         !make_map_cached(dev.maps, &tms2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.scale2, (uint64_t)a.K / 16, (uint64_t)a.N, 16, kRT,
+                          CU_TENSOR_MAP_SWIZZLE_NONE)))
         return cudaErrorInvalidValue;
     const int terms = fp4::terms_for(a.M);
     // One or two plain tokens on a short k range per CTA: the kernel expands them itself and no pre-pass runs.
@@ -610,6 +633,9 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     p.pairs = p.scratch + pairs_offset;
     p.out.inv_gs = a.inv_gs;
     p.out.out_f32 = a.out_f32 ? 1 : 0;
+    p.out2 = p.out;
+    p.out2.C = static_cast<__nv_bfloat16*>(a.C2);
+    p.out2.inv_gs = a.inv_gs2;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(pl.grid);
     cfg.blockDim = dim3(kThreads);
@@ -620,9 +646,9 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = own ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, true>, tmp, tms, tma, p)
-            : (terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, false>, tmp, tms, tma, p)
-                          : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5, false>, tmp, tms, tma, p));
+    e = own ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, true>, tmp, tms, tmp2, tms2, tma, p)
+            : (terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, false>, tmp, tms, tmp2, tms2, tma, p)
+                          : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5, false>, tmp, tms, tmp2, tms2, tma, p));
     if (launches) *launches = own ? 1 : 2;
     return e;
 }

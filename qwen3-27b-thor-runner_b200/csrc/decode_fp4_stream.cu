@@ -464,7 +464,7 @@ bool plan_fp4(const LinearArgs& a, const nvfp4_device_info& dev, Fp4Plan* out) {
 bool decode_fp4_stream_supported(const LinearArgs& a, const nvfp4_device_info& dev) {
     if (a.M < 1 || a.M > fp4::kMaxTokens || (a.K % kKC) != 0 || a.N < 1) return false;
     if ((reinterpret_cast<uintptr_t>(a.packed) & 15u) || (reinterpret_cast<uintptr_t>(a.scale) & 15u)) return false;
-    if (a.px || !act_to_fp4_supported(a)) return false;
+    if (a.px || a.packed2 || !act_to_fp4_supported(a)) return false;
     if (a.swiglu_out && (a.residual || a.out_f32 || (a.N & 15))) return false;
     Fp4Plan pl;
     return plan_fp4(a, dev, &pl);

@@ -27,6 +27,15 @@ struct LinearArgs {
     bool swiglu_out = false;           // weight rows interleaved (8 gate, 8 up per 16): C is [M, N/2] = bf16(silu(gate) * up)
     const void* norm_w = nullptr;      // [K] BF16: activations = rmsnorm(A) with the centred weight (1 + w)
     float norm_eps = 0.0f;
+    // The reference's arithmetic above 8 tokens (fp4_dequant_kernel + BF16 GEMM, src/engine/dense_gemm_fp4_sm110.cu:444-467,
+    // 558-583): weights rounded to BF16 AFTER the global scale, bf16(lut * (scale * 1/gs)).  The tcgen05 GEMM only.
+    bool round_weights = false;
+    // A second weight of the same shape on the same activations, its own output (the reference's dual GEMV,
+    // src/engine/dense_gemm_fp4_sm110.cu:264-351): one launch of the NVFP4 tensor-core GEMV takes both.
+    const uint8_t* packed2 = nullptr;
+    const uint8_t* scale2 = nullptr;
+    float inv_gs2 = 0.0f;
+    void* C2 = nullptr;
 };
 
 // Encoded tensor maps of recently used tensors, keyed by everything that goes into the encoding: a decode

@@ -29,6 +29,7 @@
 // Every mbarrier wait is bounded; a wait that runs out records its code in the handle's status
 // word and the kernel winds down (TMEM is always freed).
 #include <cuda.h>
+#include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -76,6 +77,11 @@ struct PrefillParams {
     int swiglu_out;            // weight rows interleaved in slabs of 16 (8 gate, 8 up): C is [M, N/2] = bf16(silu(gate) * up)
     int dense;                 // 1 = BF16 weights and activations as they are: no token scale, no 2^8, no global scale
     int out_f32;               // C is FP32 [M,N]: the scaled sums unrounded, no residual (partials a caller reduces itself)
+    // wround: the weight operand is bf16(lut * (scale * inv_gs)) * wshift (a power of two that keeps it in FP16's normal
+    // range; 8 significant bits, so exact), the reference's arithmetic above 8 tokens, instead of exact lut * scale / 2^8.
+    int wround;
+    float wshift;
+    float out_mul;             // what the epilogue multiplies the sums by besides the token factor: 2^8 / gs, or 1 / wshift
 };
 
 // ---------------------------------------------------------------- tcgen05 helpers
@@ -105,7 +111,7 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, unsign
     const int j1 = me + 1 == P ? kPartialVec : ((int)((long long)(me + 1) * kPartialVec / P) & ~(BM - 1));
     const int nt = tile / p.m_tiles, mt = tile % p.m_tiles;
     const int m = mt * BM + (t & (BM - 1));
-    const float mul = p.dense ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
+    const float mul = p.dense ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * p.out_mul;
     const float4* head = p.partials + ((size_t)first * 2 + 1) * kPartialVec;
     // sum of the participants' partials of one chunk (4 columns x this token row), in CTA order
     auto chunk_sum = [&](int j) {
@@ -165,7 +171,7 @@ __device__ __forceinline__ void reduce_split_tile(const PrefillParams& p, unsign
 // DENSE: the weight is BF16 [N,K] (tm_packed is its tensor map, boxes of 64 k x 256 rows; tm_scale is
 // unused) and the activations are the caller's BF16 rows: the producer loads the B blocks straight
 // into the operand buffers, the dequantisation warps have nothing to do.
-template <bool DENSE>
+template <bool DENSE, bool WROUND = false>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_packed,
                     const __grid_constant__ CUtensorMap tm_scale, const PrefillParams p) {
@@ -321,9 +327,23 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                     unsigned char* bp = s_b + sb * kBBytes + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {          // chunk c = 8 consecutive k = one 32-bit word of codes
-                        const uint32_t S = scale_byte_to_f16x2(scw[j], c >> 1);     // scale / 2^8, undone in the epilogue
                         uint32_t e[4];
                         ptx::cvt_e2m1x8_to_f16x2(q[c], e);
+                        if (WROUND) {
+                            // the reference's dequantisation, operation for operation: FP32 block scale times 1/gs, FP32
+                            // product with the code's value, one rounding to BF16; then a power of two into FP16 (exact)
+                            const float bs = ue4m3_to_float((scw[j] >> (8 * (c >> 1))) & 0xFFu) * p.inv_gs;
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 l = __half22float2(*reinterpret_cast<const __half2*>(&e[i]));
+                                const float2 b = __bfloat1622float2(__floats2bfloat162_rn(l.x * bs, l.y * bs));
+                                o[i] = ptx::pack_f16x2(b.x * p.wshift, b.y * p.wshift);
+                            }
+                            *reinterpret_cast<uint4*>(bp + ((c ^ sw7) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                            continue;
+                        }
+                        const uint32_t S = scale_byte_to_f16x2(scw[j], c >> 1);     // scale / 2^8, undone in the epilogue
                         *reinterpret_cast<uint4*>(bp + ((c ^ sw7) << 4)) =
                             make_uint4(ptx::mul_f16x2(e[0], S), ptx::mul_f16x2(e[1], S), ptx::mul_f16x2(e[2], S),
                                        ptx::mul_f16x2(e[3], S));
@@ -378,7 +398,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
                 if (te == 0) ptx::st_release_gpu(&p.flags[blockIdx.x * 2 + which], epoch);
                 pend[which] = tile;
             } else {
-                const float mul = DENSE ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * kBlockScaleUnfold * p.inv_gs;
+                const float mul = DENSE ? 1.0f : (m < p.M ? p.unscale[m] : 0.0f) * p.out_mul;
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     uint32_t r[32];
                     tmem_ld32(t_addr + c0, r);
@@ -512,6 +532,7 @@ size_t prefill_umma_scratch_bytes(int max_M, int /*max_N*/, int max_K) {
 
 cudaError_t configure_prefill_umma() {
     cudaError_t e = configure_large_smem(prefill_umma_kernel<true>, kSmemBytes);
+    if (e == cudaSuccess) e = configure_large_smem(prefill_umma_kernel<false, true>, kSmemBytes);
     if (e != cudaSuccess) return e;
     return configure_large_smem(prefill_umma_kernel<false>, kSmemBytes);
 }
@@ -571,6 +592,15 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.unscale = unscale;
     p.status = static_cast<unsigned int*>(scratch);
     p.inv_gs = a.inv_gs;
+    p.out_mul = kBlockScaleUnfold * a.inv_gs;
+    if (a.round_weights) {
+        // largest weight 6 * 448 / gs -> just under 2^15 (FP16's largest binade); the smallest, 0.5 * 2^-9 / gs, then sits at 2^-7
+        int ex = 0;
+        std::frexp(2688.0f * a.inv_gs, &ex);                 // 2688 / gs = f * 2^ex, f in [0.5, 1)
+        p.wround = 1;
+        p.wshift = std::ldexp(1.0f, 15 - ex);
+        p.out_mul = std::ldexp(1.0f, ex - 15);
+    }
     p.swiglu_out = a.swiglu_out ? 1 : 0;
     p.out_f32 = a.out_f32 ? 1 : 0;
     p.M = a.M; p.N = a.N; p.K = a.K;
@@ -579,7 +609,8 @@ cudaError_t launch_prefill_umma(const LinearArgs& a, nvfp4_device_info& dev, voi
     p.flags = reinterpret_cast<unsigned int*>(sk);
     p.partials = reinterpret_cast<float4*>(sk + 4096);
     const int grid = plan_tiles(p, dev);
-    prefill_umma_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
+    if (p.wround) prefill_umma_kernel<false, true><<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
+    else prefill_umma_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(tma, tmp, tms, p);
     if (launches) *launches = 2;
     return cudaGetLastError();
 }

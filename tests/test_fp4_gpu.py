@@ -170,6 +170,32 @@ def test_fp4_own_expansion_equals_prepass(handle, M, N, K):
     assert handle.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 17408, 5120), (1, 300, 1024), (2, 4096, 2048), (4, 1000, 5120), (8, 640, 17408)])
+def test_fp4_dual_is_one_launch(handle, M, N, K):
+    """Two weights of one shape on the same activations (the reference's dual GEMV, gate and up projection of one
+    token): one pre-pass and ONE GEMV launch whose row tiles run over both weights."""
+    import torch
+    p1, s1 = util.make_weight(N, K, seed=N + 1)
+    p2, s2 = util.make_weight(N, K, seed=N + 2, sigma=0.05)
+    A = util.make_bf16((M, K), seed=M + 21)
+    dA, dp1, ds1, dp2, ds2 = map(util.to_dev, (A, p1, s1, p2, s2))
+    c1 = torch.full((M, N), 0x7FC0, dtype=torch.int16, device="cuda")
+    c2 = torch.full((M, N), 0x7FC0, dtype=torch.int16, device="cuda")
+    l0 = handle.launch_count()
+    handle.linear_dual(dA, M, dp1, ds1, 1.0, dp2, ds2, 2.5, N, K, c1, c2)
+    launches = handle.launch_count() - l0
+    torch.cuda.synchronize()
+    assert launches <= 2
+    g1, g2 = util.to_host_u16(c1), util.to_host_u16(c2)
+    assert ob.rel_frobenius(g1, ob.linear(A, p1, s1, 1.0, mode=ob.GEMV, threads=8)) <= TOL
+    assert ob.rel_frobenius(g2, ob.linear(A, p2, s2, 2.5, mode=ob.GEMV, threads=8)) <= TOL
+    single1, _ = run(handle, A, p1, s1, 1.0)
+    single2, _ = run(handle, A, p2, s2, 2.5)
+    # the single calls split their row tiles over the CTAs at other places: same products, another summation order
+    assert ob.rel_frobenius(g1, single1) <= 2e-4 and ob.rel_frobenius(g2, single2) <= 2e-4
+    assert handle.device_status() == 0
+
+
 def test_fp4_graph_replay(handle):
     """One captured call (pre-pass + GEMV), replayed with new activations in the same buffer."""
     import torch

@@ -215,6 +215,29 @@ def test_decode_extreme_scales(handle, impl):
     assert ob.rel_frobenius(got, want) <= TOL
 
 
+@pytest.mark.parametrize("M", [9, 24, 200])
+@pytest.mark.parametrize("gs", [0.37, 7.25, 2688.0])
+def test_gemm_weight_rounding_reproduces_the_reference_gemm_branch(handle, M, gs):
+    """Above 8 tokens the reference rounds bf16(e2m1 * (ue4m3 / gs)) and runs a BF16 GEMM
+    (src/engine/dense_gemm_fp4_sm110.cu:444-467, 558-583).  By default the kernels keep exact weights and sit up
+    to 3e-3 from that when gs is not a power of two; with the option they follow it within the linear's own bar."""
+    N, K = 1000, 2048
+    packed, scale = util.make_weight(N, K, seed=61, sigma=0.14)
+    A = util.make_bf16((M, K), seed=62)
+    R = util.make_bf16((M, N), seed=63)
+    ref_form = ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMM, threads=8)
+    default = run_linear(handle, A, packed, scale, gs, residual=R)
+    handle.set_option("gemm_weight_rounding", 1)
+    try:
+        got = run_linear(handle, A, packed, scale, gs, residual=R)
+    finally:
+        handle.set_option("gemm_weight_rounding", 0)
+    assert ob.rel_frobenius(got, ref_form) <= TOL
+    assert ob.rel_frobenius(default, ob.linear(A, packed, scale, gs, residual=R, mode=ob.GEMV, threads=8)) <= TOL
+    print(f"M={M} gs={gs}: option {ob.rel_frobenius(got, ref_form):.2e}, default {ob.rel_frobenius(default, ref_form):.2e} from the reference's GEMM form")
+    assert handle.device_status() == 0
+
+
 def test_one_hot_activation_returns_dequantised_column(handle):
     """A = e_k  =>  C[0,:] == dequant(W)[:,k] bit for bit (products and sums are exact)."""
     N, K = 300, 640
