@@ -147,9 +147,9 @@ act_to_fp4_kernel(const ActParams p) {
         for (int w = 0; w < kPreThreads / 32; ++w) tot += s_part[w];
         inv_rms = 1.0f / sqrtf(tot / (float)K + p.eps);
         // the bound of the normalised row, as BF16 magnitude bits rounded up
-        float bound = __uint_as_float(s_max) * inv_rms;
-        bound = bound < 3.0e38f ? bound : 3.0e38f;        // also catches a NaN row: the scale stays finite
-        amax = (__float_as_uint(bound) + 0xFFFFu) >> 16;
+        const float bound = __uint_as_float(s_max) * inv_rms;
+        // an infinity or a NaN anywhere in the row (in x, in its sum of squares) marks the token as non-finite
+        amax = (bound < 3.0e38f && tot < 3.0e38f) ? (__float_as_uint(bound) + 0xFFFFu) >> 16 : 0x7F80u;
     } else {
         amax = __reduce_max_sync(0xffffffffu, amax);
         if ((threadIdx.x & 31) == 0 && amax) atomicMax(&s_max, amax);
@@ -158,7 +158,7 @@ act_to_fp4_kernel(const ActParams p) {
     }
     const int se = token_scale_exponent(amax);
     const float c = __uint_as_float((uint32_t)se << 23);
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.unscale[m] = token_unscale(amax, se);
     float r[4];
     r[0] = __uint_as_float(own.x << 16);
     r[1] = __uint_as_float(own.x & 0xFFFF0000u);

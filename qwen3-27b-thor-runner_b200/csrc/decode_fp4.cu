@@ -127,7 +127,7 @@ constexpr int kOwnTokens = 2;       // most tokens the kernel expands itself
 constexpr int kOwnThreads = 8 * 32; // warps 4-11
 constexpr int kOwnMaxChunks = 8;    // ... and most resident 256-k chunks x tokens it does so for
 
-template <int TERMS, bool OWN>
+template <int TERMS, bool OWN, bool DUAL = false>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const __grid_constant__ CUtensorMap tm_packed2, const __grid_constant__ CUtensorMap tm_scale2,
@@ -214,7 +214,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         for (int m = 0; m < kOwnTokens; ++m) {
             const int se = token_scale_exponent(s_amax[m]);
             c[m] = __uint_as_float((uint32_t)se << 23);
-            if (tq == m) s_unscale[m] = __uint_as_float((uint32_t)(254 - se) << 23);
+            if (tq == m) s_unscale[m] = token_unscale(s_amax[m], se);
         }
         // One task = a quarter (4 elements) of a 16-element block of one token in one resident chunk; a quad of
         // lanes holds the block.  64 tasks per token and chunk, so whole warps are in or out of range together.
@@ -275,7 +275,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
         if (lane == 0) {
             ptx::prefetch_tensormap(&tm_packed);
             ptx::prefetch_tensormap(&tm_scale);
-            if (p.tiles0 * p.kchunks < p.units) {
+            if (DUAL) {
                 ptx::prefetch_tensormap(&tm_packed2);
                 ptx::prefetch_tensormap(&tm_scale2);
             }
@@ -286,7 +286,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
             while (hu < u_end) {
                 const int tile_end = hu - kc + p.kchunks;
                 const int seg_end = tile_end < u_end ? tile_end : u_end;
-                const bool second = tile >= p.tiles0;             // a dual call: the second weight's row tiles follow the first's
+                const bool second = DUAL && tile >= p.tiles0;     // a dual call: the second weight's row tiles follow the first's
                 const int row0 = (second ? tile - p.tiles0 : tile) * kRT;
                 const CUtensorMap* mp = second ? &tm_packed2 : &tm_packed;
                 const CUtensorMap* ms = second ? &tm_scale2 : &tm_scale;
@@ -513,7 +513,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                         }
                     }
                 }
-                if (tile < p.tiles0) fp4_store_rows(v, p.out, tile, te);
+                if (!DUAL || tile < p.tiles0) fp4_store_rows(v, p.out, tile, te);
                 else fp4_store_rows(v, p.out2, tile - p.tiles0, te);
             }
             if (kc >= p.kchunks) { kc = 0; ++tile; }
@@ -585,6 +585,9 @@ cudaError_t configure_decode_fp4() {
     cudaError_t e = configure_large_smem(decode_fp4_kernel<5, false>, kSmemBudget);
     if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<6, false>, kSmemBudget);
     if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<6, true>, kSmemBudget);
+    if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<5, false, true>, kSmemBudget);
+    if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<6, false, true>, kSmemBudget);
+    if (e == cudaSuccess) e = configure_large_smem(decode_fp4_kernel<6, true, true>, kSmemBudget);
     return e;
 }
 
@@ -646,9 +649,14 @@ cudaError_t launch_decode_fp4(const LinearArgs& a, nvfp4_device_info& dev, void*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = own ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, true>, tmp, tms, tmp2, tms2, tma, p)
-            : (terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, false>, tmp, tms, tmp2, tms2, tma, p)
-                          : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5, false>, tmp, tms, tmp2, tms2, tma, p));
+    if (a.packed2)
+        e = own ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, true, true>, tmp, tms, tmp2, tms2, tma, p)
+                : (terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, false, true>, tmp, tms, tmp2, tms2, tma, p)
+                              : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5, false, true>, tmp, tms, tmp2, tms2, tma, p));
+    else
+        e = own ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, true>, tmp, tms, tmp2, tms2, tma, p)
+                : (terms == 6 ? cudaLaunchKernelEx(&cfg, decode_fp4_kernel<6, false>, tmp, tms, tmp2, tms2, tma, p)
+                              : cudaLaunchKernelEx(&cfg, decode_fp4_kernel<5, false>, tmp, tms, tmp2, tms2, tma, p));
     if (launches) *launches = own ? 1 : 2;
     return e;
 }

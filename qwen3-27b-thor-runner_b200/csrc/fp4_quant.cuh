@@ -29,6 +29,12 @@ __device__ __forceinline__ int token_scale_exponent(unsigned int amax_bf16_bits)
     int se = 263 - (int)(amax_bf16_bits >> 7);
     return se < 1 ? 1 : (se > 254 ? 254 : se);
 }
+// 1 / c for the epilogue.  A token that holds an infinity or a NaN has no finite expansion: its factor is NaN, so
+// every output of that token is NaN (what FP32 accumulation of such an input gives, up to inf versus NaN) and no
+// other token is touched.
+__device__ __forceinline__ float token_unscale(unsigned int amax_bf16_bits, int se) {
+    return (amax_bf16_bits >> 7) >= 0xFFu ? __uint_as_float(0x7FC00000u) : __uint_as_float((uint32_t)(254 - se) << 23);
+}
 // Exponent of the first term's scale: the smallest p with bmax <= 6 * 2^p, clamped to the powers of two unsigned E4M3 holds.
 __device__ __forceinline__ int first_term_exponent(float bmax) {
     int p0 = -9;

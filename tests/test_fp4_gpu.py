@@ -113,6 +113,23 @@ def test_fp4_one_hot_and_power_of_two_activations_are_exact(handle):
     assert np.array_equal(z, R)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (2, 300, 6144), (5, 1000, 2048), (12, 640, 1024)])
+def test_fp4_non_finite_activations_poison_their_token_only(handle, M, N, K):
+    """An infinity or a NaN in a token makes that token's outputs NaN (the pre-pass has no finite expansion for it);
+    the other tokens come out as if it were not there."""
+    packed, scale = util.make_weight(N, K, seed=N)
+    A = util.make_bf16((M, K), seed=M + 31)
+    clean, _ = run(handle, A, packed, scale, 1.0)
+    for bad_bits in (0x7F80, 0xFF80, 0x7FC0):             # +inf, -inf, NaN
+        B = A.copy()
+        B[M - 1, K // 3] = bad_bits
+        got, _ = run(handle, B, packed, scale, 1.0)
+        is_nan = ((got & 0x7F80) == 0x7F80) & ((got & 0x007F) != 0)
+        assert is_nan[M - 1].all()
+        assert np.array_equal(got[:M - 1], clean[:M - 1])
+    assert handle.device_status() == 0
+
+
 def test_fp4_scale_codes(handle):
     """Every scale code the format's finite range holds (0x00 .. 0x7E, and the same with bit 7 set, which
     the format ignores) in one weight.  0x7F / 0xFF are NaN to the tensor core and are left out: no finite
