@@ -486,33 +486,7 @@ decode_fp4_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_co
                 for (int m = 0; m < kTokens; ++m)
                     if (m < p.M) ptx::st_volatile_v2(slot + (m * kRT + te) * 8, __float_as_uint(v[m]), epoch);
             } else {
-                const long long t0 = clock64();
-                bool failed = false;
-                for (int c = cta + 1; c <= last && !failed; ++c) {
-                    const unsigned char* src = pairs + (size_t)c * (kPairTokens * kRT) * 8;
-                    while (true) {
-                        uint2 x[kTokens];
-#pragma unroll
-                        for (int m = 0; m < kTokens; ++m) {
-                            x[m] = make_uint2(0u, epoch);
-                            if (m < p.M) x[m] = ptx::ld_volatile_v2(src + (m * kRT + te) * 8);
-                        }
-                        bool ready = true;
-#pragma unroll
-                        for (int m = 0; m < kTokens; ++m) ready &= (x[m].y == epoch);
-                        if (ready) {
-#pragma unroll
-                            for (int m = 0; m < kTokens; ++m) v[m] += __uint_as_float(x[m].x);
-                            break;
-                        }
-                        if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
-                            *s_abort = 1;
-                            atomicCAS(status, 0u, 0xA60u);
-                            failed = true;
-                            break;
-                        }
-                    }
-                }
+                fp4_gather_pairs(v, pairs, (size_t)(kPairTokens * kRT) * 8, cta + 1, last, p.M, te, epoch, s_abort, status, 0xA60u);
                 if (!DUAL || tile < p.tiles0) fp4_store_rows(v, p.out, tile, te);
                 else fp4_store_rows(v, p.out2, tile - p.tiles0, te);
             }

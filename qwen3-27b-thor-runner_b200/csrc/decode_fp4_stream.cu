@@ -116,8 +116,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+// At most 136 registers: with more, the next call's pre-pass (launched while this kernel runs) finds no room in
+// the register file beside a CTA of this kernel, and the two calls serialize.
 template <int TERMS>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(136)
 decode_fp4_stream_kernel(const __grid_constant__ CUtensorMap tm_packed, const __grid_constant__ CUtensorMap tm_scale,
                   const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_sfb,
                   const __grid_constant__ Fp4Params p) {
@@ -379,35 +381,7 @@ decode_fp4_stream_kernel(const __grid_constant__ CUtensorMap tm_packed, const __
                 for (int m = 0; m < fp4::kMaxTokens; ++m)
                     if (m < p.M) ptx::st_volatile_v2(slot + (m * kRT + te) * 8, __float_as_uint(v[m]), epoch);
             } else {
-                const long long t0 = clock64();
-                bool failed = false;
-                for (int c = cta + 1; c <= last && !failed; ++c) {
-                    const unsigned char* src = pairs + (size_t)c * (kPairTokens * kRT) * 8;
-                    // four tokens at a time (all loads of a group in flight together, few registers)
-#pragma unroll
-                    for (int m0 = 0; m0 < fp4::kMaxTokens; m0 += 4) {
-                        if (m0 >= p.M || failed) continue;
-                        while (true) {
-                            uint2 x[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                x[j] = make_uint2(0u, epoch);
-                                if (m0 + j < p.M) x[j] = ptx::ld_volatile_v2(src + ((m0 + j) * kRT + te) * 8);
-                            }
-                            if (x[0].y == epoch && x[1].y == epoch && x[2].y == epoch && x[3].y == epoch) {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[m0 + j] += __uint_as_float(x[j].x);
-                                break;
-                            }
-                            if (*s_abort || clock64() - t0 > ptx::kWaitBudgetClocks) {
-                                *s_abort = 1;
-                                atomicCAS(status, 0u, 0xB60u);
-                                failed = true;
-                                break;
-                            }
-                        }
-                    }
-                }
+                fp4_gather_pairs(v, pairs, (size_t)(kPairTokens * kRT) * 8, cta + 1, last, p.M, te, epoch, s_abort, status, 0xB60u);
                 fp4_store_rows(v, p.out, tile, te);
             }
             if (kc >= p.kchunks) { kc = 0; ++tile; }
