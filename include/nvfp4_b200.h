@@ -87,6 +87,10 @@ const char* nvfp4_status_string(int status);
  *                   power of two the two forms lie 2.7e-3 apart.  Plain calls with N % 8 == 0 and
  *                   K % 256 == 0 only (NVFP4_E_LIMIT otherwise); slower (the tcgen05 GEMM with a longer
  *                   dequantisation)
+ *   "fp4_stream_min_m": token count from which that kernel's activations travel through the shared-memory
+ *                   ring with the weights instead of staying resident beside it (they must from 10 on:
+ *                   48 MMA columns are the resident form's limit).  10 (default) = chosen per call below
+ *                   10: streamed from seven tokens on where a CTA's share of the weights is long
  *   "fp4_own_quant": 1 (default) = for one or two tokens (no SwiGLU or RMSNorm in front) that kernel
  *                   expands the activations itself and no pre-pass kernel is launched; 0 = always
  *                   the pre-pass

@@ -25,6 +25,7 @@ struct nvfp4_handle {
     int skinny_min_m = 9, skinny_max_m = 64;     // token counts routed to the weights-in-TMEM kernel
     int fp4_native = 1;                          // the NVFP4 tensor-core GEMV (weights untouched, activations as NVFP4 terms) ...
     int fp4_min_m = 1;                           // ... from this token count on (up to 16)
+    int fp4_stream_min_m = 10;                   // from this token count on its activations travel through the ring (decode_fp4_stream.cu)
     int gemm_weight_rounding = 0;                // above 8 tokens: the reference's BF16-rounded weights (its GEMM branch)
     unsigned long long launches = 0;
 };
@@ -122,7 +123,19 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
                             (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m));
     if (fp4_wanted && !a.px && decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
         // up to 9 tokens with the activations resident beside the ring, else streamed through it
-        const bool res = decode_fp4_supported(a, h->dev);
+        // Resident activations win on few tokens and wherever a CTA's share of the weights is short (qkv, o: 0.7-1.0 us
+        // per call); from seven tokens on with a long share (gate_up, down) the streamed form's larger ring of weights
+        // wins (gate_up at 8 tokens 23.4 against 25.2 us).  At four to six tokens the streamed form is 0.4 us ahead
+        // call by call but 2 us per layer behind in a 64-layer sequence of distinct weights, so it is not taken there.
+        // A threshold set by the caller is taken as it is.
+        bool want_stream = a.M >= h->fp4_stream_min_m;
+        if (h->fp4_stream_min_m == 10 && a.M >= 7 && !a.packed2) {
+            const long long units = (long long)((a.N + 127) / 128) * (a.K / 256);
+            const long long ctas = units < h->dev.sm_count ? units : h->dev.sm_count;
+            if (ctas > 0 && (units + ctas - 1) / ctas >= 12) want_stream = true;
+        }
+        if (want_stream && !decode_fp4_stream_supported(a, h->dev)) want_stream = false;
+        const bool res = !want_stream && decode_fp4_supported(a, h->dev);
         if (res || decode_fp4_stream_supported(a, h->dev)) {
             int nl = 0;
             cudaError_t e = res ? launch_decode_fp4(a, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, s)
@@ -307,6 +320,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "fp4_min_m")) {
         if (value < 1 || value > 16) return NVFP4_E_OPTION;
         h->fp4_min_m = value;
+    } else if (!std::strcmp(name, "fp4_stream_min_m")) {
+        if (value < 1 || value > 17) return NVFP4_E_OPTION;
+        h->fp4_stream_min_m = value;
     } else if (!std::strcmp(name, "gemm_weight_rounding")) {
         if (value < 0 || value > 1) return NVFP4_E_OPTION;
         h->gemm_weight_rounding = value;
@@ -342,6 +358,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "fp4_min_m")) *value = h->fp4_min_m;
     else if (!std::strcmp(name, "fp4_own_quant")) *value = h->dev.fp4_own_quant;
     else if (!std::strcmp(name, "gemm_weight_rounding")) *value = h->gemm_weight_rounding;
+    else if (!std::strcmp(name, "fp4_stream_min_m")) *value = h->fp4_stream_min_m;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;
