@@ -272,6 +272,9 @@ def main(args, world, rank, local_rank):
     dist.init_process_group("nccl", device_id=dev)
     H, I = bench.H, bench.I
     h = nvfp4.Handle(local_rank, 1 << 30)
+    for kv in getattr(args, "option", None) or []:      # kernel-selection options, as in the single-GPU benchmark
+        name, _, val = kv.partition("=")
+        h.set_option(name, int(val))
     if rank == 0:
         uid = torch.tensor(list(nvfp4_tp.unique_id()), dtype=torch.uint8, device=dev)
     else:

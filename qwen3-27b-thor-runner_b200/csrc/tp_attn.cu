@@ -122,6 +122,7 @@ int nvfp4_tp_attn_set_fused(nvfp4_tp_attn* a, int on) {
 int nvfp4_tp_attn_qkv(nvfp4_tp_attn* a, const void* X, int M, void* qkv_out, nvfp4_stream_t s) {
     if (!a || !X || !qkv_out) return NVFP4_E_NULL;
     if (M < 0 || M > a->max_M) return NVFP4_E_SHAPE;
+    nvfp4::tp::SameGemvScope same_gemv(a->h, a->comm, a->x, a->fused, M);
     return nvfp4_linear(a->h, X, M, a->qkv_packed, a->qkv_scale, a->qkv_gs, a->q_local + 2 * a->kv_local, a->H, nullptr, qkv_out, s);
 }
 
@@ -131,6 +132,7 @@ int nvfp4_tp_attn_out(nvfp4_tp_attn* a, const void* attn, long long row_stride, 
     if (M < 0 || M > a->max_M || row_stride < 0 || (row_stride != 0 && row_stride < a->o_local)) return NVFP4_E_SHAPE;
     if (M == 0) return NVFP4_OK;
     if (row_stride == 0) row_stride = a->o_local;
+    nvfp4::tp::SameGemvScope same_gemv(a->h, a->comm, a->x, a->fused, M);
     nvfp4_linear_desc d{};
     d.M = M;
     d.packed = a->o_packed; d.scale = a->o_scale; d.global_scale = a->o_gs; d.N = a->H; d.K = a->Kp;

@@ -45,6 +45,25 @@ constexpr int kFusedMaxM = xchg::kMaxTokens;
 // error or after the deadline (the communicator is aborted then).
 int settle(nvfp4_tp_comm* comm, ncclResult_t r);
 
+// Where the row-split linear sums over the group inside the mma.sync GEMV (mode 1, up to 16 tokens), the block's
+// other linears take that GEMV too: a step that alternates between it and the NVFP4 tensor-core GEMV with its
+// pre-pass is slower than either alone (2 GPUs, 64-layer token-step: 3.51 ms mixed, 3.09 ms mma.sync only).
+// Sets the handle's "decode_impl" to 2 for the scope, if it was on automatic.
+struct SameGemvScope {
+    nvfp4_handle* h;
+    bool on;
+    SameGemvScope(nvfp4_handle* handle, const nvfp4_tp_comm* comm, const nvfp4_tp_exchange* x, int mode, int M)
+        : h(handle), on(false) {
+        int impl = 0;
+        if (comm && comm->world > 1 && mode == 1 && x && x->attached && M <= kFusedMaxM &&
+            nvfp4_get_option(h, "decode_impl", &impl) == NVFP4_OK && impl == 0)
+            on = nvfp4_set_option(h, "decode_impl", 2) == NVFP4_OK;
+    }
+    ~SameGemvScope() {
+        if (on) nvfp4_set_option(h, "decode_impl", 0);
+    }
+};
+
 // Room for [max_M, H] FP32 partial sums on the communicator (grown at block-creation time, never in a forward).
 int reserve_f32_partials(nvfp4_tp_comm* comm, int max_M, int H);
 

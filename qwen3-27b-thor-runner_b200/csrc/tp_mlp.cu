@@ -92,6 +92,7 @@ int nvfp4_tp_mlp_forward(nvfp4_tp_mlp* m, const void* X, int M, const void* resi
     if (!m || !X || !out) return NVFP4_E_NULL;
     if (M < 0 || M > m->max_M) return NVFP4_E_SHAPE;
     if (M == 0) return NVFP4_OK;
+    nvfp4::tp::SameGemvScope same_gemv(m->h, m->comm, m->x, m->fused, M);
     nvfp4_linear_desc d{};
     d.M = M;
     d.packed = m->dn_packed; d.scale = m->dn_scale; d.global_scale = m->dn_gs; d.N = m->H; d.K = m->Kp;
