@@ -12,6 +12,8 @@
 // conversion).  After a term the remainder is at most half the local E2M1 spacing (half the
 // term's scale for values up to 4), which gives |remainder| <= s_0 / 4096 after five terms and
 // s_0 / 32768 after six: 8e-5 and 1e-5 of the block's largest element, whose own BF16 rounding step is 4e-3.
+// (A block far below its token's largest reaches the smallest scale, 2^-9, before its last term: its
+// remainder is then at most 2^-11, which is 2^-20 of the token's largest element.)
 // All scales are powers of two, so every product and every remainder is exact in FP32.  The term
 // rows become columns of the MMA's B operand (tokens x T, padded to a multiple of 16); the GEMV's
 // epilogue adds the T columns of a token.
