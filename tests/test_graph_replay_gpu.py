@@ -78,7 +78,7 @@ def _sample_rows(N, seed, count=96):
     (4, 5120, 17408),     # down projection: every row tile shared by 3-4 CTAs, middle contributors publish at their very end
     (1, 1024, 2048),      # two half-units per CTA: owners look for their contributors at once
     (8, 640, 5120),       # few row tiles over all CTAs
-    (12, 5120, 17408),    # 9..16 tokens: the wide GEMV
+    (12, 5120, 17408),    # 10..16 tokens: activations streamed through the ring
     (16, 1024, 2048),
     (40, 1000, 17408),    # few-token tcgen05 kernel, every tile split along k
     (64, 5120, 4352),
@@ -86,6 +86,25 @@ def _sample_rows(N, seed, count=96):
     (130, 512, 5120),     # prefill kernel, every tile split
 ])
 def test_graph_replay_linear(handle, M, N, K):
+    _graph_replay_linear(handle, M, N, K)
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (4, 5120, 17408),     # the mma.sync GEMV (pairs cleared after use): the kernel of the group reduction and of chains
+    (1, 1024, 2048),
+    (8, 640, 5120),
+    (12, 5120, 17408),    # its wide variant (tag from the device-side counter)
+    (16, 1024, 2048),
+])
+def test_graph_replay_linear_mma_sync_kernels(handle, M, N, K):
+    handle.set_option("decode_impl", 2)
+    try:
+        _graph_replay_linear(handle, M, N, K)
+    finally:
+        handle.set_option("decode_impl", 0)
+
+
+def _graph_replay_linear(handle, M, N, K):
     import torch
     packed, scale = util.make_weight(N, K, seed=M + N, sigma=0.14 if M > 16 else 0.02)
     dp, ds = util.to_dev(packed), util.to_dev(scale)
