@@ -28,6 +28,9 @@ struct nvfp4_handle {
     int fp4_stream_min_m = 10;                   // from this token count on its activations travel through the ring (decode_fp4_stream.cu)
     int gemm_weight_rounding = 0;                // above 8 tokens: the reference's BF16-rounded weights (its GEMM branch)
     unsigned long long launches = 0;
+    int host_direct_out = 1;                     // nvfp4_linear_host: kernels store into a pinned, device-mapped C_host themselves
+    const void* host_out_seen = nullptr;         // the last C_host looked up, and its device address (null: not pinned)
+    void* host_out_dev = nullptr;
 };
 
 #include <atomic>
@@ -320,6 +323,9 @@ int nvfp4_set_option(nvfp4_handle* h, const char* name, int value) {
     } else if (!std::strcmp(name, "fp4_min_m")) {
         if (value < 1 || value > 16) return NVFP4_E_OPTION;
         h->fp4_min_m = value;
+    } else if (!std::strcmp(name, "host_direct_out")) {
+        if (value < 0 || value > 1) return NVFP4_E_OPTION;
+        h->host_direct_out = value;
     } else if (!std::strcmp(name, "fp4_stream_min_m")) {
         if (value < 1 || value > 17) return NVFP4_E_OPTION;
         h->fp4_stream_min_m = value;
@@ -359,6 +365,7 @@ int nvfp4_get_option(nvfp4_handle* h, const char* name, int* value) {
     else if (!std::strcmp(name, "fp4_own_quant")) *value = h->dev.fp4_own_quant;
     else if (!std::strcmp(name, "gemm_weight_rounding")) *value = h->gemm_weight_rounding;
     else if (!std::strcmp(name, "fp4_stream_min_m")) *value = h->fp4_stream_min_m;
+    else if (!std::strcmp(name, "host_direct_out")) *value = h->host_direct_out;
     else if (!std::strcmp(name, "skinny_min_m")) *value = h->skinny_min_m;
     else if (!std::strcmp(name, "skinny_max_m")) *value = h->skinny_max_m;
     else if (!std::strcmp(name, "skinny_split_cost")) *value = h->dev.skinny_split_cost;
@@ -665,12 +672,29 @@ int nvfp4_linear_host(nvfp4_handle* h, const void* A_host, int M, const uint8_t*
         dR = dC;
     }
     if (!aligned16(dA) || !aligned16(dC)) return NVFP4_E_ALIGN;
+    // Without a residual the kernels may write a pinned, device-mapped C_host themselves (coalesced stores over PCIe
+    // that overlap the kernel's tail) and the copy back, with its own start-up latency, is not needed.
+    void* out = dC;
+    if (h->host_direct_out && !residual_host && aligned16(C_host) && (size_t)M * N * 2 <= (2u << 20)) {
+        if (C_host != h->host_out_seen) {
+            cudaPointerAttributes at{};
+            h->host_out_seen = C_host;
+            h->host_out_dev = nullptr;
+            if (cudaPointerGetAttributes(&at, C_host) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer)
+                h->host_out_dev = at.devicePointer;
+            else
+                cudaGetLastError();
+        }
+        if (h->host_out_dev) out = h->host_out_dev;
+    }
     // The kernels see the workspace without the staging area, so their scratch never reaches it.
-    LinearArgs a{dA, packed, scale, 1.0f / global_scale, dR, dC, M, N, K};
+    LinearArgs a{dA, packed, scale, 1.0f / global_scale, dR, out, M, N, K};
     int st = run_linear(h, a, stream, h->workspace_bytes - tail);
     if (st) return st;
-    e = cudaMemcpyAsync(C_host, dC, (size_t)M * N * 2, cudaMemcpyDeviceToHost, stream);
-    if (e != cudaSuccess) return (int)e;
+    if (out == dC) {
+        e = cudaMemcpyAsync(C_host, dC, (size_t)M * N * 2, cudaMemcpyDeviceToHost, stream);
+        if (e != cudaSuccess) return (int)e;
+    }
     return cuda_status(cudaStreamSynchronize(stream));
 }
 

@@ -452,6 +452,32 @@ def test_linear_host(handle):
     assert ob.rel_frobenius(hC.numpy().view(np.uint16), ob.linear(A, packed, scale, 1.0, residual=R)) <= TOL
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 5120, 5120), (4, 300, 17408), (16, 1000, 2048), (40, 512, 1024)])
+def test_linear_host_direct_output_equals_staged(handle, M, N, K):
+    """Without a residual the kernels store into the pinned output themselves; the bits are those of the staged
+    path (same kernels, another destination), also for a pageable output, which is always staged."""
+    import torch
+    packed, scale = util.make_weight(N, K, seed=N + 5)
+    dp, ds = util.to_dev(packed), util.to_dev(scale)
+    A = util.make_bf16((M, K), seed=71)
+    hA = torch.from_numpy(A.view(np.int16)).pin_memory()
+    outs = []
+    for direct in (1, 0):
+        handle.set_option("host_direct_out", direct)
+        try:
+            hC = torch.full((M, N), 0x7FC0, dtype=torch.int16).pin_memory()
+            handle.linear_host(hA, M, dp, ds, 1.7, N, K, hC)
+            outs.append(hC.numpy().view(np.uint16).copy())
+        finally:
+            handle.set_option("host_direct_out", 1)
+    pC = torch.full((M, N), 0x7FC0, dtype=torch.int16)           # pageable
+    handle.linear_host(hA, M, dp, ds, 1.7, N, K, pC)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], pC.numpy().view(np.uint16))
+    want = ob.linear(A, packed, scale, 1.7, mode=ob.GEMV, threads=8)
+    assert ob.rel_frobenius(outs[0], want) <= (TOL if M <= 16 else 3e-3)
+    assert handle.device_status() == 0
+
+
 def test_linear_host_odd_workspace_size():
     """A workspace size that is not a multiple of 16: the staging buffers at its end stay aligned."""
     import torch
