@@ -12,7 +12,8 @@ def _events(torch):
 
 def e2e(h, shapes, rot, args, torch, alg_bytes, decode_ms):
     """The decode sweep through nvfp4_linear_host: activations start in pinned HOST memory and
-    outputs end there, every call copies H2D, launches, copies D2H and synchronises."""
+    outputs end there; every call copies H2D, launches, gets its outputs into host memory (a copy back, or
+    the kernels' own stores into the pinned buffer) and synchronises."""
     hin, hout = {}, {}
     for name in rot:
         N, K = shapes[name]
@@ -43,7 +44,9 @@ def e2e(h, shapes, rot, args, torch, alg_bytes, decode_ms):
     d2h = sum(hout[k].numel() * 2 for k in hout)
     return {"value": round(step_bytes / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "ms_per_step": round(ms, 4),
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "nvfp4_linear_host (pinned host activations in, pinned host outputs back, weights device-resident)"}
+            "api": "nvfp4_linear_host (pinned host activations copied in; the outputs end in pinned host memory, written "
+                   "there by the kernels themselves over PCIe -- no residual in this sweep -- and are complete when the call "
+                   "returns; weights device-resident)"}
 
 
 def prefill(h, shapes, rot, peaks, torch, small=False, ms_list=(64, 256, 2048, 8192)):
