@@ -78,7 +78,8 @@ const char* nvfp4_status_string(int status);
  *                   block's largest value, whose own BF16 rounding step is 4e-3.  A scale byte 0x7F / 0xFF is NaN to the
  *                   tensor core, as it is in FP8 E4M3; every other kernel, like the reference's
  *                   table-free decoder (dense_gemm_fp4_sm110.cu:30-41), reads it as 480.  No finite
- *                   FP8 E4M3 value encodes to it.  0 = off
+ *                   FP8 E4M3 value encodes to it; nvfp4_scan_scales finds such a weight at load time
+ *                   and keeps it off this kernel.  0 = off
  *   "gemm_weight_rounding": 0 (default) = every kernel multiplies the exact block-scaled weights and applies
  *                   1 / global_scale once, in FP32 (the reference's arithmetic up to 8 tokens,
  *                   dense_gemm_fp4_sm110.cu:96-141).  1 = above 8 tokens the weights are rounded to BF16
@@ -253,6 +254,16 @@ int nvfp4_linear_dual(nvfp4_handle* h, const void* A_bf16, int M,
                       const uint8_t* packed1, const uint8_t* scale1, float global_scale1,
                       const uint8_t* packed2, const uint8_t* scale2, float global_scale2,
                       int N, int K, void* C1_bf16, void* C2_bf16, nvfp4_stream_t stream);
+
+/* Load-time check of a weight's block scales [N, K/16] (device memory): *count (may be NULL) = how many
+ * of the bytes are 0x7F or 0xFF, which the reference's decoder (dense_gemm_fp4_sm110.cu:30-41) reads as
+ * 480 and the tensor core's FP8 E4M3 as NaN.  If there are any, the handle remembers the pointer and
+ * every later call on that scale tensor takes the kernels that decode the scale as the reference does,
+ * so its results match the reference on such a weight too; a later scan that finds none forgets it.
+ * Synchronises the stream and allocates 8 bytes for the duration of the call: not for capture, not
+ * for the decode loop.  No counterpart in the reference, whose one decoder needs none. */
+int nvfp4_scan_scales(nvfp4_handle* h, const uint8_t* scale_ue4m3, int N, int K, long long* count,
+                      nvfp4_stream_t stream);
 
 /* out[n,k] = bf16( e2m1 * (ue4m3 * (1.0f/global_scale)) ), bit-exact to
  * fp4_dequant_kernel (:444-467). */

@@ -1,9 +1,10 @@
 // Host side of the C ABI: handle lifecycle, argument validation, kernel selection
 // and the reference-shaped entry points.  No call here allocates, frees or
-// synchronises after nvfp4_create (nvfp4_linear_host excepted: it is the
-// host-buffer convenience path and synchronises by contract).
+// synchronises after nvfp4_create (two excepted, both by contract: nvfp4_linear_host, the
+// host-buffer convenience path, and nvfp4_scan_scales, a load-time check that returns a count).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -31,6 +32,13 @@ struct nvfp4_handle {
     int host_direct_out = 1;                     // nvfp4_linear_host: kernels store into a pinned, device-mapped C_host themselves
     const void* host_out_seen = nullptr;         // the last C_host looked up, and its device address (null: not pinned)
     void* host_out_dev = nullptr;
+    // scale tensors in which nvfp4_scan_scales found a byte 0x7F / 0xFF: the tensor core reads those as NaN, so
+    // these weights stay on the kernels that decode the scale themselves
+    std::vector<const void*> nan_scales;
+    bool has_nan_scales(const void* scale) const {
+        if (nan_scales.empty()) return false;
+        return std::find(nan_scales.begin(), nan_scales.end(), scale) != nan_scales.end();
+    }
 };
 
 #include <atomic>
@@ -124,7 +132,8 @@ int run_linear(nvfp4_handle* h, const LinearArgs& a, cudaStream_t s, size_t ws_b
     }
     const bool fp4_wanted = a.M <= h->decode_max_m &&
                             (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && a.M >= h->fp4_min_m));
-    if (fp4_wanted && !a.px && decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes) {
+    if (fp4_wanted && !a.px && decode_fp4_scratch_bytes(a.K) <= kFp4ActBytes && kDecodeScratchBytes <= ws_bytes &&
+        !h->has_nan_scales(a.scale)) {
         // up to 9 tokens with the activations resident beside the ring, else streamed through it
         // Resident activations win on few tokens and wherever a CTA's share of the weights is short (qkv, o: 0.7-1.0 us
         // per call); from seven tokens on with a long share (gate_up, down) the streamed form's larger ring of weights
@@ -544,7 +553,7 @@ int nvfp4_linear_dual(nvfp4_handle* h, const void* A, int M, const uint8_t* pack
         d.packed2 = packed2; d.scale2 = scale2; d.inv_gs2 = 1.0f / gs2; d.C2 = C2;
         const bool fp4_wanted = M <= h->decode_max_m && (h->decode_impl == 3 || (h->decode_impl == 0 && h->fp4_native && M >= h->fp4_min_m));
         if (fp4_wanted && decode_fp4_scratch_bytes(K) <= kFp4ActBytes && kDecodeScratchBytes <= h->workspace_bytes &&
-            decode_fp4_supported(d, h->dev)) {
+            !h->has_nan_scales(scale1) && !h->has_nan_scales(scale2) && decode_fp4_supported(d, h->dev)) {
             int nl = 0;
             cudaError_t e = launch_decode_fp4(d, h->dev, h->workspace, kFp4PairsOffset, h->workspace + kFp4ActOffset, &nl, stream);
             h->launches += (unsigned long long)nl;
@@ -566,6 +575,28 @@ int nvfp4_dequant_bf16(nvfp4_handle* h, const uint8_t* packed, const uint8_t* sc
     cudaError_t e = launch_dequant_bf16(packed, scale, 1.0f / global_scale, N, K, out, stream);
     h->launches += 1;
     return cuda_status(e);
+}
+
+int nvfp4_scan_scales(nvfp4_handle* h, const uint8_t* scale, int N, int K, long long* count, nvfp4_stream_t stream) {
+    if (!h || !scale) return NVFP4_E_NULL;
+    if (N <= 0 || K <= 0 || (K & 15) != 0) return NVFP4_E_SHAPE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned long long* d_count = nullptr;
+    unsigned long long n = 0;
+    cudaError_t e = cudaMalloc(&d_count, sizeof(n));
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemsetAsync(d_count, 0, sizeof(n), s);
+    if (e == cudaSuccess) e = launch_count_nan_scales(scale, (long long)N * (K >> 4), d_count, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&n, d_count, sizeof(n), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(d_count);
+    if (e != cudaSuccess) return (int)e;
+    h->launches += 1;
+    auto it = std::find(h->nan_scales.begin(), h->nan_scales.end(), static_cast<const void*>(scale));
+    if (n != 0 && it == h->nan_scales.end()) h->nan_scales.push_back(scale);
+    if (n == 0 && it != h->nan_scales.end()) h->nan_scales.erase(it);        // the tensor was rewritten since
+    if (count) *count = (long long)n;
+    return NVFP4_OK;
 }
 
 int nvfp4_swiglu_strided(nvfp4_handle* h, const void* gate, const void* up, int M, int I, long long in_stride,

@@ -86,6 +86,33 @@ cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, flo
 
 namespace {
 
+// How many block-scale bytes of a weight are 0x7F or 0xFF: 480 to the reference's decoder
+// (src/engine/dense_gemm_fp4_sm110.cu:30-41), NaN to the tensor core's FP8 E4M3.  16 bytes per load where the
+// pointer allows it, byte by byte for the rest.
+__global__ void __launch_bounds__(256)
+count_nan_scales_kernel(const uint8_t* __restrict__ scale, long long bytes, unsigned long long* count) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    const long long vecs = (reinterpret_cast<uintptr_t>(scale) & 15u) == 0 ? bytes >> 4 : 0;
+    unsigned int n = 0;
+    for (long long i = tid; i < vecs; i += nthr) {
+        const uint4 x = __ldg(reinterpret_cast<const uint4*>(scale) + i);
+        n += (__popc(__vcmpeq4(x.x | 0x80808080u, 0xFFFFFFFFu)) + __popc(__vcmpeq4(x.y | 0x80808080u, 0xFFFFFFFFu)) +
+              __popc(__vcmpeq4(x.z | 0x80808080u, 0xFFFFFFFFu)) + __popc(__vcmpeq4(x.w | 0x80808080u, 0xFFFFFFFFu))) >> 3;
+    }
+    for (long long i = (vecs << 4) + tid; i < bytes; i += nthr) n += (scale[i] & 0x7Fu) == 0x7Fu;
+    n = __reduce_add_sync(0xffffffffu, n);
+    if ((threadIdx.x & 31) == 0 && n) atomicAdd(count, (unsigned long long)n);
+}
+
+}  // namespace
+
+cudaError_t launch_count_nan_scales(const uint8_t* scale, long long bytes, unsigned long long* count, cudaStream_t s) {
+    count_nan_scales_kernel<<<grid_for((bytes + 15) >> 4, 256), 256, 0, s>>>(scale, bytes, count);
+    return cudaGetLastError();
+}
+
+namespace {
+
 // RMSNorm with the centred weight, one CTA per token:
 //   out = bf16( (x * rsqrt(mean(x^2) + eps)) * (1 + w) ), FP32 throughout
 // (rmsnorm_kernel, src/engine/light_ops.cu:65-106).  With `bias` the row is x + bias first, kept

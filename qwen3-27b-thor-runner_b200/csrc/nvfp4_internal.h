@@ -78,6 +78,8 @@ cudaError_t launch_decode_simple(const LinearArgs& a, cudaStream_t s);
 // --- dequant_swiglu.cu
 cudaError_t launch_dequant_bf16(const uint8_t* packed, const uint8_t* scale, float inv_gs, int N, int K,
                                 void* out, cudaStream_t s);
+// adds to *count (zeroed by the caller) the block-scale bytes that are 0x7F or 0xFF
+cudaError_t launch_count_nan_scales(const uint8_t* scale, long long bytes, unsigned long long* count, cudaStream_t s);
 cudaError_t launch_swiglu(const void* gate, const void* up, long long row_stride_in, int M, int I,
                           void* out, long long row_stride_out, cudaStream_t s, bool interleaved = false);
 // out = rmsnorm(x (+ bias)) with the centred weight; with a bias, x is updated in place.  One CTA per token.

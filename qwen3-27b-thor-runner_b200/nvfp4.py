@@ -61,6 +61,7 @@ SIGNATURES = {
     "nvfp4_linear_dual": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
                                   c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvfp4_dequant_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p]),
+    "nvfp4_scan_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(ctypes.c_longlong), c_void_p]),
     "nvfp4_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "nvfp4_swiglu_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p,
                                      ctypes.c_longlong, c_void_p]),
@@ -215,6 +216,13 @@ class Handle:
     def dequant(self, packed, scale, global_scale, N, K, out, stream=None):
         self._check(self.lib.nvfp4_dequant_bf16(self.h, _ptr(packed), _ptr(scale), global_scale, N, K,
                                                 _ptr(out), _stream(stream)))
+
+    def scan_scales(self, scale, N, K, stream=None):
+        """Block-scale bytes 0x7F / 0xFF in a weight (480 to the reference, NaN to the tensor core); a weight
+        that holds any stays off the tensor-core GEMV from here on.  Synchronises."""
+        n = ctypes.c_longlong(0)
+        self._check(self.lib.nvfp4_scan_scales(self.h, _ptr(scale), N, K, ctypes.byref(n), _stream(stream)))
+        return n.value
 
     def swiglu(self, gate, up, M, I, out, stream=None):
         self._check(self.lib.nvfp4_swiglu(self.h, _ptr(gate), _ptr(up), M, I, _ptr(out), _stream(stream)))

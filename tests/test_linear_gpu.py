@@ -215,6 +215,38 @@ def test_decode_extreme_scales(handle, impl):
     assert ob.rel_frobenius(got, want) <= TOL
 
 
+@pytest.mark.parametrize("M", [1, 3, 12])
+def test_scanned_weight_with_scale_480_matches_the_reference_by_default(handle, M):
+    """A weight whose scales hold 0x7F / 0xFF (480 to the reference, src/engine/dense_gemm_fp4_sm110.cu:30-41):
+    the scan counts them exactly, and after it the default path gives the reference's result on that weight,
+    where the tensor-core GEMV would give NaN.  A scan of the repaired tensor at the same address lifts the mark."""
+    import torch
+    N, K = 200, 1024
+    rng = np.random.default_rng(19)
+    packed = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    scale = rng.integers(0, 256, (N, K // 16), dtype=np.uint8)
+    bad = int(((scale & 0x7F) == 0x7F).sum())
+    assert bad > 0
+    A = util.make_bf16((M, K), seed=5)
+    dA, dp, ds = util.to_dev(A), util.to_dev(packed), util.to_dev(scale)
+    dC = torch.full((M, N), 0x7FC0, dtype=torch.int16, device="cuda")
+    assert handle.scan_scales(ds, N, K) == bad
+    part = ds.view(-1)[3:3 + 1600]                                # a start that is not 16-byte aligned: the byte loop
+    assert handle.scan_scales(part, 1, 1600 * 16) == int(((scale.reshape(-1)[3:1603] & 0x7F) == 0x7F).sum())
+    handle.linear(dA, M, dp, ds, 1.0, N, K, dC)
+    torch.cuda.synchronize()
+    want = ob.linear(A, packed, scale, 1.0, mode=ob.GEMV)
+    assert ob.rel_frobenius(util.to_host_u16(dC), want) <= TOL
+    fixed = scale.copy()
+    fixed[(fixed & 0x7F) == 0x7F] = 0x7E
+    ds.copy_(util.to_dev(fixed))
+    assert handle.scan_scales(ds, N, K) == 0 and handle.scan_scales(part, 1, 1600 * 16) == 0
+    handle.linear(dA, M, dp, ds, 1.0, N, K, dC)
+    torch.cuda.synchronize()
+    assert ob.rel_frobenius(util.to_host_u16(dC), ob.linear(A, packed, fixed, 1.0, mode=ob.GEMV)) <= TOL
+    assert handle.device_status() == 0
+
+
 @pytest.mark.parametrize("M", [9, 24, 200])
 @pytest.mark.parametrize("gs", [0.37, 7.25, 2688.0])
 def test_gemm_weight_rounding_reproduces_the_reference_gemm_branch(handle, M, gs):
