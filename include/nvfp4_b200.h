@@ -136,10 +136,10 @@ int nvfp4_linear(nvfp4_handle* h, const void* A_bf16, int M,
  * FP16 copy of <= 8 tokens' activations must fit in shared memory beside the weight ring; the
  * grid is capped at 160 CTAs, the size the array was laid out for.
  * The first call on each device looks up the array's device address and sets the kernel's
- * shared-memory attribute; make that first call before capturing a stream.  All calls share the
+ * shared-memory attribute (host-side work that later calls skip).  All calls share the
  * one array: it keeps the previous call's partial sums, which is harmless because every partial
- * carries the sequence number of its launch, taken from a counter in the array itself (so a captured
- * call can be replayed), and is rewritten before it is read; but two calls that overlap on the GPU
+ * carries the sequence number of its launch, taken from a counter in the array itself, and is
+ * rewritten before it is read; but two calls that overlap on the GPU
  * (different streams) race on it -- issue them on one stream.  The device of `stream` must be the
  * current device.  nvfp4_noalloc_status reads back whether a device-side wait ever ran out. */
 int nvfp4_linear_decode_noalloc(const void* A_bf16, int M, const uint8_t* packed, const uint8_t* scale_ue4m3,
