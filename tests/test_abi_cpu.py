@@ -83,6 +83,7 @@ def test_workspace_query_and_null_checks():
     assert lib.nvfp4_workspace_bytes(16, 0, 5120, ctypes.byref(n)) == -2
     assert lib.nvfp4_linear(None, None, 1, None, None, 1.0, 16, 16, None, None, None) == -1
     assert lib.nvfp4_destroy(None) == -1
+    assert lib.nvfp4_scan_scales(None, None, 16, 16, None, None) == -1
 
 
 def test_no_cluster_multicast_anywhere():
